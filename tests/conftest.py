@@ -1,0 +1,46 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def load_golden(name):
+    """Load tests/golden/<name>.npz; keys ending in _bf16 hold bf16 bit patterns and are
+    returned as torch.bfloat16 tensors under the key without the suffix."""
+    raw = np.load(os.path.join(GOLDEN_DIR, f"{name}.npz"))
+    out = {}
+    for key in raw.files:
+        arr = raw[key]
+        if key.endswith("_bf16"):
+            out[key[:-5]] = torch.from_numpy(arr.copy()).view(torch.bfloat16)
+        else:
+            out[key] = torch.from_numpy(arr.copy())
+    return out
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return load_golden
+
+
+def has_cuda():
+    return torch.cuda.is_available()
+
+
+@pytest.fixture(scope="session")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
