@@ -1,0 +1,353 @@
+"""Benchmark of the NSA selection hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1 and per rank for N > 1): op-level bf16 selection forward + backward at the
+Wan2.1-1.3B layer shape - B=1, H=12, D=128, Q = a 3-latent-frame chunk (4680 tokens, frames
+18..20), KV = 21 latent frames (32760 tokens) in 64-token blocks, top-16 per 64-query group,
+block-causal by frame, Q/K/V/dO ~ N(0,1) from a fixed seed.  One step = query-group pooling,
+key-block pooling + scoring + top-k, selection forward, inverted index, dQ, dK/dV.
+
+`value` is executed TFLOP/s (4*D*sum(n_q*n_keys) forward, x2.5 backward) with the inputs
+resident in HBM; `e2e` is the same metric with the step's inputs copied from pinned host
+memory and its results copied back inside the timed region.  `--impl reference` times the CPU
+restatement of the reference's path (oracle/nsa_oracle.py) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(B=1, H=12, D=128, M=4680, N=32760, block=64, group=64, topk=16, frame=1560, q_frame0=18)
+METRIC = "nsa_selection_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = ("config2: bf16 NSA selection fwd+bwd, B=1 H=12 D=128, Q=4680 (3 latent frames), "
+            "KV=32760 (21 frames) in 64-token blocks, top-16 per 64-query group")
+# kernels launched by one step: pool(q), pool(k), score, select, fwd, index count/scan/scatter, dq, dkv
+LAUNCHES_PER_STEP = 10
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tensor=p["bf16_tflops"], tensor_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+def make_inputs(seed: int, pin: bool):
+    c = CFG
+    g = torch.Generator().manual_seed(seed)
+    shp_q, shp_k = (c["B"], c["M"], c["H"], c["D"]), (c["B"], c["N"], c["H"], c["D"])
+    t = {n: torch.randn(s, generator=g).to(torch.bfloat16) for n, s in
+         (("q", shp_q), ("k", shp_k), ("v", shp_k), ("do", shp_q))}
+    if pin:
+        t = {n: x.pin_memory() for n, x in t.items()}
+    return t
+
+
+def executed_flops_fwd(idx: torch.Tensor) -> int:
+    """4*D*sum over (group, head) rows of n_queries * n_valid_selected_tokens."""
+    c = CFG
+    MG = idx.shape[1]
+    g = torch.arange(MG, device=idx.device)
+    n_q = torch.clamp(c["M"] - g * c["group"], max=c["group"]).view(1, MG, 1)
+    t0 = idx.long() * c["block"]
+    n_tok = torch.clamp(c["N"] - t0, min=0, max=c["block"])
+    n_keys = torch.where(idx >= 0, n_tok, torch.zeros_like(n_tok)).sum(-1)
+    return int(4 * c["D"] * (n_keys * n_q).sum().item())
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", delete=False, suffix=".csv")
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def gpu_step(ops, d, ev=None):
+    """One pass of the hot path over device tensors; `ev` collects (name, start, stop) events."""
+    c = CFG
+    scale = c["D"] ** -0.5
+
+    def timed(name, fn):
+        if ev is None:
+            return fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        ev.append((name, a, b))
+        return r
+
+    qp = timed("pool_q", lambda: ops.pool_rows(d["q"], c["group"]))
+    kp = timed("pool_k", lambda: ops.pool_rows(d["k"], c["block"]))
+    idx = timed("score_topk", lambda: ops.topk(qp, kp, c["topk"], scale, c["block"], c["frame"], c["frame"], True,
+                                               q_chunk_offset=c["q_frame0"], q_group_size=c["group"]))
+    kv = ops.DenseKV(d["k"], d["v"])
+    out, lse = timed("sel_fwd", lambda: ops.sel_fwd(d["q"], kv, idx, c["block"], 1, scale, False, c["group"]))
+    groups, offsets = timed("inverted_index", lambda: ops.inverted_index(idx, -(-c["N"] // c["block"]), c["block"],
+                                                                         1, False, c["group"]))
+    dq, delta = timed("sel_bwd_dq", lambda: ops.sel_bwd_dq(d["q"], kv, idx, out, lse, d["do"], c["block"], 1, scale,
+                                                           False, c["group"]))
+    dk, dv = timed("sel_bwd_dkv", lambda: ops.sel_bwd_dkv(d["q"], kv, groups, offsets, lse, delta, d["do"],
+                                                          c["topk"], c["block"], 1, scale, False, c["group"]))
+    return idx, out, dq, dk, dv
+
+
+def run_gpu(args):
+    from omnimem_b200 import ops
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the GPU arm has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    host = make_inputs(1234 + rank, pin=True)
+    d = {n: x.to(dev) for n, x in host.items()}
+    c = CFG
+    for _ in range(max(args.warmup, 3)):
+        idx, out, dq, dk, dv = gpu_step(ops, d)
+    torch.cuda.synchronize()
+    flops_fwd = executed_flops_fwd(idx)
+    flops_step = int(flops_fwd * 3.5)
+
+    # ---- device-resident timing
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        gpu_step(ops, d, ev)
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+
+    # ---- end to end: pinned host -> device, step, results -> pinned host
+    res_host = {n: torch.empty_like(x, device="cpu").pin_memory() for n, x in
+                (("out", out), ("dq", dq), ("dk", dk), ("dv", dv))}
+    h2d = sum(x.numel() * x.element_size() for x in host.values())
+    d2h = sum(x.numel() * x.element_size() for x in res_host.values())
+
+    def e2e_step():
+        dd = {n: x.to(dev, non_blocking=True) for n, x in host.items()}
+        _, o, a, b_, c_ = gpu_step(ops, dd)
+        for n, x in (("out", o), ("dq", a), ("dk", b_), ("dv", c_)):
+            res_host[n].copy_(x, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if dist is not None:
+        t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = t.tolist()
+
+    if rank == 0:
+        pk = peaks()
+        per = {}
+        for name, a, b in ev:
+            per.setdefault(name, []).append(a.elapsed_time(b))
+        per = {n: sum(v) / len(v) for n, v in per.items()}
+        esz = 2
+        bytes_pool_k = c["N"] * c["H"] * c["D"] * esz + (-(-c["N"] // c["block"])) * c["H"] * c["D"] * esz
+        work = {"sel_fwd": ("tensor", flops_fwd), "sel_bwd_dq": ("tensor", int(flops_fwd * 1.5)),
+                "sel_bwd_dkv": ("tensor", flops_fwd), "pool_k": ("hbm", bytes_pool_k)}
+        kernels = {}
+        for n, ms in per.items():
+            entry = {"ms": round(ms, 5)}
+            if n in work:
+                bound, amount = work[n]
+                ach = amount / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+                peak = pk["tensor"] if bound == "tensor" else pk["hbm"]
+                entry.update(bound=bound, achieved=round(ach, 2), peak=peak, frac=round(ach / peak, 4),
+                             unit="TFLOP/s" if bound == "tensor" else "GB/s")
+            kernels[n] = entry
+        dom = max((n for n in per if n in work), key=lambda n: per[n])
+        roof = dict(kernels[dom])
+        roof.pop("ms")
+        roof.update(kernel=dom, traffic=None, peak_source=pk["source"] + " (burst)",
+                    note="achieved = algorithmic work of the kernel / mean CUDA-event time over the timed steps")
+        value = world * flops_step * args.steps / (ms_total * 1e-3) / 1e12
+        e2e_val = world * flops_step * args.steps / (ms_e2e * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "flops_per_step": flops_step, "flops_fwd": flops_fwd,
+                       "l2": "inputs (Q,K,V,dO = 230 MB) and outputs (230 MB) exceed the 126 MB L2; no explicit flush",
+                       "parallelism": "one independent workload per GPU, no collective" if world > 1 else "1 GPU"},
+            "e2e": {"value": round(e2e_val, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+            "clocks": clocks, "roofline": roof, "kernels": kernels,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(host, steps=1)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------ CPU reference
+def cpu_pass(O, t, groups=None):
+    """The oracle's restatement of the same step on host tensors; `groups` limits the pass to a
+    sample of query groups (the whole K/V is still pooled and scored)."""
+    c = CFG
+    q, k, v, do = (t[n].float() for n in ("q", "k", "v", "do"))
+    qp = O.pool_rows(t["q"], c["group"])
+    kp = O.pool_rows(t["k"], c["block"])
+    idx = O.topk_select(qp, kp, c["topk"], block_size=c["block"], chunk_size=c["frame"], chunk_size_k=c["frame"],
+                        causal=True, q_chunk_offset=c["q_frame0"], q_group_size=c["group"])
+    if groups is not None:
+        lo, hi = groups
+        m0, m1 = lo * c["group"], min(c["M"], hi * c["group"])
+        q, do, idx = q[:, m0:m1], do[:, m0:m1], idx[:, lo:hi]
+    out, lse = O.selection_fwd(q, k, v, idx, c["block"], 1, None, False, c["group"])
+    O.selection_bwd(q, k, v, idx, out, lse, do, c["block"], 1, None, False, c["group"])
+    return O.selection_flops(idx, q.shape[1], c["N"], c["D"], c["block"], 1, False, c["group"]) * 3.5
+
+
+def cpu_baseline(host, steps: int, groups=None):
+    from oracle import nsa_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    flops = 0.0
+    for _ in range(steps):
+        flops += cpu_pass(O, host, groups)
+    dt = time.perf_counter() - t0
+    n_groups = -(-CFG["M"] // CFG["group"])
+    sample = "full workload" if groups is None else f"query groups [{groups[0]}, {groups[1]}) of {n_groups}"
+    return {"value": round(flops / dt / 1e12, 5), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sample}, {steps} pass(es), {dt:.1f} s, torch CPU ops in fp32", "seconds": round(dt, 2)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import nsa_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    host = make_inputs(1234, pin=False)
+    n_groups = -(-CFG["M"] // CFG["group"])
+    # size the per-step sample so that warm-up + steps stay near two minutes
+    t0 = time.perf_counter()
+    cpu_pass(O, host, (0, 8))
+    probe = time.perf_counter() - t0
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    take = int(max(4, min(n_groups, 8 * budget / max(probe, 1e-3))))
+    groups = None if take >= n_groups else (n_groups - take, n_groups)
+    for _ in range(args.warmup):
+        cpu_pass(O, host, groups)
+    t0 = time.perf_counter()
+    flops = 0.0
+    for _ in range(args.steps):
+        flops += cpu_pass(O, host, groups)
+    dt = time.perf_counter() - t0
+    val = round(flops / dt / 1e12, 5)
+    sample = "full workload" if groups is None else f"query groups [{groups[0]}, {groups[1]}) of {n_groups}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample_per_step": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{sample} per step; CPU restatement of the reference's torch path, fp32"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,275 @@
+/*
+ * omnimem_b200 - C ABI of the B200 (sm_100a) NSA selection path.
+ *
+ * Every function takes raw device pointers, sizes, element strides and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches on that stream, never synchronises,
+ * never allocates device memory and never throws: it returns 0 on success or a negative
+ * nsa_status, and nsa_last_error() then returns a human-readable message (thread local).
+ * Scratch memory is owned by the caller: each *_workspace_bytes() function says how much
+ * a call needs; pass a device buffer of at least that size (256-byte aligned).
+ *
+ * Tensors follow the reference operator layouts: q/out [B,M,H,D], k/v [B,N,H,D],
+ * block_indices int32 [B,MG,H,T], lse float [B,H,M] (natural log).  Strides are in
+ * elements; the innermost (D) stride must be 1 and every row must start on a 16-byte
+ * boundary (the host wrapper copies a tensor that does not satisfy this).
+ *
+ * Each declaration cites the reference interface it replaces, as
+ * path:line inside the reference project (src/omnimem/nsa/cuda_backend/csrc/...).
+ */
+#ifndef OMNIMEM_B200_H_
+#define OMNIMEM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nsa_status {
+  NSA_OK = 0,
+  NSA_ERR_INVALID = -1,     /* bad argument (shape, range, null pointer) */
+  NSA_ERR_LAYOUT = -2,      /* stride / alignment the kernels cannot address */
+  NSA_ERR_UNSUPPORTED = -3, /* dtype / head dim / size outside the built kernels */
+  NSA_ERR_WORKSPACE = -4,   /* workspace too small */
+  NSA_ERR_CUDA = -5,        /* a CUDA runtime call or launch failed */
+  NSA_ERR_EXHAUSTED = -6    /* page pool has no free page */
+} nsa_status;
+
+typedef enum nsa_dtype { NSA_BF16 = 0, NSA_F16 = 1, NSA_F32 = 2 } nsa_dtype;
+
+/* Where the selection kernels find the K/V tokens of block `bid` of head h. */
+typedef enum nsa_kv_mode {
+  NSA_KV_DENSE = 0, /* k/v [B,N,H,D] with element strides (common.cuh:158-190 DenseKV)   */
+  NSA_KV_PAGED = 1, /* fixed-page pool + int32 block table [H][max_blocks] -> page or -1;
+                       the B200-native replacement of the int64 pointer tables            */
+  NSA_KV_PTR = 2    /* int64 byte-address tables [B,MG,H,T] laid out like block_indices, 0 =
+                       skip, whole blocks only (common.cuh:193-215 PtrKV); block_indices is
+                       ignored by the forward in this mode                                */
+} nsa_kv_mode;
+
+typedef struct nsa_kv_source {
+  int32_t mode;              /* nsa_kv_mode */
+  const void* k;             /* dense: k base; paged: K page pool base */
+  const void* v;             /* dense: v base; paged: V page pool base */
+  int64_t k_stride[3];       /* dense: element strides of (b, n, h); paged: unused */
+  int64_t v_stride[3];
+  int64_t n_tokens;          /* N: tokens that exist (last block may be partial) */
+  const int32_t* block_table;/* paged: [H][max_blocks] page id or -1 (not resident) */
+  int32_t max_blocks;        /* paged: row length of block_table */
+  int32_t page_tokens;       /* paged: tokens per page (== block_size); page = [page_tokens][D] */
+  const int64_t* ptr_k;      /* ptr: K block addresses, element strides = idx_stride */
+  const int64_t* ptr_v;      /* ptr: V block addresses */
+  int64_t ptr_stride_n;      /* ptr: elements between consecutive tokens of a block */
+} nsa_kv_source;
+
+/* Visibility rules of the top-k (topk.cu:16-97 TopkMask / visible()). */
+typedef struct nsa_topk_mask {
+  int32_t block_size;     /* tokens per key block */
+  int32_t chunk_size;     /* query chunk length, in query TOKENS (rows * q_group_size) */
+  int32_t chunk_size_k;   /* key chunk length in tokens */
+  int32_t q_group_size;   /* tokens one pooled query row stands for (1: rows are tokens) */
+  int32_t q_chunk_offset; /* added to every query chunk id */
+  int32_t ex_win;
+  int32_t ex_sink;
+  int32_t causal;
+  int32_t tf_mask;
+  int32_t prog_excl;
+  int32_t id_base;        /* global block id of local column c is id_base + c*id_stride */
+  int32_t id_stride;      /* (block-sharded KV: rank r of R owns ids r, r+R, ...)        */
+} nsa_topk_mask;
+
+const char* nsa_last_error(void);
+/* Library version string; also a cheap "does the library load" probe. */
+const char* nsa_version(void);
+
+/* Mean over runs of `size` rows of dim 1: x [B,N,H,D] -> out [B,ceil(N/size),H,D], fp32
+ * accumulation, rounded to the input dtype; a short last run averages the rows that exist.
+ * Replaces the torch expressions k.view(b, s//bs, bs, n, d).mean(2)
+ * (models/transformers/causal_wan_nsa_model.py:408-409,481,487) and the query-group
+ * pooling of nsa/ops/index_topk.py:72-79. */
+int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out, const int64_t out_stride[3],
+                  int32_t B, int64_t N, int32_t H, int32_t D, int32_t size, int32_t dtype,
+                  void* stream);
+
+/* Top-k block selection.  q_pooled [B,MG,H,D], k_pooled [B,NC,H,D] ->
+ * out_idx int32 [B,MG,H,topk] (contiguous), visible blocks by (score desc, id asc), -1 in
+ * unused slots; out_scores (may be NULL) float [B,MG,H,topk], -inf in unused slots.
+ * Replaces topk_cuda (topk.cu:664-808; schema bindings.cpp `topk`). */
+size_t nsa_topk_workspace_bytes(int32_t B, int32_t MG, int32_t H, int64_t NC);
+int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const void* k_pooled,
+             const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D, int64_t NC,
+             int32_t topk, float scale, const nsa_topk_mask* mask, int32_t* out_idx,
+             float* out_scores, void* workspace, size_t workspace_bytes, int32_t dtype,
+             void* stream);
+
+/* Fused block-compressed key scoring: pools the raw keys k [B,N,H,D] block by block
+ * (writes k_pooled_out [B,NC,H,D] contiguous when not NULL), scores them against
+ * q_pooled and selects, reading K exactly once.  Same outputs as nsa_topk.
+ * Replaces pooling + topk_cuda of the two citations above in one pass over K. */
+int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
+                        const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
+                        int64_t N, int32_t topk, float scale, const nsa_topk_mask* mask,
+                        void* k_pooled_out, int32_t* out_idx, float* out_scores, void* workspace,
+                        size_t workspace_bytes, int32_t dtype, void* stream);
+
+/* Merge R candidate lists (idx/scores [R][rows][T], global ids) into the global top-k with
+ * the same order rule.  New for block-sharded KV; the order rule is topk.cu:100-102 and the
+ * packed-key merge it mirrors is topk.cu:442-471. */
+int nsa_merge_candidates(const int32_t* idx, const float* scores, int32_t R, int64_t rows,
+                         int32_t T, int32_t topk, int32_t* out_idx, float* out_scores,
+                         void* stream);
+
+/* Selection attention forward: out [B,M,H,D] (q dtype) and lse float [B,H,M].
+ * Rows with no visible key give out = 0, lse = -inf.
+ * Replaces sel_fwd_cuda (selection_fwd.cu:934-966) and, with NSA_KV_PAGED,
+ * sel_fwd_ptr_cuda (selection_fwd.cu:968-992). */
+int nsa_sel_fwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                const int32_t* block_indices, const int64_t idx_stride[4], void* out,
+                const int64_t out_stride[3], float* lse, int32_t B, int64_t M, int32_t H,
+                int32_t D, int32_t T, int32_t block_size, int32_t chunk_size, int32_t causal,
+                int32_t group_size, float scale, int32_t dtype, void* stream);
+
+/* Inverted (block -> query groups) CSR index: groups int32 [B,H,MG*T], offsets int32
+ * [B,H,NS+1]; pairs that are negative, out of range or causally invisible are dropped.
+ * Replaces build_inverted_index_impl (inverted_index.cu:106-178). */
+size_t nsa_inverted_index_workspace_bytes(int32_t B, int32_t H, int64_t NS);
+int nsa_inverted_index(const int32_t* block_indices, const int64_t idx_stride[4], int32_t B,
+                       int32_t MG, int32_t H, int32_t T, int64_t NS, int32_t block_size,
+                       int32_t chunk_size, int32_t causal, int32_t group_size, int32_t* groups,
+                       int32_t* offsets, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Selection attention backward: dq (q dtype, q layout), dk/dv (k dtype, contiguous
+ * [B,N,H,D]); dk/dv of every token are written (zero where no group selected it), with no
+ * atomics: one thread block owns each dK/dV tile and walks its bucket of query groups in
+ * ascending group order, so results are bit-reproducible.
+ * Replaces sel_bwd_cuda (selection_bwd.cu:1329-1407). */
+size_t nsa_sel_bwd_workspace_bytes(int32_t B, int64_t M, int32_t H, int64_t N, int32_t T,
+                                   int32_t block_size, int32_t group_size);
+int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                const int32_t* block_indices, const int64_t idx_stride[4], const void* out,
+                const int64_t out_stride[3], const float* lse, const void* d_out,
+                const int64_t do_stride[3], void* dq, const int64_t dq_stride[3], void* dk,
+                void* dv, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
+                int32_t block_size, int32_t chunk_size, int32_t causal, int32_t group_size,
+                float scale, void* workspace, size_t workspace_bytes, int32_t dtype,
+                void* stream);
+
+/* The two halves of nsa_sel_bwd as separate calls (the inverted index is built with
+ * nsa_inverted_index in between).  nsa_sel_bwd_dq also writes delta = sum_d(out * d_out),
+ * float [B,H,M], which nsa_sel_bwd_dkv reads together with the CSR index.
+ * Replace sel_bwd_dq_*_kernel (selection_bwd.cu:310-912) and sel_bwd_dkv_mma_kernel
+ * (selection_bwd.cu:916-1044). */
+int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                   const int32_t* block_indices, const int64_t idx_stride[4], const void* out,
+                   const int64_t out_stride[3], const float* lse, const void* d_out,
+                   const int64_t do_stride[3], void* dq, const int64_t dq_stride[3], float* delta,
+                   int32_t B, int64_t M, int32_t H, int32_t D, int32_t T, int32_t block_size,
+                   int32_t chunk_size, int32_t causal, int32_t group_size, float scale,
+                   int32_t dtype, void* stream);
+int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                    const int32_t* groups, const int32_t* offsets, const float* lse,
+                    const float* delta, const void* d_out, const int64_t do_stride[3], void* dk,
+                    void* dv, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
+                    int32_t block_size, int32_t chunk_size, int32_t causal, int32_t group_size,
+                    float scale, int32_t dtype, void* stream);
+
+/* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
+ * lses float [R][B,H,M] -> out, lse.  O = sum_r exp(lse_r - lse) O_r.  New for
+ * block-sharded KV (no counterpart: the reference never splits one row's keys). */
+int nsa_merge_partials(const void* outs, const float* lses, int32_t R, int32_t B, int64_t M,
+                       int32_t H, int32_t D, void* out, float* lse, int32_t dtype, void* stream);
+
+/* Block id -> int64 byte address tables, same contract as build_ptr_table_cuda
+ * (ptr_table.cu:59-127): 0 for id < 0, id >= n_blocks_per_head[h], chunk >= max_chunks or a
+ * zero chunk base. */
+int nsa_build_ptr_table(const int32_t* block_indices, const int64_t idx_stride[4],
+                        const int64_t* base_k, const int64_t* base_v,
+                        const int32_t* n_blocks_per_head, int32_t B, int32_t MG, int32_t H,
+                        int32_t T, int32_t max_chunks, int64_t batch_stride,
+                        int32_t blocks_per_chunk, int64_t in_chunk_block_bytes, int64_t* ptr_k,
+                        int64_t* ptr_v, void* stream);
+
+/* ---- fixed-page block KV cache ----------------------------------------------------
+ * Pool: k_pool / v_pool [num_pages][page_tokens][D]; a page holds one (head, block); block j
+ * = tokens [j*page_tokens, (j+1)*page_tokens).  block_table int32 [H][max_blocks] -> page or
+ * -1; page_owner int32 [num_pages] -> key h*max_blocks + bid or -1 (free); page_stamp int64
+ * [num_pages] = epoch of last use (the LRU clock); k_pooled / v_pooled [H][max_blocks][D]
+ * hold the mean key / value of EVERY block ever appended (evicted blocks stay candidates of
+ * the top-k, as in the reference, and come back from the host tier when selected).
+ * `status` is a device int32 the kernels set to a negative nsa_status on a device-detected
+ * problem (pool exhausted); the host reads it when it chooses to.  Data-dependent counts
+ * stay on the device (n_dev pointers), so no call needs a host synchronisation. */
+
+/* Append S new tokens (k_new/v_new [S,H,D]; kv_stride = element strides of (s, h)) at
+ * absolute token position pos0.  A touched block that has no page takes
+ * new_pages[h*n_touched_blocks + j] (device int32; e.g. fresh page ids or the victims list).
+ * Writes the tokens with 16-byte stores, stamps the pages with `epoch`, and recomputes the
+ * pooled key / value of every touched block over the tokens it now holds (v_pooled may be
+ * NULL).  Replaces MMCache.update_cache, chunk-per-head branch (models/cache.py:478-502), the
+ * pooled-cache append of models/transformers/causal_wan_nsa_model.py:479-504, and
+ * block_range_kernel (block_kv_range.cu:13-37). */
+int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2], int64_t S,
+                     int64_t pos0, int32_t H, int32_t D, void* k_pool, void* v_pool,
+                     int32_t page_tokens, int32_t* block_table, int32_t max_blocks,
+                     const int32_t* new_pages, int32_t n_touched_blocks, int32_t* page_owner,
+                     int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
+                     int32_t* status, int32_t dtype, void* stream);
+
+/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
+ * unique keys (cid*H + h)*bpc + loc (cid = bid / bpc, loc = bid % bpc): out_unique[0] = count
+ * (may exceed cap), out_unique[1..cap] keys.  `stamp` is a persistent int32 [H*max_blocks]
+ * scratch of the cache; epoch32 >= 1 must differ from call to call.  With a block_table
+ * (needs bpc == max_blocks, so key = h*max_blocks + bid): resident pages among the keys get
+ * page_stamp = epoch (the LRU touch) and out_missing (may be NULL) receives, in the same
+ * format, the keys whose block has no page.
+ * Replaces dedup_run (block_kv_dedup.cu:16-120; block_kv_ops.h:26-31) and the host LRU touch
+ * loop of nsa/ops/selection/padded_ptr/wrapper.py:253-362. */
+size_t nsa_cache_dedup_workspace_bytes(int64_t n_keys);
+int nsa_cache_dedup_touch(const int32_t* block_indices, int64_t n_entries, int32_t H, int32_t T,
+                          int32_t max_blocks, int32_t bpc, int32_t* stamp, int32_t epoch32,
+                          const int32_t* block_table, int64_t* page_stamp, int64_t epoch,
+                          int32_t* out_unique, int32_t* out_missing, int32_t cap,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* The n least recently used pages, ascending (stamp, page): owned, owner's block id below
+ * protect_from_bid, and not stamped with the current epoch.  n = *n_dev when n_dev != NULL
+ * (clamped to cap), else the host value n.  Sets *status = NSA_ERR_EXHAUSTED and pads with
+ * -1 when fewer pages qualify.  Replaces the OrderedDict pop of
+ * MMCache.lru_touch_per_head (models/cache.py:673-699). */
+int nsa_cache_select_victims(const int32_t* page_owner, const int64_t* page_stamp,
+                             int32_t num_pages, int32_t max_blocks, int32_t protect_from_bid,
+                             int64_t epoch, int32_t n, const int32_t* n_dev, int32_t cap,
+                             int32_t* victims, int32_t* status, void* stream);
+
+/* Move pages between the pool and the host tier (pinned, device-mapped memory; the slot of
+ * key is host_k/host_v + key*page_bytes) and publish AFTER the copy of the page is complete:
+ *   direction 0 (evict): pages[i] -> slot of its owner; then block_table[owner] = -1 and the
+ *                        page is free (host_k == NULL drops the data instead of saving it);
+ *   direction 1 (fetch): slot of keys[1+i] -> pages[i]; then block_table[key] = page,
+ *                        owner and stamp set.  keys is a count-first list as written by
+ *                        nsa_cache_dedup_touch (out_missing).
+ * n = *n_dev when n_dev != NULL (grid sized by cap), else n.
+ * Replaces gather_publish_clear (block_kv_gather.cu:13-45) and the copies of
+ * MMCache.flush_offload (models/cache.py:1032-1142). */
+int nsa_cache_move_pages(int32_t direction, const int32_t* pages, const int32_t* keys, int32_t n,
+                         const int32_t* n_dev, int32_t cap, void* k_pool, void* v_pool,
+                         int64_t page_bytes, void* host_k, void* host_v, int32_t* block_table,
+                         int32_t* page_owner, int64_t* page_stamp, int64_t epoch, void* stream);
+
+/* The reference's K1 and K2 entry points with their own contracts (block_kv_ops.h:12-24):
+ * desc int64 SoA [src_k|src_v|dst_k|dst_v|pub_k|pub_v] x n_fetch then clear x n_clear;
+ * *ctas_launched = n_fetch + ceil(n_clear/256).  K3 (dedup_run) is nsa_cache_dedup_touch with
+ * block_table = NULL. */
+int nsa_gather_publish_clear(const int64_t* desc, int64_t n_fetch, int64_t n_clear,
+                             int64_t block_bytes, int32_t wide, int32_t num_warps,
+                             int64_t* ctas_launched, void* stream);
+int nsa_block_range(int64_t* table, int32_t* n_valid, int32_t H, int64_t MB, int64_t first_bid,
+                    int64_t n_blocks, int64_t k_base, int64_t v_base, int64_t head_stride_bytes,
+                    int64_t block_bytes, int64_t n_valid_value, int32_t write_k, int32_t write_v,
+                    int32_t clear, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMNIMEM_B200_H_ */

@@ -1,0 +1,192 @@
+"""Fixed-page block KV cache with an LRU block table, resident on the device.
+
+Re-expresses, at 64-token block granularity and without host round trips, what the
+reference's ``MMCache`` does per chunk with Python lists, ``OrderedDict`` LRUs and pinned
+offload buffers (models/cache.py:438-522 update_cache, :673-699 lru_touch_per_head,
+:1032-1142 flush_offload) together with the selected-chunk reload of
+nsa/ops/selection/padded_ptr/wrapper.py:253-362 and the block-KV kernels K1-K3
+(nsa/cuda_backend/csrc/block_kv_ops.h:12-31):
+
+* a page holds one (head, block); ``block_table[h, bid]`` maps a block to its page or -1;
+* pooled keys / values of EVERY block ever appended stay on the device and remain top-k
+  candidates; full-resolution K/V of evicted blocks live in fixed pinned-host slots and are
+  fetched back when a selection asks for them (history is never dropped);
+* the LRU clock is a per-page epoch stamp; victims are the pages with the oldest stamp
+  outside the protected tail window;
+* appends may start in the middle of the last page; the pooled key of a partially filled
+  block is the mean of the tokens it holds and is refreshed when more arrive.
+
+All decisions that depend on data (which selected blocks are missing, which pages to evict
+for them) are taken by kernels; the host only supplies sizes it knows by construction.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+from ._lib import NSABackendError, call
+
+
+class BlockKVCache:
+    def __init__(self, num_heads: int, head_dim: int, num_pages: int, max_blocks: int,
+                 page_tokens: int = 64, dtype: torch.dtype = torch.bfloat16, device="cuda",
+                 host_tier: bool = True, protect_blocks: int = 0):
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise NSABackendError("BlockKVCache lives on a CUDA device")
+        self.H, self.D, self.page_tokens = num_heads, head_dim, page_tokens
+        self.num_pages, self.max_blocks = num_pages, max_blocks
+        self.dtype, self.device = dtype, dev
+        self.protect_blocks = protect_blocks
+        self.k_pool = torch.empty(num_pages, page_tokens, head_dim, dtype=dtype, device=dev)
+        self.v_pool = torch.empty_like(self.k_pool)
+        self.block_table = torch.full((num_heads, max_blocks), -1, dtype=torch.int32, device=dev)
+        self.page_owner = torch.full((num_pages,), -1, dtype=torch.int32, device=dev)
+        self.page_stamp = torch.zeros(num_pages, dtype=torch.int64, device=dev)
+        self.k_pooled = torch.zeros(num_heads, max_blocks, head_dim, dtype=dtype, device=dev)
+        self.v_pooled = torch.zeros_like(self.k_pooled)
+        self._stamp32 = torch.zeros(num_heads * max_blocks, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.host_k = self.host_v = None
+        if host_tier:
+            # one fixed slot per (head, block); pinned memory is addressable from the device
+            self.host_k = torch.empty(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
+            self.host_v = torch.empty(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
+        self.n_tokens = 0
+        self.epoch = 0
+        self._pages_used = 0            # high-water mark of pages handed out while the pool fills
+        self._evicted_any = False
+        self.page_bytes = page_tokens * head_dim * self.k_pool.element_size()
+        self._dtype_code = ops._dtype(self.k_pool)
+
+    # ------------------------------------------------------------------------------ helpers
+    @property
+    def n_blocks(self) -> int:
+        return -(-self.n_tokens // self.page_tokens)
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def pooled_keys(self) -> torch.Tensor:
+        """[1, n_blocks, H, D] view of the pooled keys (the top-k's `k` argument)."""
+        return self.k_pooled[:, : self.n_blocks].permute(1, 0, 2).unsqueeze(0)
+
+    def pooled_values(self) -> torch.Tensor:
+        return self.v_pooled[:, : self.n_blocks].permute(1, 0, 2).unsqueeze(0)
+
+    def kv_source(self) -> ops.PagedKV:
+        return ops.PagedKV(self.k_pool, self.v_pool, self.block_table, self.n_tokens, self.page_tokens)
+
+    def check_status(self) -> None:
+        """Synchronising read of the device status word; raises if a kernel reported a problem."""
+        st = int(self.status.item())
+        if st != 0:
+            self.status.zero_()
+            raise NSABackendError(f"block cache: device status {st} (page pool exhausted)")
+
+    def _select_victims(self, n: int, n_dev: Optional[torch.Tensor], cap: int) -> torch.Tensor:
+        victims = torch.full((max(cap, 1),), -1, dtype=torch.int32, device=self.device)
+        protect_from = max(self.n_blocks - self.protect_blocks, 0)
+        call("nsa_cache_select_victims", self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.num_pages,
+             self.max_blocks, protect_from, self.epoch, n, None if n_dev is None else n_dev.data_ptr(), cap,
+             victims.data_ptr(), self.status.data_ptr(), self._stream())
+        return victims
+
+    def _move(self, direction: int, pages, keys, n: int, n_dev, cap: int) -> None:
+        call("nsa_cache_move_pages", direction, pages.data_ptr(), None if keys is None else keys.data_ptr(), n,
+             None if n_dev is None else n_dev.data_ptr(), cap, self.k_pool.data_ptr(), self.v_pool.data_ptr(),
+             self.page_bytes, None if self.host_k is None else self.host_k.data_ptr(),
+             None if self.host_v is None else self.host_v.data_ptr(), self.block_table.data_ptr(),
+             self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.epoch, self._stream())
+
+    # ------------------------------------------------------------------------------- append
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, pos0: Optional[int] = None) -> None:
+        """Write k_new / v_new [S,H,D] at token position pos0 (default: the end).  Re-writing
+        existing positions is allowed (each denoising step of a chunk overwrites the chunk)."""
+        S = k_new.shape[0]
+        if S == 0:
+            return
+        pos0 = self.n_tokens if pos0 is None else int(pos0)
+        if pos0 > self.n_tokens:
+            raise NSABackendError(f"append at {pos0} would leave a gap after {self.n_tokens} tokens")
+        k_new, v_new = ops._rows16(k_new), ops._rows16(v_new)
+        if v_new.stride() != k_new.stride():
+            v_new = v_new.contiguous()
+            k_new = k_new.contiguous()
+        first, last = pos0 // self.page_tokens, (pos0 + S - 1) // self.page_tokens
+        if last >= self.max_blocks:
+            raise NSABackendError(f"token {pos0 + S - 1} is past the block table ({self.max_blocks} blocks)")
+        n_touched = last - first + 1
+        n_new = max(0, last + 1 - self.n_blocks)            # blocks that have never had a page
+        self.epoch += 1
+        with torch.cuda.device(self.device):
+            new_pages = torch.full((self.H, n_touched), -1, dtype=torch.int32, device=self.device)
+            need = n_new * self.H
+            if need:
+                fresh = min(need, self.num_pages - self._pages_used)
+                ids = []
+                if fresh:
+                    ids.append(torch.arange(self._pages_used, self._pages_used + fresh, dtype=torch.int32,
+                                            device=self.device))
+                    self._pages_used += fresh
+                if need > fresh:
+                    victims = self._select_victims(need - fresh, None, need - fresh)
+                    self._move(0, victims, None, need - fresh, None, need - fresh)
+                    ids.append(victims)
+                    self._evicted_any = True
+                new_pages[:, n_touched - n_new:] = torch.cat(ids).view(self.H, n_new)
+            call("nsa_cache_append", k_new.data_ptr(), v_new.data_ptr(),
+                 (C.c_int64 * 2)(k_new.stride(0), k_new.stride(1)), S, pos0, self.H, self.D,
+                 self.k_pool.data_ptr(), self.v_pool.data_ptr(), self.page_tokens, self.block_table.data_ptr(),
+                 self.max_blocks, new_pages.data_ptr(), n_touched, self.page_owner.data_ptr(),
+                 self.page_stamp.data_ptr(), self.epoch, self.k_pooled.data_ptr(), self.v_pooled.data_ptr(),
+                 self.status.data_ptr(), self._dtype_code, self._stream())
+        self.n_tokens = max(self.n_tokens, pos0 + S)
+
+    # ------------------------------------------------------------------- selection residency
+    def touch(self, block_indices: torch.Tensor, return_lists: bool = False):
+        """LRU-touch the selected blocks and make the missing ones resident (evicting the least
+        recently used pages to make room) - all on the device.  block_indices int32 [1,MG,H,T]."""
+        ids = block_indices.contiguous().view(-1)
+        T = block_indices.shape[-1]
+        self.epoch += 1
+        cap = min(ids.numel(), self.H * self.max_blocks)
+        with torch.cuda.device(self.device):
+            uniq = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
+            miss = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
+            wsb = _lib.load().nsa_cache_dedup_workspace_bytes(self.H * self.max_blocks)
+            ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=self.device)
+            call("nsa_cache_dedup_touch", ids.data_ptr(), ids.numel(), self.H, T, self.max_blocks, self.max_blocks,
+                 self._stamp32.data_ptr(), self.epoch, self.block_table.data_ptr(), self.page_stamp.data_ptr(),
+                 self.epoch, uniq.data_ptr(), miss.data_ptr(), cap, ws.data_ptr(), wsb, self._stream())
+            if self._evicted_any and self.host_k is not None:
+                n_dev = miss[:1]
+                victims = self._select_victims(0, n_dev, cap)
+                self._move(0, victims, None, 0, n_dev, cap)
+                self._move(1, victims, miss, 0, n_dev, cap)
+        return (uniq, miss) if return_lists else None
+
+    def selection_attention(self, q: torch.Tensor, block_indices: torch.Tensor, scale: Optional[float] = None,
+                            group_size: int = 64, return_lse: bool = False):
+        """Selection attention of q [1,M,H,D] over the selected blocks of this cache (the role of
+        selection_attention_block_store, padded_ptr/block_wrapper.py:15-89)."""
+        if q.shape[0] != 1:
+            raise NSABackendError("the block cache serves batch size 1")
+        self.touch(block_indices)
+        sc = q.shape[-1] ** -0.5 if scale is None else scale
+        out, lse = ops.sel_fwd(q, self.kv_source(), block_indices, self.page_tokens, 1, sc, False, group_size)
+        return (out, lse) if return_lse else out
+
+    def reset(self) -> None:
+        self.block_table.fill_(-1)
+        self.page_owner.fill_(-1)
+        self.page_stamp.zero_()
+        self._stamp32.zero_()
+        self.status.zero_()
+        self.n_tokens = 0
+        self.epoch = 0
+        self._pages_used = 0
+        self._evicted_any = False

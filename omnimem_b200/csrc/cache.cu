@@ -1,0 +1,468 @@
+// Fixed-page block KV cache kernels: append (+ pooled key/value refresh), selected-block
+// dedup + LRU touch, LRU victim selection, evict / fetch page moves with publish-after-copy,
+// and the reference's three block-KV entry points.  All byte / integer work, 16-byte
+// vectorised, no host synchronisation: data-dependent counts stay on the device.
+#include "common.cuh"
+
+namespace nsa {
+namespace {
+
+__device__ __forceinline__ void copy16(char* dst, const char* src, int64_t bytes) {
+  for (int64_t i = static_cast<int64_t>(threadIdx.x) * 16; i < bytes; i += static_cast<int64_t>(blockDim.x) * 16)
+    *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+}
+
+// ------------------------------------------------------------------------------------ append
+struct AppendParams {
+  const char* k_new; const char* v_new;
+  int64_t s_stride, h_stride;      // elements
+  int64_t S, pos0;
+  int H, D, page_tokens, max_blocks, n_touched;
+  char* k_pool; char* v_pool;
+  int32_t* block_table; const int32_t* new_pages;
+  int32_t* page_owner; int64_t* page_stamp; int64_t epoch;
+  char* k_pooled; char* v_pooled;
+  int32_t* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ float s_part[];          // [2][rp][D]
+  __shared__ int s_page;
+  const int j = blockIdx.x, h = blockIdx.y;
+  const int64_t first_block = p.pos0 / p.page_tokens;
+  const int64_t bid = first_block + j;
+  const int64_t key = static_cast<int64_t>(h) * p.max_blocks + bid;
+  if (threadIdx.x == 0) {
+    int page = p.block_table[key];
+    if (page < 0) {
+      page = p.new_pages ? p.new_pages[static_cast<int64_t>(h) * p.n_touched + j] : -1;
+      if (page >= 0) {
+        p.block_table[key] = page;
+        p.page_owner[page] = static_cast<int32_t>(key);
+      } else {
+        atomicExch(p.status, NSA_ERR_EXHAUSTED);
+      }
+    }
+    if (page >= 0) p.page_stamp[page] = p.epoch;
+    s_page = page;
+  }
+  __syncthreads();
+  const int page = s_page;
+  if (page < 0) return;
+  const int64_t blk0 = bid * p.page_tokens;
+  const int64_t lo = max(p.pos0, blk0), hi = min(p.pos0 + p.S, blk0 + p.page_tokens);
+  const int64_t row_bytes = static_cast<int64_t>(p.D) * sizeof(T);
+  char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes;
+  char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes;
+  const int cpr = p.D / VEC;
+  const int nrows = static_cast<int>(hi - lo);
+  for (int c = threadIdx.x; c < nrows * cpr; c += blockDim.x) {
+    const int r = c / cpr, cc = c - r * cpr;
+    const int64_t src = ((lo - p.pos0 + r) * p.s_stride + h * p.h_stride) * sizeof(T) + cc * 16;
+    const int64_t dst = (lo - blk0 + r) * row_bytes + cc * 16;
+    *reinterpret_cast<uint4*>(kp + dst) = *reinterpret_cast<const uint4*>(p.k_new + src);
+    *reinterpret_cast<uint4*>(vp + dst) = *reinterpret_cast<const uint4*>(p.v_new + src);
+  }
+  __syncthreads();
+  // pooled key / value over the tokens the block now holds (rows [0, n_present))
+  const int n_present = static_cast<int>(hi - blk0);
+  const int rp = blockDim.x / cpr;
+  const int col = threadIdx.x % cpr, r0 = threadIdx.x / cpr;
+  float ak[VEC], av[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) ak[i] = av[i] = 0.f;
+  if (r0 < rp) {
+    for (int r = r0; r < n_present; r += rp) {
+      const uint4 a = *reinterpret_cast<const uint4*>(kp + r * row_bytes + col * 16);
+      const uint4 b = *reinterpret_cast<const uint4*>(vp + r * row_bytes + col * 16);
+      const T* ea = reinterpret_cast<const T*>(&a);
+      const T* eb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) { ak[i] += to_f32<T>(ea[i]); av[i] += to_f32<T>(eb[i]); }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      s_part[r0 * p.D + col * VEC + i] = ak[i];
+      s_part[(rp + r0) * p.D + col * VEC + i] = av[i];
+    }
+  }
+  __syncthreads();
+  const float inv = 1.f / static_cast<float>(n_present);
+  T* ok = reinterpret_cast<T*>(p.k_pooled + key * row_bytes);
+  T* ov = reinterpret_cast<T*>(p.v_pooled + key * row_bytes);
+  for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
+    float sk = 0.f, sv = 0.f;
+    for (int r = 0; r < rp; ++r) { sk += s_part[r * p.D + d]; sv += s_part[(rp + r) * p.D + d]; }
+    ok[d] = from_f32<T>(sk * inv);
+    if (p.v_pooled) ov[d] = from_f32<T>(sv * inv);
+  }
+}
+
+// ------------------------------------------------------------------------ dedup + LRU touch
+constexpr int kTileKeys = 1024;
+
+// key of (head h, block bid) = (cid*H + h)*bpc + loc with cid = bid / bpc, loc = bid % bpc; with
+// bpc == max_blocks this is h*max_blocks + bid, the index into the [H][max_blocks] block table.
+__global__ void dedup_mark_kernel(const int32_t* __restrict__ ids, int64_t n_entries, int H, int T,
+                                  int max_blocks, int bpc, int32_t* __restrict__ stamp, int32_t epoch) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_entries) return;
+  const int32_t bid = ids[i];
+  if (bid < 0 || bid >= max_blocks) return;
+  const int h = static_cast<int>((i / T) % H);
+  const int cid = bid / bpc, loc = bid - cid * bpc;
+  stamp[(static_cast<int64_t>(cid) * H + h) * bpc + loc] = epoch;   // idempotent store
+}
+
+// counts[2*tile] = keys marked this epoch, counts[2*tile+1] = marked keys with no page
+__global__ void __launch_bounds__(kTileKeys) dedup_count_kernel(const int32_t* __restrict__ stamp, int32_t epoch,
+                                                                const int32_t* __restrict__ table, int64_t n_keys,
+                                                                int32_t* __restrict__ counts) {
+  const int64_t key = static_cast<int64_t>(blockIdx.x) * kTileKeys + threadIdx.x;
+  const bool hit = key < n_keys && stamp[key] == epoch;
+  const bool miss = hit && table && table[key] < 0;
+  const int a = __syncthreads_count(hit);
+  const int b = __syncthreads_count(miss);
+  if (threadIdx.x == 0) { counts[2 * blockIdx.x] = a; counts[2 * blockIdx.x + 1] = b; }
+}
+
+// single block: exclusive scan of the tile counts; writes totals to out_unique[0] / out_missing[0]
+__global__ void dedup_scan_kernel(int32_t* __restrict__ counts, int n_tiles, int32_t* out_unique,
+                                  int32_t* out_missing) {
+  if (threadIdx.x != 0) return;
+  int a = 0, b = 0;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int ca = counts[2 * t], cb = counts[2 * t + 1];
+    counts[2 * t] = a; counts[2 * t + 1] = b;
+    a += ca; b += cb;
+  }
+  out_unique[0] = a;
+  if (out_missing) out_missing[0] = b;
+}
+
+__global__ void __launch_bounds__(kTileKeys) dedup_compact_kernel(
+    const int32_t* __restrict__ stamp, int32_t epoch, const int32_t* __restrict__ table, int64_t n_keys,
+    const int32_t* __restrict__ offsets, int64_t* __restrict__ page_stamp, int64_t epoch64,
+    int32_t* __restrict__ out_unique, int32_t* __restrict__ out_missing, int cap) {
+  __shared__ int s_warp[2][32];
+  const int64_t key = static_cast<int64_t>(blockIdx.x) * kTileKeys + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool hit = key < n_keys && stamp[key] == epoch;
+  const int page = (hit && table) ? table[key] : 0;
+  const bool miss = hit && page < 0;
+  if (hit && table && page >= 0 && page_stamp) page_stamp[page] = epoch64;       // LRU touch
+  const unsigned mh = __ballot_sync(0xffffffffu, hit), mm = __ballot_sync(0xffffffffu, miss);
+  if (lane == 0) { s_warp[0][warp] = __popc(mh); s_warp[1][warp] = __popc(mm); }
+  __syncthreads();
+  int ph = offsets[2 * blockIdx.x], pm = offsets[2 * blockIdx.x + 1];
+  for (int w = 0; w < warp; ++w) { ph += s_warp[0][w]; pm += s_warp[1][w]; }
+  ph += __popc(mh & ((1u << lane) - 1));
+  pm += __popc(mm & ((1u << lane) - 1));
+  if (hit && ph < cap) out_unique[1 + ph] = static_cast<int32_t>(key);
+  if (miss && out_missing && pm < cap) out_missing[1 + pm] = static_cast<int32_t>(key);
+}
+
+// ------------------------------------------------------------------------- victim selection
+// Single block.  Picks the n least-recently-used pages: owner >= 0, owner's block id below
+// protect_from_bid, stamp < epoch (not touched by the current call); order (stamp, page) asc.
+__global__ void __launch_bounds__(1024) select_victims_kernel(
+    const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp, int num_pages,
+    int max_blocks, int protect_from_bid, int64_t epoch, int n_host, const int32_t* __restrict__ n_dev,
+    int cap, int32_t* __restrict__ victims, int32_t* status) {
+  __shared__ unsigned long long s_red[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int n = n_dev ? *n_dev : n_host;
+  if (n > cap) n = cap;
+  auto key_at = [&](int pg) -> unsigned long long {
+    const int owner = page_owner[pg];
+    if (owner < 0) return ~0ull;
+    if (owner % max_blocks >= protect_from_bid) return ~0ull;
+    const int64_t st = page_stamp[pg];
+    if (st >= epoch) return ~0ull;
+    return (static_cast<unsigned long long>(st) << 24) | static_cast<unsigned>(pg);
+  };
+  auto scan_above = [&](unsigned long long bound, bool any) {
+    unsigned long long best = ~0ull;
+    for (int pg = threadIdx.x; pg < num_pages; pg += blockDim.x) {
+      const unsigned long long k = key_at(pg);
+      if ((any || k > bound) && k < best) best = k;
+    }
+    return best;
+  };
+  unsigned long long local = scan_above(0ull, true);
+  for (int r = 0; r < n; ++r) {
+    unsigned long long best = local;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+      const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, d);
+      best = o < best ? o : best;
+    }
+    if (lane == 0) s_red[warp] = best;
+    __syncthreads();
+    best = s_red[0];
+    for (int w = 1; w < nw; ++w) best = s_red[w] < best ? s_red[w] : best;
+    __syncthreads();
+    if (best == ~0ull) {          // fewer evictable pages than requested
+      if (threadIdx.x == 0) atomicExch(status, NSA_ERR_EXHAUSTED);
+      for (int i = r + threadIdx.x; i < n; i += blockDim.x) victims[i] = -1;
+      return;
+    }
+    if (threadIdx.x == 0) victims[r] = static_cast<int32_t>(best & 0xffffffu);
+    if (local == best) local = scan_above(best, false);
+  }
+}
+
+// ----------------------------------------------------------------------------- page movement
+struct MoveParams {
+  const int32_t* pages;        // [n] page per move (evict: the victim; fetch: the destination)
+  const int32_t* keys;         // fetch: [1 + n] list written by the dedup (count first); evict: null
+  int n_host; const int32_t* n_dev;
+  char* k_pool; char* v_pool; int64_t page_bytes;
+  char* host_k; char* host_v;  // slot of key = base + key * page_bytes (device-mapped pinned memory)
+  int32_t* block_table; int32_t* page_owner; int64_t* page_stamp; int64_t epoch;
+};
+
+template <bool FETCH>
+__global__ void __launch_bounds__(256) move_pages_kernel(const MoveParams p) {
+  const int i = blockIdx.x;
+  const int n = p.n_dev ? *p.n_dev : p.n_host;
+  if (i >= n) return;
+  const int page = p.pages[i];
+  if (page < 0) return;
+  char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_bytes;
+  char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_bytes;
+  if (FETCH) {
+    const int key = p.keys[1 + i];
+    copy16(kp, p.host_k + static_cast<int64_t>(key) * p.page_bytes, p.page_bytes);
+    copy16(vp, p.host_v + static_cast<int64_t>(key) * p.page_bytes, p.page_bytes);
+    __threadfence();
+    __syncthreads();             // publish only after the whole page has landed
+    if (threadIdx.x == 0) {
+      p.page_owner[page] = key;
+      p.page_stamp[page] = p.epoch;
+      p.block_table[key] = page;
+    }
+  } else {
+    const int key = p.page_owner[page];
+    if (key < 0) return;
+    if (p.host_k) {
+      copy16(p.host_k + static_cast<int64_t>(key) * p.page_bytes, kp, p.page_bytes);
+      copy16(p.host_v + static_cast<int64_t>(key) * p.page_bytes, vp, p.page_bytes);
+      __threadfence_system();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.block_table[key] = -1;
+      p.page_owner[page] = -1;
+    }
+  }
+}
+
+// --------------------------------------------- the reference's K1 / K2 contracts, re-expressed
+__global__ void gather_publish_clear_kernel(const int64_t* __restrict__ desc, int64_t n_fetch,
+                                            int64_t n_clear, int64_t block_bytes, int wide) {
+  const int64_t i = blockIdx.x;
+  if (i < n_fetch) {
+    const char* src_k = reinterpret_cast<const char*>(desc[i]);
+    const char* src_v = reinterpret_cast<const char*>(desc[n_fetch + i]);
+    char* dst_k = reinterpret_cast<char*>(desc[2 * n_fetch + i]);
+    char* dst_v = reinterpret_cast<char*>(desc[3 * n_fetch + i]);
+    int64_t* pub_k = reinterpret_cast<int64_t*>(desc[4 * n_fetch + i]);
+    int64_t* pub_v = reinterpret_cast<int64_t*>(desc[5 * n_fetch + i]);
+    const bool v16 = wide && block_bytes % 16 == 0 &&
+                     ((desc[i] | desc[n_fetch + i] | desc[2 * n_fetch + i] | desc[3 * n_fetch + i]) & 15) == 0;
+    if (v16) {
+      copy16(dst_k, src_k, block_bytes);
+      copy16(dst_v, src_v, block_bytes);
+    } else if (wide) {
+      for (int64_t o = static_cast<int64_t>(threadIdx.x) * 8; o < block_bytes; o += static_cast<int64_t>(blockDim.x) * 8) {
+        *reinterpret_cast<uint64_t*>(dst_k + o) = *reinterpret_cast<const uint64_t*>(src_k + o);
+        *reinterpret_cast<uint64_t*>(dst_v + o) = *reinterpret_cast<const uint64_t*>(src_v + o);
+      }
+    } else {
+      for (int64_t o = static_cast<int64_t>(threadIdx.x) * 2; o < block_bytes; o += static_cast<int64_t>(blockDim.x) * 2) {
+        *reinterpret_cast<uint16_t*>(dst_k + o) = *reinterpret_cast<const uint16_t*>(src_k + o);
+        *reinterpret_cast<uint16_t*>(dst_v + o) = *reinterpret_cast<const uint16_t*>(src_v + o);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *pub_k = reinterpret_cast<int64_t>(dst_k);
+      *pub_v = reinterpret_cast<int64_t>(dst_v);
+    }
+  } else {
+    const int64_t base = (i - n_fetch) * 256;
+    for (int64_t e = threadIdx.x; e < 256; e += blockDim.x)
+      if (base + e < n_clear) *reinterpret_cast<int64_t*>(desc[6 * n_fetch + base + e]) = 0;
+  }
+}
+
+__global__ void block_range_kernel(int64_t* __restrict__ table, int32_t* __restrict__ n_valid, int H,
+                                   int64_t MB, int64_t first_bid, int64_t n_blocks, int64_t k_base,
+                                   int64_t v_base, int64_t head_stride, int64_t block_bytes,
+                                   int64_t n_valid_value, int write_k, int write_v, int clear) {
+  const int h = blockIdx.x;
+  const int64_t j = static_cast<int64_t>(blockIdx.y) * blockDim.x + threadIdx.x;
+  if (j < n_blocks) {
+    const int64_t off = h * head_stride + j * block_bytes;
+    if (write_k) table[(0 * H + h) * MB + first_bid + j] = clear ? 0 : k_base + off;
+    if (write_v) table[(1 * H + h) * MB + first_bid + j] = clear ? 0 : v_base + off;
+  }
+  if (blockIdx.y == 0 && threadIdx.x == 0 && n_valid_value >= 0) n_valid[h] = static_cast<int32_t>(n_valid_value);
+}
+
+}  // namespace
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2],
+                                int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                                void* v_pool, int32_t page_tokens, int32_t* block_table,
+                                int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
+                                int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
+                                void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
+                                void* stream) {
+  NSA_REQUIRE(S >= 0 && pos0 >= 0 && H > 0 && D > 0 && page_tokens > 0 && max_blocks > 0, NSA_ERR_INVALID,
+              "cache_append: bad size");
+  NSA_REQUIRE(dtype == NSA_BF16 || dtype == NSA_F16, NSA_ERR_UNSUPPORTED, "cache_append: bf16 / fp16 only");
+  if (S == 0) return NSA_OK;
+  const int esz = 2;
+  NSA_REQUIRE((D * esz) % 16 == 0 && D * esz / 16 <= 128, NSA_ERR_UNSUPPORTED, "cache_append: head dim %d", D);
+  const int64_t first = pos0 / page_tokens, last = (pos0 + S - 1) / page_tokens;
+  NSA_REQUIRE(last < max_blocks, NSA_ERR_INVALID, "cache_append: token %lld is past the block table (%d blocks)",
+              static_cast<long long>(pos0 + S - 1), max_blocks);
+  NSA_REQUIRE(n_touched_blocks == last - first + 1, NSA_ERR_INVALID,
+              "cache_append: n_touched_blocks must be %lld", static_cast<long long>(last - first + 1));
+  NSA_REQUIRE(k_new && v_new && k_pool && v_pool && block_table && page_owner && page_stamp && k_pooled && status,
+              NSA_ERR_INVALID, "cache_append: null pointer");
+  NSA_REQUIRE(aligned16(k_new) && aligned16(v_new) && (kv_stride[0] * esz) % 16 == 0 && (kv_stride[1] * esz) % 16 == 0,
+              NSA_ERR_LAYOUT, "cache_append: new K/V rows must be 16-byte aligned");
+  NSA_REQUIRE(H <= 65535, NSA_ERR_INVALID, "cache_append: H must be <= 65535");
+  AppendParams p{static_cast<const char*>(k_new), static_cast<const char*>(v_new), kv_stride[0], kv_stride[1],
+                 S, pos0, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
+                 static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
+                 static_cast<char*>(k_pooled), static_cast<char*>(v_pooled), status};
+  const int cpr = D * esz / 16, rp = 128 / cpr;
+  const size_t smem = 2 * static_cast<size_t>(rp) * D * sizeof(float);
+  const dim3 grid(n_touched_blocks, H);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(p);
+  else cache_append_kernel<__half><<<grid, 128, smem, s>>>(p);
+  NSA_LAUNCH_OK("cache_append_kernel");
+  return NSA_OK;
+}
+
+extern "C" size_t nsa_cache_dedup_workspace_bytes(int64_t n_keys) {
+  return align_up(static_cast<size_t>(cdiv64(n_keys, kTileKeys)) * 2 * sizeof(int32_t), 256);
+}
+
+extern "C" int nsa_cache_dedup_touch(const int32_t* block_indices, int64_t n_entries, int32_t H,
+                                     int32_t T, int32_t max_blocks, int32_t bpc, int32_t* stamp, int32_t epoch32,
+                                     const int32_t* block_table, int64_t* page_stamp, int64_t epoch,
+                                     int32_t* out_unique, int32_t* out_missing, int32_t cap,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  NSA_REQUIRE(n_entries >= 0 && H > 0 && T > 0 && max_blocks > 0 && cap >= 0, NSA_ERR_INVALID, "cache_dedup: bad size");
+  NSA_REQUIRE(stamp && out_unique, NSA_ERR_INVALID, "cache_dedup: null pointer");
+  NSA_REQUIRE(bpc > 0 && max_blocks % bpc == 0, NSA_ERR_INVALID, "cache_dedup: bpc must divide max_blocks");
+  NSA_REQUIRE(epoch32 >= 1, NSA_ERR_INVALID, "cache_dedup: epoch must be >= 1");
+  NSA_REQUIRE(block_table == nullptr || bpc == max_blocks, NSA_ERR_INVALID,
+              "cache_dedup: a block table needs bpc == max_blocks (keys index the table)");
+  const int64_t n_keys = static_cast<int64_t>(H) * max_blocks;
+  NSA_REQUIRE(n_keys <= 0x7fffffff, NSA_ERR_INVALID, "cache_dedup: too many keys");
+  NSA_REQUIRE(workspace && workspace_bytes >= nsa_cache_dedup_workspace_bytes(n_keys), NSA_ERR_WORKSPACE,
+              "cache_dedup: workspace too small");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* counts = static_cast<int32_t*>(workspace);
+  const int n_tiles = static_cast<int>(cdiv64(n_keys, kTileKeys));
+  if (n_entries > 0) {
+    NSA_REQUIRE(block_indices != nullptr, NSA_ERR_INVALID, "cache_dedup: block_indices is null");
+    dedup_mark_kernel<<<static_cast<unsigned>(cdiv64(n_entries, 256)), 256, 0, s>>>(block_indices, n_entries, H, T,
+                                                                                    max_blocks, bpc, stamp, epoch32);
+    NSA_LAUNCH_OK("dedup_mark_kernel");
+  }
+  dedup_count_kernel<<<n_tiles, kTileKeys, 0, s>>>(stamp, epoch32, block_table, n_keys, counts);
+  NSA_LAUNCH_OK("dedup_count_kernel");
+  dedup_scan_kernel<<<1, 32, 0, s>>>(counts, n_tiles, out_unique, out_missing);
+  NSA_LAUNCH_OK("dedup_scan_kernel");
+  dedup_compact_kernel<<<n_tiles, kTileKeys, 0, s>>>(stamp, epoch32, block_table, n_keys, counts, page_stamp,
+                                                     epoch, out_unique, out_missing, cap);
+  NSA_LAUNCH_OK("dedup_compact_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_cache_select_victims(const int32_t* page_owner, const int64_t* page_stamp,
+                                        int32_t num_pages, int32_t max_blocks, int32_t protect_from_bid,
+                                        int64_t epoch, int32_t n, const int32_t* n_dev, int32_t cap,
+                                        int32_t* victims, int32_t* status, void* stream) {
+  NSA_REQUIRE(num_pages > 0 && num_pages < (1 << 24) && max_blocks > 0 && cap >= 0 && n >= 0, NSA_ERR_INVALID,
+              "cache_select_victims: bad size");
+  NSA_REQUIRE(page_owner && page_stamp && victims && status, NSA_ERR_INVALID, "cache_select_victims: null pointer");
+  NSA_REQUIRE(n_dev != nullptr || n <= cap, NSA_ERR_INVALID, "cache_select_victims: n > cap");
+  if (cap == 0 || (!n_dev && n == 0)) return NSA_OK;
+  select_victims_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      page_owner, page_stamp, num_pages, max_blocks, protect_from_bid, epoch, n, n_dev, cap, victims, status);
+  NSA_LAUNCH_OK("select_victims_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_cache_move_pages(int32_t direction, const int32_t* pages, const int32_t* keys,
+                                    int32_t n, const int32_t* n_dev, int32_t cap, void* k_pool,
+                                    void* v_pool, int64_t page_bytes, void* host_k, void* host_v,
+                                    int32_t* block_table, int32_t* page_owner, int64_t* page_stamp,
+                                    int64_t epoch, void* stream) {
+  NSA_REQUIRE(direction == 0 || direction == 1, NSA_ERR_INVALID, "cache_move_pages: direction must be 0 or 1");
+  NSA_REQUIRE(n >= 0 && cap >= 0 && page_bytes > 0 && page_bytes % 16 == 0, NSA_ERR_INVALID, "cache_move_pages: bad size");
+  NSA_REQUIRE(pages && k_pool && v_pool && block_table && page_owner && page_stamp, NSA_ERR_INVALID,
+              "cache_move_pages: null pointer");
+  NSA_REQUIRE(direction == 0 || (keys && host_k && host_v), NSA_ERR_INVALID, "cache_move_pages: fetch needs keys and host slots");
+  const int grid = n_dev ? cap : n;
+  if (grid == 0) return NSA_OK;
+  MoveParams p{pages, keys, n, n_dev, static_cast<char*>(k_pool), static_cast<char*>(v_pool), page_bytes,
+               static_cast<char*>(host_k), static_cast<char*>(host_v), block_table, page_owner, page_stamp, epoch};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (direction == 1) move_pages_kernel<true><<<grid, 256, 0, s>>>(p);
+  else move_pages_kernel<false><<<grid, 256, 0, s>>>(p);
+  NSA_LAUNCH_OK("move_pages_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_gather_publish_clear(const int64_t* desc, int64_t n_fetch, int64_t n_clear,
+                                        int64_t block_bytes, int32_t wide, int32_t num_warps,
+                                        int64_t* ctas_launched, void* stream) {
+  if (ctas_launched) *ctas_launched = 0;
+  if (n_fetch == 0 && n_clear == 0) return NSA_OK;
+  NSA_REQUIRE(n_fetch >= 0 && n_clear >= 0, NSA_ERR_INVALID, "gather_publish_clear: n_fetch / n_clear must be >= 0");
+  NSA_REQUIRE(block_bytes > 0 && block_bytes % 2 == 0, NSA_ERR_INVALID,
+              "gather_publish_clear: block_bytes=%lld must be a positive multiple of 2", static_cast<long long>(block_bytes));
+  NSA_REQUIRE(!wide || block_bytes % 8 == 0, NSA_ERR_INVALID, "gather_publish_clear: wide copies need block_bytes % 8 == 0");
+  NSA_REQUIRE(num_warps >= 1 && num_warps <= 32, NSA_ERR_INVALID, "gather_publish_clear: num_warps=%d outside [1, 32]", num_warps);
+  const int64_t ctas = n_fetch + cdiv64(n_clear, 256);
+  if (ctas_launched) *ctas_launched = ctas;
+  NSA_REQUIRE(desc != nullptr, NSA_ERR_INVALID, "gather_publish_clear: desc is null");
+  NSA_REQUIRE(ctas <= 0x7fffffff, NSA_ERR_INVALID, "gather_publish_clear: too many blocks");
+  gather_publish_clear_kernel<<<static_cast<unsigned>(ctas), 32 * num_warps, 0, static_cast<cudaStream_t>(stream)>>>(
+      desc, n_fetch, n_clear, block_bytes, wide);
+  NSA_LAUNCH_OK("gather_publish_clear_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_block_range(int64_t* table, int32_t* n_valid, int32_t H, int64_t MB, int64_t first_bid,
+                               int64_t n_blocks, int64_t k_base, int64_t v_base, int64_t head_stride_bytes,
+                               int64_t block_bytes, int64_t n_valid_value, int32_t write_k, int32_t write_v,
+                               int32_t clear, void* stream) {
+  NSA_REQUIRE(H > 0 && H <= 65535 && MB > 0, NSA_ERR_INVALID, "block_range: bad table shape");
+  NSA_REQUIRE(n_blocks > 0 && first_bid >= 0 && first_bid + n_blocks <= MB, NSA_ERR_INVALID,
+              "block_range: range [%lld, %lld) is outside the table (%lld blocks)", static_cast<long long>(first_bid),
+              static_cast<long long>(first_bid + n_blocks), static_cast<long long>(MB));
+  NSA_REQUIRE(table && n_valid, NSA_ERR_INVALID, "block_range: null pointer");
+  const dim3 grid(H, static_cast<unsigned>(cdiv64(n_blocks, 128)));
+  block_range_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(table, n_valid, H, MB, first_bid, n_blocks,
+                                                                          k_base, v_base, head_stride_bytes, block_bytes,
+                                                                          n_valid_value, write_k, write_v, clear);
+  NSA_LAUNCH_OK("block_range_kernel");
+  return NSA_OK;
+}

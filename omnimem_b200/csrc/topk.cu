@@ -1,0 +1,472 @@
+// Block-compressed key scoring and top-k block selection.
+//   pool_rows_kernel   mean over runs of rows (key blocks / query groups), 16-byte loads
+//   score_kernel       fp32 scores of pooled queries against pooled keys
+//   select_kernel      per (b, group, h) row: top-k by (score desc, id asc) over packed
+//                      64-bit keys, -1 padding; also merges per-shard candidate lists
+#include "common.cuh"
+
+namespace nsa {
+namespace {
+
+// ---------------------------------------------------------------------------------- pooling
+struct PoolParams {
+  const char* x; int64_t x_sb, x_sn, x_sh;
+  char* out; int64_t o_sb, o_sn, o_sh;
+  int64_t N;
+  int D, size;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) pool_rows_kernel(const PoolParams p) {
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ float s_part[];                  // [rp][D]
+  const int64_t c = blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int lpr = p.D / VEC;                         // threads per row
+  const int rp = blockDim.x / lpr;                   // rows in flight
+  const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
+  const int64_t n0 = c * p.size;
+  const int n = static_cast<int>(p.N - n0 < p.size ? p.N - n0 : p.size);
+  float acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  if (r0 < rp) {
+    const char* base = p.x + (b * p.x_sb + n0 * p.x_sn + h * p.x_sh) * sizeof(T) + col * 16;
+    const int64_t row_bytes = p.x_sn * sizeof(T);
+    int r = r0;
+    // four independent 16-byte loads in flight per thread
+    for (; r + 3 * rp < n; r += 4 * rp) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(base + (r + u * rp) * row_bytes);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+      }
+    }
+    for (; r < n; r += rp) {
+      const uint4 v = *reinterpret_cast<const uint4*>(base + r * row_bytes);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_part[r0 * p.D + col * VEC + i] = acc[i];
+  }
+  __syncthreads();
+  const float inv = 1.f / static_cast<float>(n);
+  T* orow = reinterpret_cast<T*>(p.out + (b * p.o_sb + c * p.o_sn + h * p.o_sh) * sizeof(T));
+  for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
+    float s = 0.f;
+    for (int r = 0; r < rp; ++r) s += s_part[r * p.D + d];
+    orow[d] = from_f32<T>(s * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------- scoring
+struct ScoreParams {
+  const char* q; int64_t q_sb, q_sg, q_sh;
+  const char* k; int64_t k_sb, k_sc, k_sh;
+  float* scores;          // [B,H,MG,NC]
+  int MG, H, D;
+  int64_t NC;
+  float scale;
+};
+
+constexpr int kScoreCols = 64;
+constexpr int kScoreRows = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) score_kernel(const ScoreParams p) {
+  extern __shared__ float s_f[];
+  float* ks = s_f;                                   // [64][D+1]
+  float* qs = s_f + kScoreCols * (p.D + 1);          // [32][D]
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kScoreCols;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int ncol = static_cast<int>(p.NC - c0 < kScoreCols ? p.NC - c0 : kScoreCols);
+  for (int i = threadIdx.x; i < kScoreCols * p.D; i += blockDim.x) {
+    const int c = i / p.D, d = i - c * p.D;
+    float v = 0.f;
+    if (c < ncol)
+      v = to_f32<T>(*reinterpret_cast<const T*>(p.k + (b * p.k_sb + (c0 + c) * p.k_sc + h * p.k_sh + d) * sizeof(T)));
+    ks[c * (p.D + 1) + d] = v;
+  }
+  const int cl = threadIdx.x & 63, gq = threadIdx.x >> 6;   // 4 row groups of 8 rows
+  float* out = p.scores + ((static_cast<int64_t>(b) * p.H + h) * p.MG) * p.NC + c0 + cl;
+  for (int g0 = 0; g0 < p.MG; g0 += kScoreRows) {
+    __syncthreads();
+    const int nrow = min(kScoreRows, p.MG - g0);
+    for (int i = threadIdx.x; i < kScoreRows * p.D; i += blockDim.x) {
+      const int r = i / p.D, d = i - r * p.D;
+      float v = 0.f;
+      if (r < nrow)
+        v = to_f32<T>(*reinterpret_cast<const T*>(p.q + (b * p.q_sb + (g0 + r) * p.q_sg + h * p.q_sh + d) * sizeof(T)));
+      qs[i] = v;
+    }
+    __syncthreads();
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const float* kr = ks + cl * (p.D + 1);
+    const float* qr = qs + gq * 8 * p.D;
+    for (int d = 0; d < p.D; ++d) {
+      const float kv = kr[d];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(qr[i * p.D + d], kv, acc[i]);
+    }
+    if (cl < ncol) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int g = g0 + gq * 8 + i;
+        if (g < p.MG) out[static_cast<int64_t>(g) * p.NC] = acc[i] * p.scale + 0.f;
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------- selection
+struct Mask {
+  int block_size, chunk_size, chunk_size_k, G, q_off, ex_win, ex_sink;
+  int causal, tf, prog;
+  int q_half, k_half;
+  int id_base, id_stride;
+};
+
+struct RowMask { int q_cid, q_rel; bool q_clean, do_excl; };
+
+__device__ __forceinline__ RowMask make_row_mask(const Mask& m, int g) {
+  RowMask r;
+  r.q_cid = static_cast<int>((static_cast<int64_t>(g) * m.G) / m.chunk_size) + m.q_off;
+  if (m.tf) {
+    r.q_clean = r.q_cid < m.q_half;
+    r.q_rel = r.q_clean ? r.q_cid : r.q_cid - m.q_half;
+  } else {
+    r.q_clean = true;
+    r.q_rel = r.q_cid;
+  }
+  r.do_excl = m.prog ? (r.q_rel >= m.ex_sink + m.ex_win) : true;
+  return r;
+}
+
+// Visibility of the key block with GLOBAL id `bid` for a query row.
+__device__ __forceinline__ bool visible(const Mask& m, const RowMask& r, int bid) {
+  const int k_cid = static_cast<int>((static_cast<int64_t>(bid) * m.block_size) / m.chunk_size_k);
+  const bool k_clean = m.tf ? (k_cid < m.k_half) : true;
+  const int k_rel = (m.tf && !k_clean) ? k_cid - m.k_half : k_cid;
+  bool valid;
+  if (m.tf) {
+    valid = (r.q_clean && k_clean && k_rel <= r.q_rel) || (!r.q_clean && k_clean && k_rel < r.q_rel) ||
+            (!r.q_clean && !k_clean && k_rel == r.q_rel);
+  } else {
+    valid = m.causal ? (k_cid <= r.q_cid) : true;
+  }
+  if (m.ex_sink > 0) {
+    const bool sink_ok = !k_clean || k_rel >= m.ex_sink;
+    valid = valid && (sink_ok || !r.do_excl);
+  }
+  if (m.ex_win > 0) {
+    bool in_win;
+    if (m.tf) {
+      in_win = k_clean && k_rel >= r.q_rel - m.ex_win + 1;
+    } else {
+      in_win = k_cid >= r.q_cid - m.ex_win + 1;
+      if (!m.causal) in_win = in_win && k_cid <= r.q_cid + m.ex_win - 1;
+    }
+    valid = valid && (!in_win || !r.do_excl);
+  }
+  return valid;
+}
+
+// (score, id) -> 64-bit key; a larger key is a better candidate: higher score first, then the
+// lower id.  0 is reserved for "not a candidate".
+__device__ __forceinline__ unsigned long long pack_key(float s, int id) {
+  uint32_t u = __float_as_uint(s + 0.f);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  if (s != s) u = 1u;
+  if (u == 0u) u = 1u;
+  return (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - static_cast<uint32_t>(id));
+}
+__device__ __forceinline__ float key_score(unsigned long long k) {
+  uint32_t u = static_cast<uint32_t>(k >> 32);
+  u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+  return __uint_as_float(u);
+}
+__device__ __forceinline__ int key_id(unsigned long long k) {
+  return static_cast<int>(0xffffffffu - static_cast<uint32_t>(k & 0xffffffffu));
+}
+
+struct SelectParams {
+  const float* scores;    // MASKED mode: [rows_bh][MG][NC]; MERGE mode: [R][rows][T]
+  const int32_t* cand_ids;// MERGE mode only
+  int64_t NC;             // candidates per row
+  int MG, H;              // MASKED: row = (b*MG + g)*H + h
+  int seg_len;            // MERGE: T of the inputs
+  int64_t seg_stride;     // MERGE: rows*T
+  int topk;
+  int32_t* out_idx;       // [rows][topk]
+  float* out_scores;      // may be null
+  Mask mask;
+};
+
+template <bool MERGE>
+__global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
+  extern __shared__ unsigned long long s_keys[];     // [NC] when it fits (flag below), else unused
+  __shared__ unsigned long long s_red[4];
+  const int64_t row = blockIdx.x;
+  const bool in_smem = p.NC * 8 <= 64 * 1024;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+
+  RowMask rm{};
+  const float* srow;
+  if (MERGE) {
+    srow = p.scores + row * p.seg_len;
+  } else {
+    const int h = static_cast<int>(row % p.H);
+    const int64_t bg = row / p.H;
+    const int g = static_cast<int>(bg % p.MG);
+    const int64_t b = bg / p.MG;
+    rm = make_row_mask(p.mask, g);
+    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC;
+  }
+  auto key_at = [&](int64_t c) -> unsigned long long {
+    if (MERGE) {
+      const int64_t off = (c / p.seg_len) * p.seg_stride + (c % p.seg_len);
+      const int id = p.cand_ids[row * p.seg_len + off];
+      return id < 0 ? 0ull : pack_key(srow[off], id);
+    }
+    const int bid = p.mask.id_base + static_cast<int>(c) * p.mask.id_stride;
+    return visible(p.mask, rm, bid) ? pack_key(srow[c], bid) : 0ull;
+  };
+  if (in_smem) {
+    for (int64_t c = threadIdx.x; c < p.NC; c += blockDim.x) s_keys[c] = key_at(c);
+    __syncthreads();
+  }
+  auto scan_below = [&](unsigned long long bound) {
+    unsigned long long best = 0ull;
+    for (int64_t c = threadIdx.x; c < p.NC; c += blockDim.x) {
+      const unsigned long long k = in_smem ? s_keys[c] : key_at(c);
+      if (k < bound && k > best) best = k;
+    }
+    return best;
+  };
+
+  unsigned long long local = scan_below(~0ull);
+  int32_t* oi = p.out_idx + row * p.topk;
+  float* os = p.out_scores ? p.out_scores + row * p.topk : nullptr;
+  int r = 0;
+  for (; r < p.topk; ++r) {
+    unsigned long long best = local;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+      const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, d);
+      best = o > best ? o : best;
+    }
+    if (lane == 0) s_red[warp] = best;
+    __syncthreads();
+    best = s_red[0];
+    for (int w = 1; w < nw; ++w) best = s_red[w] > best ? s_red[w] : best;
+    __syncthreads();
+    if (best == 0ull) break;
+    if (threadIdx.x == 0) {
+      oi[r] = key_id(best);
+      if (os) os[r] = key_score(best);
+    }
+    if (local == best) local = scan_below(best);
+  }
+  for (int i = r + threadIdx.x; i < p.topk; i += blockDim.x) {
+    oi[i] = -1;
+    if (os) os[i] = -INFINITY;
+  }
+}
+
+int fill_mask(const nsa_topk_mask* in, int MG, int64_t NC_global, Mask* m) {
+  NSA_REQUIRE(in != nullptr, NSA_ERR_INVALID, "topk: mask is null");
+  NSA_REQUIRE(in->block_size > 0 && in->chunk_size > 0 && in->chunk_size_k > 0 && in->q_group_size > 0,
+              NSA_ERR_INVALID, "topk: block_size / chunk_size / chunk_size_k / q_group_size must be > 0");
+  NSA_REQUIRE(in->ex_win >= 0 && in->ex_sink >= 0 && in->q_chunk_offset >= 0, NSA_ERR_INVALID,
+              "topk: ex_win / ex_sink / q_chunk_offset must be >= 0");
+  NSA_REQUIRE(!(in->tf_mask && in->q_chunk_offset != 0), NSA_ERR_INVALID,
+              "topk: tf_mask assumes a full [clean|noisy] layout, q_chunk_offset must be 0");
+  NSA_REQUIRE(in->id_stride >= 1 && in->id_base >= 0, NSA_ERR_INVALID, "topk: id_stride must be >= 1, id_base >= 0");
+  m->block_size = in->block_size; m->chunk_size = in->chunk_size; m->chunk_size_k = in->chunk_size_k;
+  m->G = in->q_group_size; m->q_off = in->q_chunk_offset; m->ex_win = in->ex_win; m->ex_sink = in->ex_sink;
+  m->causal = in->causal; m->tf = in->tf_mask; m->prog = in->prog_excl;
+  m->id_base = in->id_base; m->id_stride = in->id_stride;
+  const int rows_per_chunk = in->chunk_size / in->q_group_size > 0 ? in->chunk_size / in->q_group_size : 1;
+  m->q_half = in->tf_mask ? MG / (2 * rows_per_chunk) : 0;
+  m->k_half = in->tf_mask ? static_cast<int>((NC_global * in->block_size) / (2 * static_cast<int64_t>(in->chunk_size_k))) : 0;
+  return NSA_OK;
+}
+
+template <typename T>
+int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
+  const int vec = 16 / static_cast<int>(sizeof(T));
+  const int lpr = p.D / vec;
+  const int rp = 128 / lpr;
+  const size_t smem = static_cast<size_t>(rp) * p.D * sizeof(float);
+  pool_rows_kernel<T><<<dim3(static_cast<unsigned>(NB), H, B), 128, smem, s>>>(p);
+  NSA_LAUNCH_OK("pool_rows_kernel");
+  return NSA_OK;
+}
+
+int check_rows16(const char* what, const void* ptr, const int64_t* stride, int esz) {
+  NSA_REQUIRE(ptr != nullptr, NSA_ERR_INVALID, "%s: null pointer", what);
+  NSA_REQUIRE(aligned16(ptr), NSA_ERR_LAYOUT, "%s: base address must be 16-byte aligned", what);
+  for (int i = 0; i < 3; ++i)
+    NSA_REQUIRE((stride[i] * esz) % 16 == 0, NSA_ERR_LAYOUT, "%s: stride %d is not a multiple of 16 bytes", what, i);
+  return NSA_OK;
+}
+
+int run_score_select(const void* qp, const int64_t* qs, const void* kp, const int64_t* ks, int B,
+                     int MG, int H, int D, int64_t NC, int topk, float scale, const Mask& m,
+                     int32_t* out_idx, float* out_scores, float* scores, int dtype, cudaStream_t s) {
+  ScoreParams sp{static_cast<const char*>(qp), qs[0], qs[1], qs[2], static_cast<const char*>(kp),
+                 ks[0], ks[1], ks[2], scores, MG, H, D, NC, scale};
+  const size_t smem = (static_cast<size_t>(kScoreCols) * (D + 1) + static_cast<size_t>(kScoreRows) * D) * sizeof(float);
+  const dim3 grid(static_cast<unsigned>(cdiv64(NC, kScoreCols)), H, B);
+  if (dtype == NSA_BF16) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    score_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(sp);
+  } else if (dtype == NSA_F16) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    score_kernel<__half><<<grid, 256, smem, s>>>(sp);
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    score_kernel<float><<<grid, 256, smem, s>>>(sp);
+  }
+  NSA_LAUNCH_OK("score_kernel");
+  SelectParams sel{};
+  sel.scores = scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
+  sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
+  sel.mask = m;
+  const size_t ksmem = NC * 8 <= 64 * 1024 ? static_cast<size_t>(NC) * 8 : 0;
+  NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+  const int64_t rows = static_cast<int64_t>(B) * MG * H;
+  select_kernel<false><<<static_cast<unsigned>(rows), 128, ksmem, s>>>(sel);
+  NSA_LAUNCH_OK("select_kernel");
+  return NSA_OK;
+}
+
+__global__ void fill_empty_kernel(int32_t* __restrict__ out_idx, float* __restrict__ out_scores, int64_t n) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    out_idx[i] = -1;
+    if (out_scores) out_scores[i] = -INFINITY;
+  }
+}
+
+int fill_minus_one(int32_t* out_idx, float* out_scores, int64_t n, cudaStream_t s) {
+  const int blocks = static_cast<int>(n / 256 + 1 < 1024 ? n / 256 + 1 : 1024);
+  fill_empty_kernel<<<blocks, 256, 0, s>>>(out_idx, out_scores, n);
+  NSA_LAUNCH_OK("fill_empty_kernel");
+  return NSA_OK;
+}
+
+}  // namespace
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out,
+                             const int64_t out_stride[3], int32_t B, int64_t N, int32_t H, int32_t D,
+                             int32_t size, int32_t dtype, void* stream) {
+  NSA_REQUIRE(B >= 0 && N >= 0 && H >= 0 && D > 0 && size > 0, NSA_ERR_INVALID, "pool_rows: bad size");
+  NSA_REQUIRE(dtype >= NSA_BF16 && dtype <= NSA_F32, NSA_ERR_UNSUPPORTED, "pool_rows: unknown dtype %d", dtype);
+  const int esz = dtype_size(dtype);
+  NSA_REQUIRE((D * esz) % 16 == 0 && D * esz / 16 <= 128, NSA_ERR_UNSUPPORTED,
+              "pool_rows: head dim %d not supported (row must be a multiple of 16 bytes, <= 2 KiB)", D);
+  if (B == 0 || N == 0 || H == 0) return NSA_OK;
+  NSA_REQUIRE(B <= 65535 && H <= 65535, NSA_ERR_INVALID, "pool_rows: B and H must be <= 65535");
+  int rc;
+  if ((rc = check_rows16("pool_rows x", x, x_stride, esz))) return rc;
+  NSA_REQUIRE(out != nullptr, NSA_ERR_INVALID, "pool_rows: out is null");
+  PoolParams p{static_cast<const char*>(x), x_stride[0], x_stride[1], x_stride[2],
+               static_cast<char*>(out), out_stride[0], out_stride[1], out_stride[2], N, D, size};
+  const int64_t NB = cdiv64(N, size);
+  NSA_REQUIRE(NB <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == NSA_BF16) return launch_pool<__nv_bfloat16>(p, B, H, NB, s);
+  if (dtype == NSA_F16) return launch_pool<__half>(p, B, H, NB, s);
+  return launch_pool<float>(p, B, H, NB, s);
+}
+
+extern "C" size_t nsa_topk_workspace_bytes(int32_t B, int32_t MG, int32_t H, int64_t NC) {
+  return align_up(static_cast<size_t>(B) * MG * H * NC * sizeof(float), 256);
+}
+
+static int topk_common_checks(int32_t B, int32_t MG, int32_t H, int32_t D, int64_t NC, int32_t topk,
+                              int32_t dtype, const int32_t* out_idx) {
+  NSA_REQUIRE(B >= 0 && MG >= 0 && H >= 0 && NC >= 0, NSA_ERR_INVALID, "topk: negative size");
+  NSA_REQUIRE(D >= 1 && D <= 256, NSA_ERR_INVALID, "topk: head dim must be in [1, 256], got %d", D);
+  NSA_REQUIRE(topk >= 1, NSA_ERR_INVALID, "topk: topk must be >= 1, got %d", topk);
+  NSA_REQUIRE(dtype >= NSA_BF16 && dtype <= NSA_F32, NSA_ERR_UNSUPPORTED, "topk: unknown dtype %d", dtype);
+  NSA_REQUIRE(static_cast<int64_t>(B) <= 65535 && H <= 65535, NSA_ERR_INVALID, "topk: B and H must be <= 65535");
+  NSA_REQUIRE(static_cast<int64_t>(B) * MG * H <= 0x7fffffff, NSA_ERR_INVALID, "topk: too many rows");
+  NSA_REQUIRE(out_idx != nullptr || static_cast<int64_t>(B) * MG * H == 0, NSA_ERR_INVALID, "topk: out_idx is null");
+  return NSA_OK;
+}
+
+extern "C" int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const void* k_pooled,
+                        const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
+                        int64_t NC, int32_t topk, float scale, const nsa_topk_mask* mask,
+                        int32_t* out_idx, float* out_scores, void* workspace, size_t workspace_bytes,
+                        int32_t dtype, void* stream) {
+  int rc;
+  if ((rc = topk_common_checks(B, MG, H, D, NC, topk, dtype, out_idx))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t rows = static_cast<int64_t>(B) * MG * H;
+  if (rows == 0) return NSA_OK;
+  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+  NSA_REQUIRE(q_pooled && k_pooled, NSA_ERR_INVALID, "topk: null pointer");
+  NSA_REQUIRE(workspace && workspace_bytes >= nsa_topk_workspace_bytes(B, MG, H, NC), NSA_ERR_WORKSPACE,
+              "topk: workspace too small");
+  Mask m;
+  const int64_t nc_global = mask ? mask->id_base + NC * static_cast<int64_t>(mask->id_stride > 0 ? mask->id_stride : 1) : NC;
+  if ((rc = fill_mask(mask, MG, mask && mask->id_stride > 1 ? nc_global : NC, &m))) return rc;
+  return run_score_select(q_pooled, q_stride, k_pooled, k_stride, B, MG, H, D, NC, topk, scale, m,
+                          out_idx, out_scores, static_cast<float*>(workspace), dtype, s);
+}
+
+extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
+                                   const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H,
+                                   int32_t D, int64_t N, int32_t topk, float scale,
+                                   const nsa_topk_mask* mask, void* k_pooled_out, int32_t* out_idx,
+                                   float* out_scores, void* workspace, size_t workspace_bytes,
+                                   int32_t dtype, void* stream) {
+  NSA_REQUIRE(mask != nullptr && mask->block_size > 0, NSA_ERR_INVALID, "pool_score_topk: mask / block_size");
+  NSA_REQUIRE(N >= 0, NSA_ERR_INVALID, "pool_score_topk: N < 0");
+  const int64_t NC = cdiv64(N, mask->block_size);
+  int rc;
+  if ((rc = topk_common_checks(B, MG, H, D, NC, topk, dtype, out_idx))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t rows = static_cast<int64_t>(B) * MG * H;
+  if (rows == 0 && (NC == 0 || !k_pooled_out)) return NSA_OK;
+  NSA_REQUIRE(k_pooled_out != nullptr, NSA_ERR_INVALID, "pool_score_topk: k_pooled_out is null");
+  const int64_t ps[3] = {NC * H * D, static_cast<int64_t>(H) * D, D};
+  if (NC > 0) {
+    if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
+  }
+  if (rows == 0) return NSA_OK;
+  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+  return nsa_topk(q_pooled, q_stride, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx,
+                  out_scores, workspace, workspace_bytes, dtype, stream);
+}
+
+extern "C" int nsa_merge_candidates(const int32_t* idx, const float* scores, int32_t R, int64_t rows,
+                                    int32_t T, int32_t topk, int32_t* out_idx, float* out_scores,
+                                    void* stream) {
+  NSA_REQUIRE(R >= 1 && rows >= 0 && T >= 1 && topk >= 1, NSA_ERR_INVALID, "merge_candidates: bad size");
+  NSA_REQUIRE(rows <= 0x7fffffff, NSA_ERR_INVALID, "merge_candidates: too many rows");
+  if (rows == 0) return NSA_OK;
+  NSA_REQUIRE(idx && scores && out_idx, NSA_ERR_INVALID, "merge_candidates: null pointer");
+  SelectParams sel{};
+  sel.scores = scores; sel.cand_ids = idx; sel.NC = static_cast<int64_t>(R) * T; sel.MG = 1; sel.H = 1;
+  sel.seg_len = T; sel.seg_stride = rows * T; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
+  const size_t ksmem = sel.NC * 8 <= 64 * 1024 ? static_cast<size_t>(sel.NC) * 8 : 0;
+  NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+  select_kernel<true><<<static_cast<unsigned>(rows), 128, ksmem, static_cast<cudaStream_t>(stream)>>>(sel);
+  NSA_LAUNCH_OK("select_kernel<merge>");
+  return NSA_OK;
+}

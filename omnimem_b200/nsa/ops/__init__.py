@@ -1,0 +1,5 @@
+from .index_topk import parallel_nsa_topk, parallel_nsa_topk_grouped_heads, should_use_selection_attention
+from .selection import selection_attention
+
+__all__ = ["parallel_nsa_topk", "parallel_nsa_topk_grouped_heads", "should_use_selection_attention",
+           "selection_attention"]

@@ -467,3 +467,96 @@ def dedup_keys(block_indices: torch.Tensor, heads: int, mb: int) -> torch.Tensor
     h = torch.arange(heads, dtype=torch.int64).view(1, 1, heads, 1).expand_as(ids)
     ok = (ids >= 0) & (ids < mb)
     return torch.unique(h[ok] * mb + ids[ok])
+
+
+class EpochLRUPagePool:
+    """Host model of the device page pool's policy, page ids included, for parity tests of
+    the cache kernels.  The LRU clock is an epoch counter bumped once per append / touch call;
+    victims are the owned, unprotected pages not stamped in the current epoch, in ascending
+    (stamp, page id) order.  With one key touched per epoch this is exactly the OrderedDict
+    LRU of cache.py:673-699 (`LRUBlockCacheModel`)."""
+
+    def __init__(self, num_heads: int, num_pages: int, max_blocks: int, page_tokens: int,
+                 protect_blocks: int = 0):
+        self.H, self.P, self.MB, self.PT = num_heads, num_pages, max_blocks, page_tokens
+        self.protect = protect_blocks
+        self.table = {}                 # key -> page
+        self.owner = [-1] * num_pages
+        self.stamp = [0] * num_pages
+        self.n_tokens = 0
+        self.epoch = 0
+        self.used = 0
+        self.host = set()               # keys whose K/V were saved to the host tier
+        self.evicted_any = False
+
+    @property
+    def n_blocks(self):
+        return -(-self.n_tokens // self.PT)
+
+    def _victims(self, n):
+        protect_from = max(self.n_blocks - self.protect, 0)
+        cand = [(self.stamp[p], p) for p in range(self.P)
+                if self.owner[p] >= 0 and self.owner[p] % self.MB < protect_from and self.stamp[p] < self.epoch]
+        cand.sort()
+        out = [p for _, p in cand[:n]]
+        return out + [-1] * (n - len(out))
+
+    def _evict(self, pages):
+        for p in pages:
+            if p < 0 or self.owner[p] < 0:
+                continue
+            key = self.owner[p]
+            self.host.add(key)
+            del self.table[key]
+            self.owner[p] = -1
+
+    def append(self, S, pos0=None):
+        pos0 = self.n_tokens if pos0 is None else pos0
+        first, last = pos0 // self.PT, (pos0 + S - 1) // self.PT
+        n_touched = last - first + 1
+        n_new = max(0, last + 1 - self.n_blocks)
+        self.epoch += 1
+        ids = []
+        need = n_new * self.H
+        if need:
+            fresh = min(need, self.P - self.used)
+            ids += list(range(self.used, self.used + fresh))
+            self.used += fresh
+            if need > fresh:
+                v = self._victims(need - fresh)
+                self._evict(v)
+                ids += v
+                self.evicted_any = True
+        for h in range(self.H):
+            for j in range(n_touched):
+                bid = first + j
+                key = h * self.MB + bid
+                page = self.table.get(key, -1)
+                if page < 0:
+                    jn = j - (n_touched - n_new)
+                    page = ids[h * n_new + jn] if jn >= 0 else -1
+                    if page >= 0:
+                        self.table[key] = page
+                        self.owner[page] = key
+                if page >= 0:
+                    self.stamp[page] = self.epoch
+        self.n_tokens = max(self.n_tokens, pos0 + S)
+
+    def touch(self, block_indices):
+        """block_indices [1,MG,H,T]; returns (unique keys, missing keys), both ascending."""
+        self.epoch += 1
+        uniq = [int(x) for x in dedup_keys(block_indices, self.H, self.MB).tolist()]
+        miss = [k for k in uniq if k not in self.table]
+        for k in uniq:
+            if k in self.table:
+                self.stamp[self.table[k]] = self.epoch
+        if self.evicted_any and miss:
+            v = self._victims(len(miss))
+            self._evict(v)
+            for k, p in zip(miss, v):
+                if p < 0:
+                    continue
+                self.table[k] = p
+                self.owner[p] = k
+                self.stamp[p] = self.epoch
+        return uniq, miss

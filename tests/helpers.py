@@ -1,0 +1,84 @@
+"""Shared comparison helpers of the parity tests."""
+import torch
+
+from oracle import nsa_oracle as O
+
+# tolerances for bf16 outputs and gradients of the selection attention
+MAX_ABS = 2e-2
+MEAN_ABS = 2e-3
+# index parity: ids may differ only where the score is within this band of the k-th score
+TIE_BAND = 1e-3
+
+
+def assert_close_bf16(got: torch.Tensor, want: torch.Tensor, what: str, max_abs=MAX_ABS, mean_abs=MEAN_ABS):
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    diff = (got - want).abs()
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    assert diff.max().item() <= max_abs, f"{what}: max abs {diff.max().item():.4g} > {max_abs}"
+    assert diff.mean().item() <= mean_abs, f"{what}: mean abs {diff.mean().item():.4g} > {mean_abs}"
+
+
+def masked_scores(qp, kp, scale, **mask_kw):
+    """fp32 [B,H,MG,NC] oracle scores with -inf at invisible blocks."""
+    s = O.scores(qp, kp, scale) + 0.0
+    vis = O.visibility_mask(qp.shape[1], kp.shape[1], **mask_kw)
+    return s.masked_fill(~vis[None, None], float("-inf"))
+
+
+def assert_topk_parity(idx_gpu, s_masked, topk, exact=False):
+    """idx_gpu int32 [B,MG,H,T] against oracle scores [B,H,MG,NC]: every row lists only
+    visible blocks, in (score desc, id asc) order, and its id set equals the oracle's except
+    for blocks whose score lies within TIE_BAND of the k-th score."""
+    idx_gpu = idx_gpu.cpu().long()
+    B, MG, H, T = idx_gpu.shape
+    NC = s_masked.shape[-1]
+    order = torch.sort(s_masked, dim=-1, descending=True, stable=True)
+    want = order.indices[..., :T].permute(0, 2, 1, 3)
+    want_v = order.values[..., :T].permute(0, 2, 1, 3)
+    if NC < T:
+        pad = torch.full((B, MG, H, T - NC), -1, dtype=torch.long)
+        want = torch.cat([want, pad], -1)
+        want_v = torch.cat([want_v, torch.full((B, MG, H, T - NC), float("-inf"))], -1)
+    want = torch.where(want_v == float("-inf"), torch.full_like(want, -1), want)
+    if exact:
+        assert torch.equal(idx_gpu, want), "top-k ids differ from the oracle"
+        return 0
+    n_valid_gpu = (idx_gpu >= 0).sum(-1)
+    assert torch.equal(n_valid_gpu, (want >= 0).sum(-1)), "number of selected blocks differs"
+    # valid ids first, -1 after
+    assert ((idx_gpu >= 0).long().diff(dim=-1) <= 0).all(), "-1 padding is not at the end"
+    sg = torch.gather(s_masked.permute(0, 2, 1, 3), -1, idx_gpu.clamp_min(0))
+    sg = torch.where(idx_gpu >= 0, sg, torch.full_like(sg, float("-inf")))
+    assert (sg[idx_gpu >= 0] > float("-inf")).all(), "an invisible block was selected"
+    # order: scores non-increasing (up to the band), equal scores by ascending id
+    d = sg[..., 1:] - sg[..., :-1]
+    both = (idx_gpu[..., 1:] >= 0)
+    assert (d[both] <= TIE_BAND).all(), "scores are not in descending order"
+    mismatch = 0
+    kth = want_v.clone()
+    kth[want < 0] = float("inf")
+    kth = kth.min(-1).values                                   # score of the last valid slot
+    for b in range(B):
+        for g in range(MG):
+            for h in range(H):
+                a = set(idx_gpu[b, g, h].tolist()) - {-1}
+                w = set(want[b, g, h].tolist()) - {-1}
+                if a == w:
+                    continue
+                mismatch += 1
+                for bid in a ^ w:
+                    sc = s_masked[b, h, g, bid].item()
+                    assert abs(sc - kth[b, g, h].item()) <= TIE_BAND, (
+                        f"row {(b, g, h)}: block {bid} score {sc} is not within {TIE_BAND} of the k-th "
+                        f"score {kth[b, g, h].item()}")
+    return mismatch
+
+
+def separated_keys(B, NC, H, D, gen, spread=3.0):
+    """Pooled keys with well separated scores: a random direction per block scaled by distinct
+    magnitudes, so bf16 rounding cannot reorder the top-k."""
+    k = torch.randn(B, NC, H, D, generator=gen)
+    k = k / k.norm(dim=-1, keepdim=True)
+    mag = torch.linspace(1.0, spread, NC)[torch.randperm(NC, generator=gen)]
+    return (k * mag.view(1, NC, 1, 1) * 4.0).to(torch.bfloat16)

@@ -1,0 +1,181 @@
+"""Block KV cache kernels: append (mid-page starts, pooled-key refresh), selected-block
+dedup + LRU touch, eviction to / fetch from the host tier, the reference's K1-K3 contracts."""
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.helpers import assert_close_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(dev, H=3, D=128, pages=64, max_blocks=32, pt=64, **kw):
+    from omnimem_b200.cache import BlockKVCache
+    return BlockKVCache(H, D, pages, max_blocks, pt, torch.bfloat16, dev, **kw)
+
+
+def _dense_from_cache(cache):
+    """Reassemble [n_tokens, H, D] K and V through the block table (resident blocks only)."""
+    tab = cache.block_table.cpu()
+    kp, vp = cache.k_pool.cpu(), cache.v_pool.cpu()
+    K = torch.zeros(cache.n_blocks * cache.page_tokens, cache.H, cache.D, dtype=kp.dtype)
+    V = torch.zeros_like(K)
+    for h in range(cache.H):
+        for b in range(cache.n_blocks):
+            p = int(tab[h, b])
+            if p >= 0:
+                K[b * cache.page_tokens:(b + 1) * cache.page_tokens, h] = kp[p]
+                V[b * cache.page_tokens:(b + 1) * cache.page_tokens, h] = vp[p]
+    return K[: cache.n_tokens], V[: cache.n_tokens]
+
+
+def test_append_mid_page_and_pooled_refresh(dev):
+    g = torch.Generator().manual_seed(1)
+    cache = _mk(dev, host_tier=False)
+    H, D = cache.H, cache.D
+    chunks = [100, 28, 1, 200, 64, 7]            # starts and ends inside pages
+    ks, vs = [], []
+    for S in chunks:
+        k = torch.randn(S, H, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(S, H, D, generator=g).to(torch.bfloat16)
+        cache.append(k.to(dev), v.to(dev))
+        ks.append(k)
+        vs.append(v)
+        K, V = torch.cat(ks), torch.cat(vs)
+        Kc, Vc = _dense_from_cache(cache)
+        assert torch.equal(Kc, K) and torch.equal(Vc, V)
+        want = O.pool_rows(K.unsqueeze(0), 64)                       # [1, nb, H, D]
+        got = cache.pooled_keys().cpu()
+        assert got.shape == want.shape
+        assert (got.float() - want.float()).abs().max() <= 2 ** -8 * 4
+        assert (got == want).float().mean() > 0.97
+        wantv = O.pool_rows(V.unsqueeze(0), 64)
+        assert (cache.pooled_values().cpu().float() - wantv.float()).abs().max() <= 2 ** -8 * 4
+    cache.check_status()
+    # overwrite the last chunk in place (what each denoising step does)
+    k2 = torch.randn(7, H, D, generator=g).to(torch.bfloat16)
+    cache.append(k2.to(dev), k2.to(dev), pos0=cache.n_tokens - 7)
+    Kc, _ = _dense_from_cache(cache)
+    assert torch.equal(Kc[-7:], k2) and torch.equal(Kc[:-7], torch.cat(ks)[:-7])
+
+
+def test_paged_attention_equals_dense(dev):
+    from omnimem_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    H, D, N, M, G, T = 2, 128, 1000, 200, 64, 5
+    cache = _mk(dev, H=H, pages=40, max_blocks=16, host_tier=False)
+    k = torch.randn(N, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(N, H, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, M, H, D, generator=g).to(torch.bfloat16)
+    for a in range(0, N, 300):
+        cache.append(k[a:a + 300].to(dev), v[a:a + 300].to(dev))
+    ids = O.parallel_nsa_topk(q, cache.pooled_keys().cpu(), T, 64, None, 10 ** 6, False, G)
+    out, lse = cache.selection_attention(q.to(dev), ids.to(dev), group_size=G, return_lse=True)
+    o_ref, l_ref = O.selection_fwd(q.float(), k.unsqueeze(0).float(), v.unsqueeze(0).float(), ids, 64, 1, None, False, G)
+    assert_close_bf16(out, o_ref, "paged out")
+    dense, _ = ops.sel_fwd(q.to(dev), ops.DenseKV(k.unsqueeze(0).to(dev), v.unsqueeze(0).to(dev)), ids.to(dev), 64, 1,
+                           D ** -0.5, False, G)
+    assert torch.equal(out, dense)                       # same kernel, same tiles: bit-identical
+
+
+def test_dedup_touch_lists(dev):
+    g = torch.Generator().manual_seed(3)
+    cache = _mk(dev, H=3, pages=30, max_blocks=10, host_tier=False)
+    k = torch.randn(640, 3, 128, generator=g).to(torch.bfloat16).to(dev)
+    cache.append(k, k)
+    ids = torch.randint(-1, 12, (1, 5, 3, 4), generator=g, dtype=torch.int32)
+    uniq, miss = cache.touch(ids.to(dev), return_lists=True)
+    want = O.dedup_keys(ids, 3, 10)
+    n = int(uniq[0])
+    assert n == want.numel() and uniq[1:1 + n].cpu().tolist() == want.tolist()
+    assert int(miss[0]) == 0
+    # touched pages carry the new epoch
+    tab = cache.block_table.cpu().view(-1)
+    st = cache.page_stamp.cpu()
+    for key in want.tolist():
+        assert st[tab[key]] == cache.epoch
+
+
+def test_reference_block_kv_contracts(dev):
+    """Smoke vectors of the reference's own warm-up (nsa/cuda_backend/block_kv_ops.py:90-111)."""
+    from omnimem_b200 import ops
+    for wide in (True, False):
+        src = torch.arange(32, dtype=torch.int16, device=dev).view(2, 16) + 1
+        dst = torch.zeros(2, 16, dtype=torch.int16, device=dev)
+        table = torch.full((4,), -1, dtype=torch.int64, device=dev)
+        a = table.data_ptr()
+        desc = torch.tensor([src[0].data_ptr(), src[1].data_ptr(), dst[0].data_ptr(), dst[1].data_ptr(),
+                             a, a + 8, a + 16, a + 24], dtype=torch.int64, device=dev)
+        assert ops.gather_publish_clear(desc, 1, 2, 32, wide, 1) == 2
+        assert torch.equal(dst, src)
+        assert table.tolist() == [dst[0].data_ptr(), dst[1].data_ptr(), 0, 0]
+    assert ops.gather_publish_clear(desc, 0, 0, 32, True, 1) == 0
+    tab = torch.zeros(2, 1, 4, dtype=torch.int64, device=dev)
+    nv = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.block_range(tab, nv, 0, 4, 4096, 8192, 64, 16, 4, True, True, False)
+    assert tab[0, 0].tolist() == [4096 + 16 * j for j in range(4)]
+    assert tab[1, 0].tolist() == [8192 + 16 * j for j in range(4)]
+    assert nv.item() == 4
+    ops.block_range(tab, nv, 1, 2, 0, 0, 0, 0, -1, True, False, True)
+    assert tab[0, 0].tolist() == [4096, 0, 0, 4096 + 48] and tab[1, 0, 1].item() == 8192 + 16 and nv.item() == 4
+    ids = torch.tensor([0, -1, 3, 3], dtype=torch.int32, device=dev)
+    stamp = torch.full((4,), -1, dtype=torch.int32, device=dev)
+    out = torch.zeros(1 + 4, dtype=torch.int32, device=dev)
+    ops.dedup_run(ids, stamp, out, 1, 4, 1, 4, 4, 4)
+    assert out[:3].tolist() == [2, 0, 3]
+    # chunked key order (cid*H + h)*bpc + loc with 2 heads, 2 blocks per chunk
+    ids = torch.tensor([[3, 0], [2, 3]], dtype=torch.int32, device=dev).view(-1)     # [MG=1,H=2,T=2]
+    stamp = torch.zeros(8, dtype=torch.int32, device=dev)
+    out = torch.zeros(1 + 8, dtype=torch.int32, device=dev)
+    ops.dedup_run(ids, stamp, out, 5, 4, 2, 2, 2, 8)
+    # head0: bids 3,0 -> keys (1*2+0)*2+1=5, 0 ; head1: bids 2,3 -> (1*2+1)*2+0=6, 7
+    assert out[:5].tolist() == [4, 0, 5, 6, 7]
+
+
+def test_lru_eviction_and_fetch_follow_the_policy_model(dev):
+    g = torch.Generator().manual_seed(4)
+    H, D, PT, MB, P = 2, 128, 64, 24, 16                 # 16 pages for up to 48 (head, block) pairs
+    cache = _mk(dev, H=H, D=D, pages=P, max_blocks=MB, pt=PT, host_tier=True, protect_blocks=2)
+    model = O.EpochLRUPagePool(H, P, MB, PT, protect_blocks=2)
+    K = torch.randn(MB * PT, H, D, generator=g).to(torch.bfloat16)
+    V = torch.randn(MB * PT, H, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, 64, H, D, generator=g).to(torch.bfloat16)
+    pos = 0
+    for step in range(8):
+        S = [150, 64, 100, 200, 30, 128, 90, 70][step]
+        cache.append(K[pos:pos + S].to(dev), V[pos:pos + S].to(dev))
+        model.append(S)
+        pos += S
+        nb = cache.n_blocks
+        ids = torch.stack([torch.randperm(nb, generator=g)[:3] for _ in range(H)]).to(torch.int32).view(1, 1, H, 3)
+        uniq, miss = cache.touch(ids.to(dev), return_lists=True)
+        mu, mm = model.touch(ids)
+        assert uniq[1:1 + int(uniq[0])].cpu().tolist() == mu
+        assert miss[1:1 + int(miss[0])].cpu().tolist() == mm
+        tab = cache.block_table.cpu().view(-1)
+        for key in range(H * MB):
+            assert int(tab[key]) == model.table.get(key, -1), f"step {step} key {key}"
+        assert cache.page_owner.cpu().tolist() == model.owner
+        # every selected block is resident now and holds the right data (fetched from the host tier)
+        out, lse = ops_sel(cache, q.to(dev), ids.to(dev))
+        o_ref, l_ref = O.selection_fwd(q.float(), K[:pos].unsqueeze(0).float(), V[:pos].unsqueeze(0).float(), ids,
+                                       PT, 1, None, False, 64)
+        assert_close_bf16(out, o_ref, f"step {step} out after fetch")
+    cache.check_status()
+    assert model.evicted_any and len(model.host) > 0
+
+
+def ops_sel(cache, q, ids):
+    from omnimem_b200 import ops
+    return ops.sel_fwd(q, cache.kv_source(), ids, cache.page_tokens, 1, q.shape[-1] ** -0.5, False, 64)
+
+
+def test_pool_exhaustion_sets_status(dev):
+    from omnimem_b200 import NSABackendError
+    cache = _mk(dev, H=2, pages=4, max_blocks=8, host_tier=False, protect_blocks=8)   # everything protected
+    k = torch.randn(128, 2, 128).to(torch.bfloat16).to(dev)
+    cache.append(k, k)                      # 2 blocks x 2 heads = 4 pages: full
+    cache.check_status()
+    cache.append(k[:64], k[:64])            # needs 2 more pages, nothing may be evicted
+    with pytest.raises(NSABackendError, match="exhausted"):
+        cache.check_status()

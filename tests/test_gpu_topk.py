@@ -1,0 +1,203 @@
+"""Pooling, scoring and top-k selection kernels against the CPU oracle (through the C ABI)."""
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from tests.helpers import assert_topk_parity, masked_scores, separated_keys
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from omnimem_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("N,size,H,D", [(300, 60, 3, 128), (1560, 64, 2, 128), (70, 64, 1, 64), (33, 1, 2, 96), (40, 15, 2, 32)])
+def test_pool_rows(dev, dtype, N, size, H, D):
+    g = torch.Generator().manual_seed(N + size)
+    x = torch.randn(2, N, H, D, generator=g).to(dtype)
+    want = O.pool_rows(x, size)
+    got = _ops().pool_rows(x.to(dev), size).cpu()
+    assert got.shape == want.shape and got.dtype == dtype
+    # fp32 sums in a different order may round a value to the neighbouring representable number
+    ulp = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11, torch.float32: 2 ** -22}[dtype]
+    err = (got.float() - want.float()).abs()
+    assert (err <= ulp * want.float().abs().clamp_min(2 ** -6) * 1.01).all()
+    assert (err == 0).float().mean() > 0.97
+
+
+def test_pool_rows_matches_reference_expression(dev, golden):
+    d = golden("pool")
+    B, N, H, D, bs, G, M = d["meta"].tolist()
+    kc = _ops().pool_rows(d["k"].to(dev), bs).cpu()
+    qg = _ops().pool_rows(d["q"].to(dev), G).cpu()
+    assert ((kc.float() - d["k_cmp"].float()).abs() <= 2 ** -8 * d["k_cmp"].float().abs().clamp_min(2 ** -6)).all()
+    assert ((qg.float() - d["q_grp"].float()).abs() <= 2 ** -8 * d["q_grp"].float().abs().clamp_min(2 ** -6)).all()
+    assert (kc == d["k_cmp"]).float().mean() > 0.97
+
+
+def test_pool_rows_strided_input(dev):
+    x = torch.randn(1, 128, 4, 256).to(torch.bfloat16)
+    xs = x.to(dev)[..., :128]                       # rows 256 B apart in a 512 B pitch
+    assert not xs.is_contiguous()
+    got = _ops().pool_rows(xs, 32).cpu()
+    assert torch.equal(got, O.pool_rows(x[..., :128].contiguous(), 32)) or \
+        (got.float() - O.pool_rows(x[..., :128].contiguous(), 32).float()).abs().max() < 2 ** -7
+
+
+@pytest.mark.parametrize("name", ["topk_causal", "topk_full"])
+def test_topk_golden_from_reference_naive(dev, golden, name):
+    d = golden(name)
+    B, M, NC, H, D, T, bs, chunk, causal = d["meta"].tolist()
+    idx = _ops().topk(d["q"].to(dev), d["k_cmp"].to(dev), T, D ** -0.5, bs, chunk, chunk, bool(causal)).cpu()
+    vis = O.visibility_mask(M, NC, block_size=bs, chunk_size=chunk, chunk_size_k=chunk, causal=bool(causal))
+    ref = d["top_idx_sorted"]
+    s = masked_scores(d["q"].float(), d["k_cmp"].float(), D ** -0.5, block_size=bs, chunk_size=chunk,
+                      chunk_size_k=chunk, causal=bool(causal))
+    assert_topk_parity(idx, s, T)
+    same = 0
+    for b in range(B):
+        for g in range(M):
+            for h in range(H):
+                mine = set(idx[b, g, h].tolist()) - {-1}
+                theirs = set(int(x) for x in ref[b, g, h].tolist() if vis[g, int(x)])
+                same += mine == theirs
+    assert same >= 0.98 * B * M * H           # the rest are ties inside the band (checked above)
+
+
+MASKS = [
+    dict(causal=True, ex_win=0, ex_sink=0, prog_excl=False, q_chunk_offset=0, q_group_size=1),
+    dict(causal=False, ex_win=3, ex_sink=0, prog_excl=True, q_chunk_offset=4, q_group_size=4),
+    dict(causal=True, ex_win=2, ex_sink=1, prog_excl=False, q_chunk_offset=0, q_group_size=2),
+    dict(causal=False, ex_win=1, ex_sink=2, prog_excl=True, q_chunk_offset=2, q_group_size=1),
+    dict(causal=True, ex_win=3, ex_sink=1, prog_excl=True, q_chunk_offset=1, q_group_size=4),
+    dict(causal=False, ex_win=0, ex_sink=0, prog_excl=False, q_chunk_offset=0, q_group_size=8),
+]
+
+
+@pytest.mark.parametrize("mk", MASKS)
+def test_topk_mask_modes_exact_on_separated_scores(dev, mk):
+    g = torch.Generator().manual_seed(5)
+    B, MG, NC, H, D, T, bs, cs = 2, 24, 40, 3, 64, 6, 8, 16
+    q = torch.randn(B, MG, H, D, generator=g).to(torch.bfloat16)
+    k = separated_keys(B, NC, H, D, g)
+    kw = dict(block_size=bs, chunk_size=cs, chunk_size_k=cs, causal=mk["causal"], ex_win=mk["ex_win"],
+              ex_sink=mk["ex_sink"], prog_excl=mk["prog_excl"], q_chunk_offset=mk["q_chunk_offset"],
+              q_group_size=mk["q_group_size"])
+    want, want_s = O.topk_select(q, k, T, 0.125, return_scores=True, **kw)
+    got, got_s = _ops().topk(q.to(dev), k.to(dev), T, 0.125, bs, cs, cs, mk["causal"], mk["ex_win"], mk["ex_sink"],
+                             mk["prog_excl"], False, mk["q_chunk_offset"], mk["q_group_size"], return_scores=True)
+    s = masked_scores(q, k, 0.125, **kw)
+    assert_topk_parity(got, s, T)
+    assert (got.cpu() == want).float().mean() > 0.995
+    fin = torch.isfinite(want_s)
+    assert torch.equal(torch.isfinite(got_s.cpu()), fin)
+    assert torch.allclose(got_s.cpu()[fin], want_s[fin], atol=1e-4, rtol=1e-5)
+
+
+def test_topk_tf_mask(dev):
+    g = torch.Generator().manual_seed(6)
+    B, MG, NC, H, D, T, bs, cs = 1, 32, 32, 2, 32, 5, 4, 8       # 2 clean + 2 noisy chunks
+    q = torch.randn(B, MG, H, D, generator=g).to(torch.bfloat16)
+    k = separated_keys(B, NC, H, D, g)
+    kw = dict(block_size=bs, chunk_size=cs, chunk_size_k=cs, causal=False, tf_mask=True, ex_win=1, ex_sink=0)
+    want = O.topk_select(q, k, T, 0.2, **kw)
+    got = _ops().topk(q.to(dev), k.to(dev), T, 0.2, bs, cs, cs, False, 1, 0, False, True, 0, 1).cpu()
+    assert (got == want).float().mean() > 0.99
+    assert_topk_parity(got, masked_scores(q, k, 0.2, **kw), T)
+
+
+def test_topk_ties_pick_lowest_id_and_pad_with_minus_one(dev):
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(1, 2, 1, 16, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 3, 1, 16, generator=g).to(torch.bfloat16).repeat(1, 2, 1, 1)   # ids j and j+3 tie exactly
+    got = _ops().topk(q.to(dev), k.to(dev), 8, 0.25, 4, 1, 4, False).cpu()
+    want = O.topk_select(q, k, 8, 0.25, block_size=4, chunk_size=1, chunk_size_k=4, causal=False)
+    assert torch.equal(got, want)
+    for r in range(2):
+        row = got[0, r, 0].tolist()
+        assert row[6:] == [-1, -1]
+        assert all(row[a + 1] == row[a] + 3 for a in range(0, 6, 2))
+
+
+def test_topk_edge_sizes(dev):
+    q = torch.randn(1, 3, 2, 32).to(torch.bfloat16).to(dev)
+    empty = torch.empty(1, 0, 2, 32, dtype=torch.bfloat16, device=dev)
+    got, sc = _ops().topk(q, empty, 4, 1.0, 8, 8, 8, False, return_scores=True)
+    assert (got == -1).all() and got.shape == (1, 3, 2, 4)
+    assert torch.isinf(sc).all() and (sc < 0).all()
+    # a row that sees nothing (causal, query chunk before every key chunk)
+    k = torch.randn(1, 4, 2, 32).to(torch.bfloat16).to(dev)
+    got = _ops().topk(q[:, :0], k, 4, 1.0, 8, 8, 8, True)
+    assert got.shape == (1, 0, 2, 4)
+
+
+def test_topk_fp32_inputs(dev):
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn(1, 25, 12, 128, generator=g)
+    k = torch.randn(1, 98, 12, 128, generator=g)
+    kw = dict(block_size=64, chunk_size=1560, chunk_size_k=1560, causal=True, q_chunk_offset=3, q_group_size=64)
+    got = _ops().topk(q.to(dev), k.to(dev), 16, 128 ** -0.5, 64, 1560, 1560, True, q_chunk_offset=3, q_group_size=64)
+    assert_topk_parity(got, masked_scores(q, k, 128 ** -0.5, **kw), 16)
+
+
+def test_facade_config1_shape_ragged(dev):
+    """B=1, H=12, D=128, one 1560-token frame of queries against 4 frames of keys in 64-token
+    blocks: last block has 32 tokens, last query group 24 queries."""
+    from omnimem_b200.nsa.ops import parallel_nsa_topk
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 1560, 12, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 6240, 12, 128, generator=g).to(torch.bfloat16)
+    kp_gpu = _ops().pool_rows(k.to(dev), 64)
+    idx = parallel_nsa_topk(q.to(dev), kp_gpu, 16, 64, None, 1560, True, group_size=64, q_chunk_offset=3,
+                            allow_ragged=True)
+    assert idx.shape == (1, 25, 12, 16) and idx.dtype == torch.int32
+    # oracle on the SAME pooled operands (pooling parity is tested separately)
+    qp = _ops().pool_rows(q.to(dev), 64).cpu()
+    s = masked_scores(qp, kp_gpu.cpu(), 128 ** -0.5, block_size=64, chunk_size=1560, chunk_size_k=1560,
+                      causal=True, q_chunk_offset=3, q_group_size=64)
+    assert_topk_parity(idx, s, 16)
+    with pytest.raises(AssertionError):
+        parallel_nsa_topk(q.to(dev), kp_gpu, 16, 64, None, 1560, True, group_size=64, q_chunk_offset=3)
+
+
+def test_pool_score_topk_equals_two_step(dev):
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(1, 10, 4, 128, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(1, 1000, 4, 128, generator=g).to(torch.bfloat16).to(dev)
+    idx, kp, sc = _ops().pool_score_topk(q, k, 8, 0.1, 64, 640, 640, False, q_group_size=64, return_scores=True)
+    kp2 = _ops().pool_rows(k, 64)
+    idx2, sc2 = _ops().topk(q, kp2, 8, 0.1, 64, 640, 640, False, q_group_size=64, return_scores=True)
+    assert torch.equal(kp, kp2) and torch.equal(idx, idx2) and torch.equal(sc, sc2)
+
+
+def test_topk_many_blocks_uses_global_path(dev):
+    g = torch.Generator().manual_seed(10)
+    NC = 9000                                           # more keys than fit the shared-memory key cache
+    q = torch.randn(1, 3, 2, 64, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, NC, 2, 64, generator=g).to(torch.bfloat16)
+    got = _ops().topk(q.to(dev), k.to(dev), 32, 0.125, 64, 10 ** 6, 10 ** 6, False)
+    s = masked_scores(q, k, 0.125, block_size=64, chunk_size=10 ** 6, chunk_size_k=10 ** 6, causal=False)
+    assert_topk_parity(got, s, 32)
+
+
+def test_sharded_candidates_merge_to_global_topk(dev):
+    g = torch.Generator().manual_seed(11)
+    B, MG, NC, H, D, T, R = 1, 9, 203, 3, 128, 16, 4
+    q = torch.randn(B, MG, H, D, generator=g).to(torch.bfloat16).to(dev)
+    k = separated_keys(B, NC, H, D, g).to(dev)
+    full, full_s = _ops().topk(q, k, T, 0.09, 64, 4680, 4680, True, q_chunk_offset=2, q_group_size=64,
+                               return_scores=True)
+    parts_i, parts_s = [], []
+    for r in range(R):
+        li, ls = _ops().topk(q, k[:, r::R].contiguous(), T, 0.09, 64, 4680, 4680, True, q_chunk_offset=2,
+                             q_group_size=64, id_base=r, id_stride=R, return_scores=True)
+        parts_i.append(li)
+        parts_s.append(ls)
+    mi, ms = _ops().merge_candidates(torch.stack(parts_i), torch.stack(parts_s), T)
+    assert torch.equal(mi, full)
+    assert torch.equal(ms, full_s)
+    oi, _ = O.merge_candidates([p.cpu() for p in parts_i], [p.cpu() for p in parts_s], T)
+    assert torch.equal(mi.cpu(), oi)
