@@ -47,10 +47,10 @@ def test_append_mid_page_and_pooled_refresh(dev):
         want = O.pool_rows(K.unsqueeze(0), 64)                       # [1, nb, H, D]
         got = cache.pooled_keys().cpu()
         assert got.shape == want.shape
-        assert (got.float() - want.float()).abs().max() <= 2 ** -8 * 4
+        assert ((got.float() - want.float()).abs() <= 2 ** -7 * want.float().abs() + 1e-6).all()
         assert (got == want).float().mean() > 0.97
         wantv = O.pool_rows(V.unsqueeze(0), 64)
-        assert (cache.pooled_values().cpu().float() - wantv.float()).abs().max() <= 2 ** -8 * 4
+        assert ((cache.pooled_values().cpu().float() - wantv.float()).abs() <= 2 ** -7 * wantv.float().abs() + 1e-6).all()
     cache.check_status()
     # overwrite the last chunk in place (what each denoising step does)
     k2 = torch.randn(7, H, D, generator=g).to(torch.bfloat16)
