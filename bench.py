@@ -191,6 +191,16 @@ def run_gpu(args):
     barrier()
     ms_total = t0.elapsed_time(t1)
 
+    if args.kernels_only:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"metric": METRIC, "kernels_only": True, "steps": args.steps,
+                              "ms_per_step": round(ms_total / args.steps, 4),
+                              "value": round(world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, 3)}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
     # ---- end to end: pinned host -> device, step, results -> pinned host
     res_host = {n: torch.empty_like(x, device="cpu").pin_memory() for n, x in
                 (("out", out), ("dq", dq), ("dk", dk), ("dv", dv))}
@@ -342,6 +352,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="device-resident steps only (no end-to-end leg, no CPU baseline): the command profiled by ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

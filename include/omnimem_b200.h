@@ -61,6 +61,7 @@ typedef struct nsa_kv_source {
   const int64_t* ptr_k;      /* ptr: K block addresses, element strides = idx_stride */
   const int64_t* ptr_v;      /* ptr: V block addresses */
   int64_t ptr_stride_n;      /* ptr: elements between consecutive tokens of a block */
+  int64_t num_pages;         /* paged: pages in the pool (0 = unknown) */
 } nsa_kv_source;
 
 /* Visibility rules of the top-k (topk.cu:16-97 TopkMask / visible()). */
@@ -82,6 +83,11 @@ typedef struct nsa_topk_mask {
 const char* nsa_last_error(void);
 /* Library version string; also a cheap "does the library load" probe. */
 const char* nsa_version(void);
+
+/* Reads and clears the sticky device-side status word: 0, or a negative nsa_status when a
+ * kernel gave up on a bounded wait (its outputs are then undefined).  Synchronises with the
+ * device; meant for tests and debugging, not for the hot path. */
+int nsa_device_status(int32_t* value);
 
 /* Mean over runs of `size` rows of dim 1: x [B,N,H,D] -> out [B,ceil(N/size),H,D], fp32
  * accumulation, rounded to the input dtype; a short last run averages the rows that exist.

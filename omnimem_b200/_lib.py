@@ -27,7 +27,7 @@ class KVSource(C.Structure):
         ("mode", C.c_int32), ("k", C.c_void_p), ("v", C.c_void_p),
         ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("n_tokens", C.c_int64),
         ("block_table", C.c_void_p), ("max_blocks", C.c_int32), ("page_tokens", C.c_int32),
-        ("ptr_k", C.c_void_p), ("ptr_v", C.c_void_p), ("ptr_stride_n", C.c_int64),
+        ("ptr_k", C.c_void_p), ("ptr_v", C.c_void_p), ("ptr_stride_n", C.c_int64), ("num_pages", C.c_int64),
     ]
 
 
@@ -44,6 +44,7 @@ _S3 = C.POINTER(C.c_int64)
 PROTOTYPES = {
     "nsa_last_error": (C.c_char_p, []),
     "nsa_version": (C.c_char_p, []),
+    "nsa_device_status": (_i32, [C.POINTER(C.c_int32)]),
     "nsa_pool_rows": (_i32, [_vp, _S3, _vp, _S3, _i32, _i64, _i32, _i32, _i32, _i32, _vp]),
     "nsa_topk_workspace_bytes": (_sz, [_i32, _i32, _i32, _i64]),
     "nsa_topk": (_i32, [_vp, _S3, _vp, _S3, _i32, _i32, _i32, _i32, _i64, _i32, _f32,
@@ -113,6 +114,13 @@ def call(name: str, *args) -> None:
     if rc != 0:
         msg = lib.nsa_last_error().decode("utf-8", "replace")
         raise NSABackendError(f"{name} failed ({rc}): {msg}")
+
+
+def device_status() -> int:
+    """Read and clear the device-side status word (synchronises)."""
+    v = C.c_int32(0)
+    call("nsa_device_status", C.byref(v))
+    return int(v.value)
 
 
 def strides3(t, dims=(0, 1, 2)):

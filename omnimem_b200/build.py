@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libomnimem_b200.so")
-SOURCES = ["capi.cu", "topk.cu", "sel_fwd.cu", "sel_bwd.cu", "cache.cu", "misc.cu"]
+SOURCES = ["capi.cu", "topk.cu", "sel_fwd.cu", "sel_fwd_tc.cu", "sel_bwd.cu", "cache.cu", "misc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",

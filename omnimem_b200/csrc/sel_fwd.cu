@@ -202,6 +202,11 @@ int launch(const FwdParams& p, int MG, cudaStream_t stream) {
 
 }  // namespace
 
+int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
+                          const int64_t* idx_stride, void* out, const int64_t* out_stride, float* lse, int B,
+                          int64_t M, int H, int D, int T, int block_size, int chunk_size, int causal, int G,
+                          float scale, int dtype, int32_t* status, cudaStream_t stream, bool* launched);
+
 int check_strides16(const char* what, const void* ptr, const int64_t* stride, int n, int esz) {
   NSA_REQUIRE(ptr != nullptr, NSA_ERR_INVALID, "%s: null pointer", what);
   NSA_REQUIRE(aligned16(ptr), NSA_ERR_LAYOUT, "%s: base address must be 16-byte aligned", what);
@@ -293,6 +298,14 @@ extern "C" int nsa_sel_fwd(const void* q, const int64_t q_stride[3], const nsa_k
   const int64_t MG = cdiv64(M, group_size);
   NSA_REQUIRE(MG <= 0x7fffffff, NSA_ERR_INVALID, "sel_fwd: too many query groups");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    // the page geometry runs on the tcgen05 kernel; every other shape on the general one
+    bool launched = false;
+    rc = try_launch_sel_fwd_tc(q, q_stride, kv, block_indices, idx_stride, out, out_stride, lse, B, M, H, D, T,
+                               block_size, chunk_size, causal, group_size, scale, dtype, nullptr, s, &launched);
+    if (rc) return rc;
+    if (launched) return NSA_OK;
+  }
   if (dtype == NSA_BF16) {
     return D == 128 ? launch<__nv_bfloat16, 128>(p, static_cast<int>(MG), s)
                     : launch<__nv_bfloat16, 64>(p, static_cast<int>(MG), s);

@@ -1,0 +1,483 @@
+// Selection attention forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA) for
+// the page geometry: bf16, D = 128, 64-token blocks, query groups of up to 64 rows, K/V read
+// from a dense [B,N,H,D] tensor or straight from the fixed-page pool through the block table.
+//
+// One thread block per (batch, query group, head), six warps:
+//   warp 4  TMA producer: Q once, then per step the K and V tiles of TWO selected blocks
+//           (128 keys) into two-stage rings, coordinates taken from the compacted block list;
+//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into a double-buffered TMEM tile,
+//           then O += P V (M=128, N=128, K=128) with P read from TMEM;
+//   warps 0-3  softmax: one TMEM lane (matrix row) per thread.
+// The 64 query rows are loaded twice, into rows 0-63 and 64-127 of the A tile: rows 0-63 do
+// the online softmax over the EVEN block of each step (S columns 0-63), rows 64-127 over the
+// ODD block (columns 64-127); the other half of each P row is zero, so the two halves
+// accumulate attention over disjoint key sets in their own O rows and are merged exactly
+// (log-sum-exp weights) in the epilogue.  Every softmax thread therefore has 64 useful
+// columns per step and no cross-thread reduction is needed.
+// O stays in TMEM across steps; it is rescaled only when a row's running maximum grows by
+// more than 2^8 (the reference maximum is otherwise kept, which is exact because P and the
+// row sum use the same reference).
+#include "sel_common.cuh"
+#include "tc_common.cuh"
+
+#include <cstdlib>
+#include <mutex>
+#include <string>
+
+namespace nsa {
+namespace tc {
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                  const uint32_t* box) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  NSA_REQUIRE(enc != nullptr, NSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t d[5], s[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), d, s, bx, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NSA_REQUIRE(r == CUDA_SUCCESS, NSA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+  return NSA_OK;
+}
+
+}  // namespace tc
+
+// Sticky device-side status of the tensor-core kernels: set to a negative nsa_status when a
+// bounded wait gave up; read (and cleared) by nsa_device_status().
+__device__ int g_device_status = 0;
+
+namespace {
+
+using namespace tc;
+
+constexpr int kTcThreads = 192;
+constexpr int kMaxSlots = 256;
+constexpr uint32_t kTileBytes = 32768;        // 128 rows x 256 bytes, as two 64-column halves of 16 KiB
+constexpr uint32_t kSmemTiles = 5 * kTileBytes;   // Q, K x2, V x2
+constexpr float kRescaleGap = 8.f;            // log2 units
+
+// TMEM columns
+constexpr uint32_t kColS = 0;      // 2 x 128
+constexpr uint32_t kColP = 256;    // 2 x 64 (bf16 pairs)
+constexpr uint32_t kColO = 384;    // 128
+
+struct TcFwdParams {
+  const int32_t* ids;
+  int64_t i_sb, i_sg, i_sh, i_st;
+  char* out;
+  int64_t o_sb, o_sm, o_sh;
+  float* lse;
+  const int32_t* block_table;
+  int max_blocks;
+  int paged;
+  int64_t n_tokens, M;
+  int H, T, G, chunk_size, causal;
+  float scale_log2;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                  const __grid_constant__ CUtensorMap mapV, const TcFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = tiles;
+  uint8_t* sK = tiles + kTileBytes;           // 2 stages
+  uint8_t* sV = tiles + 3 * kTileBytes;       // 2 stages
+  float* stage = reinterpret_cast<float*>(tiles + kTileBytes);   // epilogue: 128 x 129 floats over the K/V rings
+
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full[2], pv_done, o_final;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort, s_nb;
+  __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
+  __shared__ float s_m[128], s_l[128];
+
+  const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t m0 = static_cast<int64_t>(g) * p.G;
+  const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
+  const int q_chunk = static_cast<int>(m0 / p.chunk_size);
+
+  // ---- compacted list of the visible selected blocks: TMA row coordinate and visible tokens
+  if (threadIdx.x == 0) s_abort = 0;
+  for (int t = threadIdx.x; t < p.T; t += blockDim.x) {
+    const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
+    int row = -1, nv = 0;
+    if (bid >= 0) {
+      const int64_t t0 = static_cast<int64_t>(bid) * 64;
+      if (t0 < p.n_tokens) {
+        int64_t n = p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64;
+        bool ok = true;
+        if (p.causal) {
+          if (t0 / p.chunk_size > q_chunk) ok = false;
+          const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - t0;
+          if (lim < n) n = lim;
+          if (n <= 0) ok = false;
+        }
+        if (ok) {
+          if (p.paged) {
+            const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
+            if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
+          } else {
+            row = static_cast<int>(t0);
+            nv = static_cast<int>(n);
+          }
+        }
+      }
+    }
+    s_row[t] = row;
+    s_nvis[t] = nv;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int nb = 0;
+    for (int t = 0; t < p.T; ++t) {
+      const int row = s_row[t], nv = s_nvis[t];
+      if (nv > 0) { s_row[nb] = row; s_nvis[nb] = nv; ++nb; }
+    }
+    s_nb = nb;
+  }
+  __syncthreads();
+  const int nb = s_nb;
+  char* out_row0 = p.out + (b * p.o_sb + m0 * p.o_sm + h * p.o_sh) * 2;
+  float* lse_row0 = p.lse + (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
+  if (nb == 0) {   // nothing visible: O = 0, LSE = -inf
+    for (int i = threadIdx.x; i < n_q * 16; i += blockDim.x)
+      *reinterpret_cast<uint4*>(out_row0 + (i >> 4) * p.o_sm * 2 + (i & 15) * 16) = make_uint4(0, 0, 0, 0);
+    for (int r = threadIdx.x; r < n_q; r += blockDim.x) lse_row0[r] = -INFINITY;
+    return;
+  }
+  const int NT = (nb + 1) >> 1;
+
+  // ---- barriers, TMEM
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128);
+    }
+    mbar_init(&pv_done, 1);
+    mbar_init(&o_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_base_s;
+  volatile int* abort = &s_abort;
+
+  if (warp == 4) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, kTileBytes);
+      for (int dh = 0; dh < 2; ++dh)
+        for (int dup = 0; dup < 2; ++dup)
+          tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
+      int t = 0;
+      for (; t < NT; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort)) break;
+        mbar_expect_tx(&k_full[s], kTileBytes);
+        uint8_t* dk = sK + s * kTileBytes;
+        if (p.paged) {
+          tma_load_2d(dk, &mapK, 0, re, &k_full[s]);
+          tma_load_2d(dk + 8192, &mapK, 0, ro, &k_full[s]);
+          tma_load_2d(dk + 16384, &mapK, 64, re, &k_full[s]);
+          tma_load_2d(dk + 24576, &mapK, 64, ro, &k_full[s]);
+        } else {
+          tma_load_4d(dk, &mapK, 0, h, re, b, &k_full[s]);
+          tma_load_4d(dk + 8192, &mapK, 0, h, ro, b, &k_full[s]);
+          tma_load_4d(dk + 16384, &mapK, 64, h, re, b, &k_full[s]);
+          tma_load_4d(dk + 24576, &mapK, 64, h, ro, b, &k_full[s]);
+        }
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort)) {
+          mbar_wait(&k_full[s], ph, abort);   // let the copies just issued land before leaving
+          break;
+        }
+        mbar_expect_tx(&v_full[s], kTileBytes);
+        uint8_t* dv = sV + s * kTileBytes;
+        if (p.paged) {
+          tma_load_2d(dv, &mapV, 0, re, &v_full[s]);
+          tma_load_2d(dv + 8192, &mapV, 0, ro, &v_full[s]);
+          tma_load_2d(dv + 16384, &mapV, 64, re, &v_full[s]);
+          tma_load_2d(dv + 24576, &mapV, 64, ro, &v_full[s]);
+        } else {
+          tma_load_4d(dv, &mapV, 0, h, re, b, &v_full[s]);
+          tma_load_4d(dv + 8192, &mapV, 0, h, ro, b, &v_full[s]);
+          tma_load_4d(dv + 16384, &mapV, 64, h, re, b, &v_full[s]);
+          tma_load_4d(dv + 24576, &mapV, 64, h, ro, b, &v_full[s]);
+        }
+      }
+      if (*abort) {
+        // the other roles have stopped consuming: wait (bounded) for what is still in flight
+        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) {
+          mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort);
+          mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
+        }
+        mbar_wait(&q_full, 0, abort);
+      }
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
+      const uint32_t aQ = smem_u32(sQ);
+      auto issue_pv = [&](int u) -> bool {
+        const int s = u & 1, ph = (u >> 1) & 1;
+        if (!mbar_wait(&v_full[s], ph, abort)) return false;
+        if (!mbar_wait(&p_full[s], ph, abort)) return false;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + s * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tm + kColO, tm + kColP + s * 64 + kk * 8, smem_desc(aV + kk * 2048, 16384, 1024), idesc_pv,
+                  (u > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&v_empty[s]);
+        umma_commit(&pv_done);
+        return true;
+      };
+      bool ok = mbar_wait(&q_full, 0, abort);
+      for (int t = 0; ok && t < NT; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, abort)) { ok = false; break; }
+        if (!mbar_wait(&s_free[s], ph ^ 1, abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + s * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + kColS + s * 128, smem_desc(aQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                  smem_desc(aK + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        umma_commit(&s_full[s]);
+        umma_commit(&k_empty[s]);
+        if (t > 0) ok = issue_pv(t - 1);
+      }
+      if (ok && issue_pv(NT - 1)) umma_commit(&o_final);
+    }
+  } else {
+    // ======================= softmax (warps 0-3), one matrix row per thread =======================
+    const int half = warp >> 1;                       // 0: even block of each step, 1: odd block
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    {
+      uint32_t z[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) z[j] = 0u;
+      tmem_st32_nowait(tm + lane_base + kColP + (1 - half) * 32, z);
+      tmem_st32_nowait(tm + lane_base + kColP + 64 + (1 - half) * 32, z);
+      tmem_st_wait();
+    }
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int t = 0; t < NT; ++t) {
+      const int s = t & 1, ph = (t >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], ph, abort));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t x0[32], x1[32];
+      tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64, x0);
+      tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64 + 32, x1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_free[s]);
+      const int blk = 2 * t + half;
+      const int nv = blk < nb ? s_nvis[blk] : 0;
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float a = __uint_as_float(x0[j]) * p.scale_log2, c = __uint_as_float(x1[j]) * p.scale_log2;
+        x0[j] = __float_as_uint(a);
+        x1[j] = __float_as_uint(c);
+        if (j < nv) tmax = fmaxf(tmax, a);
+        if (j + 32 < nv) tmax = fmaxf(tmax, c);
+      }
+      const bool need = tmax > m_ref + kRescaleGap;      // also true for the first visible key (m_ref = -inf)
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = need ? tmax : m_ref;
+        if (t > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (t - 1) & 1, abort));
+          if (!ok) break;
+          tc_fence_after();
+          const float sc = need ? fast_exp2(m_ref - m_new) : 1.f;
+          l_sum *= sc;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32_nowait(tm + lane_base + kColO + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * sc);
+            tmem_st32_nowait(tm + lane_base + kColO + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+        m_ref = m_new;
+      }
+      uint32_t pk[32];
+      float rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a0 = (2 * j < nv) ? fast_exp2(__uint_as_float(x0[2 * j]) - m_ref) : 0.f;
+        const float a1 = (2 * j + 1 < nv) ? fast_exp2(__uint_as_float(x0[2 * j + 1]) - m_ref) : 0.f;
+        const float c0 = (2 * j + 32 < nv) ? fast_exp2(__uint_as_float(x1[2 * j]) - m_ref) : 0.f;
+        const float c1 = (2 * j + 33 < nv) ? fast_exp2(__uint_as_float(x1[2 * j + 1]) - m_ref) : 0.f;
+        rs += (a0 + a1) + (c0 + c1);
+        pk[j] = pack2<__nv_bfloat16>(a0, a1);
+        pk[16 + j] = pack2<__nv_bfloat16>(c0, c1);
+      }
+      l_sum += rs;
+      tmem_st32_nowait(tm + lane_base + kColP + s * 64 + half * 32, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_full[s]);
+    }
+    // ---- epilogue: wait for the last P V, merge the two halves, normalise, store.  (pv_done is
+    // only polled when a rescale needs it, so its parity is ambiguous here; o_final is not.)
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_final, 0, abort));
+    if (ok) {
+      tc_fence_after();
+      const int tid = threadIdx.x;                    // 0..127 = TMEM lane = A-tile row
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32_nowait(tm + lane_base + kColO + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stage[tid * 129 + c * 32 + j] = __uint_as_float(o[j]);
+      }
+      s_m[tid] = m_ref;
+      s_l[tid] = l_sum;
+    }
+    named_barrier(1, 128);
+    if (ok) {
+      const int qrow = threadIdx.x & 63;
+      if (qrow < n_q) {
+        const float ma = s_m[qrow], mb = s_m[64 + qrow];
+        const float m = fmaxf(ma, mb);
+        const float wa = (ma == -INFINITY) ? 0.f : fast_exp2(ma - m);
+        const float wb = (mb == -INFINITY) ? 0.f : fast_exp2(mb - m);
+        const float L = s_l[qrow] * wa + s_l[64 + qrow] * wb;
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        const float* ra = stage + qrow * 129 + half * 64;
+        const float* rb = stage + (64 + qrow) * 129 + half * 64;
+        char* orow = out_row0 + qrow * p.o_sm * 2 + half * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack2<__nv_bfloat16>((ra[c * 8 + 2 * e] * wa + rb[c * 8 + 2 * e] * wb) * inv,
+                                        (ra[c * 8 + 2 * e + 1] * wa + rb[c * 8 + 2 * e + 1] * wb) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (half == 0) lse_row0[qrow] = L > 0.f ? (m + log2f(L)) * kLn2 : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+  if (threadIdx.x == 0 && s_abort) atomicExch(p.status ? p.status : &g_device_status, NSA_ERR_CUDA);
+}
+
+}  // namespace
+
+// Returns NSA_OK after launching, or NSA_ERR_UNSUPPORTED (without setting an error) when the
+// tensor-core kernel does not cover the call and the caller should use the general kernel.
+int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
+                          const int64_t* idx_stride, void* out, const int64_t* out_stride, float* lse, int B,
+                          int64_t M, int H, int D, int T, int block_size, int chunk_size, int causal, int G,
+                          float scale, int dtype, int32_t* status, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  // test hook: OMNIMEM_B200_FWD_KERNEL=general sends every shape to the general kernel
+  const char* env = getenv("OMNIMEM_B200_FWD_KERNEL");
+  if (env != nullptr && std::string(env) == "general") return NSA_OK;
+  if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || T > kMaxSlots) return NSA_OK;
+  if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
+  if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
+  if (encode_tiled_fn() == nullptr) return NSA_OK;
+  const int64_t MG = cdiv64(M, G);
+
+  CUtensorMap mapQ, mapK, mapV;
+  int rc;
+  {
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), static_cast<uint64_t>(M), static_cast<uint64_t>(B)};
+    const uint64_t st[3] = {static_cast<uint64_t>(q_stride[2]) * 2, static_cast<uint64_t>(q_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(q_stride[0]) * 2 : static_cast<uint64_t>(q_stride[1]) * 2 * M};
+    const uint32_t box[4] = {64, 1, 64, 1};
+    if (H == 1) return NSA_OK;   // a size-1 head dimension may carry an arbitrary stride: leave it to the general kernel
+    if ((rc = make_bf16_map(&mapQ, q, 4, dims, st, box))) return rc;
+  }
+  if (kv->mode == NSA_KV_DENSE) {
+    const uint64_t N = static_cast<uint64_t>(kv->n_tokens);
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), N, static_cast<uint64_t>(B)};
+    const uint32_t box[4] = {64, 1, 64, 1};
+    const uint64_t sk[3] = {static_cast<uint64_t>(kv->k_stride[2]) * 2, static_cast<uint64_t>(kv->k_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(kv->k_stride[0]) * 2 : static_cast<uint64_t>(kv->k_stride[1]) * 2 * N};
+    const uint64_t sv[3] = {static_cast<uint64_t>(kv->v_stride[2]) * 2, static_cast<uint64_t>(kv->v_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(kv->v_stride[0]) * 2 : static_cast<uint64_t>(kv->v_stride[1]) * 2 * N};
+    if ((rc = make_bf16_map(&mapK, kv->k, 4, dims, sk, box))) return rc;
+    if ((rc = make_bf16_map(&mapV, kv->v, 4, dims, sv, box))) return rc;
+  } else {
+    const uint64_t rows = kv->num_pages > 0 ? static_cast<uint64_t>(kv->num_pages) * 64 : (1ull << 31);
+    const uint64_t dims[2] = {128, rows};
+    const uint64_t st[1] = {256};
+    const uint32_t box[2] = {64, 64};
+    if ((rc = make_bf16_map(&mapK, kv->k, 2, dims, st, box))) return rc;
+    if ((rc = make_bf16_map(&mapV, kv->v, 2, dims, st, box))) return rc;
+  }
+
+  TcFwdParams p;
+  p.ids = ids;
+  p.i_sb = idx_stride[0]; p.i_sg = idx_stride[1]; p.i_sh = idx_stride[2]; p.i_st = idx_stride[3];
+  p.out = static_cast<char*>(out);
+  p.o_sb = out_stride[0]; p.o_sm = out_stride[1]; p.o_sh = out_stride[2];
+  p.lse = lse;
+  p.block_table = kv->block_table; p.max_blocks = kv->max_blocks; p.paged = kv->mode == NSA_KV_PAGED;
+  p.n_tokens = kv->n_tokens; p.M = M;
+  p.H = H; p.T = T; p.G = G; p.chunk_size = chunk_size; p.causal = causal;
+  p.scale_log2 = scale * kLog2e;
+  p.status = status;
+  const size_t smem = kSmemTiles + 1024;
+  NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  sel_fwd_tc_kernel<<<dim3(static_cast<unsigned>(MG), H, B), kTcThreads, smem, stream>>>(mapQ, mapK, mapV, p);
+  NSA_LAUNCH_OK("sel_fwd_tc_kernel");
+  *launched = true;
+  return NSA_OK;
+}
+
+}  // namespace nsa
+
+extern "C" int nsa_device_status(int32_t* value) {
+  NSA_REQUIRE(value != nullptr, NSA_ERR_INVALID, "device_status: null pointer");
+  int v = 0;
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(&v, nsa::g_device_status, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    NSA_CUDA_OK(cudaMemcpyToSymbol(nsa::g_device_status, &zero, sizeof(int)));
+  }
+  *value = v;
+  return NSA_OK;
+}

@@ -187,6 +187,7 @@ class PagedKV:
         s.block_table = self.block_table.data_ptr()
         s.max_blocks = self.block_table.shape[-1]
         s.page_tokens = self.page_tokens
+        s.num_pages = self.k_pool.shape[0]
         return s
 
 

@@ -44,3 +44,13 @@ def dev():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel gave up on a bounded wait."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None and torch.cuda.is_available():
+        from omnimem_b200 import _lib
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0, "a kernel reported a device-side error"

@@ -70,7 +70,7 @@ def test_ctypes_prototypes_match_the_header():
 
 def test_struct_layouts_match_the_header():
     # nsa_kv_source: int32, 2 ptr, 2x3 int64, int64, ptr, 2 int32, 2 ptr, int64
-    assert C.sizeof(_lib.KVSource) == 8 + 16 + 48 + 8 + 8 + 8 + 16 + 8
+    assert C.sizeof(_lib.KVSource) == 8 + 16 + 48 + 8 + 8 + 8 + 16 + 8 + 8
     assert C.sizeof(_lib.TopkMask) == 12 * 4
 
 

@@ -83,6 +83,27 @@ def test_forward_backward_geometries(dev, case):
     _check(dev, q, k, v, do, ids, bs, chunk, causal, G, f"case{seed}")
 
 
+def test_tensor_core_kernel_agrees_with_general_kernel(dev, monkeypatch):
+    """The tcgen05 forward (64-token blocks, 64-query groups, D=128, bf16) against the general
+    kernel on the same inputs: dense and paged sources, ragged tails, odd block counts, -1 slots."""
+    ops = _ops()
+    for seed, M, N, T, chunk, causal in ((41, 256, 4096, 16, 256, False), (42, 200, 1000, 5, 100, True),
+                                          (43, 150, 3000, 1, 150, False), (44, 4680, 6000, 7, 1560, True)):
+        q, k, v, do, ids = _rand_case(seed, 1, M, N, 3, 128, T, 64, 64, chunk, causal)
+        ids[0, 0, 0, T // 2:] = -1
+        args = (q.to(dev), ops.DenseKV(k.to(dev), v.to(dev)), ids.to(dev), 64, chunk, 128 ** -0.5, causal, 64)
+        monkeypatch.setenv("OMNIMEM_B200_FWD_KERNEL", "general")
+        o_g, l_g = ops.sel_fwd(*args)
+        monkeypatch.delenv("OMNIMEM_B200_FWD_KERNEL")
+        o_t, l_t = ops.sel_fwd(*args)
+        assert_close_bf16(o_t, o_g, f"tc vs general out (seed {seed})", max_abs=1.6e-2, mean_abs=1e-3)
+        fin = torch.isfinite(l_g)
+        assert torch.equal(torch.isfinite(l_t), fin)
+        assert torch.allclose(l_t[fin], l_g[fin], atol=1e-3, rtol=1e-4)
+        o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), ids, 64, chunk, None, causal, 64)
+        assert_close_bf16(o_t, o_ref, f"tc out vs oracle (seed {seed})")
+
+
 def test_fp16(dev):
     q, k, v, do, ids = _rand_case(21, 1, 128, 512, 2, 128, 4, 64, 64, 128, True, dtype=torch.float16)
     _check(dev, q, k, v, do, ids, 64, 128, True, 64, "fp16")

@@ -24,7 +24,7 @@ def test_pool_rows(dev, dtype, N, size, H, D):
     # fp32 sums in a different order may round a value to the neighbouring representable number
     ulp = {torch.bfloat16: 2 ** -7, torch.float16: 2 ** -10, torch.float32: 2 ** -20}[dtype]
     err = (got.float() - want.float()).abs()
-    assert (err <= ulp * want.float().abs() + 1e-6).all()
+    assert (err <= ulp * want.float().abs() + (2e-6 if dtype == torch.float32 else 1e-6)).all()
     assert (err == 0).float().mean() > (0.97 if dtype != torch.float32 else 0.5)
 
 
