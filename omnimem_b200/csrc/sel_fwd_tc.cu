@@ -61,11 +61,20 @@ int make_bf16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* 
 // bounded wait gave up; read (and cleared) by nsa_device_status().
 __device__ int g_device_status = 0;
 
+#ifdef NSA_TC_TRACE
+// Debug build only: clock64 stamps of thread block (0,0,0); [0][..] MMA issuer, [1][..] softmax thread 0,
+// [2][..] producer.
+__device__ long long g_trace[3][512];
+#define TRACE(role, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512) g_trace[role][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace tc;
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 224;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTileBytes = 32768;        // 128 rows x 256 bytes, as two 64-column halves of 16 KiB
 constexpr uint32_t kSmemTiles = 5 * kTileBytes;   // Q, K x2, V x2
@@ -113,8 +122,26 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
 
-  // ---- compacted list of the visible selected blocks: TMA row coordinate and visible tokens
-  if (threadIdx.x == 0) s_abort = 0;
+  if (threadIdx.x == 0) TRACE(1, 0);
+  // ---- barriers and TMEM first, so that they overlap the loads of the block ids below
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128);
+    }
+    mbar_init(&pv_done, 1);
+    mbar_init(&o_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  // ---- list of the selected blocks: TMA row coordinate and visible tokens of each slot
   for (int t = threadIdx.x; t < p.T; t += blockDim.x) {
     const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
     int row = -1, nv = 0;
@@ -143,7 +170,18 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     s_row[t] = row;
     s_nvis[t] = nv;
   }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_base_s;
+  volatile int* abort = &s_abort;
+  // Q does not depend on the list: start its copy while thread 0 compacts the list
+  if (warp == 4 && lane == 0) {
+    mbar_expect_tx(&q_full, kTileBytes);
+    for (int dh = 0; dh < 2; ++dh)
+      for (int dup = 0; dup < 2; ++dup)
+        tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
+  }
   if (threadIdx.x == 0) {
     int nb = 0;
     for (int t = 0; t < p.T; ++t) {
@@ -156,87 +194,51 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int nb = s_nb;
   char* out_row0 = p.out + (b * p.o_sb + m0 * p.o_sm + h * p.o_sh) * 2;
   float* lse_row0 = p.lse + (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
-  if (nb == 0) {   // nothing visible: O = 0, LSE = -inf
+  const int NT = (nb + 1) >> 1;
+  if (threadIdx.x == 0) TRACE(1, 1);
+
+  // K / V tile of one step: the even block in rows 0-63, the odd block in rows 64-127 of each
+  // 64-column half (the even block again when the step has no odd block).
+  auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, int re, int ro, uint64_t* bar) {
+    mbar_expect_tx(bar, kTileBytes);
+    if (p.paged) {
+      tma_load_2d(dst, map, 0, re, bar);
+      tma_load_2d(dst + 8192, map, 0, ro, bar);
+      tma_load_2d(dst + 16384, map, 64, re, bar);
+      tma_load_2d(dst + 24576, map, 64, ro, bar);
+    } else {
+      tma_load_4d(dst, map, 0, h, re, b, bar);
+      tma_load_4d(dst + 8192, map, 0, h, ro, b, bar);
+      tma_load_4d(dst + 16384, map, 64, h, re, b, bar);
+      tma_load_4d(dst + 24576, map, 64, h, ro, b, bar);
+    }
+  };
+
+  if (nb == 0) {
+    // nothing visible: O = 0, LSE = -inf (the Q copy already in flight is awaited before leaving)
     for (int i = threadIdx.x; i < n_q * 16; i += blockDim.x)
       *reinterpret_cast<uint4*>(out_row0 + (i >> 4) * p.o_sm * 2 + (i & 15) * 16) = make_uint4(0, 0, 0, 0);
     for (int r = threadIdx.x; r < n_q; r += blockDim.x) lse_row0[r] = -INFINITY;
-    return;
-  }
-  const int NT = (nb + 1) >> 1;
-
-  // ---- barriers, TMEM
-  if (threadIdx.x == 0) {
-    mbar_init(&q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
-      mbar_init(&p_full[i], 128);
-    }
-    mbar_init(&pv_done, 1);
-    mbar_init(&o_final, 1);
-    fence_barrier_init();
-  }
-  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tm = tmem_base_s;
-  volatile int* abort = &s_abort;
-
-  if (warp == 4) {
-    // ======================= TMA producer =======================
+    if (warp == 4 && lane == 0) mbar_wait(&q_full, 0, abort);
+  } else if (warp == 4 || warp == 6) {
+    // ======================= TMA producers: warp 4 feeds the K ring, warp 6 the V ring =======================
     if (lane == 0) {
-      mbar_expect_tx(&q_full, kTileBytes);
-      for (int dh = 0; dh < 2; ++dh)
-        for (int dup = 0; dup < 2; ++dup)
-          tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
+      const bool isK = warp == 4;
+      uint64_t* full = isK ? k_full : v_full;
+      uint64_t* empty = isK ? k_empty : v_empty;
+      uint8_t* ring = isK ? sK : sV;
+      const CUtensorMap* map = isK ? &mapK : &mapV;
       int t = 0;
       for (; t < NT; ++t) {
         const int s = t & 1, ph = (t >> 1) & 1;
         const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort)) break;
-        mbar_expect_tx(&k_full[s], kTileBytes);
-        uint8_t* dk = sK + s * kTileBytes;
-        if (p.paged) {
-          tma_load_2d(dk, &mapK, 0, re, &k_full[s]);
-          tma_load_2d(dk + 8192, &mapK, 0, ro, &k_full[s]);
-          tma_load_2d(dk + 16384, &mapK, 64, re, &k_full[s]);
-          tma_load_2d(dk + 24576, &mapK, 64, ro, &k_full[s]);
-        } else {
-          tma_load_4d(dk, &mapK, 0, h, re, b, &k_full[s]);
-          tma_load_4d(dk + 8192, &mapK, 0, h, ro, b, &k_full[s]);
-          tma_load_4d(dk + 16384, &mapK, 64, h, re, b, &k_full[s]);
-          tma_load_4d(dk + 24576, &mapK, 64, h, ro, b, &k_full[s]);
-        }
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort)) {
-          mbar_wait(&k_full[s], ph, abort);   // let the copies just issued land before leaving
-          break;
-        }
-        mbar_expect_tx(&v_full[s], kTileBytes);
-        uint8_t* dv = sV + s * kTileBytes;
-        if (p.paged) {
-          tma_load_2d(dv, &mapV, 0, re, &v_full[s]);
-          tma_load_2d(dv + 8192, &mapV, 0, ro, &v_full[s]);
-          tma_load_2d(dv + 16384, &mapV, 64, re, &v_full[s]);
-          tma_load_2d(dv + 24576, &mapV, 64, ro, &v_full[s]);
-        } else {
-          tma_load_4d(dv, &mapV, 0, h, re, b, &v_full[s]);
-          tma_load_4d(dv + 8192, &mapV, 0, h, ro, b, &v_full[s]);
-          tma_load_4d(dv + 16384, &mapV, 64, h, re, b, &v_full[s]);
-          tma_load_4d(dv + 24576, &mapV, 64, h, ro, b, &v_full[s]);
-        }
+        if (!mbar_wait(&empty[s], ph ^ 1, abort)) break;
+        load_tile(ring + s * kTileBytes, map, re, ro, &full[s]);
       }
       if (*abort) {
         // the other roles have stopped consuming: wait (bounded) for what is still in flight
-        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) {
-          mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort);
-          mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
-        }
-        mbar_wait(&q_full, 0, abort);
+        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) mbar_wait(&full[u & 1], (u >> 1) & 1, abort);
+        if (isK) mbar_wait(&q_full, 0, abort);
       }
     }
   } else if (warp == 5) {
@@ -248,7 +250,9 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       auto issue_pv = [&](int u) -> bool {
         const int s = u & 1, ph = (u >> 1) & 1;
         if (!mbar_wait(&v_full[s], ph, abort)) return false;
+        TRACE(0, 8 + (u + 1) * 8 + 3);
         if (!mbar_wait(&p_full[s], ph, abort)) return false;
+        TRACE(0, 8 + (u + 1) * 8 + 4);
         tc_fence_after();
         const uint32_t aV = smem_u32(sV + s * kTileBytes);
 #pragma unroll
@@ -260,10 +264,13 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         return true;
       };
       bool ok = mbar_wait(&q_full, 0, abort);
+      TRACE(0, 0);
       for (int t = 0; ok && t < NT; ++t) {
         const int s = t & 1, ph = (t >> 1) & 1;
         if (!mbar_wait(&k_full[s], ph, abort)) { ok = false; break; }
+        TRACE(0, 8 + t * 8 + 0);
         if (!mbar_wait(&s_free[s], ph ^ 1, abort)) { ok = false; break; }
+        TRACE(0, 8 + t * 8 + 1);
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + s * kTileBytes);
 #pragma unroll
@@ -272,7 +279,9 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                   smem_desc(aK + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         umma_commit(&s_full[s]);
         umma_commit(&k_empty[s]);
+        TRACE(0, 8 + t * 8 + 2);
         if (t > 0) ok = issue_pv(t - 1);
+        TRACE(0, 8 + t * 8 + 5);
       }
       if (ok && issue_pv(NT - 1)) umma_commit(&o_final);
     }
@@ -292,13 +301,16 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     bool ok = true;
     for (int t = 0; t < NT; ++t) {
       const int s = t & 1, ph = (t >> 1) & 1;
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], ph, abort));
       if (!ok) break;
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
       tc_fence_after();
       uint32_t x0[32], x1[32];
       tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64, x0);
       tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64 + 32, x1);
       tmem_ld_wait();
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
       tc_fence_before();
       mbar_arrive(&s_free[s]);
       const int blk = 2 * t + half;
@@ -313,6 +325,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (j + 32 < nv) tmax = fmaxf(tmax, c);
       }
       const bool need = tmax > m_ref + kRescaleGap;      // also true for the first visible key (m_ref = -inf)
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 3);
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? tmax : m_ref;
         if (t > 0) {
@@ -334,6 +347,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
         m_ref = m_new;
       }
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 4);
       uint32_t pk[32];
       float rs = 0.f;
 #pragma unroll
@@ -347,14 +361,18 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         pk[16 + j] = pack2<__nv_bfloat16>(c0, c1);
       }
       l_sum += rs;
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 5);
       tmem_st32_nowait(tm + lane_base + kColP + s * 64 + half * 32, pk);
       tmem_st_wait();
+      if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 6);
       tc_fence_before();
       mbar_arrive(&p_full[s]);
     }
+    if (threadIdx.x == 0) TRACE(1, 2);
     // ---- epilogue: wait for the last P V, merge the two halves, normalise, store.  (pv_done is
     // only polled when a rescale needs it, so its parity is ambiguous here; o_final is not.)
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_final, 0, abort));
+    if (threadIdx.x == 0) TRACE(1, 3);
     if (ok) {
       tc_fence_after();
       const int tid = threadIdx.x;                    // 0..127 = TMEM lane = A-tile row
@@ -396,9 +414,11 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     }
   }
 
+  if (threadIdx.x == 0) TRACE(1, 4);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+  if (threadIdx.x == 0) TRACE(1, 5);
   if (threadIdx.x == 0 && s_abort) atomicExch(p.status ? p.status : &g_device_status, NSA_ERR_CUDA);
 }
 
@@ -481,3 +501,10 @@ extern "C" int nsa_device_status(int32_t* value) {
   *value = v;
   return NSA_OK;
 }
+
+#ifdef NSA_TC_TRACE
+extern "C" int nsa_debug_trace(long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace, sizeof(long long) * 3 * 512));
+  return NSA_OK;
+}
+#endif
