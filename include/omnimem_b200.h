@@ -109,6 +109,26 @@ int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const void* k_pool
              float* out_scores, void* workspace, size_t workspace_bytes, int32_t dtype,
              void* stream);
 
+/* nsa_topk without a caller-provided workspace, for callers that cannot allocate device
+ * memory: a process whose device memory was all handed to another allocator when it started,
+ * a host runtime behind an FFI boundary that owns no device memory and only forwards the
+ * pointers it is given, or a loop whose memory plan is frozen.  The score buffer is a fixed
+ * 4 MiB array inside the library's device image (present on every GPU that loads the library,
+ * until the process exits).  It holds nsa_topk_static_scratch_max_scores() = 1,048,576 scores:
+ * a call with B*MG*H*NC above that returns NSA_ERR_WORKSPACE and launches nothing.
+ * The call makes no cudaMalloc / cudaFree and calls no allocating library routine.  Its first
+ * call on each device looks up the array's device address (cudaGetSymbolAddress) with that
+ * device current; make that first call before any stream capture begins.  All calls on a
+ * device share the one array: calls whose kernels overlap on the GPU (different streams) race
+ * on it and must be serialised by the caller; nothing in it needs clearing between calls,
+ * because every score that is read was written earlier in the same call.
+ * No counterpart in the reference (its top-k allocates its buffers through torch). */
+size_t nsa_topk_static_scratch_max_scores(void);
+int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_stride[3], const void* k_pooled,
+                            const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
+                            int64_t NC, int32_t topk, float scale, const nsa_topk_mask* mask,
+                            int32_t* out_idx, float* out_scores, int32_t dtype, void* stream);
+
 /* Fused block-compressed key scoring: pools the raw keys k [B,N,H,D] block by block
  * (writes k_pooled_out [B,NC,H,D] contiguous when not NULL), scores them against
  * q_pooled and selects, reading K exactly once.  Same outputs as nsa_topk.

@@ -49,6 +49,9 @@ PROTOTYPES = {
     "nsa_topk_workspace_bytes": (_sz, [_i32, _i32, _i32, _i64]),
     "nsa_topk": (_i32, [_vp, _S3, _vp, _S3, _i32, _i32, _i32, _i32, _i64, _i32, _f32,
                         C.POINTER(TopkMask), _vp, _vp, _vp, _sz, _i32, _vp]),
+    "nsa_topk_static_scratch_max_scores": (_sz, []),
+    "nsa_topk_static_scratch": (_i32, [_vp, _S3, _vp, _S3, _i32, _i32, _i32, _i32, _i64, _i32, _f32,
+                                       C.POINTER(TopkMask), _vp, _vp, _i32, _vp]),
     "nsa_pool_score_topk": (_i32, [_vp, _S3, _vp, _S3, _i32, _i32, _i32, _i32, _i64, _i32, _f32,
                                    C.POINTER(TopkMask), _vp, _vp, _vp, _vp, _sz, _i32, _vp]),
     "nsa_merge_candidates": (_i32, [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),

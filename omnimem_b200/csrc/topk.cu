@@ -5,6 +5,8 @@
 //                      64-bit keys, -1 padding; also merges per-shard candidate lists
 #include "common.cuh"
 
+#include <mutex>
+
 namespace nsa {
 namespace {
 
@@ -469,4 +471,72 @@ extern "C" int nsa_merge_candidates(const int32_t* idx, const float* scores, int
   select_kernel<true><<<static_cast<unsigned>(rows), 128, ksmem, static_cast<cudaStream_t>(stream)>>>(sel);
   NSA_LAUNCH_OK("select_kernel<merge>");
   return NSA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Top-k for callers that must not allocate.
+//
+// nsa_topk needs a score buffer of B*MG*H*NC floats and asks its caller to supply it.  Some
+// callers cannot: a serving process that hands the whole device to another allocator at start-up
+// (a later cudaMalloc would fail or fragment its plan), a host runtime behind an FFI boundary that
+// owns no device memory at all and only forwards pointers it was given, or a latency-critical loop
+// whose memory plan is frozen once it starts.  For them the library carries its own score buffer:
+// a fixed array in device global memory that is part of the loaded module, so it exists on every
+// GPU that loads the library, from load until the process exits, and costs kStaticScratchBytes
+// there whether or not this entry point is ever called.
+namespace nsa {
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(1) << 20;          // 4 MiB
+constexpr size_t kStaticScratchBytes = kStaticScratchFloats * sizeof(float);
+static __device__ __align__(256) float g_topk_scratch[kStaticScratchFloats];
+
+namespace {
+// In host code `g_topk_scratch` is only a handle for the runtime, not an address a kernel can
+// use; the device address is looked up once per device (with that device current) and cached.
+int static_scratch_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* cached[kMaxDevices] = {};
+  int dev = -1;
+  NSA_CUDA_OK(cudaGetDevice(&dev));
+  NSA_REQUIRE(dev >= 0 && dev < kMaxDevices, NSA_ERR_UNSUPPORTED, "topk_static_scratch: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    NSA_CUDA_OK(cudaGetSymbolAddress(&p, g_topk_scratch));
+    NSA_REQUIRE(p != nullptr, NSA_ERR_CUDA, "topk_static_scratch: the scratch array has no device address");
+    cached[dev] = static_cast<float*>(p);
+  }
+  *out = cached[dev];
+  return NSA_OK;
+}
+}  // namespace
+}  // namespace nsa
+
+extern "C" size_t nsa_topk_static_scratch_max_scores(void) { return nsa::kStaticScratchFloats; }
+
+extern "C" int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_stride[3], const void* k_pooled,
+                                       const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
+                                       int64_t NC, int32_t topk, float scale, const nsa_topk_mask* mask,
+                                       int32_t* out_idx, float* out_scores, int32_t dtype, void* stream) {
+  int rc;
+  if ((rc = topk_common_checks(B, MG, H, D, NC, topk, dtype, out_idx))) return rc;
+  const int64_t rows = static_cast<int64_t>(B) * MG * H;
+  const int64_t need = rows * NC;
+  NSA_REQUIRE(need <= static_cast<int64_t>(nsa::kStaticScratchFloats), NSA_ERR_WORKSPACE,
+              "topk_static_scratch: B*MG*H*NC = %lld scores exceed the built-in scratch of %zu scores (%zu MiB); "
+              "use nsa_topk with a caller-provided workspace for this size",
+              static_cast<long long>(need), nsa::kStaticScratchFloats, nsa::kStaticScratchBytes >> 20);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0) return NSA_OK;
+  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+  NSA_REQUIRE(q_pooled && k_pooled, NSA_ERR_INVALID, "topk_static_scratch: null pointer");
+  Mask m;
+  if ((rc = fill_mask(mask, MG, mask && mask->id_stride > 1 ? mask->id_base + NC * static_cast<int64_t>(mask->id_stride) : NC, &m)))
+    return rc;
+  float* scratch = nullptr;
+  if ((rc = nsa::static_scratch_address(&scratch))) return rc;
+  // Every score the selection reads is written by the scoring kernel of the same call, so nothing
+  // in the array has to start at zero and whatever an earlier call left behind is never read.
+  return run_score_select(q_pooled, q_stride, k_pooled, k_stride, B, MG, H, D, NC, topk, scale, m, out_idx,
+                          out_scores, scratch, dtype, s);
 }
