@@ -586,6 +586,11 @@ int run_inverted_index(const IdxParams& ip, int32_t* groups, int32_t* offsets, i
 }  // namespace
 
 int check_strides16(const char* what, const void* ptr, const int64_t* stride, int n, int esz);
+int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
+                             const int64_t* idx_stride, const void* out, const int64_t* out_stride, const float* lse,
+                             const void* d_out, const int64_t* do_stride, void* dq, const int64_t* dq_stride,
+                             float* delta, int B, int64_t M, int H, int D, int T, int block_size, int chunk_size,
+                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched);
 
 }  // namespace nsa
 
@@ -670,6 +675,15 @@ extern "C" int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const ns
   if ((rc = check_strides16("dq", dq, dq_stride, 3, esz))) return rc;
   BwdParams p{};
   if ((rc = make_kvsrc(kv, D, esz, block_size, &p.kv))) return rc;
+  {
+    // the page geometry runs on the tcgen05 kernel; every other shape on the general one
+    bool launched = false;
+    rc = try_launch_sel_bwd_dq_tc(q, q_stride, kv, block_indices, idx_stride, out, out_stride, lse, d_out, do_stride,
+                                  dq, dq_stride, delta, B, M, H, D, T, block_size, chunk_size, causal, group_size,
+                                  scale, dtype, static_cast<cudaStream_t>(stream), &launched);
+    if (rc) return rc;
+    if (launched) return NSA_OK;
+  }
   p.q = static_cast<const char*>(q); p.q_sb = q_stride[0]; p.q_sm = q_stride[1]; p.q_sh = q_stride[2];
   p.o = static_cast<const char*>(out); p.o_sb = out_stride[0]; p.o_sm = out_stride[1]; p.o_sh = out_stride[2];
   p.dO = static_cast<const char*>(d_out); p.do_sb = do_stride[0]; p.do_sm = do_stride[1]; p.do_sh = do_stride[2];

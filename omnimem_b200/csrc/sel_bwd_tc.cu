@@ -1,0 +1,370 @@
+// Selection attention backward, dQ half, on tcgen05 / TMEM / TMA for the page geometry
+// (bf16, D = 128, 64-token blocks, query groups of up to 64 rows, dense or paged K/V).
+//
+// Same skeleton as the tensor-core forward: one thread block per (batch, query group, head);
+// warp 4 feeds the K ring, warp 6 the V ring (plus the Q and dO tiles once), warp 5 issues
+// the MMAs, warps 0-3 own one TMEM lane (matrix row) per thread.  Q and dO are loaded twice
+// (rows 0-63 and 64-127 of their A tiles); per step two selected blocks (128 keys) are
+// processed: rows 0-63 work on the even block (columns 0-63 of S and dP), rows 64-127 on the
+// odd block (columns 64-127); the other half of each dS row is zero.  Per step:
+//     S  = [Q;Q]   K^T          (M=128, N=128, K=128)   recomputed scores
+//     dP = [dO;dO] V^T          (M=128, N=128, K=128)
+//     dS = exp2(S c - LSE) (dP - delta) scale           (threads, written to TMEM as bf16)
+//     dQ += dS K                (M=128, N=128, K=128, A from TMEM, K tile read MN-major)
+// The two halves of dQ are summed in the epilogue.  delta = sum_d(O dO) is computed in the
+// prologue and stored for the dK/dV kernel.
+#include "sel_common.cuh"
+#include "tc_common.cuh"
+
+#include <cstdlib>
+#include <string>
+
+namespace nsa {
+
+int device_status_address(int32_t** out);
+
+namespace {
+
+using namespace tc;
+
+constexpr int kThreads = 224;
+constexpr int kMaxSlots = 256;
+constexpr uint32_t kTileBytes = 32768;
+constexpr uint32_t kSmemTiles = 6 * kTileBytes;   // Q, dO, K x2, V x2
+
+constexpr uint32_t kColS = 0;      // 128
+constexpr uint32_t kColDP = 128;   // 128
+constexpr uint32_t kColDS = 256;   // 64 (bf16 pairs)
+constexpr uint32_t kColDQ = 384;   // 128
+
+struct TcDqParams {
+  const int32_t* ids;
+  int64_t i_sb, i_sg, i_sh, i_st;
+  const char* o; int64_t o_sb, o_sm, o_sh;      // forward output (for delta)
+  const char* dO; int64_t do_sb, do_sm, do_sh;
+  char* dq; int64_t dq_sb, dq_sm, dq_sh;
+  const float* lse;
+  float* delta;
+  const int32_t* block_table;
+  int max_blocks, paged;
+  int64_t n_tokens, M;
+  int H, T, G, chunk_size, causal;
+  float scale, scale_log2;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapDO,
+                     const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                     const TcDqParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = tiles;
+  uint8_t* sDO = tiles + kTileBytes;
+  uint8_t* sK = tiles + 2 * kTileBytes;
+  uint8_t* sV = tiles + 4 * kTileBytes;
+  float* stage = reinterpret_cast<float*>(tiles + 2 * kTileBytes);   // epilogue: 128 x 129 floats over the rings
+
+  __shared__ uint64_t qdo_full, k_full[2], k_empty[2], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full, dq_final;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort, s_nb;
+  __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
+
+  const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t m0 = static_cast<int64_t>(g) * p.G;
+  const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
+  const int q_chunk = static_cast<int>(m0 / p.chunk_size);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(&qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(&sdp_full, 1);
+    mbar_init(&sdp_free, 128);
+    mbar_init(&ds_full, 128);
+    mbar_init(&dq_final, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapDO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  for (int t = threadIdx.x; t < p.T; t += blockDim.x) {
+    const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
+    int row = -1, nv = 0;
+    if (bid >= 0) {
+      const int64_t t0 = static_cast<int64_t>(bid) * 64;
+      if (t0 < p.n_tokens) {
+        int64_t n = p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64;
+        bool ok = true;
+        if (p.causal) {
+          if (t0 / p.chunk_size > q_chunk) ok = false;
+          const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - t0;
+          if (lim < n) n = lim;
+          if (n <= 0) ok = false;
+        }
+        if (ok) {
+          if (p.paged) {
+            const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
+            if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
+          } else {
+            row = static_cast<int>(t0);
+            nv = static_cast<int>(n);
+          }
+        }
+      }
+    }
+    s_row[t] = row;
+    s_nvis[t] = nv;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_base_s;
+  volatile int* abort = &s_abort;
+  if (warp == 4 && lane == 0) {
+    mbar_expect_tx(&qdo_full, 2 * kTileBytes);
+    for (int dh = 0; dh < 2; ++dh)
+      for (int dup = 0; dup < 2; ++dup) {
+        tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
+        tma_load_4d(sDO + dh * 16384 + dup * 8192, &mapDO, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
+      }
+  }
+  if (threadIdx.x == 0) {
+    int nb = 0;
+    for (int t = 0; t < p.T; ++t) {
+      const int row = s_row[t], nv = s_nvis[t];
+      if (nv > 0) { s_row[nb] = row; s_nvis[nb] = nv; ++nb; }
+    }
+    s_nb = nb;
+  }
+  __syncthreads();
+  const int nb = s_nb;
+  const int NT = (nb + 1) >> 1;
+  char* dq_row0 = p.dq + (b * p.dq_sb + m0 * p.dq_sm + h * p.dq_sh) * 2;
+  const int64_t bhm = (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
+
+  auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, int re, int ro, uint64_t* bar) {
+    mbar_expect_tx(bar, kTileBytes);
+    if (p.paged) {
+      tma_load_2d(dst, map, 0, re, bar);
+      tma_load_2d(dst + 8192, map, 0, ro, bar);
+      tma_load_2d(dst + 16384, map, 64, re, bar);
+      tma_load_2d(dst + 24576, map, 64, ro, bar);
+    } else {
+      tma_load_4d(dst, map, 0, h, re, b, bar);
+      tma_load_4d(dst + 8192, map, 0, h, ro, b, bar);
+      tma_load_4d(dst + 16384, map, 64, h, re, b, bar);
+      tma_load_4d(dst + 24576, map, 64, h, ro, b, bar);
+    }
+  };
+
+  if (warp == 4 || warp == 6) {
+    // ======================= TMA producers =======================
+    if (lane == 0) {
+      const bool isK = warp == 4;
+      uint64_t* full = isK ? k_full : v_full;
+      uint64_t* empty = isK ? k_empty : v_empty;
+      uint8_t* ring = isK ? sK : sV;
+      const CUtensorMap* map = isK ? &mapK : &mapV;
+      int t = 0;
+      for (; t < NT; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort)) break;
+        load_tile(ring + s * kTileBytes, map, re, ro, &full[s]);
+      }
+      if (*abort || nb == 0) {
+        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) mbar_wait(&full[u & 1], (u >> 1) & 1, abort);
+        if (isK) mbar_wait(&qdo_full, 0, abort);
+      }
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer =======================
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t idesc_kk = instr_desc_bf16(128, 128, 0, 0);   // both operands K-major
+      constexpr uint32_t idesc_mn = instr_desc_bf16(128, 128, 0, 1);   // B read MN-major
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      bool ok = mbar_wait(&qdo_full, 0, abort);
+      for (int t = 0; ok && t < NT; ++t) {
+        const int s = t & 1, ph = (t >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, abort)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], ph, abort)) { ok = false; break; }
+        if (!mbar_wait(&sdp_free, (t & 1) ^ 1, abort)) { ok = false; break; }   // S / dP of step t-1 were read
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + s * kTileBytes), aV = smem_u32(sV + s * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tm + kColS, smem_desc(aQ + off, 16, 1024), smem_desc(aK + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_ss(tm + kColDP, smem_desc(aDO + off, 16, 1024), smem_desc(aV + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full);
+        umma_commit(&v_empty[s]);
+        if (!mbar_wait(&ds_full, t & 1, abort)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tm + kColDQ, tm + kColDS + kk * 8, smem_desc(aK + kk * 2048, 16384, 1024), idesc_mn,
+                  (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&k_empty[s]);
+      }
+      if (ok) umma_commit(&dq_final);
+    }
+  } else if (warp < 4) {
+    // ======================= per-row math (warps 0-3) =======================
+    const int half = warp >> 1;
+    const int qrow = threadIdx.x & 63;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // delta = sum_d O dO and LSE of this thread's query row (both halves hold the same row)
+    float delta = 0.f, lse2 = INFINITY;
+    if (qrow < n_q) {
+      const uint4* orow = reinterpret_cast<const uint4*>(p.o + (b * p.o_sb + (m0 + qrow) * p.o_sm + h * p.o_sh) * 2);
+      const uint4* drow = reinterpret_cast<const uint4*>(p.dO + (b * p.do_sb + (m0 + qrow) * p.do_sm + h * p.do_sh) * 2);
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        const uint4 a = orow[c], d = drow[c];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = unpack2<__nv_bfloat16>(aw[e]), y = unpack2<__nv_bfloat16>(dw[e]);
+          delta += x.x * y.x + x.y * y.y;
+        }
+      }
+      lse2 = p.lse[bhm + qrow] * kLog2e;
+      if (half == 0) p.delta[bhm + qrow] = delta;
+    }
+    if (nb == 0) {
+      if (qrow < n_q) {
+        char* drow = dq_row0 + qrow * p.dq_sm * 2 + half * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(drow + c * 16) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      {
+        uint32_t z[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = 0u;
+        tmem_st32_nowait(tm + lane_base + kColDS + (1 - half) * 32, z);
+        tmem_st_wait();
+      }
+      bool ok = true;
+      for (int t = 0; t < NT; ++t) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full, t & 1, abort));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t x0[32], x1[32], y0[32], y1[32];
+        tmem_ld32_nowait(tm + lane_base + kColS + half * 64, x0);
+        tmem_ld32_nowait(tm + lane_base + kColS + half * 64 + 32, x1);
+        tmem_ld32_nowait(tm + lane_base + kColDP + half * 64, y0);
+        tmem_ld32_nowait(tm + lane_base + kColDP + half * 64 + 32, y1);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&sdp_free);
+        const int blk = 2 * t + half;
+        const int nv = blk < nb ? s_nvis[blk] : 0;
+        uint32_t pk[32];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float d[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = (e < 2) ? 2 * j + e : 32 + 2 * j + (e - 2);
+            const float sv = __uint_as_float((e < 2) ? x0[2 * j + e] : x1[2 * j + e - 2]);
+            const float dp = __uint_as_float((e < 2) ? y0[2 * j + e] : y1[2 * j + e - 2]);
+            const float pe = (col < nv) ? fast_exp2(sv * p.scale_log2 - lse2) : 0.f;
+            d[e] = pe * (dp - delta) * p.scale;
+          }
+          pk[j] = pack2<__nv_bfloat16>(d[0], d[1]);
+          pk[16 + j] = pack2<__nv_bfloat16>(d[2], d[3]);
+        }
+        tmem_st32_nowait(tm + lane_base + kColDS + half * 32, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&ds_full);
+      }
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_final, 0, abort));
+      if (ok) {
+        tc_fence_after();
+        const int tid = threadIdx.x;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32_nowait(tm + lane_base + kColDQ + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stage[tid * 129 + c * 32 + j] = __uint_as_float(o[j]);
+        }
+      }
+      named_barrier(1, 128);
+      if (ok && qrow < n_q) {
+        const float* ra = stage + qrow * 129 + half * 64;
+        const float* rb = stage + (64 + qrow) * 129 + half * 64;
+        char* drow = dq_row0 + qrow * p.dq_sm * 2 + half * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack2<__nv_bfloat16>(ra[c * 8 + 2 * e] + rb[c * 8 + 2 * e], ra[c * 8 + 2 * e + 1] + rb[c * 8 + 2 * e + 1]);
+          *reinterpret_cast<uint4*>(drow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, NSA_ERR_CUDA);
+}
+
+}  // namespace
+
+int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
+
+// Launches the tensor-core dQ kernel when it covers the call (*launched = true).
+int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
+                             const int64_t* idx_stride, const void* out, const int64_t* out_stride, const float* lse,
+                             const void* d_out, const int64_t* do_stride, void* dq, const int64_t* dq_stride,
+                             float* delta, int B, int64_t M, int H, int D, int T, int block_size, int chunk_size,
+                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched) {
+  *launched = false;
+  const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
+  if (env != nullptr && std::string(env) == "general") return NSA_OK;
+  if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || T > kMaxSlots || H == 1) return NSA_OK;
+  if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
+  if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
+  if (encode_tiled_fn() == nullptr) return NSA_OK;
+  CUtensorMap mapQ, mapDO, mapK, mapV;
+  int rc;
+  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  if ((rc = make_qkv_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
+  TcDqParams p;
+  p.ids = ids; p.i_sb = idx_stride[0]; p.i_sg = idx_stride[1]; p.i_sh = idx_stride[2]; p.i_st = idx_stride[3];
+  p.o = static_cast<const char*>(out); p.o_sb = out_stride[0]; p.o_sm = out_stride[1]; p.o_sh = out_stride[2];
+  p.dO = static_cast<const char*>(d_out); p.do_sb = do_stride[0]; p.do_sm = do_stride[1]; p.do_sh = do_stride[2];
+  p.dq = static_cast<char*>(dq); p.dq_sb = dq_stride[0]; p.dq_sm = dq_stride[1]; p.dq_sh = dq_stride[2];
+  p.lse = lse; p.delta = delta;
+  p.block_table = kv->block_table; p.max_blocks = kv->max_blocks; p.paged = kv->mode == NSA_KV_PAGED;
+  p.n_tokens = kv->n_tokens; p.M = M; p.H = H; p.T = T; p.G = G; p.chunk_size = chunk_size; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * kLog2e;
+  if ((rc = device_status_address(&p.status))) return rc;
+  const size_t smem = kSmemTiles + 1024;
+  NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  sel_bwd_dq_tc_kernel<<<dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, p);
+  NSA_LAUNCH_OK("sel_bwd_dq_tc_kernel");
+  *launched = true;
+  return NSA_OK;
+}
+
+}  // namespace nsa

@@ -424,6 +424,59 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
 }  // namespace
 
+// Device address of the sticky status word, for kernels in other translation units (looked up
+// once per device with that device current).
+int device_status_address(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int32_t* cached[kMaxDevices] = {};
+  int dev = -1;
+  NSA_CUDA_OK(cudaGetDevice(&dev));
+  NSA_REQUIRE(dev >= 0 && dev < kMaxDevices, NSA_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    NSA_CUDA_OK(cudaGetSymbolAddress(&p, g_device_status));
+    cached[dev] = static_cast<int32_t*>(p);
+  }
+  *out = cached[dev];
+  return NSA_OK;
+}
+
+// Tensor maps of the tensor-core kernels: a [B,M,H,128] bf16 query-like tensor as a 4-D map
+// (box = 64 columns x 64 rows of one head) and, when `kv` is given, K and V either as 4-D maps of
+// the dense tensors or as 2-D maps over the page pool [num_pages*64, 128].
+int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV) {
+  int rc;
+  const uint32_t box4[4] = {64, 1, 64, 1};
+  {
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), static_cast<uint64_t>(M), static_cast<uint64_t>(B)};
+    const uint64_t st[3] = {static_cast<uint64_t>(q_stride[2]) * 2, static_cast<uint64_t>(q_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(q_stride[0]) * 2 : static_cast<uint64_t>(q_stride[1]) * 2 * M};
+    if ((rc = tc::make_bf16_map(mapQ, q, 4, dims, st, box4))) return rc;
+  }
+  if (kv == nullptr) return NSA_OK;
+  if (kv->mode == NSA_KV_DENSE) {
+    const uint64_t N = static_cast<uint64_t>(kv->n_tokens);
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), N, static_cast<uint64_t>(B)};
+    const uint64_t sk[3] = {static_cast<uint64_t>(kv->k_stride[2]) * 2, static_cast<uint64_t>(kv->k_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(kv->k_stride[0]) * 2 : static_cast<uint64_t>(kv->k_stride[1]) * 2 * N};
+    const uint64_t sv[3] = {static_cast<uint64_t>(kv->v_stride[2]) * 2, static_cast<uint64_t>(kv->v_stride[1]) * 2,
+                            B > 1 ? static_cast<uint64_t>(kv->v_stride[0]) * 2 : static_cast<uint64_t>(kv->v_stride[1]) * 2 * N};
+    if ((rc = tc::make_bf16_map(mapK, kv->k, 4, dims, sk, box4))) return rc;
+    if ((rc = tc::make_bf16_map(mapV, kv->v, 4, dims, sv, box4))) return rc;
+  } else {
+    const uint64_t rows = kv->num_pages > 0 ? static_cast<uint64_t>(kv->num_pages) * 64 : (1ull << 31);
+    const uint64_t dims[2] = {128, rows};
+    const uint64_t st[1] = {256};
+    const uint32_t box[2] = {64, 64};
+    if ((rc = tc::make_bf16_map(mapK, kv->k, 2, dims, st, box))) return rc;
+    if ((rc = tc::make_bf16_map(mapV, kv->v, 2, dims, st, box))) return rc;
+  }
+  return NSA_OK;
+}
+
 // Returns NSA_OK after launching, or NSA_ERR_UNSUPPORTED (without setting an error) when the
 // tensor-core kernel does not cover the call and the caller should use the general kernel.
 int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
@@ -440,34 +493,10 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   if (encode_tiled_fn() == nullptr) return NSA_OK;
   const int64_t MG = cdiv64(M, G);
 
+  if (H == 1) return NSA_OK;   // a size-1 head dimension may carry an arbitrary stride: leave it to the general kernel
   CUtensorMap mapQ, mapK, mapV;
   int rc;
-  {
-    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), static_cast<uint64_t>(M), static_cast<uint64_t>(B)};
-    const uint64_t st[3] = {static_cast<uint64_t>(q_stride[2]) * 2, static_cast<uint64_t>(q_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(q_stride[0]) * 2 : static_cast<uint64_t>(q_stride[1]) * 2 * M};
-    const uint32_t box[4] = {64, 1, 64, 1};
-    if (H == 1) return NSA_OK;   // a size-1 head dimension may carry an arbitrary stride: leave it to the general kernel
-    if ((rc = make_bf16_map(&mapQ, q, 4, dims, st, box))) return rc;
-  }
-  if (kv->mode == NSA_KV_DENSE) {
-    const uint64_t N = static_cast<uint64_t>(kv->n_tokens);
-    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), N, static_cast<uint64_t>(B)};
-    const uint32_t box[4] = {64, 1, 64, 1};
-    const uint64_t sk[3] = {static_cast<uint64_t>(kv->k_stride[2]) * 2, static_cast<uint64_t>(kv->k_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(kv->k_stride[0]) * 2 : static_cast<uint64_t>(kv->k_stride[1]) * 2 * N};
-    const uint64_t sv[3] = {static_cast<uint64_t>(kv->v_stride[2]) * 2, static_cast<uint64_t>(kv->v_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(kv->v_stride[0]) * 2 : static_cast<uint64_t>(kv->v_stride[1]) * 2 * N};
-    if ((rc = make_bf16_map(&mapK, kv->k, 4, dims, sk, box))) return rc;
-    if ((rc = make_bf16_map(&mapV, kv->v, 4, dims, sv, box))) return rc;
-  } else {
-    const uint64_t rows = kv->num_pages > 0 ? static_cast<uint64_t>(kv->num_pages) * 64 : (1ull << 31);
-    const uint64_t dims[2] = {128, rows};
-    const uint64_t st[1] = {256};
-    const uint32_t box[2] = {64, 64};
-    if ((rc = make_bf16_map(&mapK, kv->k, 2, dims, st, box))) return rc;
-    if ((rc = make_bf16_map(&mapV, kv->v, 2, dims, st, box))) return rc;
-  }
+  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
 
   TcFwdParams p;
   p.ids = ids;

@@ -102,6 +102,18 @@ def test_tensor_core_kernel_agrees_with_general_kernel(dev, monkeypatch):
         assert torch.allclose(l_t[fin], l_g[fin], atol=1e-3, rtol=1e-4)
         o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), ids, 64, chunk, None, causal, 64)
         assert_close_bf16(o_t, o_ref, f"tc out vs oracle (seed {seed})")
+        # dQ half of the backward: tensor-core kernel against the general kernel and the oracle
+        bargs = (q.to(dev), ops.DenseKV(k.to(dev), v.to(dev)), ids.to(dev), o_t, l_t, do.to(dev), 64, chunk,
+                 128 ** -0.5, causal, 64)
+        monkeypatch.setenv("OMNIMEM_B200_BWD_KERNEL", "general")
+        dq_g, dl_g = ops.sel_bwd_dq(*bargs)
+        monkeypatch.delenv("OMNIMEM_B200_BWD_KERNEL")
+        dq_t, dl_t = ops.sel_bwd_dq(*bargs)
+        assert torch.allclose(dl_t, dl_g, atol=2e-3, rtol=1e-3), f"delta (seed {seed})"
+        assert_close_bf16(dq_t, dq_g, f"tc vs general dq (seed {seed})", max_abs=3e-2, mean_abs=1.5e-3)
+        dq_r, _, _ = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), 64, chunk, None,
+                                     causal, 64)
+        assert_close_bf16(dq_t, dq_r, f"tc dq vs oracle (seed {seed})", max_abs=4e-2)
 
 
 def test_fp16(dev):
