@@ -92,6 +92,24 @@ __global__ void inv_scan_kernel(int32_t* __restrict__ counts, int32_t* __restric
   if (threadIdx.x == 0) o[NS] = carry_s;
 }
 
+// One thread per bucket: insertion sort of its group ids (buckets are short; the scatter pass
+// fills them in arrival order), so every consumer sees ascending groups and sums in a fixed order.
+__global__ void inv_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __restrict__ groups, int64_t NS,
+                                int64_t groups_row, int64_t n_buckets) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_buckets) return;
+  const int64_t row = i / NS, s = i % NS;
+  const int32_t* o = offsets + row * (NS + 1);
+  int32_t* gp = groups + row * groups_row + o[s];
+  const int n = o[s + 1] - o[s];
+  for (int a = 1; a < n; ++a) {
+    const int32_t v = gp[a];
+    int c = a - 1;
+    while (c >= 0 && gp[c] > v) { gp[c + 1] = gp[c]; --c; }
+    gp[c + 1] = v;
+  }
+}
+
 // ------------------------------------------------------------------------------------ dQ
 struct BwdParams {
   const char* q; int64_t q_sb, q_sm, q_sh;
@@ -579,6 +597,10 @@ int run_inverted_index(const IdxParams& ip, int32_t* groups, int32_t* offsets, i
   if (pairs > 0) {
     inv_pass_kernel<true><<<grid, kIdxThreads, 0, stream>>>(ip, counts, groups);
     NSA_LAUNCH_OK("inv_pass_kernel<scatter>");
+    const int64_t n_buckets = rows * ip.NS;
+    inv_sort_kernel<<<static_cast<unsigned>(cdiv64(n_buckets, 128)), 128, 0, stream>>>(offsets, groups, ip.NS, pairs,
+                                                                                       n_buckets);
+    NSA_LAUNCH_OK("inv_sort_kernel");
   }
   return NSA_OK;
 }
@@ -591,6 +613,11 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
                              const void* d_out, const int64_t* do_stride, void* dq, const int64_t* dq_stride,
                              float* delta, int B, int64_t M, int H, int D, int T, int block_size, int chunk_size,
                              int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched);
+int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* groups,
+                              const int32_t* offsets, const float* lse, const float* delta, const void* d_out,
+                              const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
+                              int block_size, int chunk_size, int causal, int G, float scale, int dtype,
+                              cudaStream_t stream, bool* launched);
 
 }  // namespace nsa
 
@@ -720,6 +747,13 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
   if ((rc = check_strides16("d_out", d_out, do_stride, 3, esz))) return rc;
   BwdParams p{};
   if ((rc = make_kvsrc(kv, D, esz, block_size, &p.kv))) return rc;
+  {
+    bool launched = false;
+    rc = try_launch_sel_bwd_dkv_tc(q, q_stride, kv, groups, offsets, lse, delta, d_out, do_stride, dk, dv, B, M, H, D,
+                                   T, block_size, chunk_size, causal, group_size, scale, dtype, s, &launched);
+    if (rc) return rc;
+    if (launched) return NSA_OK;
+  }
   p.q = static_cast<const char*>(q); p.q_sb = q_stride[0]; p.q_sm = q_stride[1]; p.q_sh = q_stride[2];
   p.dO = static_cast<const char*>(d_out); p.do_sb = do_stride[0]; p.do_sm = do_stride[1]; p.do_sh = do_stride[2];
   p.dk = static_cast<char*>(dk); p.dv = static_cast<char*>(dv);

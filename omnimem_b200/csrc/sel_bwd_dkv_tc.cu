@@ -1,0 +1,389 @@
+// Selection attention backward, dK/dV half, on tcgen05 / TMEM / TMA for the page geometry
+// (bf16, D = 128, 64-token blocks, query groups of up to 64 rows, dense or paged K/V).
+//
+// Ownership as in the general kernel: one work item = one (batch, head, KV block); the item's
+// dK / dV tile is produced by exactly one thread block, from the block's bucket of query groups
+// in ascending group order - no atomics, bit-reproducible.  Persistent thread blocks (one per
+// SM) walk the items round-robin; inside a block the roles are pipelined across steps AND
+// across items:
+//   warp 8   TMA producer: K, V tile of the item; per step the Q and dO rows of TWO groups of
+//            the bucket, stacked into 128-row tiles (two-stage ring)
+//   warp 9   MMA issuer, per step:  S  = [Qa;Qb] K^T, dP = [dOa;dOb] V^T   (M=128, N=64, K=128)
+//            and, one step later:   dV^T += [dOa;dOb]^T P,  dK^T += [Qa;Qb]^T dS
+//                                   (M=128 = head dim, N=64 keys, K=128 query rows)
+//   warps 0-3  one query row per thread: P = exp2(S c - LSE), dS = P (dP - delta) scale, written
+//            as bf16 rows into shared memory in the 128-byte-swizzled layout the MMA reads
+//   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the
+//            transposed tile; items with an empty bucket are zero-filled here
+// Both operands of every MMA are full (two real groups fill the 128 rows), so no tensor work
+// is wasted; S/dP and the dV^T/dK^T accumulators are double buffered in TMEM (512 columns).
+#include "sel_common.cuh"
+#include "tc_common.cuh"
+
+#include <cstdlib>
+#include <string>
+
+namespace nsa {
+
+int device_status_address(int32_t** out);
+int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
+
+namespace {
+
+using namespace tc;
+
+constexpr int kThreads = 320;
+constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
+constexpr uint32_t kQdOBytes = 65536;    // Q2 32 KiB + dO2 32 KiB per stage
+constexpr uint32_t kPdSBytes = 32768;    // P 16 KiB + dS 16 KiB
+constexpr uint32_t kSmemTiles = kKVBytes + 2 * kQdOBytes + kPdSBytes;
+
+// TMEM columns: S / dP double buffered (64 columns each), accumulators double buffered
+__device__ __forceinline__ uint32_t col_s(int buf) { return buf * 128; }
+__device__ __forceinline__ uint32_t col_dp(int buf) { return buf * 128 + 64; }
+__device__ __forceinline__ uint32_t col_dv(int acc) { return 256 + acc * 128; }
+__device__ __forceinline__ uint32_t col_dk(int acc) { return 256 + acc * 128 + 64; }
+
+struct TcDkvParams {
+  const int32_t* groups;     // [B,H,MG*T] buckets, ascending inside a bucket
+  const int32_t* offsets;    // [B,H,NS+1]
+  const float* lse;          // [B,H,M]
+  const float* delta;        // [B,H,M]
+  char* dk; char* dv;        // contiguous [B,N,H,D]
+  const int32_t* block_table;
+  int max_blocks, paged;
+  int64_t n_tokens, M, NS;
+  int B, H, T, G, MG, chunk_size, causal;
+  float scale, scale_log2;
+  int32_t* status;
+};
+
+struct Item { int b, h, blk, beg, n_ent, row; bool active; };
+
+// Decodes work item i (block fastest, then head, then batch) and its bucket.
+__device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
+  Item it;
+  it.blk = static_cast<int>(i % p.NS);
+  const int64_t r = i / p.NS;
+  it.h = static_cast<int>(r % p.H);
+  it.b = static_cast<int>(r / p.H);
+  const int32_t* offs = p.offsets + (static_cast<int64_t>(it.b) * p.H + it.h) * (p.NS + 1);
+  it.beg = offs[it.blk];
+  it.n_ent = offs[it.blk + 1] - it.beg;
+  it.row = it.blk * 64;
+  if (p.paged) {
+    const int page = it.blk < p.max_blocks ? p.block_table[static_cast<int64_t>(it.h) * p.max_blocks + it.blk] : -1;
+    it.row = page * 64;
+    if (page < 0) it.n_ent = 0;
+  }
+  it.active = it.n_ent > 0;
+  return it;
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapDO,
+                      const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                      const TcDkvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sKV = tiles;                               // K [2][64][128 B], V [2][64][128 B]
+  uint8_t* sQdO = tiles + kKVBytes;                   // [stage]{ Q2 [2][128][128 B], dO2 [2][128][128 B] }
+  uint8_t* sP = tiles + kKVBytes + 2 * kQdOBytes;     // [128 q][128 B] swizzled
+  uint8_t* sdS = sP + 16384;
+
+  __shared__ uint64_t kv_full, kv_empty, qdo_full[2], qdo_empty[2], sdp_full[2], sdp_free[2], pds_full, pds_free,
+      acc_full[2], acc_free[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(&kv_full, 1); mbar_init(&kv_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
+      mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 128);
+      mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 128);
+    }
+    mbar_init(&pds_full, 128); mbar_init(&pds_free, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 8 && lane == 0) {
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapDO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_base_s;
+  volatile int* abort = &s_abort;
+  const int64_t n_items = static_cast<int64_t>(p.B) * p.H * p.NS;
+  const int64_t bucket_row = static_cast<int64_t>(p.MG) * p.T;
+
+  if (warp == 8) {
+    // ======================= TMA producer =======================
+    if (lane == 0) {
+      uint32_t ic = 0, sc = 0;
+      bool ok = true;
+      for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
+        const Item it = get_item(p, i);
+        if (!it.active) continue;
+        if (!mbar_wait(&kv_empty, (ic & 1) ^ 1, abort)) break;
+        mbar_expect_tx(&kv_full, kKVBytes);
+        for (int dh = 0; dh < 2; ++dh) {
+          if (p.paged) {
+            tma_load_2d(sKV + dh * 8192, &mapK, dh * 64, it.row, &kv_full);
+            tma_load_2d(sKV + 16384 + dh * 8192, &mapV, dh * 64, it.row, &kv_full);
+          } else {
+            tma_load_4d(sKV + dh * 8192, &mapK, dh * 64, it.h, it.row, it.b, &kv_full);
+            tma_load_4d(sKV + 16384 + dh * 8192, &mapV, dh * 64, it.h, it.row, it.b, &kv_full);
+          }
+        }
+        const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
+        const int nsteps = (it.n_ent + 1) >> 1;
+        for (int t = 0; t < nsteps; ++t, ++sc) {
+          const int st = sc & 1, ph = (sc >> 1) & 1;
+          if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort)) { ok = false; break; }
+          const int ga = bucket[2 * t], gb = (2 * t + 1 < it.n_ent) ? bucket[2 * t + 1] : ga;
+          uint8_t* dq = sQdO + st * kQdOBytes;
+          mbar_expect_tx(&qdo_full[st], kQdOBytes);
+          for (int dh = 0; dh < 2; ++dh) {
+            tma_load_4d(dq + dh * 16384, &mapQ, dh * 64, it.h, ga * p.G, it.b, &qdo_full[st]);
+            tma_load_4d(dq + dh * 16384 + 8192, &mapQ, dh * 64, it.h, gb * p.G, it.b, &qdo_full[st]);
+            tma_load_4d(dq + 32768 + dh * 16384, &mapDO, dh * 64, it.h, ga * p.G, it.b, &qdo_full[st]);
+            tma_load_4d(dq + 32768 + dh * 16384 + 8192, &mapDO, dh * 64, it.h, gb * p.G, it.b, &qdo_full[st]);
+          }
+        }
+        ++ic;
+      }
+      if (*abort) {
+        // consumers have stopped: wait (bounded) for the copies still in flight
+        if (ic > 0) mbar_wait(&kv_full, (ic - 1) & 1, abort);
+        for (uint32_t u = (sc > 1 ? sc - 2 : 0); u < sc; ++u) mbar_wait(&qdo_full[u & 1], (u >> 1) & 1, abort);
+      }
+    }
+  } else if (warp == 9) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      constexpr uint32_t idesc_first = instr_desc_bf16(128, 64, 0, 0);    // S, dP: both operands K-major
+      constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // dV^T, dK^T: both MN-major
+      const uint32_t aK = smem_u32(sKV), aV = smem_u32(sKV + 16384);
+      const uint32_t aP = smem_u32(sP), aDS = smem_u32(sdS);
+      struct Pending { int st, acc; uint32_t sc, ic; bool first, last, any; } pd{0, 0, 0, 0, false, false, false};
+      auto issue_second = [&]() -> bool {
+        if (!mbar_wait(&pds_full, pd.sc & 1, abort)) return false;
+        if (pd.first && !mbar_wait(&acc_free[pd.acc], ((pd.ic >> 1) & 1) ^ 1, abort)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQdO + pd.st * kQdOBytes), aDO = aQ + 32768;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + col_dv(pd.acc), smem_desc(aDO + kk * 2048, 16384, 1024), smem_desc(aP + kk * 2048, 16, 1024),
+                  idesc_second, (pd.first && kk == 0) ? 0u : 1u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ss(tm + col_dk(pd.acc), smem_desc(aQ + kk * 2048, 16384, 1024), smem_desc(aDS + kk * 2048, 16, 1024),
+                  idesc_second, (pd.first && kk == 0) ? 0u : 1u);
+        umma_commit(&qdo_empty[pd.st]);
+        umma_commit(&pds_free);
+        if (pd.last) umma_commit(&acc_full[pd.acc]);
+        return true;
+      };
+      uint32_t ic = 0, sc = 0;
+      bool ok = true;
+      for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
+        const Item it = get_item(p, i);
+        if (!it.active) continue;
+        if (!mbar_wait(&kv_full, ic & 1, abort)) { ok = false; break; }
+        const int nsteps = (it.n_ent + 1) >> 1;
+        for (int t = 0; t < nsteps; ++t, ++sc) {
+          const int st = sc & 1, ph = (sc >> 1) & 1;
+          if (!mbar_wait(&qdo_full[st], ph, abort)) { ok = false; break; }
+          if (!mbar_wait(&sdp_free[st], ph ^ 1, abort)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes), aDO = aQ + 32768;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + col_s(st), smem_desc(aQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                    smem_desc(aK + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_first, kk > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + col_dp(st), smem_desc(aDO + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                    smem_desc(aV + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_first, kk > 0 ? 1u : 0u);
+          umma_commit(&sdp_full[st]);
+          if (t == nsteps - 1) umma_commit(&kv_empty);
+          if (pd.any && !issue_second()) { ok = false; break; }
+          pd = Pending{st, static_cast<int>(ic & 1), sc, ic, t == 0, t == nsteps - 1, true};
+        }
+        ++ic;
+      }
+      if (ok && pd.any) issue_second();
+    }
+  } else if (warp < 4) {
+    // ======================= per-row math: P and dS of one query row per thread =======================
+    const int half = warp >> 1, r = threadIdx.x & 63;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = threadIdx.x;                       // row of the stacked 128-row tiles
+    uint8_t* prow = sP + row * 128;
+    uint8_t* dsrow = sdS + row * 128;
+    uint32_t sc = 0;
+    bool ok = true;
+    for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
+      const Item it = get_item(p, i);
+      if (!it.active) continue;
+      const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
+      const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
+      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
+      const int64_t bh = (static_cast<int64_t>(it.b) * p.H + it.h) * p.M;
+      const int nsteps = (it.n_ent + 1) >> 1;
+      for (int t = 0; t < nsteps; ++t, ++sc) {
+        const int st = sc & 1, ph = (sc >> 1) & 1;
+        const int ent = 2 * t + half;
+        const bool valid = ent < it.n_ent;
+        const int g = valid ? bucket[ent] : 0;
+        const int64_t m0 = static_cast<int64_t>(g) * p.G;
+        const int nq = valid ? static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G) : 0;
+        const bool rowok = r < nq;
+        const float lse2 = rowok ? p.lse[bh + m0 + r] * kLog2e : INFINITY;
+        const float dl = rowok ? p.delta[bh + m0 + r] : 0.f;
+        int nkv = n_blk;
+        if (p.causal) {
+          const int64_t lim = (m0 / p.chunk_size + 1) * p.chunk_size - t0;
+          if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
+        }
+        if (!rowok) nkv = 0;
+        ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[st], ph, abort));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t pp[32], dd[32];                       // packed bf16 pairs of the 64 keys
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          uint32_t x[32], y[32];
+          tmem_ld32_nowait(tm + lane_base + col_s(st) + hc * 32, x);
+          tmem_ld32_nowait(tm + lane_base + col_dp(st) + hc * 32, y);
+          tmem_ld_wait();
+          if (hc == 1) { tc_fence_before(); mbar_arrive(&sdp_free[st]); }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int c0 = hc * 32 + 2 * j;
+            const float p0 = (c0 < nkv) ? fast_exp2(__uint_as_float(x[2 * j]) * p.scale_log2 - lse2) : 0.f;
+            const float p1 = (c0 + 1 < nkv) ? fast_exp2(__uint_as_float(x[2 * j + 1]) * p.scale_log2 - lse2) : 0.f;
+            pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
+            dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * (__uint_as_float(y[2 * j]) - dl) * p.scale,
+                                                   p1 * (__uint_as_float(y[2 * j + 1]) - dl) * p.scale);
+          }
+        }
+        // P / dS of the previous step must have been consumed before the rows are overwritten
+        ok = __all_sync(0xffffffffu, mbar_wait(&pds_free, (sc & 1) ^ 1, abort));
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int off = ((c ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+          *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+        }
+        fence_async_smem();                           // make the rows visible to the tensor core's reads
+        mbar_arrive(&pds_full);
+      }
+    }
+  } else {
+    // ======================= epilogue (warps 4-7): one head-dim lane per thread =======================
+    const int d = (warp - 4) * 32 + lane;
+    const int te = threadIdx.x - 128;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t ic = 0;
+    bool ok = true;
+    for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
+      const Item it = get_item(p, i);
+      const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
+      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
+      const int64_t row_bytes = static_cast<int64_t>(p.H) * 256;
+      const int64_t base = ((static_cast<int64_t>(it.b) * p.n_tokens + t0) * p.H + it.h) * 256;
+      if (!it.active) {
+        for (int c = te; c < n_blk * 16; c += 128) {
+          const int64_t off = base + (c >> 4) * row_bytes + (c & 15) * 16;
+          *reinterpret_cast<uint4*>(p.dk + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(p.dv + off) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int acc = ic & 1, ph = (ic >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], ph, abort));
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int mat = 0; mat < 2; ++mat) {
+        char* outp = (mat == 0 ? p.dv : p.dk) + base;
+        const uint32_t col = mat == 0 ? col_dv(acc) : col_dk(acc);
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+          uint32_t x[32];
+          tmem_ld32_nowait(tm + lane_base + col + hc * 32, x);
+          tmem_ld_wait();
+          // lanes d (even) and d+1 trade values so that each writes one packed pair of head dims
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float a = __uint_as_float(x[2 * j]), c = __uint_as_float(x[2 * j + 1]);
+            const float got = __shfl_xor_sync(0xffffffffu, (lane & 1) ? a : c, 1);
+            const int key = hc * 32 + 2 * j + (lane & 1);
+            const uint32_t w = (lane & 1) ? pack2<__nv_bfloat16>(got, c) : pack2<__nv_bfloat16>(a, got);
+            if (key < n_blk) *reinterpret_cast<uint32_t*>(outp + key * row_bytes + (d & ~1) * 2) = w;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_free[acc]);
+      ++ic;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+  if (threadIdx.x == 0 && s_abort) atomicExch(p.status, NSA_ERR_CUDA);
+}
+
+}  // namespace
+
+// Launches the tensor-core dK/dV kernel when it covers the call (*launched = true).  `groups`
+// must be sorted ascending inside each bucket (nsa_inverted_index does that).
+int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* groups,
+                              const int32_t* offsets, const float* lse, const float* delta, const void* d_out,
+                              const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
+                              int block_size, int chunk_size, int causal, int G, float scale, int dtype,
+                              cudaStream_t stream, bool* launched) {
+  *launched = false;
+  const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
+  if (env != nullptr && std::string(env) == "general") return NSA_OK;
+  if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || H == 1) return NSA_OK;
+  if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
+  if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
+  if (encode_tiled_fn() == nullptr) return NSA_OK;
+  CUtensorMap mapQ, mapDO, mapK, mapV;
+  int rc;
+  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  if ((rc = make_qkv_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
+  TcDkvParams p;
+  p.groups = groups; p.offsets = offsets; p.lse = lse; p.delta = delta;
+  p.dk = static_cast<char*>(dk); p.dv = static_cast<char*>(dv);
+  p.block_table = kv->block_table; p.max_blocks = kv->max_blocks; p.paged = kv->mode == NSA_KV_PAGED;
+  p.n_tokens = kv->n_tokens; p.M = M; p.NS = cdiv64(kv->n_tokens, 64);
+  p.B = B; p.H = H; p.T = T; p.G = G; p.MG = static_cast<int>(cdiv64(M, G)); p.chunk_size = chunk_size; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * kLog2e;
+  if ((rc = device_status_address(&p.status))) return rc;
+  int dev = 0, sms = 0;
+  NSA_CUDA_OK(cudaGetDevice(&dev));
+  NSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int64_t n_items = static_cast<int64_t>(B) * H * p.NS;
+  const int grid = static_cast<int>(n_items < sms ? n_items : sms);
+  const size_t smem = kSmemTiles + 1024;
+  NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  sel_bwd_dkv_tc_kernel<<<grid, kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, p);
+  NSA_LAUNCH_OK("sel_bwd_dkv_tc_kernel");
+  *launched = true;
+  return NSA_OK;
+}
+
+}  // namespace nsa
