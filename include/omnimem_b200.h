@@ -183,7 +183,8 @@ int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* k
 
 /* The two halves of nsa_sel_bwd as separate calls (the inverted index is built with
  * nsa_inverted_index in between).  nsa_sel_bwd_dq also writes delta = sum_d(out * d_out),
- * float [B,H,M], which nsa_sel_bwd_dkv reads together with the CSR index.
+ * float [B,H,M], which nsa_sel_bwd_dkv reads together with the CSR index.  nsa_sel_bwd_dkv
+ * takes a 256-byte device workspace (the work counter of its persistent thread blocks).
  * Replace sel_bwd_dq_*_kernel (selection_bwd.cu:310-912) and sel_bwd_dkv_mma_kernel
  * (selection_bwd.cu:916-1044). */
 int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
@@ -198,7 +199,8 @@ int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const nsa_kv_sourc
                     const float* delta, const void* d_out, const int64_t do_stride[3], void* dk,
                     void* dv, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
                     int32_t block_size, int32_t chunk_size, int32_t causal, int32_t group_size,
-                    float scale, int32_t dtype, void* stream);
+                    float scale, void* workspace, size_t workspace_bytes, int32_t dtype,
+                    void* stream);
 
 /* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
  * lses float [R][B,H,M] -> out, lse.  O = sum_r exp(lse_r - lse) O_r.  New for

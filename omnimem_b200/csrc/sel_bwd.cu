@@ -617,7 +617,7 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
                               const int32_t* offsets, const float* lse, const float* delta, const void* d_out,
                               const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
                               int block_size, int chunk_size, int causal, int G, float scale, int dtype,
-                              cudaStream_t stream, bool* launched);
+                              int32_t* counter, cudaStream_t stream, bool* launched);
 
 }  // namespace nsa
 
@@ -653,14 +653,15 @@ static void bwd_ws_layout(int32_t B, int64_t M, int32_t H, int64_t NS, int64_t M
   off[2] = off[1] + align_up(static_cast<size_t>(B) * H * NS * 4, 256);
   off[3] = off[2] + align_up(static_cast<size_t>(B) * H * (NS + 1) * 4, 256);
   off[4] = off[3] + align_up(static_cast<size_t>(B) * H * MG * T * 4, 256);
+  off[5] = off[4] + 256;   // scheduling counter of the dK/dV kernel
 }
 
 extern "C" size_t nsa_sel_bwd_workspace_bytes(int32_t B, int64_t M, int32_t H, int64_t N, int32_t T,
                                               int32_t block_size, int32_t group_size) {
   if (block_size <= 0 || group_size <= 0) return 0;
-  size_t off[5];
+  size_t off[6];
   bwd_ws_layout(B, M, H, cdiv64(N, block_size), cdiv64(M, group_size), T, off);
-  return off[4];
+  return off[5];
 }
 
 static int bwd_common_checks(const char* op, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
@@ -729,7 +730,8 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
                                const float* delta, const void* d_out, const int64_t do_stride[3],
                                void* dk, void* dv, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
                                int32_t block_size, int32_t chunk_size, int32_t causal,
-                               int32_t group_size, float scale, int32_t dtype, void* stream) {
+                               int32_t group_size, float scale, void* workspace, size_t workspace_bytes,
+                               int32_t dtype, void* stream) {
   int rc;
   if ((rc = bwd_common_checks("sel_bwd_dkv", B, M, H, D, T, block_size, chunk_size, group_size, dtype, kv))) return rc;
   const int64_t N = kv->n_tokens;
@@ -749,8 +751,9 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
   if ((rc = make_kvsrc(kv, D, esz, block_size, &p.kv))) return rc;
   {
     bool launched = false;
+    int32_t* counter = (workspace != nullptr && workspace_bytes >= 256) ? static_cast<int32_t*>(workspace) : nullptr;
     rc = try_launch_sel_bwd_dkv_tc(q, q_stride, kv, groups, offsets, lse, delta, d_out, do_stride, dk, dv, B, M, H, D,
-                                   T, block_size, chunk_size, causal, group_size, scale, dtype, s, &launched);
+                                   T, block_size, chunk_size, causal, group_size, scale, dtype, counter, s, &launched);
     if (rc) return rc;
     if (launched) return NSA_OK;
   }
@@ -781,7 +784,7 @@ extern "C" int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_k
               NSA_ERR_WORKSPACE, "sel_bwd: workspace too small");
   if (B == 0 || H == 0) return NSA_OK;
   NSA_REQUIRE(workspace != nullptr, NSA_ERR_INVALID, "sel_bwd: workspace is null");
-  size_t off[5];
+  size_t off[6];
   bwd_ws_layout(B, M, H, NS, MG, T, off);
   char* ws = static_cast<char*>(workspace);
   float* delta = reinterpret_cast<float*>(ws + off[0]);
@@ -798,5 +801,5 @@ extern "C" int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_k
                              scale, dtype, stream))) return rc;
   }
   return nsa_sel_bwd_dkv(q, q_stride, kv, groups, offsets, lse, delta, d_out, do_stride, dk, dv, B, M, H, D, T,
-                         block_size, chunk_size, causal, group_size, scale, dtype, stream);
+                         block_size, chunk_size, causal, group_size, scale, ws + off[4], 256, dtype, stream);
 }

@@ -29,6 +29,14 @@ int device_status_address(int32_t** out);
 int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
                   CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
 
+#ifdef NSA_TC_TRACE
+// Debug build only: clock64 stamps of thread block 0; [0] MMA issuer, [1] math thread 0, [2] producer, [3] epilogue.
+__device__ long long g_trace_dkv[4][1024];
+#define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 1024) g_trace_dkv[role][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace tc;
@@ -57,6 +65,7 @@ struct TcDkvParams {
   int B, H, T, G, MG, chunk_size, causal;
   float scale, scale_log2;
   int32_t* status;
+  int32_t* counter;          // zeroed before the launch: next work item to hand out
 };
 
 struct Item { int b, h, blk, beg, n_ent, row; bool active; };
@@ -64,10 +73,11 @@ struct Item { int b, h, blk, beg, n_ent, row; bool active; };
 // Decodes work item i (block fastest, then head, then batch) and its bucket.
 __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
   Item it;
-  it.blk = static_cast<int>(i % p.NS);
-  const int64_t r = i / p.NS;
-  it.h = static_cast<int>(r % p.H);
-  it.b = static_cast<int>(r / p.H);
+  const uint32_t iu = static_cast<uint32_t>(i), ns = static_cast<uint32_t>(p.NS);   // the host keeps B*H*NS below 2^31
+  const uint32_t r = iu / ns;
+  it.blk = static_cast<int>(iu - r * ns);
+  it.b = static_cast<int>(r / static_cast<uint32_t>(p.H));
+  it.h = static_cast<int>(r - static_cast<uint32_t>(it.b) * static_cast<uint32_t>(p.H));
   const int32_t* offs = p.offsets + (static_cast<int64_t>(it.b) * p.H + it.h) * (p.NS + 1);
   it.beg = offs[it.blk];
   it.n_ent = offs[it.blk + 1] - it.beg;
@@ -78,6 +88,15 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
     if (page < 0) it.n_ent = 0;
   }
   it.active = it.n_ent > 0;
+  return it;
+}
+// Work items are handed out through a global counter (buckets differ a lot in length, a static
+// split leaves thread blocks idle).  The producer thread takes the ticket, decodes the item and
+// publishes it in a 4-deep shared-memory ring that the other roles follow; n_ent = -1 ends it.
+__device__ __forceinline__ Item fetch_item(const TcDkvParams& p, int64_t n_items) {
+  const int64_t t = atomicAdd(p.counter, 1);
+  if (t < n_items) return get_item(p, t);
+  Item it{0, 0, 0, 0, -1, 0, false};
   return it;
 }
 
@@ -96,12 +115,15 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   __shared__ uint64_t kv_full, kv_empty, qdo_full[2], qdo_empty[2], sdp_full[2], sdp_free[2], pds_full, pds_free,
       acc_full[2], acc_free[2];
+  __shared__ uint64_t sched_full[4], sched_empty[4];
+  __shared__ Item s_items[4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     s_abort = 0;
+    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 257); }
     mbar_init(&kv_full, 1); mbar_init(&kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
@@ -128,10 +150,18 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     if (lane == 0) {
       uint32_t ic = 0, sc = 0;
       bool ok = true;
-      for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
-        const Item it = get_item(p, i);
+      Item nxt = fetch_item(p, n_items);
+      for (uint32_t n = 0; ok; ++n) {
+        const Item it = nxt;
+        if (!mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort)) break;
+        s_items[n & 3] = it;
+        mbar_arrive(&sched_full[n & 3]);
+        if (it.n_ent < 0) break;
+        nxt = fetch_item(p, n_items);          // decoded while this item's copies are issued
         if (!it.active) continue;
+        TRACE(2, 16 + sc * 4 + 0);
         if (!mbar_wait(&kv_empty, (ic & 1) ^ 1, abort)) break;
+        TRACE(2, 16 + sc * 4 + 1);
         mbar_expect_tx(&kv_full, kKVBytes);
         for (int dh = 0; dh < 2; ++dh) {
           if (p.paged) {
@@ -147,6 +177,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         for (int t = 0; t < nsteps; ++t, ++sc) {
           const int st = sc & 1, ph = (sc >> 1) & 1;
           if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort)) { ok = false; break; }
+          TRACE(2, 16 + sc * 4 + 2);
           const int ga = bucket[2 * t], gb = (2 * t + 1 < it.n_ent) ? bucket[2 * t + 1] : ga;
           uint8_t* dq = sQdO + st * kQdOBytes;
           mbar_expect_tx(&qdo_full[st], kQdOBytes);
@@ -170,22 +201,25 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_first = instr_desc_bf16(128, 64, 0, 0);    // S, dP: both operands K-major
       constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // dV^T, dK^T: both MN-major
-      const uint32_t aK = smem_u32(sKV), aV = smem_u32(sKV + 16384);
-      const uint32_t aP = smem_u32(sP), aDS = smem_u32(sdS);
+      const uint64_t dK = smem_desc(smem_u32(sKV), 16, 1024), dV = smem_desc(smem_u32(sKV + 16384), 16, 1024);
+      const uint64_t dP = smem_desc(smem_u32(sP), 16, 1024), dDS = smem_desc(smem_u32(sdS), 16, 1024);
       struct Pending { int st, acc; uint32_t sc, ic; bool first, last, any; } pd{0, 0, 0, 0, false, false, false};
       auto issue_second = [&]() -> bool {
         if (!mbar_wait(&pds_full, pd.sc & 1, abort)) return false;
+        TRACE(0, 16 + (pd.sc + 1) * 8 + 4);
         if (pd.first && !mbar_wait(&acc_free[pd.acc], ((pd.ic >> 1) & 1) ^ 1, abort)) return false;
+        TRACE(0, 16 + (pd.sc + 1) * 8 + 5);
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQdO + pd.st * kQdOBytes), aDO = aQ + 32768;
+        const uint32_t aQ = smem_u32(sQdO + pd.st * kQdOBytes);
+        const uint64_t dQmn = smem_desc(aQ, 16384, 1024), dDOmn = smem_desc(aQ + 32768, 16384, 1024);
+        const uint32_t acc0 = pd.first ? 0u : 1u;
+        const uint32_t tdv = tm + col_dv(pd.acc), tdk = tm + col_dk(pd.acc);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + col_dv(pd.acc), smem_desc(aDO + kk * 2048, 16384, 1024), smem_desc(aP + kk * 2048, 16, 1024),
-                  idesc_second, (pd.first && kk == 0) ? 0u : 1u);
+          umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + col_dk(pd.acc), smem_desc(aQ + kk * 2048, 16384, 1024), smem_desc(aDS + kk * 2048, 16, 1024),
-                  idesc_second, (pd.first && kk == 0) ? 0u : 1u);
+          umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
         umma_commit(&qdo_empty[pd.st]);
         umma_commit(&pds_free);
         if (pd.last) umma_commit(&acc_full[pd.acc]);
@@ -193,28 +227,50 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       };
       uint32_t ic = 0, sc = 0;
       bool ok = true;
-      for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
-        const Item it = get_item(p, i);
-        if (!it.active) continue;
+      for (uint32_t n = 0; ok; ++n) {
+        // Never block on the item ring while the second half of a step is still owed: the
+        // epilogue warps hold ring slots until that half completes their accumulator.
+        if (pd.any && !mbar_try(&sched_full[n & 3], (n >> 2) & 1)) {
+          if (!issue_second()) { ok = false; break; }
+          pd.any = false;
+        }
+        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) { ok = false; break; }
+        const Item it = s_items[n & 3];
+        mbar_arrive(&sched_empty[n & 3]);
+        if (it.n_ent < 0) break;
+        if (!it.active) {
+          if (pd.any) {
+            if (!issue_second()) { ok = false; break; }
+            pd.any = false;
+          }
+          continue;
+        }
+        TRACE(0, 16 + sc * 8 + 0);
         if (!mbar_wait(&kv_full, ic & 1, abort)) { ok = false; break; }
+        TRACE(0, 16 + sc * 8 + 1);
         const int nsteps = (it.n_ent + 1) >> 1;
         for (int t = 0; t < nsteps; ++t, ++sc) {
           const int st = sc & 1, ph = (sc >> 1) & 1;
           if (!mbar_wait(&qdo_full[st], ph, abort)) { ok = false; break; }
+          TRACE(0, 16 + sc * 8 + 2);
           if (!mbar_wait(&sdp_free[st], ph ^ 1, abort)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes), aDO = aQ + 32768;
+          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
+          const uint64_t dQ = smem_desc(aQ, 16, 1024), dDO = smem_desc(aQ + 32768, 16, 1024);
+          const uint32_t ts = tm + col_s(st), tdp = tm + col_dp(st);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tm + col_s(st), smem_desc(aQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                    smem_desc(aK + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_first, kk > 0 ? 1u : 0u);
+            umma_ss(ts, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                    desc_advance(dK, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tm + col_dp(st), smem_desc(aDO + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                    smem_desc(aV + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), idesc_first, kk > 0 ? 1u : 0u);
+            umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 16384 + (kk & 3) * 32),
+                    desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
           umma_commit(&sdp_full[st]);
           if (t == nsteps - 1) umma_commit(&kv_empty);
+          TRACE(0, 16 + sc * 8 + 3);
           if (pd.any && !issue_second()) { ok = false; break; }
+          TRACE(0, 16 + sc * 8 + 6);
           pd = Pending{st, static_cast<int>(ic & 1), sc, ic, t == 0, t == nsteps - 1, true};
         }
         ++ic;
@@ -230,8 +286,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint8_t* dsrow = sdS + row * 128;
     uint32_t sc = 0;
     bool ok = true;
-    for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
-      const Item it = get_item(p, i);
+    for (uint32_t n = 0; ok; ++n) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
+      if (!ok) break;
+      const Item it = s_items[n & 3];
+      mbar_arrive(&sched_empty[n & 3]);
+      if (it.n_ent < 0) break;
       if (!it.active) continue;
       const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
       const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
@@ -254,8 +314,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
         }
         if (!rowok) nkv = 0;
+        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[st], ph, abort));
         if (!ok) break;
+        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 1);
         tc_fence_after();
         uint32_t pp[32], dd[32];                       // packed bf16 pairs of the 64 keys
 #pragma unroll
@@ -275,9 +337,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                                                    p1 * (__uint_as_float(y[2 * j + 1]) - dl) * p.scale);
           }
         }
+        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 2);
         // P / dS of the previous step must have been consumed before the rows are overwritten
         ok = __all_sync(0xffffffffu, mbar_wait(&pds_free, (sc & 1) ^ 1, abort));
         if (!ok) break;
+        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 3);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int off = ((c ^ (row & 7)) << 4);
@@ -286,6 +350,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         fence_async_smem();                           // make the rows visible to the tensor core's reads
         mbar_arrive(&pds_full);
+        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 4);
       }
     }
   } else {
@@ -295,8 +360,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t ic = 0;
     bool ok = true;
-    for (int64_t i = blockIdx.x; ok && i < n_items; i += gridDim.x) {
-      const Item it = get_item(p, i);
+    for (uint32_t n = 0; ok; ++n) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
+      if (!ok) break;
+      const Item it = s_items[n & 3];
+      mbar_arrive(&sched_empty[n & 3]);
+      if (it.n_ent < 0) break;
       const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
       const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
       const int64_t row_bytes = static_cast<int64_t>(p.H) * 256;
@@ -310,8 +379,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         continue;
       }
       const int acc = ic & 1, ph = (ic >> 1) & 1;
+      if (te == 0) TRACE(3, 16 + ic * 4 + 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], ph, abort));
       if (!ok) break;
+      if (te == 0) TRACE(3, 16 + ic * 4 + 1);
       tc_fence_after();
 #pragma unroll
       for (int mat = 0; mat < 2; ++mat) {
@@ -335,6 +406,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       }
       tc_fence_before();
       mbar_arrive(&acc_free[acc]);
+      if (te == 0) TRACE(3, 16 + ic * 4 + 2);
       ++ic;
     }
   }
@@ -353,8 +425,9 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
                               const int32_t* offsets, const float* lse, const float* delta, const void* d_out,
                               const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
                               int block_size, int chunk_size, int causal, int G, float scale, int dtype,
-                              cudaStream_t stream, bool* launched) {
+                              int32_t* counter, cudaStream_t stream, bool* launched) {
   *launched = false;
+  if (counter == nullptr) return NSA_OK;
   const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
   if (env != nullptr && std::string(env) == "general") return NSA_OK;
   if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || H == 1) return NSA_OK;
@@ -373,10 +446,13 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   p.B = B; p.H = H; p.T = T; p.G = G; p.MG = static_cast<int>(cdiv64(M, G)); p.chunk_size = chunk_size; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   if ((rc = device_status_address(&p.status))) return rc;
+  p.counter = counter;
+  NSA_CUDA_OK(cudaMemsetAsync(counter, 0, sizeof(int32_t), stream));
   int dev = 0, sms = 0;
   NSA_CUDA_OK(cudaGetDevice(&dev));
   NSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int64_t n_items = static_cast<int64_t>(B) * H * p.NS;
+  if (n_items > 0x7fffffff) return NSA_OK;
   const int grid = static_cast<int>(n_items < sms ? n_items : sms);
   const size_t smem = kSmemTiles + 1024;
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -387,3 +463,10 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
 }
 
 }  // namespace nsa
+
+#ifdef NSA_TC_TRACE
+extern "C" int nsa_debug_trace_dkv(long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_dkv, sizeof(long long) * 4 * 1024));
+  return NSA_OK;
+}
+#endif

@@ -188,7 +188,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_kk = instr_desc_bf16(128, 128, 0, 0);   // both operands K-major
       constexpr uint32_t idesc_mn = instr_desc_bf16(128, 128, 0, 1);   // B read MN-major
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024), dDO = smem_desc(smem_u32(sDO), 16, 1024);
       bool ok = mbar_wait(&qdo_full, 0, abort);
       for (int t = 0; ok && t < NT; ++t) {
         const int s = t & 1, ph = (t >> 1) & 1;
@@ -196,25 +196,27 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (!mbar_wait(&v_full[s], ph, abort)) { ok = false; break; }
         if (!mbar_wait(&sdp_free, (t & 1) ^ 1, abort)) { ok = false; break; }   // S / dP of step t-1 were read
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + s * kTileBytes), aV = smem_u32(sV + s * kTileBytes);
+        const uint32_t aK = smem_u32(sK + s * kTileBytes);
+        const uint64_t dK = smem_desc(aK, 16, 1024), dV = smem_desc(smem_u32(sV + s * kTileBytes), 16, 1024);
+        const uint64_t dKmn = smem_desc(aK, 16384, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tm + kColS, smem_desc(aQ + off, 16, 1024), smem_desc(aK + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+          umma_ss(tm + kColS, desc_advance(dQ, off), desc_advance(dK, off), idesc_kk, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tm + kColDP, smem_desc(aDO + off, 16, 1024), smem_desc(aV + off, 16, 1024), idesc_kk, kk > 0 ? 1u : 0u);
+          umma_ss(tm + kColDP, desc_advance(dDO, off), desc_advance(dV, off), idesc_kk, kk > 0 ? 1u : 0u);
         }
         umma_commit(&sdp_full);
         umma_commit(&v_empty[s]);
         if (!mbar_wait(&ds_full, t & 1, abort)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t acc0 = t > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tm + kColDQ, tm + kColDS + kk * 8, smem_desc(aK + kk * 2048, 16384, 1024), idesc_mn,
-                  (t > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tm + kColDQ, tm + kColDS + kk * 8, desc_advance(dKmn, kk * 2048), idesc_mn, kk > 0 ? 1u : acc0);
         umma_commit(&k_empty[s]);
       }
       if (ok) umma_commit(&dq_final);

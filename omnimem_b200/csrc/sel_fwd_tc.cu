@@ -246,7 +246,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
-      const uint32_t aQ = smem_u32(sQ);
+      const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
       auto issue_pv = [&](int u) -> bool {
         const int s = u & 1, ph = (u >> 1) & 1;
         if (!mbar_wait(&v_full[s], ph, abort)) return false;
@@ -254,11 +254,12 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (!mbar_wait(&p_full[s], ph, abort)) return false;
         TRACE(0, 8 + (u + 1) * 8 + 4);
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + s * kTileBytes);
+        const uint64_t dV = smem_desc(smem_u32(sV + s * kTileBytes), 16384, 1024);
+        const uint32_t tP = tm + kColP + s * 64;
+        const uint32_t acc0 = u > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tm + kColO, tm + kColP + s * 64 + kk * 8, smem_desc(aV + kk * 2048, 16384, 1024), idesc_pv,
-                  (u > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tm + kColO, tP + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, kk > 0 ? 1u : acc0);
         umma_commit(&v_empty[s]);
         umma_commit(&pv_done);
         return true;
@@ -272,11 +273,11 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (!mbar_wait(&s_free[s], ph ^ 1, abort)) { ok = false; break; }
         TRACE(0, 8 + t * 8 + 1);
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + s * kTileBytes);
+        const uint64_t dK = smem_desc(smem_u32(sK + s * kTileBytes), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColS + s * 128, smem_desc(aQ + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                  smem_desc(aK + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss(tm + kColS + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                  desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
         umma_commit(&s_full[s]);
         umma_commit(&k_empty[s]);
         TRACE(0, 8 + t * 8 + 2);

@@ -77,6 +77,13 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= static_cast<uint64_t>(2) << 61;   // 128-byte swizzle
   return d;
 }
+// Descriptor of the same layout `byte_offset` further into shared memory (the start-address
+// field counts 16-byte units; tiles live below 256 KiB so the sum never carries out of it).
+// Building one base descriptor per tile and advancing it keeps the single issuing thread's
+// instruction count per MMA to a couple of adds.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t base, uint32_t byte_offset) {
+  return base + static_cast<uint64_t>(byte_offset >> 4);
+}
 // kind::f16 instruction descriptor: bf16 x bf16 -> fp32, M x N tile; *_mn = operand is MN-major.
 __host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N, int a_mn, int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn) << 15) |

@@ -389,9 +389,10 @@ def sel_bwd_dkv(q, kv, groups, offsets, lse, delta, d_out, T: int, block_size: i
     dv = torch.empty(B, N, H, D, dtype=q.dtype, device=q.device)
     src = kv.struct()
     with torch.cuda.device(q.device):
+        ws = torch.empty(256, dtype=torch.uint8, device=q.device)
         call("nsa_sel_bwd_dkv", q.data_ptr(), strides3(q), C.byref(src), groups.data_ptr(), offsets.data_ptr(),
              lse.contiguous().data_ptr(), delta.data_ptr(), d_out.data_ptr(), strides3(d_out), dk.data_ptr(),
              dv.data_ptr(), B, M, H, D, _i32(T, "T"), _i32(block_size, "block_size"),
              _i32(chunk_size, "chunk_size"), int(bool(causal)), _i32(group_size, "group_size"), float(scale),
-             _dtype(q), _stream(q))
+             ws.data_ptr(), 256, _dtype(q), _stream(q))
     return dk, dv
