@@ -225,10 +225,14 @@ def run_gpu(args):
     ms_e2e = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
 
+    sharded = None
     if dist is not None:
         t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = t.tolist()
+        del d, res_host
+        torch.cuda.empty_cache()
+        sharded = run_sharded(args, dist, dev, rank, world)
 
     if rank == 0:
         pk = peaks()
@@ -269,11 +273,59 @@ def run_gpu(args):
             "gpu_launches": LAUNCHES_PER_STEP * args.steps,
             "clocks": clocks, "roofline": roof, "kernels": kernels,
         }
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(host, steps=1)
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_sharded(args, dist, dev, rank, world):
+    """Config 5: one selection forward (H=12, D=128, 4680 queries) over a 1,048,576-token KV cache
+    sharded by block across the ranks; candidates and (O, LSE) partials merged after NCCL
+    all-gathers.  Device-timed, max over ranks."""
+    from omnimem_b200 import ops
+    from omnimem_b200.sharded import ShardedSelection
+    c = CFG
+    n_total = 1 << 20
+    n_local = n_total // world                      # 16384 / world whole blocks per rank
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    q = torch.randn(1, c["M"], c["H"], c["D"], generator=torch.Generator(device=dev).manual_seed(5), device=dev,
+                    dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(1, n_local, c["H"], c["D"], generator=g, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(1, n_local, c["H"], c["D"], generator=g, device=dev, dtype=torch.bfloat16)
+    sh = ShardedSelection()
+
+    def step():
+        return sh.forward(q, k, v, c["topk"], c["block"], c["group"], c["frame"], False)
+
+    for _ in range(3):
+        out, lse, idx = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    steps = max(5, min(args.steps, 20))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        out, lse, idx = step()
+    b.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    same = torch.tensor([float(idx.sum().item())], device=dev, dtype=torch.float64)
+    lo, hi = same.clone(), same.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    flops = 4 * c["D"] * c["M"] * c["H"] * c["topk"] * c["block"]
+    esz = 2
+    return {"workload": "config5: selection forward, 4680 queries, 1,048,576-token KV sharded by block, top-16 merged "
+                        "over NCCL all-gathers", "ms_per_call": round(ms.item(), 4),
+            "fwd_tflops": round(flops / (ms.item() * 1e-3) / 1e12, 2),
+            "kv_score_gbs_per_gpu": round(n_local * c["H"] * c["D"] * esz / (ms.item() * 1e-3) / 1e9, 1),
+            "ranks_agree_on_topk": bool(lo.item() == hi.item()), "finite": bool(torch.isfinite(out.float()).all().item())}
 
 
 # ------------------------------------------------------------------------------ CPU reference

@@ -128,6 +128,74 @@ __global__ void __launch_bounds__(256) score_kernel(const ScoreParams p) {
   }
 }
 
+// 16-bit inputs: the same scores on mma.sync (products of bf16 / fp16 operands are exact in fp32,
+// the accumulation is fp32), one thread block per (64 key blocks, 64 query rows, head, batch).
+constexpr int kScoreMmaRows = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(128) score_mma_kernel(const ScoreParams p) {
+  extern __shared__ __align__(16) char s_raw[];
+  const int PITCH = p.D + 8;
+  T* sK = reinterpret_cast<T*>(s_raw);                  // [64][PITCH]
+  T* sQ = sK + kScoreCols * PITCH;                      // [64][PITCH]
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kScoreCols;
+  const int g0 = blockIdx.y * kScoreMmaRows;
+  const int h = blockIdx.z % p.H, b = blockIdx.z / p.H;
+  const int ncol = static_cast<int>(p.NC - c0 < kScoreCols ? p.NC - c0 : kScoreCols);
+  const int nrow = min(kScoreMmaRows, p.MG - g0);
+  const int cpr = p.D / 8;                              // 16-byte chunks per row
+  for (int i = threadIdx.x; i < kScoreCols * cpr; i += blockDim.x) {
+    const int r = i / cpr, cc = i - r * cpr;
+    const char* ksrc = p.k + (b * p.k_sb + (c0 + r) * p.k_sc + h * p.k_sh) * 2 + cc * 16;
+    const char* qsrc = p.q + (b * p.q_sb + (g0 + r) * p.q_sg + h * p.q_sh) * 2 + cc * 16;
+    cp_async16(sK + r * PITCH + cc * 8, r < ncol ? ksrc : p.k, r < ncol ? 16 : 0);
+    cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? qsrc : p.q, r < nrow ? 16 : 0);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
+  float acc[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+  const T* qa = sQ + (warp * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8;
+  const T* kb = sK + ((lane & 7) + ((lane >> 4) << 3)) * PITCH + ((lane >> 3) & 1) * 8;
+  for (int kk = 0; kk < p.D / 16; ++kk) {
+    uint32_t a[4];
+    ldmatrix_x4(a, qa + kk * 16);
+#pragma unroll
+    for (int n16 = 0; n16 < 4; ++n16) {
+      uint32_t bf[4];
+      ldmatrix_x4(bf, kb + n16 * 16 * PITCH + kk * 16);
+      mma16816<T>(acc[2 * n16], a, bf[0], bf[1]);
+      mma16816<T>(acc[2 * n16 + 1], a, bf[2], bf[3]);
+    }
+  }
+  float* out = p.scores + ((static_cast<int64_t>(b) * p.H + h) * p.MG + g0) * p.NC + c0;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + gid + 8 * r;
+    if (row < nrow) {
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int col = n * 8 + 2 * t4;
+        if (col < ncol) out[static_cast<int64_t>(row) * p.NC + col] = acc[n][2 * r] * p.scale + 0.f;
+        if (col + 1 < ncol) out[static_cast<int64_t>(row) * p.NC + col + 1] = acc[n][2 * r + 1] * p.scale + 0.f;
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
+  const size_t smem = static_cast<size_t>(2 * kScoreCols) * (sp.D + 8) * sizeof(T);
+  NSA_CUDA_OK(cudaFuncSetAttribute(score_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const dim3 grid(static_cast<unsigned>(cdiv64(sp.NC, kScoreCols)), cdiv(sp.MG, kScoreMmaRows), sp.H * B);
+  score_mma_kernel<T><<<grid, 128, smem, s>>>(sp);
+  NSA_LAUNCH_OK("score_mma_kernel");
+  return NSA_OK;
+}
+
 // --------------------------------------------------------------------------------- selection
 struct Mask {
   int block_size, chunk_size, chunk_size_k, G, q_off, ex_win, ex_sink;
@@ -328,7 +396,14 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
                  ks[0], ks[1], ks[2], scores, MG, H, D, NC, scale};
   const size_t smem = (static_cast<size_t>(kScoreCols) * (D + 1) + static_cast<size_t>(kScoreRows) * D) * sizeof(float);
   const dim3 grid(static_cast<unsigned>(cdiv64(NC, kScoreCols)), H, B);
-  if (dtype == NSA_BF16) {
+  // 16-bit operands with 16-byte addressable rows go to the mma kernel
+  const bool mma_ok = dtype != NSA_F32 && D % 16 == 0 && D <= 256 && static_cast<int64_t>(H) * B <= 65535 &&
+                      aligned16(qp) && aligned16(kp) && (qs[0] * 2) % 16 == 0 && (qs[1] * 2) % 16 == 0 &&
+                      (qs[2] * 2) % 16 == 0 && (ks[0] * 2) % 16 == 0 && (ks[1] * 2) % 16 == 0 && (ks[2] * 2) % 16 == 0;
+  if (mma_ok) {
+    const int rc = dtype == NSA_BF16 ? launch_score_mma<__nv_bfloat16>(sp, B, s) : launch_score_mma<__half>(sp, B, s);
+    if (rc) return rc;
+  } else if (dtype == NSA_BF16) {
     NSA_CUDA_OK(cudaFuncSetAttribute(score_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     score_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(sp);
   } else if (dtype == NSA_F16) {

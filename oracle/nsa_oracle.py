@@ -72,15 +72,17 @@ def pool_heads(x: torch.Tensor, num_groups: int) -> torch.Tensor:
 def visibility_mask(MG: int, NC: int, *, block_size: int, chunk_size: int, chunk_size_k: int,
                     causal: bool, ex_win: int = 0, ex_sink: int = 0, prog_excl: bool = False,
                     tf_mask: bool = False, q_chunk_offset: int = 0,
-                    q_group_size: int = 1) -> torch.Tensor:
+                    q_group_size: int = 1, col_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bool [MG, NC]; True where key block c is a candidate for query row g.
+    `col_ids` gives the global block id of every column (a shard of a block-sharded cache);
+    default 0..NC-1.
 
     ``chunk_size`` is measured in query tokens and row g stands for tokens
     [g*q_group_size, ...): q_cid = (g*q_group_size)//chunk_size + q_chunk_offset.  With
     q_group_size == 1 this is the reference operator's convention (rows already pooled,
     chunk_size in rows).  k_cid = (c*block_size)//chunk_size_k."""
     g = torch.arange(MG, dtype=torch.int64)
-    c = torch.arange(NC, dtype=torch.int64)
+    c = torch.arange(NC, dtype=torch.int64) if col_ids is None else col_ids.to(torch.int64)
     q_cid = (g * q_group_size) // chunk_size + q_chunk_offset
     k_cid = (c * block_size) // chunk_size_k
     if tf_mask:
@@ -133,7 +135,7 @@ def topk_select(q_pooled: torch.Tensor, k_pooled: torch.Tensor, topk: int, scale
                 *, block_size: int, chunk_size: int, chunk_size_k: Optional[int] = None,
                 causal: bool = True, ex_win: int = 0, ex_sink: int = 0, prog_excl: bool = False,
                 tf_mask: bool = False, q_chunk_offset: int = 0, q_group_size: int = 1,
-                return_scores: bool = False):
+                return_scores: bool = False, col_ids: Optional[torch.Tensor] = None):
     """int32 [B, MG, H, topk]: visible blocks ordered by (score descending, id ascending),
     -1 in the unused slots (topk.cu:100-102,388-392; ops.h:11-12)."""
     B, MG, H, D = q_pooled.shape
@@ -160,6 +162,8 @@ def topk_select(q_pooled: torch.Tensor, k_pooled: torch.Tensor, topk: int, scale
     top_i = torch.where(torch.gather(vis[None, None].expand(B, H, MG, NC), -1, top_i), top_i,
                         torch.full_like(top_i, -1))
     top_v = torch.where(top_i >= 0, top_v, torch.full_like(top_v, NEG_INF))
+    if col_ids is not None:                                  # local column -> global block id
+        top_i = torch.where(top_i >= 0, col_ids.to(torch.int64)[top_i.clamp_min(0)], top_i)
     idx[..., :kk] = top_i.permute(0, 2, 1, 3).to(torch.int32)
     val[..., :kk] = top_v.permute(0, 2, 1, 3)
     return (idx, val) if return_scores else idx

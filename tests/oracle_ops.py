@@ -1,0 +1,38 @@
+"""A stand-in for ``omnimem_b200.ops`` backed by the CPU oracle, for tests of host-side logic
+that must run without a GPU (the multi-rank exchange of ``omnimem_b200.sharded`` over gloo).
+Test infrastructure only - it mirrors just the functions that module calls."""
+import torch
+
+from oracle import nsa_oracle as O
+
+
+class DenseKV:
+    def __init__(self, k, v):
+        self.k, self.v, self.n_tokens = k, v, k.shape[1]
+
+
+def pool_rows(x, size):
+    return O.pool_rows(x, size)
+
+
+def topk(q_pooled, k_pooled, topk, scale, block_size, chunk_size, chunk_size_k, causal, ex_win=0, ex_sink=0,
+         prog_excl=False, tf_mask=False, q_chunk_offset=0, q_group_size=1, id_base=0, id_stride=1,
+         return_scores=False):
+    cols = id_base + id_stride * torch.arange(k_pooled.shape[1])
+    return O.topk_select(q_pooled, k_pooled, topk, scale, block_size=block_size, chunk_size=chunk_size,
+                         chunk_size_k=chunk_size_k, causal=causal, ex_win=ex_win, ex_sink=ex_sink,
+                         prog_excl=prog_excl, tf_mask=tf_mask, q_chunk_offset=q_chunk_offset,
+                         q_group_size=q_group_size, return_scores=return_scores, col_ids=cols)
+
+
+def merge_candidates(idx, scores, topk):
+    return O.merge_candidates(list(idx), list(scores), topk)
+
+
+def sel_fwd(q, kv, block_indices, block_size, chunk_size, scale, causal, group_size):
+    return O.selection_fwd(q, kv.k, kv.v, block_indices, block_size, chunk_size, scale, causal, group_size)
+
+
+def merge_partials(outs, lses):
+    out, lse = O.merge_partials(list(outs), list(lses))
+    return out.to(outs.dtype), lse
