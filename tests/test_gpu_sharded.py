@@ -45,8 +45,8 @@ def _run_rank(rank, world, port, ret):
         full = ops.topk(ops.pool_rows(q.to(dev), 64), ops.pool_rows(k.to(dev), 64), 8, 128 ** -0.5, 64, 100, 100, True,
                         q_chunk_offset=30, q_group_size=64)
         o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), full.cpu(), 64, 1, None, False, 64)
-        ok = bool(torch.equal(idx, full)) and (out.float().cpu() - o_ref).abs().max().item() < 2e-2 \\
-            and torch.allclose(lse.cpu(), l_ref, atol=2e-3) and _lib.device_status() == 0
+        ok = (bool(torch.equal(idx, full)) and (out.float().cpu() - o_ref).abs().max().item() < 2e-2
+              and torch.allclose(lse.cpu(), l_ref, atol=2e-3) and _lib.device_status() == 0)
         flags = [None] * world
         dist.all_gather_object(flags, ok)
         if rank == 0:
