@@ -61,20 +61,27 @@ class SelectionAttentionB200(torch.autograd.Function):
     def forward(ctx, q, k, v, block_indices, block_size, chunk_size, scale, causal, return_lse, group_size):
         if scale is None:
             scale = q.shape[-1] ** -0.5
+        # fp32 tensors are computed on bf16 operands with fp32 accumulation (the kernels are 16-bit;
+        # the reference's default for fp32 is TF32, also a reduced-precision product) and the results
+        # are returned in fp32.
+        io_dtype = q.dtype
+        if io_dtype == torch.float32:
+            q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
         kv = _ops.DenseKV(k, v)
         out, lse = _ops.sel_fwd(q, kv, block_indices, block_size, chunk_size, scale, causal, group_size)
         ctx.save_for_backward(q, k, v, block_indices, out, lse)
-        ctx.cfg = (block_size, chunk_size, scale, causal, group_size)
+        ctx.cfg = (block_size, chunk_size, scale, causal, group_size, io_dtype)
         ctx.mark_non_differentiable(lse)
+        out = out.to(io_dtype)
         return (out, lse) if return_lse else out
 
     @staticmethod
     def backward(ctx, d_out, *unused):
         q, k, v, block_indices, out, lse = ctx.saved_tensors
-        block_size, chunk_size, scale, causal, group_size = ctx.cfg
+        block_size, chunk_size, scale, causal, group_size, io_dtype = ctx.cfg
         dq, dk, dv = _ops.sel_bwd(q, _ops.DenseKV(k, v), block_indices, out, lse, d_out.to(q.dtype),
                                   block_size, chunk_size, scale, causal, group_size)
-        return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None, None, None
+        return dq.to(io_dtype), dk.to(io_dtype), dv.to(io_dtype), None, None, None, None, None, None, None
 
 
 def selection_attention(q, k, v, block_indices, block_count, block_size, chunk_size=1, scale=None,

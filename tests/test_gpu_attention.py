@@ -267,6 +267,27 @@ def test_facade_autograd_and_errors(dev):
         selection_attention(qd, kd, vd, ids.to(dev), 4, 64, variant="one-pass", group_size=64)
 
 
+def test_config1_shape_fp32_tensors(dev):
+    """B=1, H=12, D=128, fp32, one 1560-token frame of queries (frame 3) against 4 frames of keys
+    in 64-token blocks, top-16 per 64-query group, block-causal by frame, seed 0 - the reference's
+    CPU-runnable case.  fp32 tensors are computed on bf16 operands; compared with the fp32 oracle."""
+    from omnimem_b200.nsa.ops import parallel_nsa_topk, selection_attention
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 1560, 12, 128, generator=g)
+    k = torch.randn(1, 6240, 12, 128, generator=g)
+    v = torch.randn(1, 6240, 12, 128, generator=g)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    idx = parallel_nsa_topk(qd, ops.pool_rows(kd, 64), 16, 64, None, 1560, True, group_size=64, q_chunk_offset=3,
+                            allow_ragged=True)
+    out, lse = selection_attention(qd, kd, vd, idx, 16, 64, chunk_size=1, causal=False, return_lse=True, group_size=64,
+                                   allow_ragged=True)
+    assert out.dtype == torch.float32 and out.shape == q.shape
+    o_ref, l_ref = O.selection_fwd(q, k, v, idx.cpu(), 64, 1, None, False, 64)
+    assert_close_bf16(out, o_ref, "config 1 out (fp32 tensors, bf16 operands)", max_abs=3e-2, mean_abs=3e-3)
+    assert torch.allclose(lse.cpu(), l_ref, atol=3e-2)
+
+
 def test_torch_ops_namespace(dev):
     import omnimem_b200.torch_ops  # noqa: F401
     q, k, v, do, ids = _rand_case(30, 1, 128, 512, 2, 128, 4, 64, 64, 128, True)
