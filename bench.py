@@ -36,8 +36,8 @@ METRIC = "nsa_selection_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = ("config2: bf16 NSA selection fwd+bwd, B=1 H=12 D=128, Q=4680 (3 latent frames), "
             "KV=32760 (21 frames) in 64-token blocks, top-16 per 64-query group")
-# kernels launched by one step: pool(q), pool(k), score, select, fwd, index count/scan/scatter/sort, dq, dkv
-LAUNCHES_PER_STEP = 11
+# kernels launched by one step: pool(q), pool(k), score, select, fwd, inverted index, dq, dkv
+LAUNCHES_PER_STEP = 8
 
 
 def peaks():

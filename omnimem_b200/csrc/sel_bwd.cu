@@ -110,6 +110,75 @@ __global__ void inv_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __
   }
 }
 
+// The whole index of one (b, h) row in a single thread block when its NS counters fit in shared
+// memory: histogram and cursors in shared memory, scatter, then one thread per bucket sorts it.
+__global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int32_t* __restrict__ groups,
+                                                         int32_t* __restrict__ offsets) {
+  extern __shared__ int s_cnt[];                   // [NS]
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
+  const int64_t row = blockIdx.x;
+  const int NS = static_cast<int>(p.NS);
+  const int pairs = p.MG * p.T;
+  int32_t* o = offsets + row * (p.NS + 1);
+  int32_t* gr = groups + row * static_cast<int64_t>(pairs);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < NS; i += blockDim.x) s_cnt[i] = 0;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int pr = threadIdx.x; pr < pairs; pr += blockDim.x) {
+    int bucket;
+    if (pair_bucket(p, b, pr / p.T, h, pr % p.T, bucket)) atomicAdd(&s_cnt[bucket], 1);
+  }
+  __syncthreads();
+  for (int base = 0; base < NS; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int v = i < NS ? s_cnt[i] : 0;
+    int x = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = lane < nw ? warp_sums[lane] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, d);
+        if (lane >= d) w += y;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    const int excl = carry + (warp ? warp_sums[warp - 1] : 0) + x - v;
+    if (i < NS) { o[i] = excl; s_cnt[i] = excl; }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry_s = carry + warp_sums[nw - 1];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) o[NS] = carry_s;
+  for (int pr = threadIdx.x; pr < pairs; pr += blockDim.x) {
+    int bucket;
+    const int g = pr / p.T;
+    if (pair_bucket(p, b, g, h, pr % p.T, bucket)) gr[atomicAdd(&s_cnt[bucket], 1)] = g;
+  }
+  __syncthreads();                                   // scatter (global) visible to the block
+  for (int sidx = threadIdx.x; sidx < NS; sidx += blockDim.x) {
+    const int end = s_cnt[sidx];                     // cursor now points one past the bucket
+    const int beg = o[sidx];
+    for (int a = beg + 1; a < end; ++a) {
+      const int32_t v = gr[a];
+      int c = a - 1;
+      while (c >= beg && gr[c] > v) { gr[c + 1] = gr[c]; --c; }
+      gr[c + 1] = v;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------ dQ
 struct BwdParams {
   const char* q; int64_t q_sb, q_sm, q_sh;
@@ -585,8 +654,15 @@ int run_inverted_index(const IdxParams& ip, int32_t* groups, int32_t* offsets, i
     NSA_CUDA_OK(cudaMemsetAsync(offsets, 0, rows * sizeof(int32_t), stream));
     return NSA_OK;
   }
-  NSA_CUDA_OK(cudaMemsetAsync(counts, 0, rows * ip.NS * sizeof(int32_t), stream));
   const int64_t pairs = static_cast<int64_t>(ip.MG) * ip.T;
+  if (ip.NS * 4 <= 160 * 1024 && pairs <= 0x7fffffff && rows <= 0x7fffffff) {
+    const size_t smem = static_cast<size_t>(ip.NS) * 4;
+    NSA_CUDA_OK(cudaFuncSetAttribute(inv_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    inv_fused_kernel<<<static_cast<unsigned>(rows), 1024, smem, stream>>>(ip, groups, offsets);
+    NSA_LAUNCH_OK("inv_fused_kernel");
+    return NSA_OK;
+  }
+  NSA_CUDA_OK(cudaMemsetAsync(counts, 0, rows * ip.NS * sizeof(int32_t), stream));
   const dim3 grid(static_cast<unsigned>(cdiv64(pairs, kIdxThreads)), ip.H, ip.B);
   if (pairs > 0) {
     inv_pass_kernel<false><<<grid, kIdxThreads, 0, stream>>>(ip, counts, groups);

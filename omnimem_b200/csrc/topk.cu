@@ -351,6 +351,90 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
   }
 }
 
+// Rows with at most 32*ITEMS candidates: one warp per row, candidates in registers, no block-wide
+// barrier.  Same keys and order as select_kernel.
+template <int ITEMS, bool MERGE>
+__global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (row >= rows) return;
+  RowMask rm{};
+  const float* srow;
+  if (MERGE) {
+    srow = p.scores + row * p.seg_len;
+  } else {
+    const int h = static_cast<int>(row % p.H);
+    const int64_t bg = row / p.H;
+    const int g = static_cast<int>(bg % p.MG);
+    const int64_t b = bg / p.MG;
+    rm = make_row_mask(p.mask, g);
+    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC;
+  }
+  unsigned long long keys[ITEMS];
+  unsigned long long local = 0ull;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int64_t c = lane + 32 * i;
+    unsigned long long k = 0ull;
+    if (c < p.NC) {
+      if (MERGE) {
+        const int64_t off = (c / p.seg_len) * p.seg_stride + (c % p.seg_len);
+        const int id = p.cand_ids[row * p.seg_len + off];
+        k = id < 0 ? 0ull : pack_key(srow[off], id);
+      } else {
+        const int bid = p.mask.id_base + static_cast<int>(c) * p.mask.id_stride;
+        k = visible(p.mask, rm, bid) ? pack_key(srow[c], bid) : 0ull;
+      }
+    }
+    keys[i] = k;
+    local = k > local ? k : local;
+  }
+  int32_t* oi = p.out_idx + row * p.topk;
+  float* os = p.out_scores ? p.out_scores + row * p.topk : nullptr;
+  int r = 0;
+  for (; r < p.topk; ++r) {
+    unsigned long long best = local;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+      const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, d);
+      best = o > best ? o : best;
+    }
+    if (best == 0ull) break;
+    if (lane == 0) {
+      oi[r] = key_id(best);
+      if (os) os[r] = key_score(best);
+    }
+    if (local == best) {            // keys are unique: exactly one lane owns the winner
+      local = 0ull;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        if (keys[i] == best) keys[i] = 0ull;
+        local = keys[i] > local ? keys[i] : local;
+      }
+    }
+  }
+  for (int i = r + lane; i < p.topk; i += 32) {
+    oi[i] = -1;
+    if (os) os[i] = -INFINITY;
+  }
+}
+
+template <bool MERGE>
+int launch_select(const SelectParams& sel, int64_t rows, cudaStream_t s) {
+  const unsigned blocks4 = static_cast<unsigned>(cdiv64(rows, 4));
+  if (sel.NC <= 512) {
+    select_warp_kernel<16, MERGE><<<blocks4, 128, 0, s>>>(sel, rows);
+  } else if (sel.NC <= 1024) {
+    select_warp_kernel<32, MERGE><<<blocks4, 128, 0, s>>>(sel, rows);
+  } else {
+    const size_t ksmem = sel.NC * 8 <= 64 * 1024 ? static_cast<size_t>(sel.NC) * 8 : 0;
+    NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<MERGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    select_kernel<MERGE><<<static_cast<unsigned>(rows), 128, ksmem, s>>>(sel);
+  }
+  NSA_LAUNCH_OK("select kernel");
+  return NSA_OK;
+}
+
 int fill_mask(const nsa_topk_mask* in, int MG, int64_t NC_global, Mask* m) {
   NSA_REQUIRE(in != nullptr, NSA_ERR_INVALID, "topk: mask is null");
   NSA_REQUIRE(in->block_size > 0 && in->chunk_size > 0 && in->chunk_size_k > 0 && in->q_group_size > 0,
@@ -418,11 +502,7 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
   sel.scores = scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
   sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
   sel.mask = m;
-  const size_t ksmem = NC * 8 <= 64 * 1024 ? static_cast<size_t>(NC) * 8 : 0;
-  NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-  const int64_t rows = static_cast<int64_t>(B) * MG * H;
-  select_kernel<false><<<static_cast<unsigned>(rows), 128, ksmem, s>>>(sel);
-  NSA_LAUNCH_OK("select_kernel");
+  return launch_select<false>(sel, static_cast<int64_t>(B) * MG * H, s);
   return NSA_OK;
 }
 
@@ -541,11 +621,7 @@ extern "C" int nsa_merge_candidates(const int32_t* idx, const float* scores, int
   SelectParams sel{};
   sel.scores = scores; sel.cand_ids = idx; sel.NC = static_cast<int64_t>(R) * T; sel.MG = 1; sel.H = 1;
   sel.seg_len = T; sel.seg_stride = rows * T; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
-  const size_t ksmem = sel.NC * 8 <= 64 * 1024 ? static_cast<size_t>(sel.NC) * 8 : 0;
-  NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-  select_kernel<true><<<static_cast<unsigned>(rows), 128, ksmem, static_cast<cudaStream_t>(stream)>>>(sel);
-  NSA_LAUNCH_OK("select_kernel<merge>");
-  return NSA_OK;
+  return launch_select<true>(sel, rows, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

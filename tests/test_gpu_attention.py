@@ -202,6 +202,19 @@ def test_inverted_index(dev):
                 assert groups[b, h, lo:hi].tolist() == g_ref[b, h, lo:hi].tolist()   # ascending inside a bucket
 
 
+def test_inverted_index_many_blocks(dev):
+    """More blocks than one thread block can count in shared memory: the multi-kernel path."""
+    g = torch.Generator().manual_seed(31)
+    NS = 45000
+    ids = torch.randint(-1, NS, (1, 40, 2, 6), generator=g, dtype=torch.int32)
+    ids[0, :, :, 0] = 7                                     # one long bucket
+    groups, offsets = _ops().inverted_index(ids.to(dev), NS, 64, 1, False, 64)
+    g_ref, o_ref = O.inverted_index(ids, NS, 64, 1, False, 64)
+    assert torch.equal(offsets.cpu(), o_ref)
+    n = int(o_ref[0, 0, -1])
+    assert torch.equal(groups.cpu()[:, :, :n], g_ref[:, :, :n])
+
+
 def test_pointer_table_source(dev):
     g = torch.Generator().manual_seed(27)
     B, M, N, H, D, bs, G, T = 1, 128, 512, 2, 128, 64, 64, 3
