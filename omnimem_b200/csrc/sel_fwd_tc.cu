@@ -2,11 +2,13 @@
 // the page geometry: bf16, D = 128, 64-token blocks, query groups of up to 64 rows, K/V read
 // from a dense [B,N,H,D] tensor or straight from the fixed-page pool through the block table.
 //
-// One thread block per (batch, query group, head), six warps:
-//   warp 4  TMA producer: Q once, then per step the K and V tiles of TWO selected blocks
-//           (128 keys) into two-stage rings, coordinates taken from the compacted block list;
-//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into a double-buffered TMEM tile,
-//           then O += P V (M=128, N=128, K=128) with P read from TMEM;
+// One thread block per (batch, query group, head), TWO thread blocks resident per SM (96 KiB of
+// tiles and 256 TMEM columns each), so that the load / list-building prologue and the
+// merge-and-store epilogue of one block run beside the main loop of the other.  Roles:
+//   warp 4  TMA producer: Q once, then per step the K tile of TWO selected blocks (128 keys),
+//           coordinates taken from the compacted block list;   warp 6: the same for V;
+//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into TMEM, then, once the softmax
+//           warps have written P over the score columns, O += P V with P read from TMEM;
 //   warps 0-3  softmax: one TMEM lane (matrix row) per thread.
 // The 64 query rows are loaded twice, into rows 0-63 and 64-127 of the A tile: rows 0-63 do
 // the online softmax over the EVEN block of each step (S columns 0-63), rows 64-127 over the
@@ -77,13 +79,13 @@ using namespace tc;
 constexpr int kTcThreads = 224;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTileBytes = 32768;        // 128 rows x 256 bytes, as two 64-column halves of 16 KiB
-constexpr uint32_t kSmemTiles = 5 * kTileBytes;   // Q, K x2, V x2
+constexpr uint32_t kSmemTiles = 3 * kTileBytes;   // Q, K, V
 constexpr float kRescaleGap = 8.f;            // log2 units
+constexpr uint32_t kTmemCols = 256;           // per thread block; two blocks share an SM's 512
 
 // TMEM columns
-constexpr uint32_t kColS = 0;      // 2 x 128
-constexpr uint32_t kColP = 256;    // 2 x 64 (bf16 pairs)
-constexpr uint32_t kColO = 384;    // 128
+constexpr uint32_t kColS = 0;      // 128 fp32 score columns; P (64 columns of bf16 pairs) is written over them
+constexpr uint32_t kColO = 128;    // 128
 
 struct TcFwdParams {
   const int32_t* ids;
@@ -100,17 +102,17 @@ struct TcFwdParams {
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const TcFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = tiles;
-  uint8_t* sK = tiles + kTileBytes;           // 2 stages
-  uint8_t* sV = tiles + 3 * kTileBytes;       // 2 stages
-  float* stage = reinterpret_cast<float*>(tiles + kTileBytes);   // epilogue: 128 x 129 floats over the K/V rings
+  uint8_t* sK = tiles + kTileBytes;
+  uint8_t* sV = tiles + 2 * kTileBytes;
+  float* stage = reinterpret_cast<float*>(tiles);   // epilogue: 128 x 129 floats over the dead Q/K/V tiles
 
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full[2], pv_done, o_final;
+  __shared__ uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done, o_final;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
   __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
@@ -123,74 +125,68 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
 
   if (threadIdx.x == 0) TRACE(1, 0);
-  // ---- barriers and TMEM first, so that they overlap the loads of the block ids below
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
-      mbar_init(&p_full[i], 128);
-    }
+    mbar_init(&k_full, 1); mbar_init(&k_empty, 1);
+    mbar_init(&v_full, 1); mbar_init(&v_empty, 1);
+    mbar_init(&s_full, 1); mbar_init(&p_full, 128);
     mbar_init(&pv_done, 1);
     mbar_init(&o_final, 1);
     fence_barrier_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
   if (warp == 4 && lane == 0) {
+    // Q does not depend on the block list: start its copy at once (its barrier is initialised by
+    // this same thread only when threadIdx.x == 0 is, so the copy is issued after the sync below)
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
-  // ---- list of the selected blocks: TMA row coordinate and visible tokens of each slot
-  for (int t = threadIdx.x; t < p.T; t += blockDim.x) {
-    const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
-    int row = -1, nv = 0;
-    if (bid >= 0) {
-      const int64_t t0 = static_cast<int64_t>(bid) * 64;
-      if (t0 < p.n_tokens) {
-        int64_t n = p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64;
-        bool ok = true;
-        if (p.causal) {
-          if (t0 / p.chunk_size > q_chunk) ok = false;
-          const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - t0;
-          if (lim < n) n = lim;
-          if (n <= 0) ok = false;
-        }
-        if (ok) {
-          if (p.paged) {
-            const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
-            if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
-          } else {
-            row = static_cast<int>(t0);
-            nv = static_cast<int>(n);
+  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by one warp
+  if (warp == 1) {
+    int base = 0;
+    for (int t0 = 0; t0 < p.T; t0 += 32) {
+      const int t = t0 + lane;
+      int row = -1, nv = 0;
+      if (t < p.T) {
+        const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
+        if (bid >= 0) {
+          const int64_t tok0 = static_cast<int64_t>(bid) * 64;
+          if (tok0 < p.n_tokens) {
+            int64_t n = p.n_tokens - tok0 < 64 ? p.n_tokens - tok0 : 64;
+            bool ok = true;
+            if (p.causal) {
+              if (tok0 / p.chunk_size > q_chunk) ok = false;
+              const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - tok0;
+              if (lim < n) n = lim;
+              if (n <= 0) ok = false;
+            }
+            if (ok) {
+              if (p.paged) {
+                const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
+                if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
+              } else {
+                row = static_cast<int>(tok0);
+                nv = static_cast<int>(n);
+              }
+            }
           }
         }
       }
+      const unsigned live = __ballot_sync(0xffffffffu, nv > 0);
+      if (nv > 0) {
+        const int pos = base + __popc(live & ((1u << lane) - 1u));
+        s_row[pos] = row;
+        s_nvis[pos] = nv;
+      }
+      base += __popc(live);
     }
-    s_row[t] = row;
-    s_nvis[t] = nv;
+    if (lane == 0) s_nb = base;
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_base_s;
   volatile int* abort = &s_abort;
-  // Q does not depend on the list: start its copy while thread 0 compacts the list
-  if (warp == 4 && lane == 0) {
-    mbar_expect_tx(&q_full, kTileBytes);
-    for (int dh = 0; dh < 2; ++dh)
-      for (int dup = 0; dup < 2; ++dup)
-        tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
-  }
-  if (threadIdx.x == 0) {
-    int nb = 0;
-    for (int t = 0; t < p.T; ++t) {
-      const int row = s_row[t], nv = s_nvis[t];
-      if (nv > 0) { s_row[nb] = row; s_nvis[nb] = nv; ++nb; }
-    }
-    s_nb = nb;
-  }
-  __syncthreads();
   const int nb = s_nb;
   char* out_row0 = p.out + (b * p.o_sb + m0 * p.o_sm + h * p.o_sh) * 2;
   float* lse_row0 = p.lse + (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
@@ -215,105 +211,93 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   };
 
   if (nb == 0) {
-    // nothing visible: O = 0, LSE = -inf (the Q copy already in flight is awaited before leaving)
+    // nothing visible: O = 0, LSE = -inf
     for (int i = threadIdx.x; i < n_q * 16; i += blockDim.x)
       *reinterpret_cast<uint4*>(out_row0 + (i >> 4) * p.o_sm * 2 + (i & 15) * 16) = make_uint4(0, 0, 0, 0);
     for (int r = threadIdx.x; r < n_q; r += blockDim.x) lse_row0[r] = -INFINITY;
-    if (warp == 4 && lane == 0) mbar_wait(&q_full, 0, abort);
   } else if (warp == 4 || warp == 6) {
-    // ======================= TMA producers: warp 4 feeds the K ring, warp 6 the V ring =======================
+    // ======================= TMA producers: warp 4 loads Q and the K tiles, warp 6 the V tiles =======================
     if (lane == 0) {
       const bool isK = warp == 4;
-      uint64_t* full = isK ? k_full : v_full;
-      uint64_t* empty = isK ? k_empty : v_empty;
-      uint8_t* ring = isK ? sK : sV;
+      uint64_t* full = isK ? &k_full : &v_full;
+      uint64_t* empty = isK ? &k_empty : &v_empty;
+      uint8_t* dst = isK ? sK : sV;
       const CUtensorMap* map = isK ? &mapK : &mapV;
+      if (isK) {
+        mbar_expect_tx(&q_full, kTileBytes);
+        for (int dh = 0; dh < 2; ++dh)
+          for (int dup = 0; dup < 2; ++dup)
+            tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
+      }
       int t = 0;
       for (; t < NT; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
         const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort)) break;
-        load_tile(ring + s * kTileBytes, map, re, ro, &full[s]);
+        if (!mbar_wait(empty, (t & 1) ^ 1, abort)) break;
+        load_tile(dst, map, re, ro, full);
       }
       if (*abort) {
-        // the other roles have stopped consuming: wait (bounded) for what is still in flight
-        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) mbar_wait(&full[u & 1], (u >> 1) & 1, abort);
+        // the other roles have stopped consuming: wait (bounded) for the copy still in flight
+        if (t > 0) mbar_wait(full, (t - 1) & 1, abort);
         if (isK) mbar_wait(&q_full, 0, abort);
       }
     }
   } else if (warp == 5) {
     // ======================= MMA issuer =======================
+    // Per step: S = [Q;Q] K^T, (softmax writes P over S), O += P V.  The next S overwrites P, so
+    // it is issued only after the P V product that reads it has completed.
     if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
       const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
-      auto issue_pv = [&](int u) -> bool {
-        const int s = u & 1, ph = (u >> 1) & 1;
-        if (!mbar_wait(&v_full[s], ph, abort)) return false;
-        TRACE(0, 8 + (u + 1) * 8 + 3);
-        if (!mbar_wait(&p_full[s], ph, abort)) return false;
-        TRACE(0, 8 + (u + 1) * 8 + 4);
-        tc_fence_after();
-        const uint64_t dV = smem_desc(smem_u32(sV + s * kTileBytes), 16384, 1024);
-        const uint32_t tP = tm + kColP + s * 64;
-        const uint32_t acc0 = u > 0 ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tm + kColO, tP + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, kk > 0 ? 1u : acc0);
-        umma_commit(&v_empty[s]);
-        umma_commit(&pv_done);
-        return true;
-      };
+      const uint64_t dK = smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t dV = smem_desc(smem_u32(sV), 16384, 1024);
       bool ok = mbar_wait(&q_full, 0, abort);
       TRACE(0, 0);
       for (int t = 0; ok && t < NT; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort)) { ok = false; break; }
+        const uint32_t ph = t & 1;
+        if (!mbar_wait(&k_full, ph, abort)) { ok = false; break; }
+        if (t > 0 && !mbar_wait(&pv_done, ph ^ 1, abort)) { ok = false; break; }
         TRACE(0, 8 + t * 8 + 0);
-        if (!mbar_wait(&s_free[s], ph ^ 1, abort)) { ok = false; break; }
-        TRACE(0, 8 + t * 8 + 1);
         tc_fence_after();
-        const uint64_t dK = smem_desc(smem_u32(sK + s * kTileBytes), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColS + s * 128, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+          umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
                   desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-        umma_commit(&s_full[s]);
-        umma_commit(&k_empty[s]);
+        umma_commit(&s_full);
+        umma_commit(&k_empty);
+        TRACE(0, 8 + t * 8 + 1);
+        if (!mbar_wait(&v_full, ph, abort)) { ok = false; break; }
+        if (!mbar_wait(&p_full, ph, abort)) { ok = false; break; }
         TRACE(0, 8 + t * 8 + 2);
-        if (t > 0) ok = issue_pv(t - 1);
-        TRACE(0, 8 + t * 8 + 5);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&v_empty);
+        umma_commit(&pv_done);
+        if (t == NT - 1) umma_commit(&o_final);
+        TRACE(0, 8 + t * 8 + 3);
       }
-      if (ok && issue_pv(NT - 1)) umma_commit(&o_final);
     }
   } else {
     // ======================= softmax (warps 0-3), one matrix row per thread =======================
     const int half = warp >> 1;                       // 0: even block of each step, 1: odd block
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    {
-      uint32_t z[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) z[j] = 0u;
-      tmem_st32_nowait(tm + lane_base + kColP + (1 - half) * 32, z);
-      tmem_st32_nowait(tm + lane_base + kColP + 64 + (1 - half) * 32, z);
-      tmem_st_wait();
-    }
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int t = 0; t < NT; ++t) {
-      const int s = t & 1, ph = (t >> 1) & 1;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], ph, abort));
+      // s_full is committed after the previous step's P V was issued, so its completion also
+      // means that O is quiescent and may be rescaled below
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full, t & 1, abort));
       if (!ok) break;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
       tc_fence_after();
       uint32_t x0[32], x1[32];
-      tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64, x0);
-      tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64 + 32, x1);
+      tmem_ld32_nowait(tm + lane_base + kColS + half * 64, x0);
+      tmem_ld32_nowait(tm + lane_base + kColS + half * 64 + 32, x1);
       tmem_ld_wait();
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
-      tc_fence_before();
-      mbar_arrive(&s_free[s]);
       const int blk = 2 * t + half;
       const int nv = blk < nb ? s_nvis[blk] : 0;
       float tmax = -INFINITY;
@@ -330,9 +314,6 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? tmax : m_ref;
         if (t > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (t - 1) & 1, abort));
-          if (!ok) break;
-          tc_fence_after();
           const float sc = need ? fast_exp2(m_ref - m_new) : 1.f;
           l_sum *= sc;
 #pragma unroll
@@ -344,7 +325,6 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * sc);
             tmem_st32_nowait(tm + lane_base + kColO + c * 32, o);
           }
-          tmem_st_wait();
         }
         m_ref = m_new;
       }
@@ -363,15 +343,18 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       }
       l_sum += rs;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 5);
-      tmem_st32_nowait(tm + lane_base + kColP + s * 64 + half * 32, pk);
+      // P over the score columns: this row's 64 probabilities in its own half, zeros in the other
+      tmem_st32_nowait(tm + lane_base + kColS + half * 32, pk);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) pk[j] = 0u;
+      tmem_st32_nowait(tm + lane_base + kColS + (1 - half) * 32, pk);
       tmem_st_wait();
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 6);
       tc_fence_before();
-      mbar_arrive(&p_full[s]);
+      mbar_arrive(&p_full);
     }
     if (threadIdx.x == 0) TRACE(1, 2);
-    // ---- epilogue: wait for the last P V, merge the two halves, normalise, store.  (pv_done is
-    // only polled when a rescale needs it, so its parity is ambiguous here; o_final is not.)
+    // ---- epilogue: wait for the last P V, merge the two halves, normalise, store
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_final, 0, abort));
     if (threadIdx.x == 0) TRACE(1, 3);
     if (ok) {
@@ -418,7 +401,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   if (threadIdx.x == 0) TRACE(1, 4);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tm, 512);
+  if (warp == 0) tmem_dealloc(tm, kTmemCols);
   if (threadIdx.x == 0) TRACE(1, 5);
   if (threadIdx.x == 0 && s_abort) atomicExch(p.status ? p.status : &g_device_status, NSA_ERR_CUDA);
 }
@@ -512,6 +495,8 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   p.status = status;
   const size_t smem = kSmemTiles + 1024;
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   static_cast<int>(cudaSharedmemCarveoutMaxShared)));
   sel_fwd_tc_kernel<<<dim3(static_cast<unsigned>(MG), H, B), kTcThreads, smem, stream>>>(mapQ, mapK, mapV, p);
   NSA_LAUNCH_OK("sel_fwd_tc_kernel");
   *launched = true;
