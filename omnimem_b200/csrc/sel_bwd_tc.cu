@@ -23,18 +23,26 @@ namespace nsa {
 
 int device_status_address(int32_t** out);
 
+#ifdef NSA_TC_TRACE
+// Debug build only: clock64 stamps of thread block (0,0,0); [0][..] MMA issuer, [1][..] row thread 0.
+__device__ long long g_trace_dq[4][512];
+#define TRACE(role, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512) g_trace_dq[role][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 224;
-constexpr int kMaxSlots = 256;
+constexpr int kThreads = 288;
+constexpr int kMaxSlots = 128;
+constexpr int kStagesK = 3;
 constexpr uint32_t kTileBytes = 32768;
-constexpr uint32_t kSmemTiles = 6 * kTileBytes;   // Q, dO, K x2, V x2
+constexpr uint32_t kSmemTiles = 7 * kTileBytes;   // Q, dO, K x3, V x2
 
-constexpr uint32_t kColS = 0;      // 128
-constexpr uint32_t kColDP = 128;   // 128
-constexpr uint32_t kColDS = 256;   // 64 (bf16 pairs)
+constexpr uint32_t kColS = 0;      // 2 x 128: scores of even / odd steps; dS (64 columns of bf16 pairs) is written over them
+constexpr uint32_t kColDP = 256;   // 128
 constexpr uint32_t kColDQ = 384;   // 128
 
 struct TcDqParams {
@@ -62,13 +70,14 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   uint8_t* sQ = tiles;
   uint8_t* sDO = tiles + kTileBytes;
   uint8_t* sK = tiles + 2 * kTileBytes;
-  uint8_t* sV = tiles + 4 * kTileBytes;
+  uint8_t* sV = tiles + 5 * kTileBytes;
   float* stage = reinterpret_cast<float*>(tiles + 2 * kTileBytes);   // epilogue: 128 x 129 floats over the rings
 
-  __shared__ uint64_t qdo_full, k_full[2], k_empty[2], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full, dq_final;
+  __shared__ uint64_t qdo_full, k_full[kStagesK], k_empty[kStagesK], v_full[2], v_empty[2], s_full[2], s_free[2], ds_full[2], dp_full, dp_free, dq_final;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
   __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
+  __shared__ float s_delta[128];
 
   const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,16 +85,17 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
 
+  if (threadIdx.x == 0) TRACE(1, 0);
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&qdo_full, 1);
+    for (int i = 0; i < kStagesK; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 1); mbar_init(&ds_full[i], 128);
     }
-    mbar_init(&sdp_full, 1);
-    mbar_init(&sdp_free, 128);
-    mbar_init(&ds_full, 128);
+    mbar_init(&dp_full, 1);
+    mbar_init(&dp_free, 128);
     mbar_init(&dq_final, 1);
     fence_barrier_init();
   }
@@ -93,58 +103,66 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapDO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
-  for (int t = threadIdx.x; t < p.T; t += blockDim.x) {
-    const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
-    int row = -1, nv = 0;
-    if (bid >= 0) {
-      const int64_t t0 = static_cast<int64_t>(bid) * 64;
-      if (t0 < p.n_tokens) {
-        int64_t n = p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64;
-        bool ok = true;
-        if (p.causal) {
-          if (t0 / p.chunk_size > q_chunk) ok = false;
-          const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - t0;
-          if (lim < n) n = lim;
-          if (n <= 0) ok = false;
-        }
-        if (ok) {
-          if (p.paged) {
-            const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
-            if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
-          } else {
-            row = static_cast<int>(t0);
-            nv = static_cast<int>(n);
+  // ---- row threads start the loads for delta = sum_d O dO right away: the two threads that own
+  // a query row (rows r and 64 + r of the duplicated tiles) each take one 64-column half
+  const int half = (warp >> 1) & 1;
+  const int qrow = threadIdx.x & 63;
+  uint4 ro_[8], rd_[8];
+  if (warp < 4 && qrow < n_q) {
+    const uint4* orow = reinterpret_cast<const uint4*>(p.o + (b * p.o_sb + (m0 + qrow) * p.o_sm + h * p.o_sh) * 2) + half * 8;
+    const uint4* drow = reinterpret_cast<const uint4*>(p.dO + (b * p.do_sb + (m0 + qrow) * p.do_sm + h * p.do_sh) * 2) + half * 8;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) { ro_[c] = orow[c]; rd_[c] = drow[c]; }
+  }
+  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by warp 4
+  if (warp == 4) {
+    int base = 0;
+    for (int t0 = 0; t0 < p.T; t0 += 32) {
+      const int t = t0 + lane;
+      int row = -1, nv = 0;
+      if (t < p.T) {
+        const int bid = p.ids[b * p.i_sb + g * p.i_sg + h * p.i_sh + t * p.i_st];
+        if (bid >= 0) {
+          const int64_t tok0 = static_cast<int64_t>(bid) * 64;
+          if (tok0 < p.n_tokens) {
+            int64_t n = p.n_tokens - tok0 < 64 ? p.n_tokens - tok0 : 64;
+            bool ok = true;
+            if (p.causal) {
+              if (tok0 / p.chunk_size > q_chunk) ok = false;
+              const int64_t lim = static_cast<int64_t>(q_chunk + 1) * p.chunk_size - tok0;
+              if (lim < n) n = lim;
+              if (n <= 0) ok = false;
+            }
+            if (ok) {
+              if (p.paged) {
+                const int page = bid < p.max_blocks ? p.block_table[static_cast<int64_t>(h) * p.max_blocks + bid] : -1;
+                if (page >= 0) { row = page * 64; nv = static_cast<int>(n); }
+              } else {
+                row = static_cast<int>(tok0);
+                nv = static_cast<int>(n);
+              }
+            }
           }
         }
       }
+      const unsigned live = __ballot_sync(0xffffffffu, nv > 0);
+      if (nv > 0) {
+        const int pos = base + __popc(live & ((1u << lane) - 1u));
+        s_row[pos] = row;
+        s_nvis[pos] = nv;
+      }
+      base += __popc(live);
     }
-    s_row[t] = row;
-    s_nvis[t] = nv;
+    if (lane == 0) s_nb = base;
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_base_s;
   volatile int* abort = &s_abort;
-  if (warp == 4 && lane == 0) {
-    mbar_expect_tx(&qdo_full, 2 * kTileBytes);
-    for (int dh = 0; dh < 2; ++dh)
-      for (int dup = 0; dup < 2; ++dup) {
-        tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
-        tma_load_4d(sDO + dh * 16384 + dup * 8192, &mapDO, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
-      }
-  }
-  if (threadIdx.x == 0) {
-    int nb = 0;
-    for (int t = 0; t < p.T; ++t) {
-      const int row = s_row[t], nv = s_nvis[t];
-      if (nv > 0) { s_row[nb] = row; s_nvis[nb] = nv; ++nb; }
-    }
-    s_nb = nb;
-  }
-  __syncthreads();
   const int nb = s_nb;
   const int NT = (nb + 1) >> 1;
+  if (threadIdx.x == 0) TRACE(1, 1);
   char* dq_row0 = p.dq + (b * p.dq_sb + m0 * p.dq_sm + h * p.dq_sh) * 2;
   const int64_t bhm = (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
 
@@ -171,70 +189,105 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       uint64_t* empty = isK ? k_empty : v_empty;
       uint8_t* ring = isK ? sK : sV;
       const CUtensorMap* map = isK ? &mapK : &mapV;
+      const int ns = isK ? kStagesK : 2;
+      if (isK) {
+        mbar_expect_tx(&qdo_full, 2 * kTileBytes);
+        for (int dh = 0; dh < 2; ++dh)
+          for (int dup = 0; dup < 2; ++dup) {
+            tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
+            tma_load_4d(sDO + dh * 16384 + dup * 8192, &mapDO, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
+          }
+      }
       int t = 0;
       for (; t < NT; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
+        const int s = t % ns, ph = (t / ns) & 1;
         const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
         if (!mbar_wait(&empty[s], ph ^ 1, abort)) break;
+        TRACE(isK ? 2 : 3, t);
         load_tile(ring + s * kTileBytes, map, re, ro, &full[s]);
       }
       if (*abort || nb == 0) {
-        for (int u = (t > 1 ? t - 2 : 0); u < t && u < NT; ++u) mbar_wait(&full[u & 1], (u >> 1) & 1, abort);
+        // the other roles have stopped (or never started) consuming: wait (bounded) for the copies in flight
+        for (int u = (t > ns ? t - ns : 0); u < t && u < NT; ++u) mbar_wait(&full[u % ns], (u / ns) & 1, abort);
         if (isK) mbar_wait(&qdo_full, 0, abort);
       }
     }
-  } else if (warp == 5) {
-    // ======================= MMA issuer =======================
+  } else if (warp == 5 || warp == 7 || warp == 8) {
+    // ======================= MMA issuers =======================
+    // Three issuing threads, one per product, so that the tensor pipe is fed while each of them
+    // sits in its own barrier waits: warp 5 issues S(t) (double-buffered, reused once dQ(t-2) has
+    // read the dS written over it), warp 7 issues dP(t) as soon as the row threads have read
+    // dP(t-1), warp 8 issues dQ(t) when dS(t) is in TMEM.  A K tile is held from S(t) to dQ(t),
+    // hence the three-stage K ring.
     if (lane == 0 && nb > 0) {
       constexpr uint32_t idesc_kk = instr_desc_bf16(128, 128, 0, 0);   // both operands K-major
       constexpr uint32_t idesc_mn = instr_desc_bf16(128, 128, 0, 1);   // B read MN-major
-      const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024), dDO = smem_desc(smem_u32(sDO), 16, 1024);
-      bool ok = mbar_wait(&qdo_full, 0, abort);
-      for (int t = 0; ok && t < NT; ++t) {
-        const int s = t & 1, ph = (t >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort)) { ok = false; break; }
-        if (!mbar_wait(&v_full[s], ph, abort)) { ok = false; break; }
-        if (!mbar_wait(&sdp_free, (t & 1) ^ 1, abort)) { ok = false; break; }   // S / dP of step t-1 were read
-        tc_fence_after();
-        const uint32_t aK = smem_u32(sK + s * kTileBytes);
-        const uint64_t dK = smem_desc(aK, 16, 1024), dV = smem_desc(smem_u32(sV + s * kTileBytes), 16, 1024);
-        const uint64_t dKmn = smem_desc(aK, 16384, 1024);
+      if (warp == 5) {
+        const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
+        bool ok = mbar_wait(&qdo_full, 0, abort);
+        TRACE(0, 0);
+        for (int t = 0; ok && t < NT; ++t) {
+          const int s = t & 1, ks = t % kStagesK;
+          if (!mbar_wait(&k_full[ks], (t / kStagesK) & 1, abort)) break;
+          if (t >= 2 && !mbar_wait(&s_free[s], ((t - 2) >> 1) & 1, abort)) break;      // dQ(t-2) done
+          tc_fence_after();
+          TRACE(0, 8 + t * 8 + 0);
+          const uint64_t dK = smem_desc(smem_u32(sK + ks * kTileBytes), 16, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tm + kColS, desc_advance(dQ, off), desc_advance(dK, off), idesc_kk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            umma_ss(tm + kColS + s * 128, desc_advance(dQ, off), desc_advance(dK, off), idesc_kk, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[s]);
+          TRACE(0, 8 + t * 8 + 1);
         }
+      } else if (warp == 7) {
+        const uint64_t dDO = smem_desc(smem_u32(sDO), 16, 1024);
+        bool ok = mbar_wait(&qdo_full, 0, abort);
+        for (int t = 0; ok && t < NT; ++t) {
+          const int s = t & 1;
+          if (!mbar_wait(&v_full[s], (t >> 1) & 1, abort)) break;
+          if (t >= 1 && !mbar_wait(&dp_free, (t - 1) & 1, abort)) break;                  // dP(t-1) has been read
+          tc_fence_after();
+          TRACE(0, 8 + t * 8 + 2);
+          const uint64_t dV = smem_desc(smem_u32(sV + s * kTileBytes), 16, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_ss(tm + kColDP, desc_advance(dDO, off), desc_advance(dV, off), idesc_kk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            umma_ss(tm + kColDP, desc_advance(dDO, off), desc_advance(dV, off), idesc_kk, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&dp_full);
+          umma_commit(&v_empty[s]);
+          TRACE(0, 8 + t * 8 + 3);
         }
-        umma_commit(&sdp_full);
-        umma_commit(&v_empty[s]);
-        if (!mbar_wait(&ds_full, t & 1, abort)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t acc0 = t > 0 ? 1u : 0u;
+      } else {
+        for (int t = 0; t < NT; ++t) {
+          const int s = t & 1, ks = t % kStagesK;
+          if (!mbar_wait(&ds_full[s], (t >> 1) & 1, abort)) break;
+          tc_fence_after();
+          TRACE(0, 8 + t * 8 + 4);
+          const uint64_t dKmn = smem_desc(smem_u32(sK + ks * kTileBytes), 16384, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tm + kColDQ, tm + kColDS + kk * 8, desc_advance(dKmn, kk * 2048), idesc_mn, kk > 0 ? 1u : acc0);
-        umma_commit(&k_empty[s]);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tm + kColDQ, tm + kColS + s * 128 + kk * 8, desc_advance(dKmn, kk * 2048), idesc_mn,
+                    (t > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&k_empty[ks]);
+          umma_commit(&s_free[s]);
+          if (t == NT - 1) umma_commit(&dq_final);
+          TRACE(0, 8 + t * 8 + 5);
+        }
       }
-      if (ok) umma_commit(&dq_final);
     }
   } else if (warp < 4) {
     // ======================= per-row math (warps 0-3) =======================
-    const int half = warp >> 1;
-    const int qrow = threadIdx.x & 63;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    // delta = sum_d O dO and LSE of this thread's query row (both halves hold the same row)
+    // delta = sum_d O dO of this thread's query row: each of the row's two threads reduces the half
+    // it loaded at the top of the kernel, the halves meet in shared memory
     float delta = 0.f, lse2 = INFINITY;
     if (qrow < n_q) {
-      const uint4* orow = reinterpret_cast<const uint4*>(p.o + (b * p.o_sb + (m0 + qrow) * p.o_sm + h * p.o_sh) * 2);
-      const uint4* drow = reinterpret_cast<const uint4*>(p.dO + (b * p.do_sb + (m0 + qrow) * p.do_sm + h * p.do_sh) * 2);
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        const uint4 a = orow[c], d = drow[c];
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t aw[4] = {ro_[c].x, ro_[c].y, ro_[c].z, ro_[c].w}, dw[4] = {rd_[c].x, rd_[c].y, rd_[c].z, rd_[c].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 x = unpack2<__nv_bfloat16>(aw[e]), y = unpack2<__nv_bfloat16>(dw[e]);
@@ -242,8 +295,11 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
       }
       lse2 = p.lse[bhm + qrow] * kLog2e;
-      if (half == 0) p.delta[bhm + qrow] = delta;
     }
+    s_delta[threadIdx.x] = delta;
+    named_barrier(2, 128);
+    delta = s_delta[qrow] + s_delta[64 + qrow];
+    if (qrow < n_q && half == 0) p.delta[bhm + qrow] = delta;
     if (nb == 0) {
       if (qrow < n_q) {
         char* drow = dq_row0 + qrow * p.dq_sm * 2 + half * 128;
@@ -251,26 +307,23 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(drow + c * 16) = make_uint4(0, 0, 0, 0);
       }
     } else {
-      {
-        uint32_t z[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) z[j] = 0u;
-        tmem_st32_nowait(tm + lane_base + kColDS + (1 - half) * 32, z);
-        tmem_st_wait();
-      }
       bool ok = true;
+      if (threadIdx.x == 0) TRACE(1, 2);
       for (int t = 0; t < NT; ++t) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full, t & 1, abort));
+        const int s = t & 1;
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(&s_full[s], (t >> 1) & 1, abort) && mbar_wait(&dp_full, t & 1, abort));
         if (!ok) break;
         tc_fence_after();
         uint32_t x0[32], x1[32], y0[32], y1[32];
-        tmem_ld32_nowait(tm + lane_base + kColS + half * 64, x0);
-        tmem_ld32_nowait(tm + lane_base + kColS + half * 64 + 32, x1);
+        tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64, x0);
+        tmem_ld32_nowait(tm + lane_base + kColS + s * 128 + half * 64 + 32, x1);
         tmem_ld32_nowait(tm + lane_base + kColDP + half * 64, y0);
         tmem_ld32_nowait(tm + lane_base + kColDP + half * 64 + 32, y1);
         tmem_ld_wait();
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
         tc_fence_before();
-        mbar_arrive(&sdp_free);
+        mbar_arrive(&dp_free);
         const int blk = 2 * t + half;
         const int nv = blk < nb ? s_nvis[blk] : 0;
         uint32_t pk[32];
@@ -288,12 +341,20 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           pk[j] = pack2<__nv_bfloat16>(d[0], d[1]);
           pk[16 + j] = pack2<__nv_bfloat16>(d[2], d[3]);
         }
-        tmem_st32_nowait(tm + lane_base + kColDS + half * 32, pk);
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
+        // dS over the score columns of this step: this row's 64 values in its own half, zeros in the other
+        tmem_st32_nowait(tm + lane_base + kColS + s * 128 + half * 32, pk);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pk[j] = 0u;
+        tmem_st32_nowait(tm + lane_base + kColS + s * 128 + (1 - half) * 32, pk);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&ds_full);
+        mbar_arrive(&ds_full[s]);
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 3);
       }
+      if (threadIdx.x == 0) TRACE(1, 3);
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_final, 0, abort));
+      if (threadIdx.x == 0) TRACE(1, 4);
       if (ok) {
         tc_fence_after();
         const int tid = threadIdx.x;
@@ -323,9 +384,11 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     }
   }
 
+  if (threadIdx.x == 0) TRACE(1, 5);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+  if (threadIdx.x == 0) TRACE(1, 6);
   if (threadIdx.x == 0 && s_abort) atomicExch(p.status, NSA_ERR_CUDA);
 }
 
@@ -370,3 +433,10 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
 }
 
 }  // namespace nsa
+
+#ifdef NSA_TC_TRACE
+extern "C" int nsa_debug_trace_dq(long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_dq, sizeof(long long) * 4 * 512));
+  return NSA_OK;
+}
+#endif
