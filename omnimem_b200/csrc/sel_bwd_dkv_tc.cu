@@ -8,9 +8,11 @@
 // across items:
 //   warp 8   TMA producer: K, V tile of the item; per step the Q and dO rows of TWO groups of
 //            the bucket, stacked into 128-row tiles (two-stage ring)
-//   warp 9   MMA issuer, per step:  S  = [Qa;Qb] K^T, dP = [dOa;dOb] V^T   (M=128, N=64, K=128)
-//            and, one step later:   dV^T += [dOa;dOb]^T P,  dK^T += [Qa;Qb]^T dS
+//   warp 9   MMA issuer 1, per step:  S  = [Qa;Qb] K^T, dP = [dOa;dOb] V^T   (M=128, N=64, K=128)
+//   warp 10  MMA issuer 2, per step:  dV^T += [dOa;dOb]^T P,  dK^T += [Qa;Qb]^T dS
 //                                   (M=128 = head dim, N=64 keys, K=128 query rows)
+//            (two issuing threads: each spends a good part of a step in its barrier waits)
+//   warp 11  metadata: LSE, delta and visible-key count of the 128 stacked rows, a few steps ahead
 //   warps 0-3  one query row per thread: P = exp2(S c - LSE), dS = P (dP - delta) scale, written
 //            as bf16 rows into shared memory in the 128-byte-swizzled layout the MMA reads
 //   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the
@@ -41,7 +43,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
 constexpr uint32_t kQdOBytes = 65536;    // Q2 32 KiB + dO2 32 KiB per stage
 constexpr uint32_t kPdSBytes = 32768;    // P 16 KiB + dS 16 KiB
@@ -123,7 +125,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 257); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 258); }
     mbar_init(&kv_full, 1); mbar_init(&kv_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
@@ -197,58 +199,22 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       }
     }
   } else if (warp == 9) {
-    // ======================= MMA issuer =======================
+    // ======================= MMA issuer 1: S and dP of every step =======================
     if (lane == 0) {
-      constexpr uint32_t idesc_first = instr_desc_bf16(128, 64, 0, 0);    // S, dP: both operands K-major
-      constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // dV^T, dK^T: both MN-major
+      constexpr uint32_t idesc_first = instr_desc_bf16(128, 64, 0, 0);    // both operands K-major
       const uint64_t dK = smem_desc(smem_u32(sKV), 16, 1024), dV = smem_desc(smem_u32(sKV + 16384), 16, 1024);
-      const uint64_t dP = smem_desc(smem_u32(sP), 16, 1024), dDS = smem_desc(smem_u32(sdS), 16, 1024);
-      struct Pending { int st, acc; uint32_t sc, ic; bool first, last, any; } pd{0, 0, 0, 0, false, false, false};
-      auto issue_second = [&]() -> bool {
-        if (!mbar_wait(&pds_full, pd.sc & 1, abort)) return false;
-        TRACE(0, 16 + (pd.sc + 1) * 8 + 4);
-        if (pd.first && !mbar_wait(&acc_free[pd.acc], ((pd.ic >> 1) & 1) ^ 1, abort)) return false;
-        TRACE(0, 16 + (pd.sc + 1) * 8 + 5);
-        tc_fence_after();
-        const uint32_t aQ = smem_u32(sQdO + pd.st * kQdOBytes);
-        const uint64_t dQmn = smem_desc(aQ, 16384, 1024), dDOmn = smem_desc(aQ + 32768, 16384, 1024);
-        const uint32_t acc0 = pd.first ? 0u : 1u;
-        const uint32_t tdv = tm + col_dv(pd.acc), tdk = tm + col_dk(pd.acc);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
-        umma_commit(&qdo_empty[pd.st]);
-        umma_commit(&pds_free);
-        if (pd.last) umma_commit(&acc_full[pd.acc]);
-        return true;
-      };
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
-        // Never block on the item ring while the second half of a step is still owed: the
-        // epilogue warps hold ring slots until that half completes their accumulator.
-        if (pd.any && !mbar_try(&sched_full[n & 3], (n >> 2) & 1)) {
-          if (!issue_second()) { ok = false; break; }
-          pd.any = false;
-        }
-        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) { ok = false; break; }
-        const Item it = s_items[n & 3];
+        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) break;
+        const int n_ent = s_items[n & 3].n_ent;
         mbar_arrive(&sched_empty[n & 3]);
-        if (it.n_ent < 0) break;
-        if (!it.active) {
-          if (pd.any) {
-            if (!issue_second()) { ok = false; break; }
-            pd.any = false;
-          }
-          continue;
-        }
+        if (n_ent < 0) break;
+        if (n_ent == 0) continue;
         TRACE(0, 16 + sc * 8 + 0);
-        if (!mbar_wait(&kv_full, ic & 1, abort)) { ok = false; break; }
+        if (!mbar_wait(&kv_full, ic & 1, abort)) break;
         TRACE(0, 16 + sc * 8 + 1);
-        const int nsteps = (it.n_ent + 1) >> 1;
+        const int nsteps = (n_ent + 1) >> 1;
         for (int t = 0; t < nsteps; ++t, ++sc) {
           const int st = sc & 1, ph = (sc >> 1) & 1;
           if (!mbar_wait(&qdo_full[st], ph, abort)) { ok = false; break; }
@@ -269,13 +235,51 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           umma_commit(&sdp_full[st]);
           if (t == nsteps - 1) umma_commit(&kv_empty);
           TRACE(0, 16 + sc * 8 + 3);
-          if (pd.any && !issue_second()) { ok = false; break; }
-          TRACE(0, 16 + sc * 8 + 6);
-          pd = Pending{st, static_cast<int>(ic & 1), sc, ic, t == 0, t == nsteps - 1, true};
         }
         ++ic;
       }
-      if (ok && pd.any) issue_second();
+    }
+  } else if (warp == 10) {
+    // ======================= MMA issuer 2: dV^T and dK^T of every step =======================
+    // A thread of its own, so that these products start the moment P / dS are in shared memory
+    // while issuer 1 already waits for the tiles of the next step.
+    if (lane == 0) {
+      constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // both operands MN-major
+      const uint64_t dP = smem_desc(smem_u32(sP), 16, 1024), dDS = smem_desc(smem_u32(sdS), 16, 1024);
+      uint32_t ic = 0, sc = 0;
+      bool ok = true;
+      for (uint32_t n = 0; ok; ++n) {
+        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) break;
+        const int n_ent = s_items[n & 3].n_ent;
+        mbar_arrive(&sched_empty[n & 3]);
+        if (n_ent < 0) break;
+        if (n_ent == 0) continue;
+        const int acc = ic & 1;
+        const int nsteps = (n_ent + 1) >> 1;
+        for (int t = 0; t < nsteps; ++t, ++sc) {
+          const int st = sc & 1;
+          if (!mbar_wait(&pds_full, sc & 1, abort)) { ok = false; break; }
+          TRACE(0, 16 + sc * 8 + 4);
+          if (t == 0 && !mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)) { ok = false; break; }
+          TRACE(0, 16 + sc * 8 + 5);
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
+          const uint64_t dQmn = smem_desc(aQ, 16384, 1024), dDOmn = smem_desc(aQ + 32768, 16384, 1024);
+          const uint32_t acc0 = t == 0 ? 0u : 1u;
+          const uint32_t tdv = tm + col_dv(acc), tdk = tm + col_dk(acc);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
+          umma_commit(&qdo_empty[st]);
+          umma_commit(&pds_free);
+          if (t == nsteps - 1) umma_commit(&acc_full[acc]);
+          TRACE(0, 16 + sc * 8 + 6);
+        }
+        ++ic;
+      }
     }
   } else if (warp < 4) {
     // ======================= per-row math: P and dS of one query row per thread =======================
@@ -353,7 +357,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 4);
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ======================= epilogue (warps 4-7): one head-dim lane per thread =======================
     const int d = (warp - 4) * 32 + lane;
     const int te = threadIdx.x - 128;
