@@ -12,7 +12,6 @@
 //   warp 10  MMA issuer 2, per step:  dV^T += [dOa;dOb]^T P,  dK^T += [Qa;Qb]^T dS
 //                                   (M=128 = head dim, N=64 keys, K=128 query rows)
 //            (two issuing threads: each spends a good part of a step in its barrier waits)
-//   warp 11  metadata: LSE, delta and visible-key count of the 128 stacked rows, a few steps ahead
 //   warps 0-3  one query row per thread: P = exp2(S c - LSE), dS = P (dP - delta) scale, written
 //            as bf16 rows into shared memory in the 128-byte-swizzled layout the MMA reads
 //   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the

@@ -7,8 +7,9 @@
 // merge-and-store epilogue of one block run beside the main loop of the other.  Roles:
 //   warp 4  TMA producer: Q once, then per step the K tile of TWO selected blocks (128 keys),
 //           coordinates taken from the compacted block list;   warp 6: the same for V;
-//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into TMEM, then, once the softmax
-//           warps have written P over the score columns, O += P V with P read from TMEM;
+//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into TMEM;
+//   warp 7  MMA issuer: once the softmax warps have written P over the score columns,
+//           O += P V with P read from TMEM;
 //   warps 0-3  softmax: one TMEM lane (matrix row) per thread.
 // The 64 query rows are loaded twice, into rows 0-63 and 64-127 of the A tile: rows 0-63 do
 // the online softmax over the EVEN block of each step (S columns 0-63), rows 64-127 over the
@@ -76,7 +77,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTcThreads = 224;
+constexpr int kTcThreads = 256;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTileBytes = 32768;        // 128 rows x 256 bytes, as two 64-column halves of 16 KiB
 constexpr uint32_t kSmemTiles = 3 * kTileBytes;   // Q, K, V
@@ -241,45 +242,52 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (isK) mbar_wait(&q_full, 0, abort);
       }
     }
-  } else if (warp == 5) {
-    // ======================= MMA issuer =======================
-    // Per step: S = [Q;Q] K^T, (softmax writes P over S), O += P V.  The next S overwrites P, so
-    // it is issued only after the P V product that reads it has completed.
+  } else if (warp == 5 || warp == 7) {
+    // ======================= MMA issuers =======================
+    // Per step: S = [Q;Q] K^T (warp 5), softmax writes P over S, O += P V (warp 7).  The next S
+    // overwrites P, so it is issued only after the P V product that reads it has completed.
+    // Two issuing threads, because each passed barrier wait costs the thread a few hundred cycles.
     if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
-      const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
-      const uint64_t dK = smem_desc(smem_u32(sK), 16, 1024);
-      const uint64_t dV = smem_desc(smem_u32(sV), 16384, 1024);
-      bool ok = mbar_wait(&q_full, 0, abort);
-      TRACE(0, 0);
-      for (int t = 0; ok && t < NT; ++t) {
-        const uint32_t ph = t & 1;
-        if (!mbar_wait(&k_full, ph, abort)) { ok = false; break; }
-        if (t > 0 && !mbar_wait(&pv_done, ph ^ 1, abort)) { ok = false; break; }
-        TRACE(0, 8 + t * 8 + 0);
-        tc_fence_after();
+      if (warp == 5) {
+        constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
+        const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t dK = smem_desc(smem_u32(sK), 16, 1024);
+        bool ok = mbar_wait(&q_full, 0, abort);
+        TRACE(0, 0);
+        for (int t = 0; ok && t < NT; ++t) {
+          const uint32_t ph = t & 1;
+          if (!mbar_wait(&k_full, ph, abort)) break;
+          if (t > 0 && !mbar_wait(&pv_done, ph ^ 1, abort)) break;
+          TRACE(0, 8 + t * 8 + 0);
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
-                  desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-        umma_commit(&s_full);
-        umma_commit(&k_empty);
-        TRACE(0, 8 + t * 8 + 1);
-        if (!mbar_wait(&v_full, ph, abort)) { ok = false; break; }
-        if (!mbar_wait(&p_full, ph, abort)) { ok = false; break; }
-        TRACE(0, 8 + t * 8 + 2);
-        tc_fence_after();
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                    desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+          umma_commit(&s_full);
+          umma_commit(&k_empty);
+          TRACE(0, 8 + t * 8 + 1);
+        }
+      } else {
+        constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
+        const uint64_t dV = smem_desc(smem_u32(sV), 16384, 1024);
+        for (int t = 0; t < NT; ++t) {
+          const uint32_t ph = t & 1;
+          if (!mbar_wait(&v_full, ph, abort)) break;
+          if (!mbar_wait(&p_full, ph, abort)) break;
+          TRACE(0, 8 + t * 8 + 2);
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&v_empty);
-        umma_commit(&pv_done);
-        if (t == NT - 1) umma_commit(&o_final);
-        TRACE(0, 8 + t * 8 + 3);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&v_empty);
+          umma_commit(&pv_done);
+          if (t == NT - 1) umma_commit(&o_final);
+          TRACE(0, 8 + t * 8 + 3);
+        }
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ======================= softmax (warps 0-3), one matrix row per thread =======================
     const int half = warp >> 1;                       // 0: even block of each step, 1: odd block
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
