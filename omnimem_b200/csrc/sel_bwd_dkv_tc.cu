@@ -330,14 +330,26 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tmem_ld32_nowait(tm + lane_base + col_dp(st) + hc * 32, y);
           tmem_ld_wait();
           if (hc == 1) { tc_fence_before(); mbar_arrive(&sdp_free[st]); }
+          const float sl = p.scale_log2, nl = -lse2, sc_ = p.scale, nds = -dl * p.scale;
+          if (nkv == 64) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int c0 = hc * 32 + 2 * j;
-            const float p0 = (c0 < nkv) ? fast_exp2(__uint_as_float(x[2 * j]) * p.scale_log2 - lse2) : 0.f;
-            const float p1 = (c0 + 1 < nkv) ? fast_exp2(__uint_as_float(x[2 * j + 1]) * p.scale_log2 - lse2) : 0.f;
-            pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
-            dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * (__uint_as_float(y[2 * j]) - dl) * p.scale,
-                                                   p1 * (__uint_as_float(y[2 * j + 1]) - dl) * p.scale);
+            for (int j = 0; j < 16; ++j) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(x[2 * j]), sl, nl));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(x[2 * j + 1]), sl, nl));
+              pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
+              dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * fmaf(__uint_as_float(y[2 * j]), sc_, nds),
+                                                     p1 * fmaf(__uint_as_float(y[2 * j + 1]), sc_, nds));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int c0 = hc * 32 + 2 * j;
+              const float p0 = (c0 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[2 * j]), sl, nl)) : 0.f;
+              const float p1 = (c0 + 1 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[2 * j + 1]), sl, nl)) : 0.f;
+              pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
+              dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * fmaf(__uint_as_float(y[2 * j]), sc_, nds),
+                                                     p1 * fmaf(__uint_as_float(y[2 * j + 1]), sc_, nds));
+            }
           }
         }
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 2);

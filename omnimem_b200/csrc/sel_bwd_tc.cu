@@ -283,7 +283,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     // delta = sum_d O dO of this thread's query row: each of the row's two threads reduces the half
     // it loaded at the top of the kernel, the halves meet in shared memory
-    float delta = 0.f, lse2 = INFINITY;
+    float delta = 0.f, lse2 = INFINITY, lse2s = INFINITY;
     if (qrow < n_q) {
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -295,6 +295,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
       }
       lse2 = p.lse[bhm + qrow] * kLog2e;
+      lse2s = lse2 - log2f(p.scale);
     }
     s_delta[threadIdx.x] = delta;
     named_barrier(2, 128);
@@ -326,20 +327,31 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_arrive(&dp_free);
         const int blk = 2 * t + half;
         const int nv = blk < nb ? s_nvis[blk] : 0;
+        // dS = P (dP - delta) scale with the scale folded into the exponent (lse2s = LSE log2e - log2 scale)
         uint32_t pk[32];
+        {
+          const float sl = p.scale_log2, nl = -lse2s;
+          if (nv == 64) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float d[4];
+            for (int j = 0; j < 16; ++j) {
+              const float d0 = fast_exp2(fmaf(__uint_as_float(x0[2 * j]), sl, nl)) * (__uint_as_float(y0[2 * j]) - delta);
+              const float d1 = fast_exp2(fmaf(__uint_as_float(x0[2 * j + 1]), sl, nl)) * (__uint_as_float(y0[2 * j + 1]) - delta);
+              const float d2 = fast_exp2(fmaf(__uint_as_float(x1[2 * j]), sl, nl)) * (__uint_as_float(y1[2 * j]) - delta);
+              const float d3 = fast_exp2(fmaf(__uint_as_float(x1[2 * j + 1]), sl, nl)) * (__uint_as_float(y1[2 * j + 1]) - delta);
+              pk[j] = pack2<__nv_bfloat16>(d0, d1);
+              pk[16 + j] = pack2<__nv_bfloat16>(d2, d3);
+            }
+          } else {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = (e < 2) ? 2 * j + e : 32 + 2 * j + (e - 2);
-            const float sv = __uint_as_float((e < 2) ? x0[2 * j + e] : x1[2 * j + e - 2]);
-            const float dp = __uint_as_float((e < 2) ? y0[2 * j + e] : y1[2 * j + e - 2]);
-            const float pe = (col < nv) ? fast_exp2(sv * p.scale_log2 - lse2) : 0.f;
-            d[e] = pe * (dp - delta) * p.scale;
+            for (int j = 0; j < 16; ++j) {
+              const float d0 = (2 * j < nv) ? fast_exp2(fmaf(__uint_as_float(x0[2 * j]), sl, nl)) * (__uint_as_float(y0[2 * j]) - delta) : 0.f;
+              const float d1 = (2 * j + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x0[2 * j + 1]), sl, nl)) * (__uint_as_float(y0[2 * j + 1]) - delta) : 0.f;
+              const float d2 = (2 * j + 32 < nv) ? fast_exp2(fmaf(__uint_as_float(x1[2 * j]), sl, nl)) * (__uint_as_float(y1[2 * j]) - delta) : 0.f;
+              const float d3 = (2 * j + 33 < nv) ? fast_exp2(fmaf(__uint_as_float(x1[2 * j + 1]), sl, nl)) * (__uint_as_float(y1[2 * j + 1]) - delta) : 0.f;
+              pk[j] = pack2<__nv_bfloat16>(d0, d1);
+              pk[16 + j] = pack2<__nv_bfloat16>(d2, d3);
+            }
           }
-          pk[j] = pack2<__nv_bfloat16>(d[0], d[1]);
-          pk[16 + j] = pack2<__nv_bfloat16>(d[2], d[3]);
         }
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
         // dS over the score columns of this step: this row's 64 values in its own half, zeros in the other
@@ -407,6 +419,7 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
   const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
   if (env != nullptr && std::string(env) == "general") return NSA_OK;
   if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || T > kMaxSlots || H == 1) return NSA_OK;
+  if (!(scale > 0.f)) return NSA_OK;   // the kernel folds log2(scale) into the exponent
   if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
   if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
   if (encode_tiled_fn() == nullptr) return NSA_OK;
