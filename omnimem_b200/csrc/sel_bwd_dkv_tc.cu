@@ -4,20 +4,20 @@
 // Ownership as in the general kernel: one work item = one (batch, head, KV block); the item's
 // dK / dV tile is produced by exactly one thread block, from the block's bucket of query groups
 // in ascending group order - no atomics, bit-reproducible.  Persistent thread blocks (one per
-// SM) walk the items round-robin; inside a block the roles are pipelined across steps AND
-// across items:
-//   warp 8   TMA producer: K, V tile of the item; per step the Q and dO rows of TWO groups of
-//            the bucket, stacked into 128-row tiles (two-stage ring)
-//   warp 9   MMA issuer 1, per step:  S  = [Qa;Qb] K^T, dP = [dOa;dOb] V^T   (M=128, N=64, K=128)
-//   warp 10  MMA issuer 2, per step:  dV^T += [dOa;dOb]^T P,  dK^T += [Qa;Qb]^T dS
-//                                   (M=128 = head dim, N=64 keys, K=128 query rows)
-//            (two issuing threads: each spends a good part of a step in its barrier waits)
-//   warps 0-3  one query row per thread: P = exp2(S c - LSE), dS = P (dP - delta) scale, written
-//            as bf16 rows into shared memory in the 128-byte-swizzled layout the MMA reads
+// SM) take items from a global counter.  A step is ONE bucket entry (one query group against
+// the item's block); most buckets hold one to three entries, so small steps in a deep pipeline
+// beat wide ones.  Roles, pipelined across steps and across items:
+//   warp 8   producer: K, V tile of the item (TMA); per step the Q and dO rows of the group
+//            into a four-stage ring (TMA), plus each row's LSE and delta and the step's visible
+//            key count into the same stage (the whole warp loads them, two rows per lane)
+//   warp 9   MMA issuer 1, per step:  S = Q K^T, dP = dO V^T          (M=64, N=64, K=128)
+//   warp 10  MMA issuer 2, per step:  dV^T += dO^T P,  dK^T += Q^T dS  (M=128 = head dim, N=64 keys, K=64 rows)
+//   warps 0-3  row arithmetic on the accumulator fragments (16 rows x 64 keys per warp):
+//            P = exp2(S c - LSE), dS = P (dP - delta) scale, stored as bf16 with stmatrix into
+//            the 128-byte-swizzled shared-memory tiles the second products read
 //   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the
 //            transposed tile; items with an empty bucket are zero-filled here
-// Both operands of every MMA are full (two real groups fill the 128 rows), so no tensor work
-// is wasted; S/dP and the dV^T/dK^T accumulators are double buffered in TMEM (512 columns).
+// S/dP, the P/dS tiles and the dV^T/dK^T accumulators are double buffered.
 #include "sel_common.cuh"
 #include "tc_common.cuh"
 
@@ -31,7 +31,7 @@ int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* k
                   CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
 
 #ifdef NSA_TC_TRACE
-// Debug build only: clock64 stamps of thread block 0; [0] MMA issuer, [1] math thread 0, [2] producer, [3] epilogue.
+// Debug build only: clock64 stamps of thread block 0; [0] MMA issuers, [1] row thread 0, [2] producer, [3] epilogue.
 __device__ long long g_trace_dkv[4][1024];
 #define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 1024) g_trace_dkv[role][slot] = clock64(); } while (0)
 #else
@@ -43,10 +43,11 @@ namespace {
 using namespace tc;
 
 constexpr int kThreads = 352;
+constexpr int kStages = 4;               // Q / dO ring
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
-constexpr uint32_t kQdOBytes = 65536;    // Q2 32 KiB + dO2 32 KiB per stage
-constexpr uint32_t kPdSBytes = 32768;    // P 16 KiB + dS 16 KiB
-constexpr uint32_t kSmemTiles = kKVBytes + 2 * kQdOBytes + kPdSBytes;
+constexpr uint32_t kQdOBytes = 32768;    // Q 16 KiB + dO 16 KiB per stage
+constexpr uint32_t kPdSBytes = 16384;    // P 8 KiB + dS 8 KiB per buffer
+constexpr uint32_t kSmemTiles = kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes;
 
 // TMEM columns: S / dP double buffered (64 columns each), accumulators double buffered
 __device__ __forceinline__ uint32_t col_s(int buf) { return buf * 128; }
@@ -92,7 +93,7 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
   return it;
 }
 // Work items are handed out through a global counter (buckets differ a lot in length, a static
-// split leaves thread blocks idle).  The producer thread takes the ticket, decodes the item and
+// split leaves thread blocks idle).  The producer takes the ticket, decodes the item and
 // publishes it in a 4-deep shared-memory ring that the other roles follow; n_ent = -1 ends it.
 __device__ __forceinline__ Item fetch_item(const TcDkvParams& p, int64_t n_items) {
   const int64_t t = atomicAdd(p.counter, 1);
@@ -110,14 +111,15 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sKV = tiles;                               // K [2][64][128 B], V [2][64][128 B]
-  uint8_t* sQdO = tiles + kKVBytes;                   // [stage]{ Q2 [2][128][128 B], dO2 [2][128][128 B] }
-  uint8_t* sP = tiles + kKVBytes + 2 * kQdOBytes;     // [128 q][128 B] swizzled
-  uint8_t* sdS = sP + 16384;
+  uint8_t* sQdO = tiles + kKVBytes;                   // [stage]{ Q [2][64][128 B], dO [2][64][128 B] }
+  uint8_t* sPdS = tiles + kKVBytes + kStages * kQdOBytes;   // [buffer]{ P [64 q][128 B], dS [64 q][128 B] } swizzled
 
-  __shared__ uint64_t kv_full, kv_empty, qdo_full[2], qdo_empty[2], sdp_full[2], sdp_free[2], pds_full, pds_free,
-      acc_full[2], acc_free[2];
+  __shared__ uint64_t kv_full, kv_empty, qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
+      pds_free[2], acc_full[2], acc_free[2];
   __shared__ uint64_t sched_full[4], sched_empty[4];
   __shared__ Item s_items[4];
+  __shared__ float2 s_meta[kStages][64];              // per row of the stage's group: LSE * log2(e) (+inf = no row), delta
+  __shared__ int s_nkv[kStages];                      // visible keys of the stage's step
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
@@ -126,12 +128,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     s_abort = 0;
     for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 258); }
     mbar_init(&kv_full, 1); mbar_init(&kv_empty, 1);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 2); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1);
       mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 128);
+      mbar_init(&pds_full[i], 128); mbar_init(&pds_free[i], 1);
       mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 128);
     }
-    mbar_init(&pds_full, 128); mbar_init(&pds_free, 1);
     fence_barrier_init();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, 512);
@@ -147,22 +149,31 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int64_t bucket_row = static_cast<int64_t>(p.MG) * p.T;
 
   if (warp == 8) {
-    // ======================= TMA producer =======================
-    if (lane == 0) {
-      uint32_t ic = 0, sc = 0;
-      bool ok = true;
-      Item nxt = fetch_item(p, n_items);
-      for (uint32_t n = 0; ok; ++n) {
-        const Item it = nxt;
-        if (!mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort)) break;
+    // ======================= producer (whole warp; lane 0 issues the copies) =======================
+    uint32_t ic = 0, sc = 0;
+    bool ok = true;
+    Item nxt{0, 0, 0, 0, -1, 0, false};
+    if (lane == 0) nxt = fetch_item(p, n_items);
+    for (uint32_t n = 0; ok; ++n) {
+      Item it;
+      it.b = __shfl_sync(0xffffffffu, nxt.b, 0); it.h = __shfl_sync(0xffffffffu, nxt.h, 0);
+      it.blk = __shfl_sync(0xffffffffu, nxt.blk, 0); it.beg = __shfl_sync(0xffffffffu, nxt.beg, 0);
+      it.n_ent = __shfl_sync(0xffffffffu, nxt.n_ent, 0); it.row = __shfl_sync(0xffffffffu, nxt.row, 0);
+      it.active = it.n_ent > 0;
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort));
+      if (!ok) break;
+      if (lane == 0) {
         s_items[n & 3] = it;
         mbar_arrive(&sched_full[n & 3]);
-        if (it.n_ent < 0) break;
-        nxt = fetch_item(p, n_items);          // decoded while this item's copies are issued
-        if (!it.active) continue;
-        TRACE(2, 16 + sc * 4 + 0);
-        if (!mbar_wait(&kv_empty, (ic & 1) ^ 1, abort)) break;
-        TRACE(2, 16 + sc * 4 + 1);
+      }
+      if (it.n_ent < 0) break;
+      if (lane == 0) nxt = fetch_item(p, n_items);       // decoded while this item's copies are issued
+      if (!it.active) continue;
+      TRACE(2, 16 + sc * 4 + 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty, (ic & 1) ^ 1, abort));
+      if (!ok) break;
+      TRACE(2, 16 + sc * 4 + 1);
+      if (lane == 0) {
         mbar_expect_tx(&kv_full, kKVBytes);
         for (int dh = 0; dh < 2; ++dh) {
           if (p.paged) {
@@ -173,34 +184,59 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tma_load_4d(sKV + 16384 + dh * 8192, &mapV, dh * 64, it.h, it.row, it.b, &kv_full);
           }
         }
-        const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
-        const int nsteps = (it.n_ent + 1) >> 1;
-        for (int t = 0; t < nsteps; ++t, ++sc) {
-          const int st = sc & 1, ph = (sc >> 1) & 1;
-          if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort)) { ok = false; break; }
-          TRACE(2, 16 + sc * 4 + 2);
-          const int ga = bucket[2 * t], gb = (2 * t + 1 < it.n_ent) ? bucket[2 * t + 1] : ga;
+      }
+      const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
+      const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
+      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
+      const int64_t bh = (static_cast<int64_t>(it.b) * p.H + it.h) * p.M;
+      int g_next = bucket[0];
+      for (int t = 0; t < it.n_ent; ++t, ++sc) {
+        const int st = sc % kStages, ph = (sc / kStages) & 1;
+        const int g = g_next;
+        if (t + 1 < it.n_ent) g_next = bucket[t + 1];
+        const int64_t m0 = static_cast<int64_t>(g) * p.G;
+        const int nq = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
+        // the rows' LSE and delta travel with the stage: two rows per lane
+        float2 mt[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int r = lane + 32 * k;
+          mt[k].x = r < nq ? p.lse[bh + m0 + r] * kLog2e : INFINITY;
+          mt[k].y = r < nq ? p.delta[bh + m0 + r] : 0.f;
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(&qdo_empty[st], ph ^ 1, abort));
+        if (!ok) break;
+        TRACE(2, 16 + sc * 4 + 2);
+        if (lane == 0) {
           uint8_t* dq = sQdO + st * kQdOBytes;
           mbar_expect_tx(&qdo_full[st], kQdOBytes);
           for (int dh = 0; dh < 2; ++dh) {
-            tma_load_4d(dq + dh * 16384, &mapQ, dh * 64, it.h, ga * p.G, it.b, &qdo_full[st]);
-            tma_load_4d(dq + dh * 16384 + 8192, &mapQ, dh * 64, it.h, gb * p.G, it.b, &qdo_full[st]);
-            tma_load_4d(dq + 32768 + dh * 16384, &mapDO, dh * 64, it.h, ga * p.G, it.b, &qdo_full[st]);
-            tma_load_4d(dq + 32768 + dh * 16384 + 8192, &mapDO, dh * 64, it.h, gb * p.G, it.b, &qdo_full[st]);
+            tma_load_4d(dq + dh * 8192, &mapQ, dh * 64, it.h, static_cast<int>(m0), it.b, &qdo_full[st]);
+            tma_load_4d(dq + 16384 + dh * 8192, &mapDO, dh * 64, it.h, static_cast<int>(m0), it.b, &qdo_full[st]);
           }
+          int nkv = n_blk;
+          if (p.causal) {
+            const int64_t lim = (m0 / p.chunk_size + 1) * p.chunk_size - t0;
+            if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
+          }
+          s_nkv[st] = nkv;
         }
-        ++ic;
+        s_meta[st][lane] = mt[0];
+        s_meta[st][lane + 32] = mt[1];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&qdo_full[st]);
       }
-      if (*abort) {
-        // consumers have stopped: wait (bounded) for the copies still in flight
-        if (ic > 0) mbar_wait(&kv_full, (ic - 1) & 1, abort);
-        for (uint32_t u = (sc > 1 ? sc - 2 : 0); u < sc; ++u) mbar_wait(&qdo_full[u & 1], (u >> 1) & 1, abort);
-      }
+      ++ic;
+    }
+    if (*abort && lane == 0) {
+      // consumers have stopped: wait (bounded) for the copies still in flight
+      if (ic > 0) mbar_wait(&kv_full, (ic - 1) & 1, abort);
+      for (uint32_t u = (sc > kStages ? sc - kStages : 0); u < sc; ++u) mbar_wait(&qdo_full[u % kStages], (u / kStages) & 1, abort);
     }
   } else if (warp == 9) {
     // ======================= MMA issuer 1: S and dP of every step =======================
     if (lane == 0) {
-      constexpr uint32_t idesc_first = instr_desc_bf16(128, 64, 0, 0);    // both operands K-major
+      constexpr uint32_t idesc_first = instr_desc_bf16(64, 64, 0, 0);     // both operands K-major
       const uint64_t dK = smem_desc(smem_u32(sKV), 16, 1024), dV = smem_desc(smem_u32(sKV + 16384), 16, 1024);
       uint32_t ic = 0, sc = 0;
       bool ok = true;
@@ -213,26 +249,25 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         TRACE(0, 16 + sc * 8 + 0);
         if (!mbar_wait(&kv_full, ic & 1, abort)) break;
         TRACE(0, 16 + sc * 8 + 1);
-        const int nsteps = (n_ent + 1) >> 1;
-        for (int t = 0; t < nsteps; ++t, ++sc) {
-          const int st = sc & 1, ph = (sc >> 1) & 1;
-          if (!mbar_wait(&qdo_full[st], ph, abort)) { ok = false; break; }
+        for (int t = 0; t < n_ent; ++t, ++sc) {
+          const int st = sc % kStages, sb = sc & 1;
+          if (!mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort)) { ok = false; break; }
           TRACE(0, 16 + sc * 8 + 2);
-          if (!mbar_wait(&sdp_free[st], ph ^ 1, abort)) { ok = false; break; }
+          if (!mbar_wait(&sdp_free[sb], ((sc >> 1) & 1) ^ 1, abort)) { ok = false; break; }
           tc_fence_after();
           const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
-          const uint64_t dQ = smem_desc(aQ, 16, 1024), dDO = smem_desc(aQ + 32768, 16, 1024);
-          const uint32_t ts = tm + col_s(st), tdp = tm + col_dp(st);
+          const uint64_t dQ = smem_desc(aQ, 16, 1024), dDO = smem_desc(aQ + 16384, 16, 1024);
+          const uint32_t ts = tm + col_s(sb), tdp = tm + col_dp(sb);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(ts, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+            umma_ss(ts, desc_advance(dQ, (kk >> 2) * 8192 + (kk & 3) * 32),
                     desc_advance(dK, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 16384 + (kk & 3) * 32),
+            umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 8192 + (kk & 3) * 32),
                     desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
-          umma_commit(&sdp_full[st]);
-          if (t == nsteps - 1) umma_commit(&kv_empty);
+          umma_commit(&sdp_full[sb]);
+          if (t == n_ent - 1) umma_commit(&kv_empty);
           TRACE(0, 16 + sc * 8 + 3);
         }
         ++ic;
@@ -241,10 +276,9 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   } else if (warp == 10) {
     // ======================= MMA issuer 2: dV^T and dK^T of every step =======================
     // A thread of its own, so that these products start the moment P / dS are in shared memory
-    // while issuer 1 already waits for the tiles of the next step.
+    // while issuer 1 already waits for the tiles of a later step.
     if (lane == 0) {
       constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // both operands MN-major
-      const uint64_t dP = smem_desc(smem_u32(sP), 16, 1024), dDS = smem_desc(smem_u32(sdS), 16, 1024);
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
@@ -254,117 +288,119 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (n_ent < 0) break;
         if (n_ent == 0) continue;
         const int acc = ic & 1;
-        const int nsteps = (n_ent + 1) >> 1;
-        for (int t = 0; t < nsteps; ++t, ++sc) {
-          const int st = sc & 1;
-          if (!mbar_wait(&pds_full, sc & 1, abort)) { ok = false; break; }
+        for (int t = 0; t < n_ent; ++t, ++sc) {
+          const int st = sc % kStages, pb = sc & 1;
+          if (!mbar_wait(&pds_full[pb], (sc >> 1) & 1, abort)) { ok = false; break; }
           TRACE(0, 16 + sc * 8 + 4);
           if (t == 0 && !mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)) { ok = false; break; }
           TRACE(0, 16 + sc * 8 + 5);
           tc_fence_after();
-          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
-          const uint64_t dQmn = smem_desc(aQ, 16384, 1024), dDOmn = smem_desc(aQ + 32768, 16384, 1024);
+          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes), aP = smem_u32(sPdS + pb * kPdSBytes);
+          // A: Q^T / dO^T, head dim contiguous, two 64-column boxes 8 KiB apart; B: P / dS, keys contiguous
+          const uint64_t dQmn = smem_desc(aQ, 8192, 1024), dDOmn = smem_desc(aQ + 16384, 8192, 1024);
+          const uint64_t dP = smem_desc(aP, 16, 1024), dDS = smem_desc(aP + 8192, 16, 1024);
           const uint32_t acc0 = t == 0 ? 0u : 1u;
           const uint32_t tdv = tm + col_dv(acc), tdk = tm + col_dk(acc);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
+          for (int kk = 0; kk < 4; ++kk)
             umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
+          for (int kk = 0; kk < 4; ++kk)
             umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
           umma_commit(&qdo_empty[st]);
-          umma_commit(&pds_free);
-          if (t == nsteps - 1) umma_commit(&acc_full[acc]);
+          umma_commit(&pds_free[pb]);
+          if (t == n_ent - 1) umma_commit(&acc_full[acc]);
           TRACE(0, 16 + sc * 8 + 6);
         }
         ++ic;
       }
     }
   } else if (warp < 4) {
-    // ======================= per-row math: P and dS of one query row per thread =======================
-    const int half = warp >> 1, r = threadIdx.x & 63;
+    // ======================= row arithmetic: P and dS on accumulator fragments =======================
+    // Warp w owns rows 16w .. 16w+15 of the step's group (TMEM lanes 32w .. 32w+15 of an M=64
+    // accumulator); thread t holds rows 16w + t/4 and + 8, keys 8i + 2(t%4), +1 for i = 0..7.
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int row = threadIdx.x;                       // row of the stacked 128-row tiles
-    uint8_t* prow = sP + row * 128;
-    uint8_t* dsrow = sdS + row * 128;
+    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+    const int cq = (lane & 3) * 2;
+    // stmatrix: this thread supplies the address of row (lane%8) of matrix (lane/8); the four
+    // matrices of one instruction are (rows +0, keys 8i), (rows +8, keys 8i), (rows +0, keys 8i+8), (rows +8, keys 8i+8)
+    const int st_row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int st_chunk = lane >> 4;                    // + 2 * instruction index
     uint32_t sc = 0;
     bool ok = true;
     for (uint32_t n = 0; ok; ++n) {
       ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
       if (!ok) break;
-      const Item it = s_items[n & 3];
+      const int n_ent = s_items[n & 3].n_ent;
       mbar_arrive(&sched_empty[n & 3]);
-      if (it.n_ent < 0) break;
-      if (!it.active) continue;
-      const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
-      const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
-      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
-      const int64_t bh = (static_cast<int64_t>(it.b) * p.H + it.h) * p.M;
-      const int nsteps = (it.n_ent + 1) >> 1;
-      for (int t = 0; t < nsteps; ++t, ++sc) {
-        const int st = sc & 1, ph = (sc >> 1) & 1;
-        const int ent = 2 * t + half;
-        const bool valid = ent < it.n_ent;
-        const int g = valid ? bucket[ent] : 0;
-        const int64_t m0 = static_cast<int64_t>(g) * p.G;
-        const int nq = valid ? static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G) : 0;
-        const bool rowok = r < nq;
-        const float lse2 = rowok ? p.lse[bh + m0 + r] * kLog2e : INFINITY;
-        const float dl = rowok ? p.delta[bh + m0 + r] : 0.f;
-        int nkv = n_blk;
-        if (p.causal) {
-          const int64_t lim = (m0 / p.chunk_size + 1) * p.chunk_size - t0;
-          if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
-        }
-        if (!rowok) nkv = 0;
+      if (n_ent < 0) break;
+      for (int t = 0; t < n_ent; ++t, ++sc) {
+        const int st = sc % kStages, sb = sc & 1, ph = (sc >> 1) & 1;
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 0);
-        ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[st], ph, abort));
+        ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[sb], ph, abort));
         if (!ok) break;
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 1);
         tc_fence_after();
-        uint32_t pp[32], dd[32];                       // packed bf16 pairs of the 64 keys
+        uint32_t x[32], y[32];
+        tmem_ld_16x256b_x8_nowait(tm + lane_base + col_s(sb), x);
+        tmem_ld_16x256b_x8_nowait(tm + lane_base + col_dp(sb), y);
+        const float2 m0 = s_meta[st][r0], m1 = s_meta[st][r1];
+        const int nkv = s_nkv[st];
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&sdp_free[sb]);
+        const float sl = p.scale_log2, sc_ = p.scale;
+        const float nl0 = -m0.x, nl1 = -m1.x, nd0 = -m0.y * sc_, nd1 = -m1.y * sc_;
+        // x[4i], x[4i+1]: row r0, keys 8i+cq, +1;  x[4i+2], x[4i+3]: row r1, same keys.  Afterwards
+        // x[2i], x[2i+1] hold the packed P of (r0, r1) for key block i, y[2i], y[2i+1] the packed dS.
+        if (nkv == 64) {
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
-          uint32_t x[32], y[32];
-          tmem_ld32_nowait(tm + lane_base + col_s(st) + hc * 32, x);
-          tmem_ld32_nowait(tm + lane_base + col_dp(st) + hc * 32, y);
-          tmem_ld_wait();
-          if (hc == 1) { tc_fence_before(); mbar_arrive(&sdp_free[st]); }
-          const float sl = p.scale_log2, nl = -lse2, sc_ = p.scale, nds = -dl * p.scale;
-          if (nkv == 64) {
+          for (int i = 0; i < 8; ++i) {
+            const float p00 = fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0));
+            const float p01 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0));
+            const float p10 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, nl1));
+            const float p11 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 3]), sl, nl1));
+            const uint32_t d0 = pack2<__nv_bfloat16>(p00 * fmaf(__uint_as_float(y[4 * i]), sc_, nd0),
+                                                     p01 * fmaf(__uint_as_float(y[4 * i + 1]), sc_, nd0));
+            const uint32_t d1 = pack2<__nv_bfloat16>(p10 * fmaf(__uint_as_float(y[4 * i + 2]), sc_, nd1),
+                                                     p11 * fmaf(__uint_as_float(y[4 * i + 3]), sc_, nd1));
+            x[2 * i] = pack2<__nv_bfloat16>(p00, p01);
+            x[2 * i + 1] = pack2<__nv_bfloat16>(p10, p11);
+            y[2 * i] = d0;
+            y[2 * i + 1] = d1;
+          }
+        } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(x[2 * j]), sl, nl));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(x[2 * j + 1]), sl, nl));
-              pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
-              dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * fmaf(__uint_as_float(y[2 * j]), sc_, nds),
-                                                     p1 * fmaf(__uint_as_float(y[2 * j + 1]), sc_, nds));
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int c0 = hc * 32 + 2 * j;
-              const float p0 = (c0 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[2 * j]), sl, nl)) : 0.f;
-              const float p1 = (c0 + 1 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[2 * j + 1]), sl, nl)) : 0.f;
-              pp[hc * 16 + j] = pack2<__nv_bfloat16>(p0, p1);
-              dd[hc * 16 + j] = pack2<__nv_bfloat16>(p0 * fmaf(__uint_as_float(y[2 * j]), sc_, nds),
-                                                     p1 * fmaf(__uint_as_float(y[2 * j + 1]), sc_, nds));
-            }
+          for (int i = 0; i < 8; ++i) {
+            const int c = 8 * i + cq;
+            const float p00 = (c < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0)) : 0.f;
+            const float p01 = (c + 1 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0)) : 0.f;
+            const float p10 = (c < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, nl1)) : 0.f;
+            const float p11 = (c + 1 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 3]), sl, nl1)) : 0.f;
+            const uint32_t d0 = pack2<__nv_bfloat16>(p00 * fmaf(__uint_as_float(y[4 * i]), sc_, nd0),
+                                                     p01 * fmaf(__uint_as_float(y[4 * i + 1]), sc_, nd0));
+            const uint32_t d1 = pack2<__nv_bfloat16>(p10 * fmaf(__uint_as_float(y[4 * i + 2]), sc_, nd1),
+                                                     p11 * fmaf(__uint_as_float(y[4 * i + 3]), sc_, nd1));
+            x[2 * i] = pack2<__nv_bfloat16>(p00, p01);
+            x[2 * i + 1] = pack2<__nv_bfloat16>(p10, p11);
+            y[2 * i] = d0;
+            y[2 * i + 1] = d1;
           }
         }
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 2);
-        // P / dS of the previous step must have been consumed before the rows are overwritten
-        ok = __all_sync(0xffffffffu, mbar_wait(&pds_free, (sc & 1) ^ 1, abort));
+        // the buffer's previous P / dS (two steps ago) must have been consumed
+        ok = __all_sync(0xffffffffu, mbar_wait(&pds_free[sb], ph ^ 1, abort));
         if (!ok) break;
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 3);
+        const uint32_t aP = smem_u32(sPdS + sb * kPdSBytes) + st_row * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int off = ((c ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-          *reinterpret_cast<uint4*>(dsrow + off) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4);
+          stmatrix_x4(aP + off, x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+          stmatrix_x4(aP + 8192 + off, y[4 * q], y[4 * q + 1], y[4 * q + 2], y[4 * q + 3]);
         }
         fence_async_smem();                           // make the rows visible to the tensor core's reads
-        mbar_arrive(&pds_full);
+        mbar_arrive(&pds_full[sb]);
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 4);
       }
     }
