@@ -47,7 +47,8 @@ constexpr int kStages = 4;               // Q / dO ring
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
 constexpr uint32_t kQdOBytes = 32768;    // Q 16 KiB + dO 16 KiB per stage
 constexpr uint32_t kPdSBytes = 16384;    // P 8 KiB + dS 8 KiB per buffer
-constexpr uint32_t kSmemTiles = kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes;
+constexpr uint32_t kOutBytes = 32768;    // epilogue staging: dV tile 16 KiB + dK tile 16 KiB
+constexpr uint32_t kSmemTiles = kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes + kOutBytes;
 
 // TMEM columns: S / dP double buffered (64 columns each), accumulators double buffered
 __device__ __forceinline__ uint32_t col_s(int buf) { return buf * 128; }
@@ -107,12 +108,14 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __global__ void __launch_bounds__(kThreads, 1)
 sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapDO,
                       const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV,
                       const TcDkvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sKV = tiles;                               // K [2][64][128 B], V [2][64][128 B]
   uint8_t* sQdO = tiles + kKVBytes;                   // [stage]{ Q [2][64][128 B], dO [2][64][128 B] }
   uint8_t* sPdS = tiles + kKVBytes + kStages * kQdOBytes;   // [buffer]{ P [64 q][128 B], dS [64 q][128 B] } swizzled
+  uint8_t* sOut = sPdS + 2 * kPdSBytes;               // { dV, dK }[2][64 keys][128 B] swizzled, for the tile stores
 
   __shared__ uint64_t kv_full, kv_empty, qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
       pds_free[2], acc_full[2], acc_free[2];
@@ -124,6 +127,16 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    // The host sizes the dynamic segment as the tiles plus the padding up to the next 1 KiB
+    // boundary after the static variables; refuse to run if that did not work out.
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (tiles + kSmemTiles > smem_raw + dyn_bytes) {
+      if (threadIdx.x == 0) atomicExch(p.status, NSA_ERR_CUDA);
+      return;
+    }
+  }
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 258); }
@@ -435,15 +448,19 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (!ok) break;
       if (te == 0) TRACE(3, 16 + ic * 4 + 1);
       tc_fence_after();
+      // the staging tiles are free once the previous item's tile stores have read them
+      if (te == 0) bulk_wait_read_all();
+      named_barrier(3, 128);
 #pragma unroll
       for (int mat = 0; mat < 2; ++mat) {
-        char* outp = (mat == 0 ? p.dv : p.dk) + base;
+        uint8_t* box = sOut + mat * 16384 + (d >> 6) * 8192;
         const uint32_t col = mat == 0 ? col_dv(acc) : col_dk(acc);
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           uint32_t x[32];
           tmem_ld32_nowait(tm + lane_base + col + hc * 32, x);
           tmem_ld_wait();
+          if (mat == 1 && hc == 1) { tc_fence_before(); mbar_arrive(&acc_free[acc]); }
           // lanes d (even) and d+1 trade values so that each writes one packed pair of head dims
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -451,15 +468,24 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const float got = __shfl_xor_sync(0xffffffffu, (lane & 1) ? a : c, 1);
             const int key = hc * 32 + 2 * j + (lane & 1);
             const uint32_t w = (lane & 1) ? pack2<__nv_bfloat16>(got, c) : pack2<__nv_bfloat16>(a, got);
-            if (key < n_blk) *reinterpret_cast<uint32_t*>(outp + key * row_bytes + (d & ~1) * 2) = w;
+            *reinterpret_cast<uint32_t*>(box + key * 128 + ((((d & 63) >> 3) ^ (key & 7)) << 4) + (d & 6) * 2) = w;
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&acc_free[acc]);
-      if (te == 0) TRACE(3, 16 + ic * 4 + 2);
+      fence_async_smem();
+      named_barrier(3, 128);
+      if (te == 0) {
+        const int tok = static_cast<int>(t0);
+        for (int dh = 0; dh < 2; ++dh) {
+          tma_store_4d(&mapDV, sOut + dh * 8192, dh * 64, it.h, tok, it.b);
+          tma_store_4d(&mapDK, sOut + 16384 + dh * 8192, dh * 64, it.h, tok, it.b);
+        }
+        bulk_commit_group();
+        TRACE(3, 16 + ic * 4 + 2);
+      }
       ++ic;
     }
+    if (te == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -485,10 +511,17 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
   if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
   if (encode_tiled_fn() == nullptr) return NSA_OK;
-  CUtensorMap mapQ, mapDO, mapK, mapV;
+  CUtensorMap mapQ, mapDO, mapK, mapV, mapDK, mapDV;
   int rc;
   if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
   if ((rc = make_qkv_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
+  {
+    // dK / dV are contiguous [B, N, H, 128]: the same 64 x 64 boxes as the loads, used for tile stores
+    const int64_t N = kv->n_tokens;
+    const int64_t st[4] = {N * H * 128, static_cast<int64_t>(H) * 128, 128, 1};
+    if ((rc = make_qkv_maps(dk, st, nullptr, B, N, H, &mapDK, nullptr, nullptr))) return rc;
+    if ((rc = make_qkv_maps(dv, st, nullptr, B, N, H, &mapDV, nullptr, nullptr))) return rc;
+  }
   TcDkvParams p;
   p.groups = groups; p.offsets = offsets; p.lse = lse; p.delta = delta;
   p.dk = static_cast<char*>(dk); p.dv = static_cast<char*>(dv);
@@ -505,9 +538,12 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   const int64_t n_items = static_cast<int64_t>(B) * H * p.NS;
   if (n_items > 0x7fffffff) return NSA_OK;
   const int grid = static_cast<int>(n_items < sms ? n_items : sms);
-  const size_t smem = kSmemTiles + 1024;
+  // the tiles start at the first 1 KiB boundary after the kernel's static shared variables
+  cudaFuncAttributes fa;
+  NSA_CUDA_OK(cudaFuncGetAttributes(&fa, sel_bwd_dkv_tc_kernel));
+  const size_t smem = kSmemTiles + (1024 - fa.sharedSizeBytes % 1024) % 1024;
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  sel_bwd_dkv_tc_kernel<<<grid, kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, p);
+  sel_bwd_dkv_tc_kernel<<<grid, kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, mapDK, mapDV, p);
   NSA_LAUNCH_OK("sel_bwd_dkv_tc_kernel");
   *launched = true;
   return NSA_OK;
