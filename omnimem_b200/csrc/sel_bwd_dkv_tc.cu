@@ -10,6 +10,7 @@
 //   warp 8   producer: K, V tile of the item (TMA); per step the Q and dO rows of the group
 //            into a four-stage ring (TMA), plus each row's LSE and delta and the step's visible
 //            key count into the same stage (the whole warp loads them, two rows per lane)
+//   warp 11  scheduler: item tickets from the global counter, decoded a few items ahead
 //   warp 9   MMA issuer 1, per step:  S = Q K^T, dP = dO V^T          (M=64, N=64, K=128)
 //   warp 10  MMA issuer 2, per step:  dV^T += dO^T P,  dK^T += Q^T dS  (M=128 = head dim, N=64 keys, K=64 rows)
 //   warps 0-3  row arithmetic on the accumulator fragments (16 rows x 64 keys per warp):
@@ -42,13 +43,13 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 352;
-constexpr int kStages = 4;               // Q / dO ring
+constexpr int kThreads = 384;
+constexpr int kStages = 3;               // Q / dO ring
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
 constexpr uint32_t kQdOBytes = 32768;    // Q 16 KiB + dO 16 KiB per stage
 constexpr uint32_t kPdSBytes = 16384;    // P 8 KiB + dS 8 KiB per buffer
 constexpr uint32_t kOutBytes = 32768;    // epilogue staging: dV tile 16 KiB + dK tile 16 KiB
-constexpr uint32_t kSmemTiles = kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes + kOutBytes;
+constexpr uint32_t kSmemTiles = 2 * kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes + kOutBytes;
 
 // TMEM columns: S / dP double buffered (64 columns each), accumulators double buffered
 __device__ __forceinline__ uint32_t col_s(int buf) { return buf * 128; }
@@ -71,7 +72,7 @@ struct TcDkvParams {
   int32_t* counter;          // zeroed before the launch: next work item to hand out
 };
 
-struct Item { int b, h, blk, beg, n_ent, row; bool active; };
+struct Item { int b, h, blk, beg, n_ent, row, g0; bool active; };   // g0: first bucket entry (query group)
 
 // Decodes work item i (block fastest, then head, then batch) and its bucket.
 __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
@@ -91,6 +92,7 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
     if (page < 0) it.n_ent = 0;
   }
   it.active = it.n_ent > 0;
+  it.g0 = 0;
   return it;
 }
 // Work items are handed out through a global counter (buckets differ a lot in length, a static
@@ -98,8 +100,13 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
 // publishes it in a 4-deep shared-memory ring that the other roles follow; n_ent = -1 ends it.
 __device__ __forceinline__ Item fetch_item(const TcDkvParams& p, int64_t n_items) {
   const int64_t t = atomicAdd(p.counter, 1);
-  if (t < n_items) return get_item(p, t);
-  Item it{0, 0, 0, 0, -1, 0, false};
+  if (t < n_items) {
+    Item it = get_item(p, t);
+    if (it.active)
+      it.g0 = p.groups[(static_cast<int64_t>(it.b) * p.H + it.h) * p.MG * p.T + it.beg];
+    return it;
+  }
+  Item it{0, 0, 0, 0, -1, 0, 0, false};
   return it;
 }
 
@@ -112,12 +119,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                       const TcDkvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sKV = tiles;                               // K [2][64][128 B], V [2][64][128 B]
-  uint8_t* sQdO = tiles + kKVBytes;                   // [stage]{ Q [2][64][128 B], dO [2][64][128 B] }
-  uint8_t* sPdS = tiles + kKVBytes + kStages * kQdOBytes;   // [buffer]{ P [64 q][128 B], dS [64 q][128 B] } swizzled
+  uint8_t* sKV = tiles;                               // [buffer]{ K [2][64][128 B], V [2][64][128 B] }, item i in buffer i & 1
+  uint8_t* sQdO = tiles + 2 * kKVBytes;               // [stage]{ Q [2][64][128 B], dO [2][64][128 B] }
+  uint8_t* sPdS = sQdO + kStages * kQdOBytes;         // [buffer]{ P [64 q][128 B], dS [64 q][128 B] } swizzled
   uint8_t* sOut = sPdS + 2 * kPdSBytes;               // { dV, dK }[2][64 keys][128 B] swizzled, for the tile stores
 
-  __shared__ uint64_t kv_full, kv_empty, qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
+  __shared__ uint64_t kv_full[2], kv_empty[2], qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
       pds_free[2], acc_full[2], acc_free[2];
   __shared__ uint64_t sched_full[4], sched_empty[4];
   __shared__ Item s_items[4];
@@ -139,10 +146,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   }
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 258); }
-    mbar_init(&kv_full, 1); mbar_init(&kv_empty, 1);
+    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 259); }
     for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 2); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
       mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 128);
       mbar_init(&pds_full[i], 128); mbar_init(&pds_free[i], 1);
       mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 128);
@@ -165,36 +172,29 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     // ======================= producer (whole warp; lane 0 issues the copies) =======================
     uint32_t ic = 0, sc = 0;
     bool ok = true;
-    Item nxt{0, 0, 0, 0, -1, 0, false};
-    if (lane == 0) nxt = fetch_item(p, n_items);
     for (uint32_t n = 0; ok; ++n) {
-      Item it;
-      it.b = __shfl_sync(0xffffffffu, nxt.b, 0); it.h = __shfl_sync(0xffffffffu, nxt.h, 0);
-      it.blk = __shfl_sync(0xffffffffu, nxt.blk, 0); it.beg = __shfl_sync(0xffffffffu, nxt.beg, 0);
-      it.n_ent = __shfl_sync(0xffffffffu, nxt.n_ent, 0); it.row = __shfl_sync(0xffffffffu, nxt.row, 0);
-      it.active = it.n_ent > 0;
-      ok = __all_sync(0xffffffffu, mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort));
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
       if (!ok) break;
-      if (lane == 0) {
-        s_items[n & 3] = it;
-        mbar_arrive(&sched_full[n & 3]);
-      }
+      const Item it = s_items[n & 3];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sched_empty[n & 3]);
       if (it.n_ent < 0) break;
-      if (lane == 0) nxt = fetch_item(p, n_items);       // decoded while this item's copies are issued
       if (!it.active) continue;
       TRACE(2, 16 + sc * 4 + 0);
-      ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty, (ic & 1) ^ 1, abort));
+      const int kb = ic & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty[kb], ((ic >> 1) & 1) ^ 1, abort));
       if (!ok) break;
       TRACE(2, 16 + sc * 4 + 1);
       if (lane == 0) {
-        mbar_expect_tx(&kv_full, kKVBytes);
+        uint8_t* kvb = sKV + kb * kKVBytes;
+        mbar_expect_tx(&kv_full[kb], kKVBytes);
         for (int dh = 0; dh < 2; ++dh) {
           if (p.paged) {
-            tma_load_2d(sKV + dh * 8192, &mapK, dh * 64, it.row, &kv_full);
-            tma_load_2d(sKV + 16384 + dh * 8192, &mapV, dh * 64, it.row, &kv_full);
+            tma_load_2d(kvb + dh * 8192, &mapK, dh * 64, it.row, &kv_full[kb]);
+            tma_load_2d(kvb + 16384 + dh * 8192, &mapV, dh * 64, it.row, &kv_full[kb]);
           } else {
-            tma_load_4d(sKV + dh * 8192, &mapK, dh * 64, it.h, it.row, it.b, &kv_full);
-            tma_load_4d(sKV + 16384 + dh * 8192, &mapV, dh * 64, it.h, it.row, it.b, &kv_full);
+            tma_load_4d(kvb + dh * 8192, &mapK, dh * 64, it.h, it.row, it.b, &kv_full[kb]);
+            tma_load_4d(kvb + 16384 + dh * 8192, &mapV, dh * 64, it.h, it.row, it.b, &kv_full[kb]);
           }
         }
       }
@@ -202,21 +202,27 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
       const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
       const int64_t bh = (static_cast<int64_t>(it.b) * p.H + it.h) * p.M;
-      int g_next = bucket[0];
-      for (int t = 0; t < it.n_ent; ++t, ++sc) {
-        const int st = sc % kStages, ph = (sc / kStages) & 1;
-        const int g = g_next;
-        if (t + 1 < it.n_ent) g_next = bucket[t + 1];
+      // Bucket entries are read two steps ahead and the rows' LSE / delta (two rows per lane) one
+      // step ahead, so that none of these dependent global loads delays the copies of a step.
+      auto load_rows = [&](int g, float2 (&mt)[2]) {
         const int64_t m0 = static_cast<int64_t>(g) * p.G;
         const int nq = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
-        // the rows' LSE and delta travel with the stage: two rows per lane
-        float2 mt[2];
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int r = lane + 32 * k;
           mt[k].x = r < nq ? p.lse[bh + m0 + r] * kLog2e : INFINITY;
           mt[k].y = r < nq ? p.delta[bh + m0 + r] : 0.f;
         }
+      };
+      int g_cur = it.g0, g_next = it.n_ent > 1 ? bucket[1] : 0;
+      float2 mt_cur[2], mt_next[2];
+      load_rows(g_cur, mt_cur);
+      for (int t = 0; t < it.n_ent; ++t, ++sc) {
+        const int st = sc % kStages, ph = (sc / kStages) & 1;
+        const int g = g_cur;
+        const int g_after = (t + 2 < it.n_ent) ? bucket[t + 2] : 0;
+        if (t + 1 < it.n_ent) load_rows(g_next, mt_next);
+        const int64_t m0 = static_cast<int64_t>(g) * p.G;
         ok = __all_sync(0xffffffffu, mbar_wait(&qdo_empty[st], ph ^ 1, abort));
         if (!ok) break;
         TRACE(2, 16 + sc * 4 + 2);
@@ -234,8 +240,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           }
           s_nkv[st] = nkv;
         }
-        s_meta[st][lane] = mt[0];
-        s_meta[st][lane + 32] = mt[1];
+        s_meta[st][lane] = mt_cur[0];
+        s_meta[st][lane + 32] = mt_cur[1];
+        mt_cur[0] = mt_next[0]; mt_cur[1] = mt_next[1];
+        g_cur = g_next; g_next = g_after;
         __syncwarp();
         if (lane == 0) mbar_arrive(&qdo_full[st]);
       }
@@ -243,14 +251,13 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
     if (*abort && lane == 0) {
       // consumers have stopped: wait (bounded) for the copies still in flight
-      if (ic > 0) mbar_wait(&kv_full, (ic - 1) & 1, abort);
+      for (uint32_t u = (ic > 2 ? ic - 2 : 0); u < ic; ++u) mbar_wait(&kv_full[u & 1], (u >> 1) & 1, abort);
       for (uint32_t u = (sc > kStages ? sc - kStages : 0); u < sc; ++u) mbar_wait(&qdo_full[u % kStages], (u / kStages) & 1, abort);
     }
   } else if (warp == 9) {
     // ======================= MMA issuer 1: S and dP of every step =======================
     if (lane == 0) {
       constexpr uint32_t idesc_first = instr_desc_bf16(64, 64, 0, 0);     // both operands K-major
-      const uint64_t dK = smem_desc(smem_u32(sKV), 16, 1024), dV = smem_desc(smem_u32(sKV + 16384), 16, 1024);
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
@@ -260,8 +267,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (n_ent < 0) break;
         if (n_ent == 0) continue;
         TRACE(0, 16 + sc * 8 + 0);
-        if (!mbar_wait(&kv_full, ic & 1, abort)) break;
+        if (!mbar_wait(&kv_full[ic & 1], (ic >> 1) & 1, abort)) break;
         TRACE(0, 16 + sc * 8 + 1);
+        const uint32_t aKV = smem_u32(sKV + (ic & 1) * kKVBytes);
+        const uint64_t dK = smem_desc(aKV, 16, 1024), dV = smem_desc(aKV + 16384, 16, 1024);
         for (int t = 0; t < n_ent; ++t, ++sc) {
           const int st = sc % kStages, sb = sc & 1;
           if (!mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort)) { ok = false; break; }
@@ -280,10 +289,24 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 8192 + (kk & 3) * 32),
                     desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
           umma_commit(&sdp_full[sb]);
-          if (t == n_ent - 1) umma_commit(&kv_empty);
+          if (t == n_ent - 1) umma_commit(&kv_empty[ic & 1]);
           TRACE(0, 16 + sc * 8 + 3);
         }
         ++ic;
+      }
+    }
+  } else if (warp == 11) {
+    // ======================= scheduler =======================
+    // Takes tickets from the global counter, decodes each item (bucket bounds, page, first
+    // group) and publishes it in the 4-deep ring the other roles follow; the three dependent
+    // global loads behind one item are paid here, several items ahead of the copies.
+    if (lane == 0) {
+      for (uint32_t n = 0;; ++n) {
+        const Item it = fetch_item(p, n_items);
+        if (!mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort)) break;
+        s_items[n & 3] = it;
+        mbar_arrive(&sched_full[n & 3]);
+        if (it.n_ent < 0) break;
       }
     }
   } else if (warp == 10) {
@@ -359,6 +382,9 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld_16x256b_x8_nowait(tm + lane_base + col_dp(sb), y);
         const float2 m0 = s_meta[st][r0], m1 = s_meta[st][r1];
         const int nkv = s_nkv[st];
+        // the buffer's previous P / dS (two steps ago) must have been consumed: normally long true,
+        // so poll once here, where the round trip hides behind the TMEM load
+        const bool pds_ok = mbar_try(&pds_free[sb], ph ^ 1);
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&sdp_free[sb]);
@@ -401,9 +427,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           }
         }
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 2);
-        // the buffer's previous P / dS (two steps ago) must have been consumed
-        ok = __all_sync(0xffffffffu, mbar_wait(&pds_free[sb], ph ^ 1, abort));
-        if (!ok) break;
+        if (!__all_sync(0xffffffffu, pds_ok)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&pds_free[sb], ph ^ 1, abort));
+          if (!ok) break;
+        }
         if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 3);
         const uint32_t aP = smem_u32(sPdS + sb * kPdSBytes) + st_row * 128;
 #pragma unroll
@@ -419,7 +446,6 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   } else if (warp < 8) {
     // ======================= epilogue (warps 4-7): one head-dim lane per thread =======================
-    const int d = (warp - 4) * 32 + lane;
     const int te = threadIdx.x - 128;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t ic = 0;
@@ -451,24 +477,32 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       // the staging tiles are free once the previous item's tile stores have read them
       if (te == 0) bulk_wait_read_all();
       named_barrier(3, 128);
+      // Accumulator fragments (16 head-dim lanes x 64 keys per load) are packed to bf16 pairs of
+      // adjacent keys and stored TRANSPOSED, 8 x 8 at a time, into the [key][head dim] tiles.
 #pragma unroll
       for (int mat = 0; mat < 2; ++mat) {
-        uint8_t* box = sOut + mat * 16384 + (d >> 6) * 8192;
         const uint32_t col = mat == 0 ? col_dv(acc) : col_dk(acc);
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
+        for (int lh = 0; lh < 2; ++lh) {                 // lanes 0-15 and 16-31 of this warp's quadrant
           uint32_t x[32];
-          tmem_ld32_nowait(tm + lane_base + col + hc * 32, x);
+          tmem_ld_16x256b_x8_nowait(tm + lane_base + (static_cast<uint32_t>(lh * 16) << 16) + col, x);
           tmem_ld_wait();
-          if (mat == 1 && hc == 1) { tc_fence_before(); mbar_arrive(&acc_free[acc]); }
-          // lanes d (even) and d+1 trade values so that each writes one packed pair of head dims
+          if (mat == 1 && lh == 1) { tc_fence_before(); mbar_arrive(&acc_free[acc]); }
+          // x[4i], x[4i+1]: head dim D0 + lane/4, keys 8i + 2(lane%4), +1;  x[4i+2], x[4i+3]: head dim + 8
+          const int D0 = (warp - 4) * 32 + lh * 16;
+          const int dsel = D0 + ((lane >> 3) & 1) * 8;   // head dims of the matrix this lane addresses
+          const uint32_t boxa = smem_u32(sOut + mat * 16384 + (dsel >> 6) * 8192);
+          const uint32_t dchunk = static_cast<uint32_t>((dsel & 63) >> 3);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float a = __uint_as_float(x[2 * j]), c = __uint_as_float(x[2 * j + 1]);
-            const float got = __shfl_xor_sync(0xffffffffu, (lane & 1) ? a : c, 1);
-            const int key = hc * 32 + 2 * j + (lane & 1);
-            const uint32_t w = (lane & 1) ? pack2<__nv_bfloat16>(got, c) : pack2<__nv_bfloat16>(a, got);
-            *reinterpret_cast<uint32_t*>(box + key * 128 + ((((d & 63) >> 3) ^ (key & 7)) << 4) + (d & 6) * 2) = w;
+          for (int q = 0; q < 4; ++q) {
+            const int i0 = 2 * q, i1 = 2 * q + 1;
+            const uint32_t a0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0]), __uint_as_float(x[4 * i0 + 1]));
+            const uint32_t b0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0 + 2]), __uint_as_float(x[4 * i0 + 3]));
+            const uint32_t a1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1]), __uint_as_float(x[4 * i1 + 1]));
+            const uint32_t b1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1 + 2]), __uint_as_float(x[4 * i1 + 3]));
+            // matrices: (keys 8 i0.., dims D0..), (keys 8 i0.., dims D0+8..), (keys 8 i1.., D0..), (keys 8 i1.., D0+8..)
+            const int key = 8 * (2 * q + (lane >> 4)) + (lane & 7);
+            stmatrix_x4_trans(boxa + key * 128 + ((dchunk ^ static_cast<uint32_t>(key & 7)) << 4), a0, b0, a1, b1);
           }
         }
       }
