@@ -13,7 +13,8 @@
 //   warp 11  scheduler: item tickets from the global counter, decoded a few items ahead
 //   warp 9   MMA issuer 1, per step:  S = Q K^T, dP = dO V^T          (M=64, N=64, K=128)
 //   warp 10  MMA issuer 2, per step:  dV^T += dO^T P,  dK^T += Q^T dS  (M=128 = head dim, N=64 keys, K=64 rows)
-//   warps 0-3  row arithmetic on the accumulator fragments (16 rows x 64 keys per warp):
+//   warps 0-3 and 12-15  row arithmetic on the accumulator fragments (16 rows x 64 keys per warp;
+//            the first group takes the even steps, the second the odd ones):
 //            P = exp2(S c - LSE), dS = P (dP - delta) scale, stored as bf16 with stmatrix into
 //            the 128-byte-swizzled shared-memory tiles the second products read
 //   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the
@@ -43,7 +44,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr int kStages = 3;               // Q / dO ring
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
 constexpr uint32_t kQdOBytes = 32768;    // Q 16 KiB + dO 16 KiB per stage
@@ -146,7 +147,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   }
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 259); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 387); }
     for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 2); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
@@ -256,41 +257,94 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   } else if (warp == 9) {
     // ======================= MMA issuer 1: S and dP of every step =======================
-    if (lane == 0) {
+    // The whole warp runs the loop (warp-uniform control flow keeps the descriptor arithmetic in
+    // uniform registers); one elected lane issues.
+    {
       constexpr uint32_t idesc_first = instr_desc_bf16(64, 64, 0, 0);     // both operands K-major
+      const uint32_t el = elect_one();
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
-        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort))) break;
         const int n_ent = s_items[n & 3].n_ent;
-        mbar_arrive(&sched_empty[n & 3]);
+        __syncwarp();
+        if (el) mbar_arrive(&sched_empty[n & 3]);
         if (n_ent < 0) break;
         if (n_ent == 0) continue;
-        TRACE(0, 16 + sc * 8 + 0);
-        if (!mbar_wait(&kv_full[ic & 1], (ic >> 1) & 1, abort)) break;
-        TRACE(0, 16 + sc * 8 + 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[ic & 1], (ic >> 1) & 1, abort))) break;
         const uint32_t aKV = smem_u32(sKV + (ic & 1) * kKVBytes);
         const uint64_t dK = smem_desc(aKV, 16, 1024), dV = smem_desc(aKV + 16384, 16, 1024);
         for (int t = 0; t < n_ent; ++t, ++sc) {
           const int st = sc % kStages, sb = sc & 1;
-          if (!mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort)) { ok = false; break; }
+          ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort) &&
+                                       mbar_wait(&sdp_free[sb], ((sc >> 1) & 1) ^ 1, abort));
+          if (!ok) break;
           TRACE(0, 16 + sc * 8 + 2);
-          if (!mbar_wait(&sdp_free[sb], ((sc >> 1) & 1) ^ 1, abort)) { ok = false; break; }
           tc_fence_after();
           const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
           const uint64_t dQ = smem_desc(aQ, 16, 1024), dDO = smem_desc(aQ + 16384, 16, 1024);
           const uint32_t ts = tm + col_s(sb), tdp = tm + col_dp(sb);
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ss(ts, desc_advance(dQ, (kk >> 2) * 8192 + (kk & 3) * 32),
-                    desc_advance(dK, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ss(ts, desc_advance(dQ, (kk >> 2) * 8192 + (kk & 3) * 32),
+                      desc_advance(dK, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 8192 + (kk & 3) * 32),
-                    desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
-          umma_commit(&sdp_full[sb]);
-          if (t == n_ent - 1) umma_commit(&kv_empty[ic & 1]);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 8192 + (kk & 3) * 32),
+                      desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
+            umma_commit(&sdp_full[sb]);
+            if (t == n_ent - 1) umma_commit(&kv_empty[ic & 1]);
+          }
+          __syncwarp();
           TRACE(0, 16 + sc * 8 + 3);
+        }
+        ++ic;
+      }
+    }
+  } else if (warp == 10) {
+    // ======================= MMA issuer 2: dV^T and dK^T of every step =======================
+    // A warp of its own, so that these products start the moment P / dS are in shared memory
+    // while issuer 1 already waits for the tiles of a later step.
+    {
+      constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // both operands MN-major
+      const uint32_t el = elect_one();
+      uint32_t ic = 0, sc = 0;
+      bool ok = true;
+      for (uint32_t n = 0; ok; ++n) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort))) break;
+        const int n_ent = s_items[n & 3].n_ent;
+        __syncwarp();
+        if (el) mbar_arrive(&sched_empty[n & 3]);
+        if (n_ent < 0) break;
+        if (n_ent == 0) continue;
+        const int acc = ic & 1;
+        for (int t = 0; t < n_ent; ++t, ++sc) {
+          const int st = sc % kStages, pb = sc & 1;
+          ok = __all_sync(0xffffffffu, mbar_wait(&pds_full[pb], (sc >> 1) & 1, abort) &&
+                                       (t > 0 || mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)));
+          if (!ok) break;
+          TRACE(0, 16 + sc * 8 + 5);
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes), aP = smem_u32(sPdS + pb * kPdSBytes);
+          // A: Q^T / dO^T, head dim contiguous, two 64-column boxes 8 KiB apart; B: P / dS, keys contiguous
+          const uint64_t dQmn = smem_desc(aQ, 8192, 1024), dDOmn = smem_desc(aQ + 16384, 8192, 1024);
+          const uint64_t dP = smem_desc(aP, 16, 1024), dDS = smem_desc(aP + 8192, 16, 1024);
+          const uint32_t acc0 = t == 0 ? 0u : 1u;
+          const uint32_t tdv = tm + col_dv(acc), tdk = tm + col_dk(acc);
+          if (el) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
+            umma_commit(&qdo_empty[st]);
+            umma_commit(&pds_free[pb]);
+            if (t == n_ent - 1) umma_commit(&acc_full[acc]);
+          }
+          __syncwarp();
+          TRACE(0, 16 + sc * 8 + 6);
         }
         ++ic;
       }
@@ -351,16 +405,20 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         ++ic;
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < 4 || warp >= 12) {
     // ======================= row arithmetic: P and dS on accumulator fragments =======================
-    // Warp w owns rows 16w .. 16w+15 of the step's group (TMEM lanes 32w .. 32w+15 of an M=64
-    // accumulator); thread t holds rows 16w + t/4 and + 8, keys 8i + 2(t%4), +1 for i = 0..7.
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+    // Two groups of four warps: warps 0-3 take the even steps, warps 12-15 the odd ones (S/dP and
+    // P/dS are double buffered by step parity, so the groups never share a buffer).
+    // Warp w (of its group) owns rows 16w .. 16w+15 of the step's query group (TMEM lanes 32w ..
+    // 32w+15 of an M=64 accumulator); thread t holds rows 16w + t/4 and + 8, keys 8i + 2(t%4), +1.
+    const int grp = warp >= 12 ? 1 : 0, w4 = warp & 3;
+    const bool tracer = threadIdx.x == 0;
+    const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+    const int r0 = w4 * 16 + (lane >> 2), r1 = r0 + 8;
     const int cq = (lane & 3) * 2;
     // stmatrix: this thread supplies the address of row (lane%8) of matrix (lane/8); the four
     // matrices of one instruction are (rows +0, keys 8i), (rows +8, keys 8i), (rows +0, keys 8i+8), (rows +8, keys 8i+8)
-    const int st_row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int st_row = w4 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
     const int st_chunk = lane >> 4;                    // + 2 * instruction index
     uint32_t sc = 0;
     bool ok = true;
@@ -372,10 +430,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (n_ent < 0) break;
       for (int t = 0; t < n_ent; ++t, ++sc) {
         const int st = sc % kStages, sb = sc & 1, ph = (sc >> 1) & 1;
-        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 0);
+        if (sb != grp) continue;
+        if (tracer) TRACE(1, 16 + sc * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[sb], ph, abort));
         if (!ok) break;
-        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 1);
+        if (tracer) TRACE(1, 16 + sc * 8 + 1);
         tc_fence_after();
         uint32_t x[32], y[32];
         tmem_ld_16x256b_x8_nowait(tm + lane_base + col_s(sb), x);
@@ -426,12 +485,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             y[2 * i + 1] = d1;
           }
         }
-        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 2);
+        if (tracer) TRACE(1, 16 + sc * 8 + 2);
         if (!__all_sync(0xffffffffu, pds_ok)) {
           ok = __all_sync(0xffffffffu, mbar_wait(&pds_free[sb], ph ^ 1, abort));
           if (!ok) break;
         }
-        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 3);
+        if (tracer) TRACE(1, 16 + sc * 8 + 3);
         const uint32_t aP = smem_u32(sPdS + sb * kPdSBytes) + st_row * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -441,7 +500,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         fence_async_smem();                           // make the rows visible to the tensor core's reads
         mbar_arrive(&pds_full[sb]);
-        if (threadIdx.x == 0) TRACE(1, 16 + sc * 8 + 4);
+        if (tracer) TRACE(1, 16 + sc * 8 + 4);
       }
     }
   } else if (warp < 8) {

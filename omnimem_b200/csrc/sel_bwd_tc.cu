@@ -219,61 +219,75 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // read the dS written over it), warp 7 issues dP(t) as soon as the row threads have read
     // dP(t-1), warp 8 issues dQ(t) when dS(t) is in TMEM.  A K tile is held from S(t) to dQ(t),
     // hence the three-stage K ring.
-    if (lane == 0 && nb > 0) {
+    // Whole warps run these loops (warp-uniform control flow keeps descriptor arithmetic in uniform
+    // registers); one elected lane issues.
+    if (nb > 0) {
       constexpr uint32_t idesc_kk = instr_desc_bf16(128, 128, 0, 0);   // both operands K-major
       constexpr uint32_t idesc_mn = instr_desc_bf16(128, 128, 0, 1);   // B read MN-major
+      const uint32_t el = elect_one();
       if (warp == 5) {
         const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
-        bool ok = mbar_wait(&qdo_full, 0, abort);
+        bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort));
         TRACE(0, 0);
         for (int t = 0; ok && t < NT; ++t) {
           const int s = t & 1, ks = t % kStagesK;
-          if (!mbar_wait(&k_full[ks], (t / kStagesK) & 1, abort)) break;
-          if (t >= 2 && !mbar_wait(&s_free[s], ((t - 2) >> 1) & 1, abort)) break;      // dQ(t-2) done
+          ok = __all_sync(0xffffffffu, mbar_wait(&k_full[ks], (t / kStagesK) & 1, abort) &&
+                                       (t < 2 || mbar_wait(&s_free[s], ((t - 2) >> 1) & 1, abort)));   // dQ(t-2) done
+          if (!ok) break;
           tc_fence_after();
           TRACE(0, 8 + t * 8 + 0);
           const uint64_t dK = smem_desc(smem_u32(sK + ks * kTileBytes), 16, 1024);
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-            umma_ss(tm + kColS + s * 128, desc_advance(dQ, off), desc_advance(dK, off), idesc_kk, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+              umma_ss(tm + kColS + s * 128, desc_advance(dQ, off), desc_advance(dK, off), idesc_kk, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[s]);
           }
-          umma_commit(&s_full[s]);
+          __syncwarp();
           TRACE(0, 8 + t * 8 + 1);
         }
       } else if (warp == 7) {
         const uint64_t dDO = smem_desc(smem_u32(sDO), 16, 1024);
-        bool ok = mbar_wait(&qdo_full, 0, abort);
+        bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort));
         for (int t = 0; ok && t < NT; ++t) {
           const int s = t & 1;
-          if (!mbar_wait(&v_full[s], (t >> 1) & 1, abort)) break;
-          if (t >= 1 && !mbar_wait(&dp_free, (t - 1) & 1, abort)) break;                  // dP(t-1) has been read
+          ok = __all_sync(0xffffffffu, mbar_wait(&v_full[s], (t >> 1) & 1, abort) &&
+                                       (t < 1 || mbar_wait(&dp_free, (t - 1) & 1, abort)));             // dP(t-1) has been read
+          if (!ok) break;
           tc_fence_after();
           TRACE(0, 8 + t * 8 + 2);
           const uint64_t dV = smem_desc(smem_u32(sV + s * kTileBytes), 16, 1024);
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-            umma_ss(tm + kColDP, desc_advance(dDO, off), desc_advance(dV, off), idesc_kk, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+              umma_ss(tm + kColDP, desc_advance(dDO, off), desc_advance(dV, off), idesc_kk, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&dp_full);
+            umma_commit(&v_empty[s]);
           }
-          umma_commit(&dp_full);
-          umma_commit(&v_empty[s]);
+          __syncwarp();
           TRACE(0, 8 + t * 8 + 3);
         }
       } else {
         for (int t = 0; t < NT; ++t) {
           const int s = t & 1, ks = t % kStagesK;
-          if (!mbar_wait(&ds_full[s], (t >> 1) & 1, abort)) break;
+          if (!__all_sync(0xffffffffu, mbar_wait(&ds_full[s], (t >> 1) & 1, abort))) break;
           tc_fence_after();
           TRACE(0, 8 + t * 8 + 4);
           const uint64_t dKmn = smem_desc(smem_u32(sK + ks * kTileBytes), 16384, 1024);
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts(tm + kColDQ, tm + kColS + s * 128 + kk * 8, desc_advance(dKmn, kk * 2048), idesc_mn,
-                    (t > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&k_empty[ks]);
-          umma_commit(&s_free[s]);
-          if (t == NT - 1) umma_commit(&dq_final);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts(tm + kColDQ, tm + kColS + s * 128 + kk * 8, desc_advance(dKmn, kk * 2048), idesc_mn,
+                      (t > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&k_empty[ks]);
+            umma_commit(&s_free[s]);
+            if (t == NT - 1) umma_commit(&dq_final);
+          }
+          __syncwarp();
           TRACE(0, 8 + t * 8 + 5);
         }
       }

@@ -247,25 +247,31 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // Per step: S = [Q;Q] K^T (warp 5), softmax writes P over S, O += P V (warp 7).  The next S
     // overwrites P, so it is issued only after the P V product that reads it has completed.
     // Two issuing threads, because each passed barrier wait costs the thread a few hundred cycles.
-    if (lane == 0) {
+    // Whole warps run these loops (warp-uniform control flow keeps descriptor arithmetic in uniform
+    // registers); one elected lane issues.
+    {
+      const uint32_t el = elect_one();
       if (warp == 5) {
         constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
         const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
         const uint64_t dK = smem_desc(smem_u32(sK), 16, 1024);
-        bool ok = mbar_wait(&q_full, 0, abort);
+        bool ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, abort));
         TRACE(0, 0);
         for (int t = 0; ok && t < NT; ++t) {
           const uint32_t ph = t & 1;
-          if (!mbar_wait(&k_full, ph, abort)) break;
-          if (t > 0 && !mbar_wait(&pv_done, ph ^ 1, abort)) break;
+          ok = __all_sync(0xffffffffu, mbar_wait(&k_full, ph, abort) && (t == 0 || mbar_wait(&pv_done, ph ^ 1, abort)));
+          if (!ok) break;
           TRACE(0, 8 + t * 8 + 0);
           tc_fence_after();
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
-                    desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-          umma_commit(&s_full);
-          umma_commit(&k_empty);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                      desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+            umma_commit(&s_full);
+            umma_commit(&k_empty);
+          }
+          __syncwarp();
           TRACE(0, 8 + t * 8 + 1);
         }
       } else {
@@ -273,16 +279,18 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const uint64_t dV = smem_desc(smem_u32(sV), 16384, 1024);
         for (int t = 0; t < NT; ++t) {
           const uint32_t ph = t & 1;
-          if (!mbar_wait(&v_full, ph, abort)) break;
-          if (!mbar_wait(&p_full, ph, abort)) break;
+          if (!__all_sync(0xffffffffu, mbar_wait(&v_full, ph, abort) && mbar_wait(&p_full, ph, abort))) break;
           TRACE(0, 8 + t * 8 + 2);
           tc_fence_after();
+          if (el) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&v_empty);
-          umma_commit(&pv_done);
-          if (t == NT - 1) umma_commit(&o_final);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&v_empty);
+            umma_commit(&pv_done);
+            if (t == NT - 1) umma_commit(&o_final);
+          }
+          __syncwarp();
           TRACE(0, 8 + t * 8 + 3);
         }
       }
