@@ -367,3 +367,38 @@ def test_config2_full_size_properties(dev):
     s = masked_scores(qp.cpu(), kp.cpu(), D ** -0.5, block_size=bs, chunk_size=frame, chunk_size_k=frame,
                       causal=True, q_chunk_offset=18, q_group_size=G)
     assert_topk_parity(idx, s, T)
+
+
+@pytest.mark.gpu
+def test_captured_step_replays_the_eager_result():
+    """A CUDA-graph replay of pooling + top-k + forward + backward gives the eager tensors."""
+    from omnimem_b200 import ops
+    from omnimem_b200.graph import CapturedStep
+    torch.manual_seed(7)
+    dev = torch.device("cuda")
+    B, M, N, H, D, T = 1, 256, 1024, 4, 128, 4
+    q = torch.randn(B, M, H, D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, N, H, D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(B, N, H, D, device=dev, dtype=torch.bfloat16)
+    do = torch.randn(B, M, H, D, device=dev, dtype=torch.bfloat16)
+    scale = D ** -0.5
+
+    def step():
+        qp, kp = ops.pool_rows(q, 64), ops.pool_rows(k, 64)
+        idx = ops.topk(qp, kp, T, scale, 64, 1 << 30, 1 << 30, False, q_group_size=64)
+        kv = ops.DenseKV(k, v)
+        out, lse = ops.sel_fwd(q, kv, idx, 64, 1, scale, False, 64)
+        groups, offsets = ops.inverted_index(idx, N // 64, 64, 1, False, 64)
+        dq, delta = ops.sel_bwd_dq(q, kv, idx, out, lse, do, 64, 1, scale, False, 64)
+        dk, dv = ops.sel_bwd_dkv(q, kv, groups, offsets, lse, delta, do, T, 64, 1, scale, False, 64)
+        return idx, out, dq, dk, dv
+
+    eager = [x.clone() for x in step()]
+    cap = CapturedStep(step)
+    q.copy_(torch.randn_like(q))          # new inputs at the same addresses
+    eager2 = [x.clone() for x in step()]
+    replayed = [x.clone() for x in cap.replay()]
+    torch.cuda.synchronize()
+    assert any(not torch.equal(a, b) for a, b in zip(eager, eager2))
+    for a, b in zip(eager2, replayed):
+        assert torch.equal(a, b)
