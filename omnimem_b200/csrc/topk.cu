@@ -222,7 +222,10 @@ __device__ __forceinline__ RowMask make_row_mask(const Mask& m, int g) {
 
 // Visibility of the key block with GLOBAL id `bid` for a query row.
 __device__ __forceinline__ bool visible(const Mask& m, const RowMask& r, int bid) {
-  const int k_cid = static_cast<int>((static_cast<int64_t>(bid) * m.block_size) / m.chunk_size_k);
+  // (32-bit division when the token index fits: the 64-bit one is a long emulated sequence)
+  const int64_t tok = static_cast<int64_t>(bid) * m.block_size;
+  const int k_cid = tok <= 0x7fffffff ? static_cast<int>(static_cast<uint32_t>(tok) / static_cast<uint32_t>(m.chunk_size_k))
+                                      : static_cast<int>(tok / m.chunk_size_k);
   const bool k_clean = m.tf ? (k_cid < m.k_half) : true;
   const int k_rel = (m.tf && !k_clean) ? k_cid - m.k_half : k_cid;
   bool valid;
@@ -352,7 +355,9 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
 }
 
 // Rows with at most 32*ITEMS candidates: one warp per row, candidates in registers, no block-wide
-// barrier.  Same keys and order as select_kernel.
+// barrier.  Same keys and order as select_kernel.  Per round the warp's best key is found with two
+// warp reductions (max of the score half, then max of the id half among the lanes that hold it);
+// the lane that owned it clears the key and rebuilds its own maximum with a reduction tree.
 template <int ITEMS, bool MERGE>
 __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -370,47 +375,67 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     rm = make_row_mask(p.mask, g);
     srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC;
   }
+  // all loads first, unconditionally (clamped index), so that they are in flight together
+  float vals[ITEMS];
+  int cids[ITEMS];
+  const int64_t last = p.NC - 1;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    int64_t c = lane + 32 * i;
+    c = c < last ? c : last;
+    if (MERGE) {
+      const int seg = static_cast<int>(c) / p.seg_len;
+      const int64_t off = static_cast<int64_t>(seg) * p.seg_stride + (static_cast<int>(c) - seg * p.seg_len);
+      cids[i] = p.cand_ids[row * p.seg_len + off];
+      vals[i] = srow[off];
+    } else {
+      cids[i] = 0;
+      vals[i] = srow[c];
+    }
+  }
   unsigned long long keys[ITEMS];
-  unsigned long long local = 0ull;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const int64_t c = lane + 32 * i;
     unsigned long long k = 0ull;
     if (c < p.NC) {
       if (MERGE) {
-        const int64_t off = (c / p.seg_len) * p.seg_stride + (c % p.seg_len);
-        const int id = p.cand_ids[row * p.seg_len + off];
-        k = id < 0 ? 0ull : pack_key(srow[off], id);
+        k = cids[i] < 0 ? 0ull : pack_key(vals[i], cids[i]);
       } else {
         const int bid = p.mask.id_base + static_cast<int>(c) * p.mask.id_stride;
-        k = visible(p.mask, rm, bid) ? pack_key(srow[c], bid) : 0ull;
+        k = visible(p.mask, rm, bid) ? pack_key(vals[i], bid) : 0ull;
       }
     }
     keys[i] = k;
-    local = k > local ? k : local;
   }
+  auto lane_max = [&]() -> unsigned long long {
+    unsigned long long t[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) t[i] = keys[i];
+#pragma unroll
+    for (int w = ITEMS / 2; w >= 1; w >>= 1)
+#pragma unroll
+      for (int i = 0; i < w; ++i) t[i] = t[i] > t[i + w] ? t[i] : t[i + w];
+    return t[0];
+  };
+  unsigned long long local = lane_max();
   int32_t* oi = p.out_idx + row * p.topk;
   float* os = p.out_scores ? p.out_scores + row * p.topk : nullptr;
   int r = 0;
   for (; r < p.topk; ++r) {
-    unsigned long long best = local;
-#pragma unroll
-    for (int d = 16; d; d >>= 1) {
-      const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, d);
-      best = o > best ? o : best;
-    }
-    if (best == 0ull) break;
+    const uint32_t lhi = static_cast<uint32_t>(local >> 32), llo = static_cast<uint32_t>(local);
+    const uint32_t bhi = __reduce_max_sync(0xffffffffu, lhi);
+    if (bhi == 0u) break;                                  // the score half of a real key is never 0
+    const uint32_t blo = __reduce_max_sync(0xffffffffu, lhi == bhi ? llo : 0u);
+    const unsigned long long best = (static_cast<unsigned long long>(bhi) << 32) | blo;
     if (lane == 0) {
       oi[r] = key_id(best);
       if (os) os[r] = key_score(best);
     }
     if (local == best) {            // keys are unique: exactly one lane owns the winner
-      local = 0ull;
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i) {
-        if (keys[i] == best) keys[i] = 0ull;
-        local = keys[i] > local ? keys[i] : local;
-      }
+      for (int i = 0; i < ITEMS; ++i) keys[i] = keys[i] == best ? 0ull : keys[i];
+      local = lane_max();
     }
   }
   for (int i = r + lane; i < p.topk; i += 32) {
