@@ -477,6 +477,16 @@ int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* k
   return NSA_OK;
 }
 
+// 4-D map of a [B,M,H,128] bf16 tensor whose box holds `box_rows` rows of one head (64 columns):
+// for tile stores of a query group shorter than 64 rows, which must not touch the next group.
+int make_rows_map(const void* q, const int64_t* q_stride, int B, int64_t M, int H, int box_rows, CUtensorMap* map) {
+  const uint32_t box4[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+  const uint64_t dims[4] = {128, static_cast<uint64_t>(H), static_cast<uint64_t>(M), static_cast<uint64_t>(B)};
+  const uint64_t st[3] = {static_cast<uint64_t>(q_stride[2]) * 2, static_cast<uint64_t>(q_stride[1]) * 2,
+                          B > 1 ? static_cast<uint64_t>(q_stride[0]) * 2 : static_cast<uint64_t>(q_stride[1]) * 2 * M};
+  return tc::make_bf16_map(map, q, 4, dims, st, box4);
+}
+
 // Returns NSA_OK after launching, or NSA_ERR_UNSUPPORTED (without setting an error) when the
 // tensor-core kernel does not cover the call and the caller should use the general kernel.
 int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* ids,
