@@ -208,6 +208,22 @@ int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const nsa_kv_sourc
 int nsa_merge_partials(const void* outs, const float* lses, int32_t R, int32_t B, int64_t M,
                        int32_t H, int32_t D, void* out, float* lse, int32_t dtype, void* stream);
 
+/* Three-branch gate + sum that consumes the selection output
+ * (models/transformers/causal_wan_nsa_model.py:378-386, 541-546):
+ *   g = clamp(g_logits, -10, 10); (g_cmp, g_slc, g_swa) = sigmoid(g) (softmax = 0) or softmax over
+ *   the three logits (softmax = 1); x = g_cmp*o_cmp + g_slc*o_slc + g_swa*o_swa.
+ * g_logits [rows, 3], branches and x [rows, D] contiguous in `dtype` (bf16 / fp16), rows = B*M*H;
+ * a NULL branch is skipped (the reference's skip_module), its gate still takes part in the softmax.
+ * Products and partial sums are rounded to `dtype` left to right, as the eager expression does. */
+int nsa_gate_combine(const void* g_logits, const void* o_cmp, const void* o_slc, const void* o_swa,
+                     void* x, int64_t rows, int32_t D, int32_t softmax, int32_t dtype, void* stream);
+/* Backward of nsa_gate_combine: d_o_i = g_i * dx (NULL = not wanted), d_g_logits [rows, 3]
+ * (zero where a logit lies outside [-10, 10]).  D = 64, 128 or 256. */
+int nsa_gate_combine_bwd(const void* g_logits, const void* o_cmp, const void* o_slc,
+                         const void* o_swa, const void* dx, void* d_g_logits, void* d_o_cmp,
+                         void* d_o_slc, void* d_o_swa, int64_t rows, int32_t D, int32_t softmax,
+                         int32_t dtype, void* stream);
+
 /* Block id -> int64 byte address tables, same contract as build_ptr_table_cuda
  * (ptr_table.cu:59-127): 0 for id < 0, id >= n_blocks_per_head[h], chunk >= max_chunks or a
  * zero chunk base. */

@@ -396,3 +396,53 @@ def sel_bwd_dkv(q, kv, groups, offsets, lse, delta, d_out, T: int, block_size: i
              _i32(chunk_size, "chunk_size"), int(bool(causal)), _i32(group_size, "group_size"), float(scale),
              ws.data_ptr(), 256, _dtype(q), _stream(q))
     return dk, dv
+
+
+def _gate_args(g_logits, o_cmp, o_slc, o_swa):
+    present = [t for t in (o_cmp, o_slc, o_swa) if t is not None]
+    if not present:
+        raise ValueError("gate_combine: at least one branch is needed")
+    ref = present[0]
+    _require_cuda(g_logits, *present)
+    if g_logits.shape[-1] != 3 or tuple(g_logits.shape[:-1]) != tuple(ref.shape[:-1]):
+        raise ValueError(f"gate_combine: gate logits {tuple(g_logits.shape)} do not match branches {tuple(ref.shape)}")
+    for t in present:
+        if t.shape != ref.shape or t.dtype != ref.dtype:
+            raise ValueError("gate_combine: branches must share shape and dtype")
+    if g_logits.dtype != ref.dtype:
+        raise ValueError("gate_combine: gate logits must have the branches' dtype")
+    cont = lambda t: None if t is None else t.contiguous()
+    return g_logits.contiguous(), cont(o_cmp), cont(o_slc), cont(o_swa), ref
+
+
+def gate_combine(g_logits: torch.Tensor, o_cmp: Optional[torch.Tensor], o_slc: Optional[torch.Tensor],
+                 o_swa: Optional[torch.Tensor], gate_mode: str = "sigmoid") -> torch.Tensor:
+    """x = g_cmp*o_cmp + g_slc*o_slc + g_swa*o_swa with (g_cmp, g_slc, g_swa) = sigmoid / softmax of
+    clamp(g_logits, -10, 10); g_logits [..., H, 3], branches [..., H, D]; None skips a branch
+    (causal_wan_nsa_model.py:378-386, 541-546)."""
+    if gate_mode not in ("sigmoid", "softmax"):
+        raise NotImplementedError(f"gate_mode={gate_mode!r} not implemented")
+    g, a, b, c, ref = _gate_args(g_logits, o_cmp, o_slc, o_swa)
+    x = torch.empty_like(ref, memory_format=torch.contiguous_format)
+    D = ref.shape[-1]
+    with torch.cuda.device(ref.device):
+        call("nsa_gate_combine", g.data_ptr(), _ptr(a), _ptr(b), _ptr(c), x.data_ptr(), ref.numel() // D, D,
+             1 if gate_mode == "softmax" else 0, _dtype(ref), _stream(ref))
+    return x
+
+
+def gate_combine_bwd(g_logits, o_cmp, o_slc, o_swa, dx: torch.Tensor, gate_mode: str = "sigmoid"):
+    """Gradients of gate_combine: (d_g_logits, d_o_cmp, d_o_slc, d_o_swa); None for skipped branches."""
+    if gate_mode not in ("sigmoid", "softmax"):
+        raise NotImplementedError(f"gate_mode={gate_mode!r} not implemented")
+    g, a, b, c, ref = _gate_args(g_logits, o_cmp, o_slc, o_swa)
+    _require_cuda(dx)
+    dx = dx.contiguous()
+    dg = torch.empty_like(g)
+    outs = [None if t is None else torch.empty_like(t) for t in (a, b, c)]
+    D = ref.shape[-1]
+    with torch.cuda.device(ref.device):
+        call("nsa_gate_combine_bwd", g.data_ptr(), _ptr(a), _ptr(b), _ptr(c), dx.data_ptr(), dg.data_ptr(),
+             _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), ref.numel() // D, D,
+             1 if gate_mode == "softmax" else 0, _dtype(ref), _stream(ref))
+    return dg, outs[0], outs[1], outs[2]

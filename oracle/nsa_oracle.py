@@ -339,6 +339,29 @@ def merge_partials(outs: List[torch.Tensor], lses: List[torch.Tensor]):
 
 
 # --------------------------------------------------------------------------------------
+# gate + sum of the three branches (a16)
+# --------------------------------------------------------------------------------------
+def gate_combine(g_logits: torch.Tensor, o_cmp, o_slc, o_swa, gate_mode: str = "sigmoid"):
+    """The reference's expression, on CPU tensors of the activations' dtype
+    (causal_wan_nsa_model.py:378-386 for the gates, 541-546 for the sum; a None branch is the
+    skipped module).  g_logits [..., H, 3], branches [..., H, D]."""
+    g = torch.clamp(g_logits, min=-10.0, max=10.0)
+    if gate_mode == "sigmoid":
+        g_cmp, g_slc, g_swa = g.sigmoid().unbind(-1)
+    elif gate_mode == "softmax":
+        g_cmp, g_slc, g_swa = g.softmax(dim=-1).unbind(-1)
+    else:
+        raise NotImplementedError(f"{gate_mode=} not implemented")
+    x = None
+    for gt, o in ((g_cmp, o_cmp), (g_slc, o_slc), (g_swa, o_swa)):
+        if o is None:
+            continue
+        term = gt.unsqueeze(-1) * o
+        x = term if x is None else x + term
+    return x
+
+
+# --------------------------------------------------------------------------------------
 # inverted index (a11) and pointer table (a9)
 # --------------------------------------------------------------------------------------
 def inverted_index(block_indices: torch.Tensor, NS: int, block_size: int, chunk_size: int,
