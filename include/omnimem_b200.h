@@ -202,7 +202,30 @@ int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const nsa_kv_sourc
                     float scale, void* workspace, size_t workspace_bytes, int32_t dtype,
                     void* stream);
 
-/* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
+/* dK/dV of the pointer path (sel_bwd_ptr_cuda, selection_bwd.cu:1409-1527; accessor
+ * bwd_common.cuh:64-121).  The K/V block with id `bid` of head h and its fp32 gradient scratch are
+ * found through four [H, MAXB] tables of int64 byte addresses (element strides base_stride[0..1]):
+ * block-level (blocks_per_chunk = 0: entry bid) or chunk-level (entry bid / blocks_per_chunk plus
+ * (bid % blocks_per_chunk) * in_chunk_block_bytes_*); batch b adds b * batch_stride_*_bytes.
+ * A block whose id is >= n_blocks_per_head[h] (table may be NULL), whose entry is >= max_base or
+ * whose four addresses are not all non-zero is skipped.  Every block with a non-empty bucket gets
+ * its [block_size, D] fp32 tiles WRITTEN (token stride stride_dbn floats); other scratch is left
+ * untouched.  groups / offsets are nsa_inverted_index's output for NS blocks, chunk_size 1,
+ * causal 0 (the pointer path carries no token ids).  dQ of the pointer path is nsa_sel_bwd_dq
+ * with an NSA_KV_PTR source. */
+int nsa_sel_bwd_dkv_ptr(const void* q, const int64_t q_stride[3], const int64_t* base_k,
+                        const int64_t* base_v, const int64_t* base_dk, const int64_t* base_dv,
+                        const int64_t base_stride[2], int32_t max_base,
+                        const int32_t* n_blocks_per_head, int64_t batch_stride_kv_bytes,
+                        int64_t batch_stride_dkv_bytes, int64_t stride_bn, int64_t stride_dbn,
+                        int32_t blocks_per_chunk, int64_t in_chunk_block_bytes_kv,
+                        int64_t in_chunk_block_bytes_dkv, const int32_t* groups,
+                        const int32_t* offsets, int64_t NS, const float* lse, const float* delta,
+                        const void* d_out, const int64_t do_stride[3], int32_t B, int64_t M,
+                        int32_t H, int32_t D, int32_t T, int32_t block_size, int32_t group_size,
+                        float scale, int32_t dtype, void* stream);
+
+/* Merge R attention partials over disjoint key sets/* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
  * lses float [R][B,H,M] -> out, lse.  O = sum_r exp(lse_r - lse) O_r.  New for
  * block-sharded KV (no counterpart: the reference never splits one row's keys). */
 int nsa_merge_partials(const void* outs, const float* lses, int32_t R, int32_t B, int64_t M,

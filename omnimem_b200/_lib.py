@@ -69,6 +69,9 @@ PROTOTYPES = {
     "nsa_sel_bwd_dkv": (_i32, [_vp, _S3, C.POINTER(KVSource), _vp, _vp, _vp, _vp, _vp, _S3, _vp, _vp,
                                _i32, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _sz, _i32, _vp]),
     "nsa_merge_partials": (_i32, [_vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),
+    "nsa_sel_bwd_dkv_ptr": (_i32, [_vp, _S3, _vp, _vp, _vp, _vp, _S3, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _i64,
+                                   _i64, _vp, _vp, _i64, _vp, _vp, _vp, _S3, _i32, _i64, _i32, _i32, _i32, _i32, _i32,
+                                   _f32, _i32, _vp]),
     "nsa_gate_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "nsa_gate_combine_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "nsa_build_ptr_table": (_i32, [_vp, _S3, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64,

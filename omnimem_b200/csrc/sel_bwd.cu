@@ -195,6 +195,19 @@ struct BwdParams {
   int B, H, T, block_size, chunk_size, causal, G, MG;
   int64_t M, NS;
   float scale, scale_log2;
+  // dK/dV kernel only, pointer mode (selection_bwd.cu:1409-1527, bwd_common.cuh:64-121): K/V blocks
+  // and the fp32 gradient scratch of a block are found through [H, MAXB] tables of byte addresses
+  // (block-level, or chunk-level plus an in-chunk offset); a zero or out-of-range entry skips the block.
+  struct Tables {
+    int on;
+    const int64_t *base_k, *base_v, *base_dk, *base_dv;
+    int64_t base_sh, base_sb;
+    int max_base;
+    const int32_t* n_blocks_per_head;
+    int64_t batch_kv_bytes, batch_dkv_bytes, in_chunk_kv_bytes, in_chunk_dkv_bytes;
+    int blocks_per_chunk;
+    int64_t s_bn, s_dbn;        // elements between tokens: K/V blocks, fp32 scratch
+  } tab;
 };
 
 template <typename T, int D>
@@ -390,7 +403,7 @@ __global__ void __launch_bounds__(128) sel_bwd_dkv_kernel(const BwdParams p, int
   auto stageD = [&](int s) { return sQd + (s * 2 + 1) * QT * PITCH; };
 
   const int64_t t0 = static_cast<int64_t>(blk) * p.block_size;
-  const int n_blk = static_cast<int>(min64(p.block_size, p.kv.n_tokens - t0));  // tokens that exist
+  const int n_blk = p.tab.on ? p.block_size : static_cast<int>(min64(p.block_size, p.kv.n_tokens - t0));  // tokens that exist
   const int row_lo = kt * kTileRows;                        // first block row of this tile
   const int n_rows = max(0, min(kTileRows, n_blk - row_lo)); // rows this tile owns
   if (n_rows == 0) return;
@@ -404,7 +417,37 @@ __global__ void __launch_bounds__(128) sel_bwd_dkv_kernel(const BwdParams p, int
   const int beg = offs[blk], n_ent = offs[blk + 1] - beg;
   const int32_t* bucket = p.groups + row * static_cast<int64_t>(p.MG) * p.T + beg;
 
-  const BlockRef br = resolve_block<ESZ>(p.kv, b, h, blk, D, p.block_size, 1, false, 0);
+  BlockRef br{nullptr, nullptr, 0};
+  float* fdk = nullptr;
+  float* fdv = nullptr;
+  if (p.tab.on) {
+    const auto& tb = p.tab;
+    if (tb.n_blocks_per_head == nullptr || blk < tb.n_blocks_per_head[h]) {
+      int64_t idx = blk, off_kv = 0, off_dkv = 0;
+      if (tb.blocks_per_chunk > 0) {
+        idx = blk / tb.blocks_per_chunk;
+        const int64_t in_chunk = blk - idx * tb.blocks_per_chunk;
+        off_kv = in_chunk * tb.in_chunk_kv_bytes;
+        off_dkv = in_chunk * tb.in_chunk_dkv_bytes;
+      }
+      if (idx < tb.max_base) {
+        const int64_t o = static_cast<int64_t>(h) * tb.base_sh + idx * tb.base_sb;
+        const int64_t bk = tb.base_k[o], bv = tb.base_v[o], bdk = tb.base_dk[o], bdv = tb.base_dv[o];
+        if (bk != 0 && bv != 0 && bdk != 0 && bdv != 0) {     // all four or nothing
+          const int64_t okv = static_cast<int64_t>(b) * tb.batch_kv_bytes + off_kv;
+          const int64_t odkv = static_cast<int64_t>(b) * tb.batch_dkv_bytes + off_dkv;
+          br.k = reinterpret_cast<const char*>(static_cast<uintptr_t>(bk + okv));
+          br.v = reinterpret_cast<const char*>(static_cast<uintptr_t>(bv + okv));
+          br.n_vis = p.block_size;
+          fdk = reinterpret_cast<float*>(static_cast<uintptr_t>(bdk + odkv)) + static_cast<int64_t>(row_lo) * tb.s_dbn;
+          fdv = reinterpret_cast<float*>(static_cast<uintptr_t>(bdv + odkv)) + static_cast<int64_t>(row_lo) * tb.s_dbn;
+        }
+      }
+    }
+    if (n_ent == 0 || br.k == nullptr) return;      // the scratch of an untouched block is left as it is
+  } else {
+    br = resolve_block<ESZ>(p.kv, b, h, blk, D, p.block_size, 1, false, 0);
+  }
   if (n_ent == 0 || br.k == nullptr) {
     for (int i = threadIdx.x; i < n_rows * (D / 8); i += blockDim.x) {
       const int r = i / (D / 8), c = i % (D / 8);
@@ -434,8 +477,8 @@ __global__ void __launch_bounds__(128) sel_bwd_dkv_kernel(const BwdParams p, int
 
   const int spg = (p.G + QT - 1) / QT;      // query sub-tiles per group
   const int n_items = n_ent * spg;
-  const int64_t k_row_bytes = kv_row_bytes(p.kv, false, D, ESZ);
-  const int64_t v_row_bytes = kv_row_bytes(p.kv, true, D, ESZ);
+  const int64_t k_row_bytes = p.tab.on ? p.tab.s_bn * ESZ : kv_row_bytes(p.kv, false, D, ESZ);
+  const int64_t v_row_bytes = p.tab.on ? p.tab.s_bn * ESZ : kv_row_bytes(p.kv, true, D, ESZ);
 
   auto issue_item = [&](int it, int stg) {
     const int g = entry(it / spg), sub = it % spg;
@@ -588,7 +631,15 @@ __global__ void __launch_bounds__(128) sel_bwd_dkv_kernel(const BwdParams p, int
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int krow = warp * 16 + gid + 8 * r;
-      if (krow < n_rows) {
+      if (krow < n_rows && p.tab.on) {
+        float* kr = fdk + static_cast<int64_t>(krow) * p.tab.s_dbn;
+        float* vr = fdv + static_cast<int64_t>(krow) * p.tab.s_dbn;
+#pragma unroll
+        for (int n = 0; n < DN; ++n) {
+          *reinterpret_cast<float2*>(kr + n * 8 + 2 * t4) = make_float2(dk[n][2 * r], dk[n][2 * r + 1]);
+          *reinterpret_cast<float2*>(vr + n * 8 + 2 * t4) = make_float2(dv[n][2 * r], dv[n][2 * r + 1]);
+        }
+      } else if (krow < n_rows) {
         char* kr = dk_base + krow * out_row_bytes;
         char* vr = dv_base + krow * out_row_bytes;
 #pragma unroll
@@ -742,7 +793,7 @@ extern "C" size_t nsa_sel_bwd_workspace_bytes(int32_t B, int64_t M, int32_t H, i
 
 static int bwd_common_checks(const char* op, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
                              int32_t block_size, int32_t chunk_size, int32_t group_size, int32_t dtype,
-                             const nsa_kv_source* kv) {
+                             const nsa_kv_source* kv, bool allow_ptr = false) {
   NSA_REQUIRE(B >= 0 && M >= 0 && H >= 0, NSA_ERR_INVALID, "%s: negative size", op);
   NSA_REQUIRE(group_size >= 1 && group_size <= 128, NSA_ERR_INVALID,
               "%s: group_size must be in [1,128], got %d", op, group_size);
@@ -752,9 +803,9 @@ static int bwd_common_checks(const char* op, int32_t B, int64_t M, int32_t H, in
   NSA_REQUIRE(D == 64 || D == 128, NSA_ERR_UNSUPPORTED, "%s: head dim %d not built (64, 128)", op, D);
   NSA_REQUIRE(kv != nullptr, NSA_ERR_INVALID, "%s: kv source is null", op);
   NSA_REQUIRE(B <= 65535 && H <= 65535, NSA_ERR_INVALID, "%s: B and H must be <= 65535", op);
-  NSA_REQUIRE(kv->mode != NSA_KV_PTR, NSA_ERR_UNSUPPORTED,
-              "%s: pointer-table K/V is forward only; use a paged or dense source", op);
-  NSA_REQUIRE(kv->mode == NSA_KV_DENSE || B == 1, NSA_ERR_INVALID, "%s: paged K/V needs B == 1", op);
+  NSA_REQUIRE(kv->mode != NSA_KV_PTR || allow_ptr, NSA_ERR_UNSUPPORTED,
+              "%s: per-slot pointer tables serve the forward and dQ; dK/dV takes block base tables (nsa_sel_bwd_dkv_ptr)", op);
+  NSA_REQUIRE(kv->mode != NSA_KV_PAGED || B == 1, NSA_ERR_INVALID, "%s: paged K/V needs B == 1", op);
   NSA_REQUIRE(cdiv64(M, group_size) <= 0x7fffffff && cdiv64(kv->n_tokens, block_size) <= 0x7fffffff, NSA_ERR_INVALID,
               "%s: too many groups / blocks", op);
   return NSA_OK;
@@ -769,9 +820,9 @@ extern "C" int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const ns
                               int32_t causal, int32_t group_size, float scale, int32_t dtype,
                               void* stream) {
   int rc;
-  if ((rc = bwd_common_checks("sel_bwd_dq", B, M, H, D, T, block_size, chunk_size, group_size, dtype, kv))) return rc;
+  if ((rc = bwd_common_checks("sel_bwd_dq", B, M, H, D, T, block_size, chunk_size, group_size, dtype, kv, true))) return rc;
   if (B == 0 || H == 0 || M == 0) return NSA_OK;
-  NSA_REQUIRE(block_indices && lse && delta, NSA_ERR_INVALID, "sel_bwd_dq: null pointer");
+  NSA_REQUIRE((block_indices || kv->mode == NSA_KV_PTR) && lse && delta, NSA_ERR_INVALID, "sel_bwd_dq: null pointer");
   const int esz = 2;
   if ((rc = check_strides16("q", q, q_stride, 3, esz))) return rc;
   if ((rc = check_strides16("out", out, out_stride, 3, esz))) return rc;
@@ -842,6 +893,57 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
   p.G = group_size; p.MG = static_cast<int>(cdiv64(M, group_size)); p.M = M; p.NS = cdiv64(N, block_size);
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   return dispatch_bwd<false>(p, dtype, D, s);
+}
+
+extern "C" int nsa_sel_bwd_dkv_ptr(const void* q, const int64_t q_stride[3], const int64_t* base_k,
+                                   const int64_t* base_v, const int64_t* base_dk, const int64_t* base_dv,
+                                   const int64_t base_stride[2], int32_t max_base,
+                                   const int32_t* n_blocks_per_head, int64_t batch_stride_kv_bytes,
+                                   int64_t batch_stride_dkv_bytes, int64_t stride_bn, int64_t stride_dbn,
+                                   int32_t blocks_per_chunk, int64_t in_chunk_block_bytes_kv,
+                                   int64_t in_chunk_block_bytes_dkv, const int32_t* groups,
+                                   const int32_t* offsets, int64_t NS, const float* lse, const float* delta,
+                                   const void* d_out, const int64_t do_stride[3], int32_t B, int64_t M,
+                                   int32_t H, int32_t D, int32_t T, int32_t block_size, int32_t group_size,
+                                   float scale, int32_t dtype, void* stream) {
+  nsa_kv_source dummy{};
+  dummy.mode = NSA_KV_DENSE;
+  dummy.n_tokens = NS * block_size;
+  int rc;
+  if ((rc = bwd_common_checks("sel_bwd_dkv_ptr", B, M, H, D, T, block_size, 1, group_size, dtype, &dummy))) return rc;
+  if (B == 0 || H == 0 || M == 0 || NS == 0) return NSA_OK;
+  NSA_REQUIRE(base_k && base_v && base_dk && base_dv && base_stride, NSA_ERR_INVALID, "sel_bwd_dkv_ptr: null base table");
+  NSA_REQUIRE(groups && offsets && lse && delta, NSA_ERR_INVALID, "sel_bwd_dkv_ptr: null pointer");
+  NSA_REQUIRE(max_base > 0, NSA_ERR_INVALID, "sel_bwd_dkv_ptr: max_base must be > 0");
+  NSA_REQUIRE(blocks_per_chunk >= 0, NSA_ERR_INVALID, "sel_bwd_dkv_ptr: blocks_per_chunk must be >= 0");
+  NSA_REQUIRE(blocks_per_chunk == 0 || (in_chunk_block_bytes_kv > 0 && in_chunk_block_bytes_dkv > 0), NSA_ERR_INVALID,
+              "sel_bwd_dkv_ptr: chunk-level bases need in_chunk_block_bytes_kv/dkv > 0");
+  NSA_REQUIRE(stride_bn > 0 && (stride_bn * 2) % 16 == 0, NSA_ERR_LAYOUT,
+              "sel_bwd_dkv_ptr: K/V token stride must be a positive multiple of 16 bytes");
+  NSA_REQUIRE(stride_dbn >= D && stride_dbn % 2 == 0, NSA_ERR_LAYOUT,
+              "sel_bwd_dkv_ptr: stride_dbn must be the fp32 scratch stride (>= D, even)");
+  const int esz = 2;
+  if ((rc = check_strides16("q", q, q_stride, 3, esz))) return rc;
+  if ((rc = check_strides16("d_out", d_out, do_stride, 3, esz))) return rc;
+  BwdParams p{};
+  p.kv.mode = NSA_KV_DENSE;
+  p.kv.n_tokens = NS * block_size;
+  p.q = static_cast<const char*>(q); p.q_sb = q_stride[0]; p.q_sm = q_stride[1]; p.q_sh = q_stride[2];
+  p.dO = static_cast<const char*>(d_out); p.do_sb = do_stride[0]; p.do_sm = do_stride[1]; p.do_sh = do_stride[2];
+  p.lse = lse; p.delta = const_cast<float*>(delta);
+  p.groups = groups; p.offsets = offsets;
+  p.B = B; p.H = H; p.T = T; p.block_size = block_size; p.chunk_size = 1; p.causal = 0;
+  p.G = group_size; p.MG = static_cast<int>(cdiv64(M, group_size)); p.M = M; p.NS = NS;
+  p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.tab.on = 1;
+  p.tab.base_k = base_k; p.tab.base_v = base_v; p.tab.base_dk = base_dk; p.tab.base_dv = base_dv;
+  p.tab.base_sh = base_stride[0]; p.tab.base_sb = base_stride[1]; p.tab.max_base = max_base;
+  p.tab.n_blocks_per_head = n_blocks_per_head;
+  p.tab.batch_kv_bytes = batch_stride_kv_bytes; p.tab.batch_dkv_bytes = batch_stride_dkv_bytes;
+  p.tab.in_chunk_kv_bytes = in_chunk_block_bytes_kv; p.tab.in_chunk_dkv_bytes = in_chunk_block_bytes_dkv;
+  p.tab.blocks_per_chunk = blocks_per_chunk;
+  p.tab.s_bn = stride_bn; p.tab.s_dbn = stride_dbn;
+  return dispatch_bwd<false>(p, dtype, D, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,

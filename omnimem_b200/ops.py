@@ -361,8 +361,10 @@ def dedup_run(block_indices_flat: torch.Tensor, stamp: torch.Tensor, out: torch.
 
 def sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: int, scale: float,
                causal: bool, group_size: int):
-    """First half of the backward: (dq, delta fp32 [B,H,M])."""
-    _require_cuda(q, block_indices, out, lse, d_out)
+    """First half of the backward: (dq, delta fp32 [B,H,M]).  With a PtrKV source block_indices may
+    be None: the address tables define the slots (the reference's pointer path)."""
+    layout = block_indices if block_indices is not None else kv.ptr_k
+    _require_cuda(q, layout, out, lse, d_out)
     B, M, H, D = q.shape
     q, out, d_out = _rows16(q), _rows16(out), _rows16(d_out)
     lse = lse.contiguous()
@@ -370,9 +372,9 @@ def sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_siz
     delta = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
     src = kv.struct()
     with torch.cuda.device(q.device):
-        call("nsa_sel_bwd_dq", q.data_ptr(), strides3(q), C.byref(src), block_indices.data_ptr(),
-             strides4(block_indices), out.data_ptr(), strides3(out), lse.data_ptr(), d_out.data_ptr(),
-             strides3(d_out), dq.data_ptr(), strides3(dq), delta.data_ptr(), B, M, H, D, block_indices.shape[-1],
+        call("nsa_sel_bwd_dq", q.data_ptr(), strides3(q), C.byref(src), _ptr(block_indices),
+             strides4(layout), out.data_ptr(), strides3(out), lse.data_ptr(), d_out.data_ptr(),
+             strides3(d_out), dq.data_ptr(), strides3(dq), delta.data_ptr(), B, M, H, D, layout.shape[-1],
              _i32(block_size, "block_size"), _i32(chunk_size, "chunk_size"), int(bool(causal)),
              _i32(group_size, "group_size"), float(scale), _dtype(q), _stream(q))
     return dq, delta
@@ -446,3 +448,34 @@ def gate_combine_bwd(g_logits, o_cmp, o_slc, o_swa, dx: torch.Tensor, gate_mode:
              _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2]), ref.numel() // D, D,
              1 if gate_mode == "softmax" else 0, _dtype(ref), _stream(ref))
     return dg, outs[0], outs[1], outs[2]
+
+
+def sel_bwd_dkv_ptr(q, base_k, base_v, base_dk, base_dv, n_blocks_per_head, groups, offsets, lse, delta, d_out,
+                    T: int, block_size: int, group_size: int, scale: float, batch_stride_kv_bytes: int,
+                    batch_stride_dkv_bytes: int, stride_bn: int, stride_dbn: int, blocks_per_chunk: int = 0,
+                    in_chunk_block_bytes_kv: int = 0, in_chunk_block_bytes_dkv: int = 0) -> None:
+    """dK/dV of the pointer path, written as fp32 tiles into the scratch the base_dk / base_dv tables
+    point at (sel_bwd_ptr_cuda, selection_bwd.cu:1409-1527).  base_* int64 [H, MAXB]; groups / offsets
+    from inverted_index(block_indices, NS, block_size, 1, False, group_size)."""
+    _require_cuda(q, base_k, base_v, base_dk, base_dv, groups, offsets, lse, delta, d_out)
+    for t in (base_k, base_v, base_dk, base_dv):
+        if t.dtype != torch.int64 or t.dim() != 2 or t.shape != base_k.shape or t.stride() != base_k.stride():
+            raise NSABackendError("sel_bwd_dkv_ptr: base tables must be int64 [H, MAXB] with identical layout")
+    B, M, H, D = q.shape
+    if base_k.shape[0] != H:
+        raise NSABackendError("sel_bwd_dkv_ptr: base_k must be [H, MAXB]")
+    q, d_out = _rows16(q), _rows16(d_out)
+    NS = offsets.shape[-1] - 1
+    nbph = None
+    if n_blocks_per_head is not None and n_blocks_per_head.numel() != 0:
+        if n_blocks_per_head.dtype != torch.int32 or n_blocks_per_head.shape != (H,):
+            raise NSABackendError("sel_bwd_dkv_ptr: n_blocks_per_head must be int32 [H]")
+        nbph = n_blocks_per_head.contiguous()
+    bs = (C.c_int64 * 3)(base_k.stride(0), base_k.stride(1), 0)
+    with torch.cuda.device(q.device):
+        call("nsa_sel_bwd_dkv_ptr", q.data_ptr(), _lib.strides3(q), base_k.data_ptr(), base_v.data_ptr(),
+             base_dk.data_ptr(), base_dv.data_ptr(), bs, base_k.shape[1], _ptr(nbph), batch_stride_kv_bytes,
+             batch_stride_dkv_bytes, stride_bn, stride_dbn, blocks_per_chunk, in_chunk_block_bytes_kv,
+             in_chunk_block_bytes_dkv, groups.data_ptr(), offsets.data_ptr(), NS, lse.data_ptr(), delta.data_ptr(),
+             d_out.data_ptr(), _lib.strides3(d_out), B, M, H, D, T, block_size, group_size, float(scale),
+             _dtype(q), _stream(q))

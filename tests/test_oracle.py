@@ -200,3 +200,20 @@ def test_inverted_index_and_ptr_table():
     pk, pv = O.build_ptr_table(ids, base_k, base_v, torch.tensor([4]), 0, 2, 16)
     assert pk[0, :, 0].tolist() == [[4096, 0], [0, 0], [4096 + 16, 0]]
     assert pv[0, 2, 0, 0] == 8192 + 16
+
+
+def test_gate_combine_matches_the_written_out_formula():
+    """oracle.gate_combine against the reference expression evaluated term by term in float64
+    (causal_wan_nsa_model.py:378-386, 541-546), all gate modes and skipped modules."""
+    g = torch.Generator().manual_seed(0)
+    gl = torch.randn(2, 5, 3, 3, generator=g, dtype=torch.float64) * 8        # some logits beyond +-10
+    o = [torch.randn(2, 5, 3, 16, generator=g, dtype=torch.float64) for _ in range(3)]
+    gc = gl.clamp(-10, 10)
+    for mode in ("sigmoid", "softmax"):
+        gates = 1 / (1 + torch.exp(-gc)) if mode == "sigmoid" else torch.exp(gc) / torch.exp(gc).sum(-1, keepdim=True)
+        for skip in (None, 0, 1):
+            want = sum(gates[..., i:i + 1] * o[i] for i in range(3) if i != skip)
+            got = O.gate_combine(gl, *[None if i == skip else o[i] for i in range(3)], mode)
+            assert torch.allclose(got, want, atol=1e-12)
+    with pytest.raises(NotImplementedError):
+        O.gate_combine(gl, *o, "tanh")
