@@ -2,24 +2,20 @@
 // the page geometry: bf16, D = 128, 64-token blocks, query groups of up to 64 rows, K/V read
 // from a dense [B,N,H,D] tensor or straight from the fixed-page pool through the block table.
 //
-// One thread block per (batch, query group, head), TWO thread blocks resident per SM (96 KiB of
-// tiles and 256 TMEM columns each), so that the load / list-building prologue and the
-// merge-and-store epilogue of one block run beside the main loop of the other.  Roles:
-//   warp 4  TMA producer: Q once, then per step the K tile of TWO selected blocks (128 keys),
-//           coordinates taken from the compacted block list;   warp 6: the same for V;
-//   warp 5  MMA issuer: S = [Q;Q] K^T (M=128, N=128, K=128) into TMEM;
-//   warp 7  MMA issuer: once the softmax warps have written P over the score columns,
-//           O += P V with P read from TMEM;
-//   warps 0-3  softmax: one TMEM lane (matrix row) per thread.
-// The 64 query rows are loaded twice, into rows 0-63 and 64-127 of the A tile: rows 0-63 do
-// the online softmax over the EVEN block of each step (S columns 0-63), rows 64-127 over the
-// ODD block (columns 64-127); the other half of each P row is zero, so the two halves
-// accumulate attention over disjoint key sets in their own O rows and are merged exactly
-// (log-sum-exp weights) in the epilogue.  Every softmax thread therefore has 64 useful
-// columns per step and no cross-thread reduction is needed.
-// O stays in TMEM across steps; it is rescaled only when a row's running maximum grows by
-// more than 2^8 (the reference maximum is otherwise kept, which is exact because P and the
-// row sum use the same reference).
+// One thread block per (batch, query group, head), TWO thread blocks resident per SM (about 97 KiB
+// of tiles and 256 TMEM columns each), so that the list-building prologue and the store epilogue
+// of one block run beside the main loop of the other.  A step is ONE selected block (64 keys):
+//   warp 4  producer: block list (ballot compaction), Q once, K and V tiles through two-stage rings (TMA);
+//   warp 5  issues S = Q K^T (M=64, N=64, K=128) into a double-buffered TMEM tile, so the scores of
+//           step t+1 are computed while the softmax of step t runs;
+//   warps 0-3  online softmax on the accumulator fragments (16 rows x 64 keys per warp, the four
+//           threads of a quad share a row); P goes as bf16 through stmatrix into a swizzled,
+//           double-buffered shared tile;
+//   warp 6  issues O += P V (M=64, N=128, K=64; the V tile is read MN-major in place).
+// O stays in TMEM across steps; it is rescaled only when a row's running maximum grows by more than
+// 2^8 (the reference maximum is otherwise kept, which is exact because P and the row sum use the
+// same reference).  The epilogue normalises the O fragments, stages them with stmatrix in the dead
+// Q tile and writes them with TMA tile stores whose box holds one group's rows.
 #include "sel_common.cuh"
 #include "tc_common.cuh"
 
@@ -77,15 +73,15 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTcThreads = 256;
+constexpr int kTcThreads = 224;
 constexpr int kMaxSlots = 256;
-constexpr uint32_t kTileBytes = 32768;        // 128 rows x 256 bytes, as two 64-column halves of 16 KiB
-constexpr uint32_t kSmemTiles = 3 * kTileBytes;   // Q, K, V
-constexpr float kRescaleGap = 8.f;            // log2 units
-constexpr uint32_t kTmemCols = 256;           // per thread block; two blocks share an SM's 512
+constexpr uint32_t kTile = 16384;              // 64 rows x 256 bytes, as two 64-column halves of 8 KiB
+constexpr uint32_t kSmemTiles = kTile + 2 * kTile + 2 * kTile + 2 * 8192;   // Q, K x2, V x2, P x2
+constexpr float kRescaleGap = 8.f;             // log2 units
+constexpr uint32_t kTmemCols = 256;            // per thread block; two blocks share an SM's 512
 
 // TMEM columns
-constexpr uint32_t kColS = 0;      // 128 fp32 score columns; P (64 columns of bf16 pairs) is written over them
+constexpr uint32_t kColS = 0;      // 2 x 64 fp32 score columns (double buffered)
 constexpr uint32_t kColO = 128;    // 128
 
 struct TcFwdParams {
@@ -103,21 +99,32 @@ struct TcFwdParams {
   int32_t* status;
 };
 
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
 __global__ void __launch_bounds__(kTcThreads, 2)
 sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                  const __grid_constant__ CUtensorMap mapV, const TcFwdParams p) {
+                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                  const TcFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = tiles;
-  uint8_t* sK = tiles + kTileBytes;
-  uint8_t* sV = tiles + 2 * kTileBytes;
-  float* stage = reinterpret_cast<float*>(tiles);   // epilogue: 128 x 129 floats over the dead Q/K/V tiles
+  uint8_t* sQ = tiles;                   // [2][64][128 B]; reused as the output staging tile by the epilogue
+  uint8_t* sK = tiles + kTile;           // 2 stages
+  uint8_t* sV = tiles + 3 * kTile;       // 2 stages
+  uint8_t* sP = tiles + 5 * kTile;       // 2 x [64 q][128 B] swizzled
 
-  __shared__ uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done, o_final;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full[2], p_free[2],
+      pv_done, o_final;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
   __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
-  __shared__ float s_m[128], s_l[128];
 
   const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -129,21 +136,22 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&q_full, 1);
-    mbar_init(&k_full, 1); mbar_init(&k_empty, 1);
-    mbar_init(&v_full, 1); mbar_init(&v_empty, 1);
-    mbar_init(&s_full, 1); mbar_init(&p_full, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 128); mbar_init(&p_free[i], 1);
+    }
     mbar_init(&pv_done, 1);
     mbar_init(&o_final, 1);
     fence_barrier_init();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
   if (warp == 4 && lane == 0) {
-    // Q does not depend on the block list: start its copy at once (its barrier is initialised by
-    // this same thread only when threadIdx.x == 0 is, so the copy is issued after the sync below)
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
-  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by one warp
-  if (warp == 1) {
+  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by warp 4
+  if (warp == 4) {
     int base = 0;
     for (int t0 = 0; t0 < p.T; t0 += 32) {
       const int t = t0 + lane;
@@ -191,226 +199,258 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int nb = s_nb;
   char* out_row0 = p.out + (b * p.o_sb + m0 * p.o_sm + h * p.o_sh) * 2;
   float* lse_row0 = p.lse + (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
-  const int NT = (nb + 1) >> 1;
   if (threadIdx.x == 0) TRACE(1, 1);
-
-  // K / V tile of one step: the even block in rows 0-63, the odd block in rows 64-127 of each
-  // 64-column half (the even block again when the step has no odd block).
-  auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, int re, int ro, uint64_t* bar) {
-    mbar_expect_tx(bar, kTileBytes);
-    if (p.paged) {
-      tma_load_2d(dst, map, 0, re, bar);
-      tma_load_2d(dst + 8192, map, 0, ro, bar);
-      tma_load_2d(dst + 16384, map, 64, re, bar);
-      tma_load_2d(dst + 24576, map, 64, ro, bar);
-    } else {
-      tma_load_4d(dst, map, 0, h, re, b, bar);
-      tma_load_4d(dst + 8192, map, 0, h, ro, b, bar);
-      tma_load_4d(dst + 16384, map, 64, h, re, b, bar);
-      tma_load_4d(dst + 24576, map, 64, h, ro, b, bar);
-    }
-  };
 
   if (nb == 0) {
     // nothing visible: O = 0, LSE = -inf
     for (int i = threadIdx.x; i < n_q * 16; i += blockDim.x)
       *reinterpret_cast<uint4*>(out_row0 + (i >> 4) * p.o_sm * 2 + (i & 15) * 16) = make_uint4(0, 0, 0, 0);
     for (int r = threadIdx.x; r < n_q; r += blockDim.x) lse_row0[r] = -INFINITY;
-  } else if (warp == 4 || warp == 6) {
-    // ======================= TMA producers: warp 4 loads Q and the K tiles, warp 6 the V tiles =======================
+  } else if (warp == 4) {
+    // ======================= TMA producer =======================
     if (lane == 0) {
-      const bool isK = warp == 4;
-      uint64_t* full = isK ? &k_full : &v_full;
-      uint64_t* empty = isK ? &k_empty : &v_empty;
-      uint8_t* dst = isK ? sK : sV;
-      const CUtensorMap* map = isK ? &mapK : &mapV;
-      if (isK) {
-        mbar_expect_tx(&q_full, kTileBytes);
-        for (int dh = 0; dh < 2; ++dh)
-          for (int dup = 0; dup < 2; ++dup)
-            tma_load_4d(sQ + dh * 16384 + dup * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
-      }
+      mbar_expect_tx(&q_full, kTile);
+      for (int dh = 0; dh < 2; ++dh) tma_load_4d(sQ + dh * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
       int t = 0;
-      for (; t < NT; ++t) {
-        const int re = s_row[2 * t], ro = (2 * t + 1 < nb) ? s_row[2 * t + 1] : re;
-        if (!mbar_wait(empty, (t & 1) ^ 1, abort)) break;
-        load_tile(dst, map, re, ro, full);
+      for (; t < nb; ++t) {
+        const int st = t & 1, ph = (t >> 1) & 1;
+        const int row = s_row[t];
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort)) break;
+        mbar_expect_tx(&k_full[st], kTile);
+        for (int dh = 0; dh < 2; ++dh) {
+          if (p.paged) tma_load_2d(sK + st * kTile + dh * 8192, &mapK, dh * 64, row, &k_full[st]);
+          else tma_load_4d(sK + st * kTile + dh * 8192, &mapK, dh * 64, h, row, b, &k_full[st]);
+        }
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) { ++t; break; }
+        mbar_expect_tx(&v_full[st], kTile);
+        for (int dh = 0; dh < 2; ++dh) {
+          if (p.paged) tma_load_2d(sV + st * kTile + dh * 8192, &mapV, dh * 64, row, &v_full[st]);
+          else tma_load_4d(sV + st * kTile + dh * 8192, &mapV, dh * 64, h, row, b, &v_full[st]);
+        }
       }
       if (*abort) {
-        // the other roles have stopped consuming: wait (bounded) for the copy still in flight
-        if (t > 0) mbar_wait(full, (t - 1) & 1, abort);
-        if (isK) mbar_wait(&q_full, 0, abort);
+        // the other roles have stopped consuming: wait (bounded) for the copies still in flight
+        for (int u = (t > 2 ? t - 2 : 0); u < t; ++u) {
+          mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort);
+          mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
+        }
+        mbar_wait(&q_full, 0, abort);
       }
     }
-  } else if (warp == 5 || warp == 7) {
-    // ======================= MMA issuers =======================
-    // Per step: S = [Q;Q] K^T (warp 5), softmax writes P over S, O += P V (warp 7).  The next S
-    // overwrites P, so it is issued only after the P V product that reads it has completed.
-    // Two issuing threads, because each passed barrier wait costs the thread a few hundred cycles.
-    // Whole warps run these loops (warp-uniform control flow keeps descriptor arithmetic in uniform
-    // registers); one elected lane issues.
-    {
-      const uint32_t el = elect_one();
-      if (warp == 5) {
-        constexpr uint32_t idesc_s = instr_desc_bf16(128, 128, 0, 0);
-        const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
-        const uint64_t dK = smem_desc(smem_u32(sK), 16, 1024);
-        bool ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, abort));
-        TRACE(0, 0);
-        for (int t = 0; ok && t < NT; ++t) {
-          const uint32_t ph = t & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(&k_full, ph, abort) && (t == 0 || mbar_wait(&pv_done, ph ^ 1, abort)));
-          if (!ok) break;
-          TRACE(0, 8 + t * 8 + 0);
-          tc_fence_after();
-          if (el) {
+  } else if (warp == 5) {
+    // ======================= MMA issuer 1: S = Q K^T (whole warp runs the loop, one elected lane issues) =======================
+    constexpr uint32_t idesc = instr_desc_bf16(64, 64, 0, 0);          // both operands K-major
+    const uint32_t el = elect_one();
+    const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024);
+    bool ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, abort));
+    TRACE(0, 0);
+    for (int t = 0; ok && t < nb; ++t) {
+      const int st = t & 1, ph = (t >> 1) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&k_full[st], ph, abort) &&
+                                   (t < 2 || mbar_wait(&s_free[st], ((t - 2) >> 1) & 1, abort)));   // S(t-2) was read
+      if (!ok) break;
+      tc_fence_after();
+      TRACE(0, 8 + t * 8 + 0);
+      const uint64_t dK = smem_desc(smem_u32(sK + st * kTile), 16, 1024);
+      if (el) {
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_ss(tm + kColS, desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
-                      desc_advance(dK, (kk >> 2) * 16384 + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-            umma_commit(&s_full);
-            umma_commit(&k_empty);
-          }
-          __syncwarp();
-          TRACE(0, 8 + t * 8 + 1);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_ss(tm + kColS + st * 64, desc_advance(dQ, off), desc_advance(dK, off), idesc, kk > 0 ? 1u : 0u);
         }
-      } else {
-        constexpr uint32_t idesc_pv = instr_desc_bf16(128, 128, 0, 1);
-        const uint64_t dV = smem_desc(smem_u32(sV), 16384, 1024);
-        for (int t = 0; t < NT; ++t) {
-          const uint32_t ph = t & 1;
-          if (!__all_sync(0xffffffffu, mbar_wait(&v_full, ph, abort) && mbar_wait(&p_full, ph, abort))) break;
-          TRACE(0, 8 + t * 8 + 2);
-          tc_fence_after();
-          if (el) {
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              umma_ts(tm + kColO, tm + kColS + kk * 8, desc_advance(dV, kk * 2048), idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&v_empty);
-            umma_commit(&pv_done);
-            if (t == NT - 1) umma_commit(&o_final);
-          }
-          __syncwarp();
-          TRACE(0, 8 + t * 8 + 3);
-        }
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
       }
+      __syncwarp();
+      TRACE(0, 8 + t * 8 + 1);
+    }
+  } else if (warp == 6) {
+    // ======================= MMA issuer 2: O += P V =======================
+    constexpr uint32_t idesc = instr_desc_bf16(64, 128, 0, 1);         // A (P) K-major, B (V tile) MN-major
+    const uint32_t el = elect_one();
+    for (int t = 0; t < nb; ++t) {
+      const int st = t & 1, ph = (t >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&v_full[st], ph, abort) && mbar_wait(&p_full[st], ph, abort))) break;
+      tc_fence_after();
+      TRACE(0, 8 + t * 8 + 2);
+      const uint64_t dP = smem_desc(smem_u32(sP + st * 8192), 16, 1024);
+      // V tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as N
+      const uint64_t dVmn = smem_desc(smem_u32(sV + st * kTile), 8192, 1024);
+      if (el) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tm + kColO, desc_advance(dP, kk * 32), desc_advance(dVmn, kk * 2048), idesc, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&v_empty[st]);
+        umma_commit(&p_free[st]);
+        umma_commit(&pv_done);
+        if (t == nb - 1) umma_commit(&o_final);
+      }
+      __syncwarp();
+      TRACE(0, 8 + t * 8 + 3);
     }
   } else if (warp < 4) {
-    // ======================= softmax (warps 0-3), one matrix row per thread =======================
-    const int half = warp >> 1;                       // 0: even block of each step, 1: odd block
+    // ======================= softmax on accumulator fragments (warps 0-3) =======================
+    // Warp w owns query rows 16w .. 16w+15 (TMEM lanes 32w .. 32w+15 of the M=64 accumulators); thread t
+    // holds rows r0 = 16w + t/4 and r1 = r0 + 8, columns 8i + 2(t%4), +1 of every 8-column block i; the
+    // four threads of a quad share a row and keep its running maximum identical (quad shuffles).
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    float m_ref = -INFINITY, l_sum = 0.f;
+    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+    const int cq = (lane & 3) * 2;
+    const int st_row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);   // stmatrix: row this lane addresses
+    const int st_chunk = lane >> 4;
+    const float sl = p.scale_log2;
+    float m_0 = -INFINITY, m_1 = -INFINITY, l_0 = 0.f, l_1 = 0.f;        // l: this thread's share of the row sums
     bool ok = true;
-    for (int t = 0; t < NT; ++t) {
+    for (int t = 0; t < nb; ++t) {
+      const int sb = t & 1, ph = (t >> 1) & 1;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
-      // s_full is committed after the previous step's P V was issued, so its completion also
-      // means that O is quiescent and may be rescaled below
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full, t & 1, abort));
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], ph, abort));
       if (!ok) break;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
       tc_fence_after();
-      uint32_t x0[32], x1[32];
-      tmem_ld32_nowait(tm + lane_base + kColS + half * 64, x0);
-      tmem_ld32_nowait(tm + lane_base + kColS + half * 64 + 32, x1);
+      uint32_t x[32];
+      tmem_ld_16x256b_x8_nowait(tm + lane_base + kColS + sb * 64, x);
+      const int nv = s_nvis[t];
+      // the P tile of step t-2 must have been consumed before it is overwritten: normally long true,
+      // so poll once here, where the round trip hides behind the TMEM load
+      const bool p_ok = t < 2 || mbar_try(&p_free[sb], ((t - 2) >> 1) & 1);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_free[sb]);
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
-      const int blk = 2 * t + half;
-      const int nv = blk < nb ? s_nvis[blk] : 0;
-      float tmax = -INFINITY;
+      // running maxima on the unscaled scores (the scale is positive)
+      float t0 = -INFINITY, t1 = -INFINITY;
+      if (nv == 64) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float a = __uint_as_float(x0[j]) * p.scale_log2, c = __uint_as_float(x1[j]) * p.scale_log2;
-        x0[j] = __float_as_uint(a);
-        x1[j] = __float_as_uint(c);
-        if (j < nv) tmax = fmaxf(tmax, a);
-        if (j + 32 < nv) tmax = fmaxf(tmax, c);
+        for (int i = 0; i < 8; ++i) {
+          t0 = fmaxf(t0, fmaxf(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1])));
+          t1 = fmaxf(t1, fmaxf(__uint_as_float(x[4 * i + 2]), __uint_as_float(x[4 * i + 3])));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = 8 * i + cq;
+          if (c < nv) { t0 = fmaxf(t0, __uint_as_float(x[4 * i])); t1 = fmaxf(t1, __uint_as_float(x[4 * i + 2])); }
+          if (c + 1 < nv) { t0 = fmaxf(t0, __uint_as_float(x[4 * i + 1])); t1 = fmaxf(t1, __uint_as_float(x[4 * i + 3])); }
+        }
       }
-      const bool need = tmax > m_ref + kRescaleGap;      // also true for the first visible key (m_ref = -inf)
+      t0 = quad_max(t0) * sl;
+      t1 = quad_max(t1) * sl;
+      const bool need0 = t0 > m_0 + kRescaleGap, need1 = t1 > m_1 + kRescaleGap;   // true at the first step (m = -inf)
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 3);
-      if (__any_sync(0xffffffffu, need)) {
-        const float m_new = need ? tmax : m_ref;
+      if (!__all_sync(0xffffffffu, p_ok)) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((t - 2) >> 1) & 1, abort));
+        if (!ok) break;
+      }
+      if (__any_sync(0xffffffffu, need0 || need1)) {
+        const float n0 = need0 ? t0 : m_0, n1 = need1 ? t1 : m_1;
         if (t > 0) {
-          const float sc = need ? fast_exp2(m_ref - m_new) : 1.f;
-          l_sum *= sc;
+          // O holds sums relative to the old maxima: rescale it once P V of step t-1 has completed
+          // (P V of step t-2 is known complete from p_free, so this wait cannot alias a phase)
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done, (t - 1) & 1, abort));
+          if (!ok) break;
+          tc_fence_after();
+          const float c0 = need0 ? fast_exp2(m_0 - n0) : 1.f, c1 = need1 ? fast_exp2(m_1 - n1) : 1.f;
+          l_0 *= c0;
+          l_1 *= c1;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int dh = 0; dh < 2; ++dh) {
             uint32_t o[32];
-            tmem_ld32_nowait(tm + lane_base + kColO + c * 32, o);
+            tmem_ld_16x256b_x8_nowait(tm + lane_base + kColO + dh * 64, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * sc);
-            tmem_st32_nowait(tm + lane_base + kColO + c * 32, o);
+            for (int i = 0; i < 8; ++i) {
+              o[4 * i] = __float_as_uint(__uint_as_float(o[4 * i]) * c0);
+              o[4 * i + 1] = __float_as_uint(__uint_as_float(o[4 * i + 1]) * c0);
+              o[4 * i + 2] = __float_as_uint(__uint_as_float(o[4 * i + 2]) * c1);
+              o[4 * i + 3] = __float_as_uint(__uint_as_float(o[4 * i + 3]) * c1);
+            }
+            tmem_st_16x256b_x8_nowait(tm + lane_base + kColO + dh * 64, o);
           }
+          tmem_st_wait();
+          tc_fence_before();
         }
-        m_ref = m_new;
+        m_0 = n0;
+        m_1 = n1;
       }
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 4);
-      uint32_t pk[32];
-      float rs = 0.f;
+      // probabilities, packed in place: x[2i] = row r0 / x[2i+1] = row r1 of key block i
+      {
+        const float g0 = -m_0, g1 = -m_1;
+        float a0 = 0.f, a1 = 0.f;
+        if (nv == 64) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a0 = (2 * j < nv) ? fast_exp2(__uint_as_float(x0[2 * j]) - m_ref) : 0.f;
-        const float a1 = (2 * j + 1 < nv) ? fast_exp2(__uint_as_float(x0[2 * j + 1]) - m_ref) : 0.f;
-        const float c0 = (2 * j + 32 < nv) ? fast_exp2(__uint_as_float(x1[2 * j]) - m_ref) : 0.f;
-        const float c1 = (2 * j + 33 < nv) ? fast_exp2(__uint_as_float(x1[2 * j + 1]) - m_ref) : 0.f;
-        rs += (a0 + a1) + (c0 + c1);
-        pk[j] = pack2<__nv_bfloat16>(a0, a1);
-        pk[16 + j] = pack2<__nv_bfloat16>(c0, c1);
+          for (int i = 0; i < 8; ++i) {
+            const float p00 = fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, g0));
+            const float p01 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, g0));
+            const float p10 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, g1));
+            const float p11 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 3]), sl, g1));
+            a0 += p00 + p01;
+            a1 += p10 + p11;
+            x[2 * i] = pack2<__nv_bfloat16>(p00, p01);
+            x[2 * i + 1] = pack2<__nv_bfloat16>(p10, p11);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = 8 * i + cq;
+            const float p00 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, g0)) : 0.f;
+            const float p01 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, g0)) : 0.f;
+            const float p10 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, g1)) : 0.f;
+            const float p11 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 3]), sl, g1)) : 0.f;
+            a0 += p00 + p01;
+            a1 += p10 + p11;
+            x[2 * i] = pack2<__nv_bfloat16>(p00, p01);
+            x[2 * i + 1] = pack2<__nv_bfloat16>(p10, p11);
+          }
+        }
+        l_0 += a0;
+        l_1 += a1;
       }
-      l_sum += rs;
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 5);
-      // P over the score columns: this row's 64 probabilities in its own half, zeros in the other
-      tmem_st32_nowait(tm + lane_base + kColS + half * 32, pk);
+      const uint32_t aP = smem_u32(sP + sb * 8192) + st_row * 128;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) pk[j] = 0u;
-      tmem_st32_nowait(tm + lane_base + kColS + (1 - half) * 32, pk);
-      tmem_st_wait();
+      for (int q = 0; q < 4; ++q)
+        stmatrix_x4(aP + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+      fence_async_smem();                           // make the rows visible to the tensor core's reads
+      mbar_arrive(&p_full[sb]);
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 6);
-      tc_fence_before();
-      mbar_arrive(&p_full);
     }
     if (threadIdx.x == 0) TRACE(1, 2);
-    // ---- epilogue: wait for the last P V, merge the two halves, normalise, store
+    // ---- epilogue: normalise the O fragments, stage them as bf16 in the dead Q tile, TMA tile stores
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&o_final, 0, abort));
     if (threadIdx.x == 0) TRACE(1, 3);
     if (ok) {
       tc_fence_after();
-      const int tid = threadIdx.x;                    // 0..127 = TMEM lane = A-tile row
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld32_nowait(tm + lane_base + kColO + c * 32, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) stage[tid * 129 + c * 32 + j] = __uint_as_float(o[j]);
+      const float L0 = quad_sum(l_0), L1 = quad_sum(l_1);
+      const float i0 = L0 > 0.f ? 1.f / L0 : 0.f, i1 = L1 > 0.f ? 1.f / L1 : 0.f;
+      if ((lane & 3) == 0) {
+        if (r0 < n_q) lse_row0[r0] = L0 > 0.f ? (m_0 + log2f(L0)) * kLn2 : -INFINITY;
+        if (r1 < n_q) lse_row0[r1] = L1 > 0.f ? (m_1 + log2f(L1)) * kLn2 : -INFINITY;
       }
-      s_m[tid] = m_ref;
-      s_l[tid] = l_sum;
+#pragma unroll
+      for (int dh = 0; dh < 2; ++dh) {
+        uint32_t o[32];
+        tmem_ld_16x256b_x8_nowait(tm + lane_base + kColO + dh * 64, o);
+        tmem_ld_wait();
+        const uint32_t aO = smem_u32(sQ) + dh * 8192 + st_row * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int j0 = 2 * q, j1 = 2 * q + 1;
+          const uint32_t a0 = pack2<__nv_bfloat16>(__uint_as_float(o[4 * j0]) * i0, __uint_as_float(o[4 * j0 + 1]) * i0);
+          const uint32_t b0 = pack2<__nv_bfloat16>(__uint_as_float(o[4 * j0 + 2]) * i1, __uint_as_float(o[4 * j0 + 3]) * i1);
+          const uint32_t a1 = pack2<__nv_bfloat16>(__uint_as_float(o[4 * j1]) * i0, __uint_as_float(o[4 * j1 + 1]) * i0);
+          const uint32_t b1 = pack2<__nv_bfloat16>(__uint_as_float(o[4 * j1 + 2]) * i1, __uint_as_float(o[4 * j1 + 3]) * i1);
+          stmatrix_x4(aO + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), a0, b0, a1, b1);
+        }
+      }
+      fence_async_smem();
     }
     named_barrier(1, 128);
-    if (ok) {
-      const int qrow = threadIdx.x & 63;
-      if (qrow < n_q) {
-        const float ma = s_m[qrow], mb = s_m[64 + qrow];
-        const float m = fmaxf(ma, mb);
-        const float wa = (ma == -INFINITY) ? 0.f : fast_exp2(ma - m);
-        const float wb = (mb == -INFINITY) ? 0.f : fast_exp2(mb - m);
-        const float L = s_l[qrow] * wa + s_l[64 + qrow] * wb;
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        const float* ra = stage + qrow * 129 + half * 64;
-        const float* rb = stage + (64 + qrow) * 129 + half * 64;
-        char* orow = out_row0 + qrow * p.o_sm * 2 + half * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = pack2<__nv_bfloat16>((ra[c * 8 + 2 * e] * wa + rb[c * 8 + 2 * e] * wb) * inv,
-                                        (ra[c * 8 + 2 * e + 1] * wa + rb[c * 8 + 2 * e + 1] * wb) * inv);
-          *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        if (half == 0) lse_row0[qrow] = L > 0.f ? (m + log2f(L)) * kLn2 : -INFINITY;
-      }
+    if (ok && threadIdx.x == 0) {
+      for (int dh = 0; dh < 2; ++dh) tma_store_4d(&mapO, sQ + dh * 8192, dh * 64, h, static_cast<int>(m0), b);
+      bulk_commit_group();
+      bulk_wait_all();
     }
   }
 
@@ -504,9 +544,15 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   const int64_t MG = cdiv64(M, G);
 
   if (H == 1) return NSA_OK;   // a size-1 head dimension may carry an arbitrary stride: leave it to the general kernel
-  CUtensorMap mapQ, mapK, mapV;
+  // the output leaves through TMA tile stores: 16-byte aligned rows
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0 || (out_stride[0] * 2) % 16 != 0 || (out_stride[1] * 2) % 16 != 0 ||
+      (out_stride[2] * 2) % 16 != 0)
+    return NSA_OK;
+  CUtensorMap mapQ, mapK, mapV, mapO;
   int rc;
   if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  // the store box holds G rows: a group shorter than 64 rows must not write into the next group
+  if ((rc = make_rows_map(out, out_stride, B, M, H, G, &mapO))) return rc;
 
   TcFwdParams p;
   p.ids = ids;
@@ -523,7 +569,7 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  sel_fwd_tc_kernel<<<dim3(static_cast<unsigned>(MG), H, B), kTcThreads, smem, stream>>>(mapQ, mapK, mapV, p);
+  sel_fwd_tc_kernel<<<dim3(static_cast<unsigned>(MG), H, B), kTcThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p);
   NSA_LAUNCH_OK("sel_fwd_tc_kernel");
   *launched = true;
   return NSA_OK;
