@@ -112,9 +112,12 @@ __global__ void inv_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __
 
 // The whole index of one (b, h) row in a single thread block when its NS counters fit in shared
 // memory: histogram and cursors in shared memory, scatter, then one thread per bucket sorts it.
+// STAGED: the row's pairs also fit, so scatter and sort run in shared memory and the bucket
+// array is written out once, coalesced.
+template <bool STAGED>
 __global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int32_t* __restrict__ groups,
                                                          int32_t* __restrict__ offsets) {
-  extern __shared__ int s_cnt[];                   // [NS]
+  extern __shared__ int s_cnt[];                   // [NS] (+ [pairs] when STAGED)
   __shared__ int warp_sums[32];
   __shared__ int carry_s;
   const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
@@ -122,7 +125,8 @@ __global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int3
   const int NS = static_cast<int>(p.NS);
   const int pairs = p.MG * p.T;
   int32_t* o = offsets + row * (p.NS + 1);
-  int32_t* gr = groups + row * static_cast<int64_t>(pairs);
+  int32_t* gr_out = groups + row * static_cast<int64_t>(pairs);
+  int32_t* gr = STAGED ? s_cnt + NS : gr_out;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < NS; i += blockDim.x) s_cnt[i] = 0;
   if (threadIdx.x == 0) carry_s = 0;
@@ -176,6 +180,11 @@ __global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int3
       while (c >= beg && gr[c] > v) { gr[c + 1] = gr[c]; --c; }
       gr[c + 1] = v;
     }
+  }
+  if (STAGED) {
+    __syncthreads();
+    const int total = carry_s;                         // pairs that landed in a bucket
+    for (int i = threadIdx.x; i < total; i += blockDim.x) gr_out[i] = gr[i];
   }
 }
 
@@ -707,9 +716,14 @@ int run_inverted_index(const IdxParams& ip, int32_t* groups, int32_t* offsets, i
   }
   const int64_t pairs = static_cast<int64_t>(ip.MG) * ip.T;
   if (ip.NS * 4 <= 160 * 1024 && pairs <= 0x7fffffff && rows <= 0x7fffffff) {
-    const size_t smem = static_cast<size_t>(ip.NS) * 4;
-    NSA_CUDA_OK(cudaFuncSetAttribute(inv_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    inv_fused_kernel<<<static_cast<unsigned>(rows), 1024, smem, stream>>>(ip, groups, offsets);
+    const size_t smem_idx = static_cast<size_t>(ip.NS) * 4, smem_all = smem_idx + static_cast<size_t>(pairs) * 4;
+    if (smem_all <= 200 * 1024) {
+      NSA_CUDA_OK(cudaFuncSetAttribute(inv_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_all)));
+      inv_fused_kernel<true><<<static_cast<unsigned>(rows), 1024, smem_all, stream>>>(ip, groups, offsets);
+    } else {
+      NSA_CUDA_OK(cudaFuncSetAttribute(inv_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_idx)));
+      inv_fused_kernel<false><<<static_cast<unsigned>(rows), 1024, smem_idx, stream>>>(ip, groups, offsets);
+    }
     NSA_LAUNCH_OK("inv_fused_kernel");
     return NSA_OK;
   }

@@ -106,7 +106,7 @@ def case_lru(MMCache, seed, heads, cap, n_ids, n_touch):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its src/ is imported)")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from omnimem.nsa.naive.index_selection import index_selection_topk, inflate_indices
