@@ -363,48 +363,6 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (it.n_ent < 0) break;
       }
     }
-  } else if (warp == 10) {
-    // ======================= MMA issuer 2: dV^T and dK^T of every step =======================
-    // A thread of its own, so that these products start the moment P / dS are in shared memory
-    // while issuer 1 already waits for the tiles of a later step.
-    if (lane == 0) {
-      constexpr uint32_t idesc_second = instr_desc_bf16(128, 64, 1, 1);   // both operands MN-major
-      uint32_t ic = 0, sc = 0;
-      bool ok = true;
-      for (uint32_t n = 0; ok; ++n) {
-        if (!mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort)) break;
-        const int n_ent = s_items[n & 3].n_ent;
-        mbar_arrive(&sched_empty[n & 3]);
-        if (n_ent < 0) break;
-        if (n_ent == 0) continue;
-        const int acc = ic & 1;
-        for (int t = 0; t < n_ent; ++t, ++sc) {
-          const int st = sc % kStages, pb = sc & 1;
-          if (!mbar_wait(&pds_full[pb], (sc >> 1) & 1, abort)) { ok = false; break; }
-          TRACE(0, 16 + sc * 8 + 4);
-          if (t == 0 && !mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)) { ok = false; break; }
-          TRACE(0, 16 + sc * 8 + 5);
-          tc_fence_after();
-          const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes), aP = smem_u32(sPdS + pb * kPdSBytes);
-          // A: Q^T / dO^T, head dim contiguous, two 64-column boxes 8 KiB apart; B: P / dS, keys contiguous
-          const uint64_t dQmn = smem_desc(aQ, 8192, 1024), dDOmn = smem_desc(aQ + 16384, 8192, 1024);
-          const uint64_t dP = smem_desc(aP, 16, 1024), dDS = smem_desc(aP + 8192, 16, 1024);
-          const uint32_t acc0 = t == 0 ? 0u : 1u;
-          const uint32_t tdv = tm + col_dv(acc), tdk = tm + col_dk(acc);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tdv, desc_advance(dDOmn, kk * 2048), desc_advance(dP, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
-          umma_commit(&qdo_empty[st]);
-          umma_commit(&pds_free[pb]);
-          if (t == n_ent - 1) umma_commit(&acc_full[acc]);
-          TRACE(0, 16 + sc * 8 + 6);
-        }
-        ++ic;
-      }
-    }
   } else if (warp < 4 || warp >= 12) {
     // ======================= row arithmetic: P and dS on accumulator fragments =======================
     // Two groups of four warps: warps 0-3 take the even steps, warps 12-15 the odd ones (S/dP and
