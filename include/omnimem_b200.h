@@ -283,7 +283,35 @@ int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stri
                      int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
                      int32_t* status, int32_t dtype, void* stream);
 
-/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
+/* Rotary embedding of a chunk of keys in the reordered token order (f h w fs hs ws) of the
+ * pooling windows (causal_reorder_rope_apply, models/transformers/causal_wan_nsa_model.py:72-105).
+ * freqs_* are complex128 tables (re, im pairs of float64; rope_params, wan_model.py:37-43):
+ * freqs_f [frames, c_f], freqs_h [rows, c_h], freqs_w [columns, c_w], c_f + c_h + c_w = D / 2
+ * (the reference's split: c_f = D/2 - 2*(D/2/3), c_h = c_w = D/2/3). */
+typedef struct nsa_rope {
+  const void* freqs_f;
+  const void* freqs_h;
+  const void* freqs_w;
+  int32_t c_f, c_h, c_w;
+  int32_t grid_h, grid_w;          /* latent rows / columns of a frame */
+  int32_t pool_f, pool_h, pool_w;  /* pooling window of the token order (1, 1, 1 = plain f h w order) */
+  int32_t start_frame;             /* frame index of the chunk's first frame */
+} nsa_rope;
+
+/* nsa_cache_append with the rotary embedding applied to the new keys on their way into the pages
+ * (float64 products, rounded float64 -> float32 -> dtype like the reference), so the un-roped
+ * keys are read once and the roped ones never exist outside the cache; the pooled keys are those
+ * of the roped keys.  S must be whole groups of pool_f frames.  Replaces
+ * causal_reorder_rope_apply + update_cache + the pooled-cache append
+ * (causal_wan_nsa_model.py:72-105, 479-504; cache.py:478-502). */
+int nsa_cache_append_rope(const void* k_new, const void* v_new, const int64_t kv_stride[2], int64_t S,
+                          int64_t pos0, int32_t H, int32_t D, void* k_pool, void* v_pool,
+                          int32_t page_tokens, int32_t* block_table, int32_t max_blocks,
+                          const int32_t* new_pages, int32_t n_touched_blocks, int32_t* page_owner,
+                          int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
+                          int32_t* status, int32_t dtype, const nsa_rope* rope, void* stream);
+
+/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
  * unique keys (cid*H + h)*bpc + loc (cid = bid / bpc, loc = bid % bpc): out_unique[0] = count
  * (may exceed cap), out_unique[1..cap] keys.  `stamp` is a persistent int32 [H*max_blocks]
  * scratch of the cache; epoch32 >= 1 must differ from call to call.  With a block_table

@@ -31,6 +31,12 @@ class KVSource(C.Structure):
     ]
 
 
+class Rope(C.Structure):
+    """nsa_rope: three complex128 frequency tables and the chunk's grid / token order."""
+    _fields_ = [("freqs_f", C.c_void_p), ("freqs_h", C.c_void_p), ("freqs_w", C.c_void_p)] + [
+        (n, C.c_int32) for n in ("c_f", "c_h", "c_w", "grid_h", "grid_w", "pool_f", "pool_h", "pool_w", "start_frame")]
+
+
 class TopkMask(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "block_size", "chunk_size", "chunk_size_k", "q_group_size", "q_chunk_offset", "ex_win",
@@ -78,6 +84,8 @@ PROTOTYPES = {
                                    _i32, _i64, _vp, _vp, _vp]),
     "nsa_cache_append": (_i32, [_vp, _vp, _S3, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
                                 _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _vp]),
+    "nsa_cache_append_rope": (_i32, [_vp, _vp, _S3, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
+                                     _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, C.POINTER(Rope), _vp]),
     "nsa_cache_dedup_workspace_bytes": (_sz, [_i64]),
     "nsa_cache_dedup_touch": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _i64,
                                      _vp, _vp, _i32, _vp, _sz, _vp]),

@@ -30,6 +30,34 @@ from . import _lib, ops
 from ._lib import NSABackendError, call
 
 
+class RopeSpec:
+    """Rotary embedding of one chunk: `freqs` is the reference's complex128 table
+    [max_len, D/2] (rope_params, wan_model.py:37-43; split D/2 - 2*(D/2//3), D/2//3, D/2//3 over
+    frame / row / column), `grid_hw` the latent rows and columns of a frame, `start_frame` the
+    chunk's first frame, `pool` the (f, h, w) pooling window that defines the token order."""
+
+    def __init__(self, freqs: torch.Tensor, grid_hw, start_frame: int, pool=(1, 1, 1)):
+        if freqs.dtype != torch.complex128 or freqs.dim() != 2:
+            raise NSABackendError("RopeSpec: freqs must be a complex128 [max_len, D/2] table")
+        self.freqs, self.grid_hw, self.start_frame, self.pool = freqs, tuple(grid_hw), int(start_frame), tuple(pool)
+        self._tables = None
+
+    def struct(self, device, D: int) -> _lib.Rope:
+        c = D // 2
+        if self.freqs.shape[1] != c:
+            raise NSABackendError(f"RopeSpec: freqs has {self.freqs.shape[1]} columns, head dim {D} needs {c}")
+        if self._tables is None or self._tables[0].device != device:
+            parts = self.freqs.split([c - 2 * (c // 3), c // 3, c // 3], dim=1)
+            self._tables = [torch.view_as_real(p.contiguous()).to(device).contiguous() for p in parts]
+        s = _lib.Rope()
+        s.freqs_f, s.freqs_h, s.freqs_w = (t.data_ptr() for t in self._tables)
+        s.c_f, s.c_h, s.c_w = c - 2 * (c // 3), c // 3, c // 3
+        s.grid_h, s.grid_w = self.grid_hw
+        s.pool_f, s.pool_h, s.pool_w = self.pool
+        s.start_frame = self.start_frame
+        return s
+
+
 class BlockKVCache:
     def __init__(self, num_heads: int, head_dim: int, num_pages: int, max_blocks: int,
                  page_tokens: int = 64, dtype: torch.dtype = torch.bfloat16, device="cuda",
@@ -103,9 +131,12 @@ class BlockKVCache:
              self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.epoch, self._stream())
 
     # ------------------------------------------------------------------------------- append
-    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, pos0: Optional[int] = None) -> None:
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor, pos0: Optional[int] = None,
+               rope: Optional["RopeSpec"] = None) -> None:
         """Write k_new / v_new [S,H,D] at token position pos0 (default: the end).  Re-writing
-        existing positions is allowed (each denoising step of a chunk overwrites the chunk)."""
+        existing positions is allowed (each denoising step of a chunk overwrites the chunk).
+        With `rope` the keys are given WITHOUT their rotary embedding and receive it on the way
+        into the pages (causal_reorder_rope_apply, causal_wan_nsa_model.py:72-105)."""
         S = k_new.shape[0]
         if S == 0:
             return
@@ -138,12 +169,17 @@ class BlockKVCache:
                     ids.append(victims)
                     self._evicted_any = True
                 new_pages[:, n_touched - n_new:] = torch.cat(ids).view(self.H, n_new)
-            call("nsa_cache_append", k_new.data_ptr(), v_new.data_ptr(),
-                 (C.c_int64 * 2)(k_new.stride(0), k_new.stride(1)), S, pos0, self.H, self.D,
-                 self.k_pool.data_ptr(), self.v_pool.data_ptr(), self.page_tokens, self.block_table.data_ptr(),
-                 self.max_blocks, new_pages.data_ptr(), n_touched, self.page_owner.data_ptr(),
-                 self.page_stamp.data_ptr(), self.epoch, self.k_pooled.data_ptr(), self.v_pooled.data_ptr(),
-                 self.status.data_ptr(), self._dtype_code, self._stream())
+            args = (k_new.data_ptr(), v_new.data_ptr(),
+                    (C.c_int64 * 3)(k_new.stride(0), k_new.stride(1), 0), S, pos0, self.H, self.D,
+                    self.k_pool.data_ptr(), self.v_pool.data_ptr(), self.page_tokens, self.block_table.data_ptr(),
+                    self.max_blocks, new_pages.data_ptr(), n_touched, self.page_owner.data_ptr(),
+                    self.page_stamp.data_ptr(), self.epoch, self.k_pooled.data_ptr(), self.v_pooled.data_ptr(),
+                    self.status.data_ptr(), self._dtype_code)
+            if rope is None:
+                call("nsa_cache_append", *args, self._stream())
+            else:
+                spec = rope.struct(self.device, self.D)
+                call("nsa_cache_append_rope", *args, C.byref(spec), self._stream())
         self.n_tokens = max(self.n_tokens, pos0 + S)
 
     # ------------------------------------------------------------------- selection residency

@@ -23,9 +23,30 @@ struct AppendParams {
   int32_t* page_owner; int64_t* page_stamp; int64_t epoch;
   char* k_pooled; char* v_pooled;
   int32_t* status;
+  // optional rotary embedding of the new keys (causal_reorder_rope_apply,
+  // models/transformers/causal_wan_nsa_model.py:72-105): token t of the chunk, in the reordered
+  // order (f h w fs hs ws), sits at frame / row / column (fr, hr, wr) of the chunk's latent grid;
+  // complex pair j of a head takes its factor from the frame table (j < c_f, row start_frame + fr),
+  // the row table (next c_h pairs) or the column table (last c_w pairs); products in float64.
+  const double2* rope_f; const double2* rope_h; const double2* rope_w;
+  int c_f, c_h, c_w;
+  int grid_h, grid_w, pool_f, pool_h, pool_w, start_frame;
 };
 
-template <typename T>
+// frame / row / column of token t of a chunk stored in (f h w fs hs ws) order
+__device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, int& fr, int& hr, int& wr) {
+  const int ws = static_cast<int>(t % p.pool_w); t /= p.pool_w;
+  const int hs = static_cast<int>(t % p.pool_h); t /= p.pool_h;
+  const int fs = static_cast<int>(t % p.pool_f); t /= p.pool_f;
+  const int wq = p.grid_w / p.pool_w, hq = p.grid_h / p.pool_h;
+  const int wo = static_cast<int>(t % wq); t /= wq;
+  const int ho = static_cast<int>(t % hq); t /= hq;
+  fr = static_cast<int>(t) * p.pool_f + fs;
+  hr = ho * p.pool_h + hs;
+  wr = wo * p.pool_w + ws;
+}
+
+template <typename T, bool ROPE>
 __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float s_part[];          // [2][rp][D]
@@ -62,7 +83,25 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     const int r = c / cpr, cc = c - r * cpr;
     const int64_t src = ((lo - p.pos0 + r) * p.s_stride + h * p.h_stride) * sizeof(T) + cc * 16;
     const int64_t dst = (lo - blk0 + r) * row_bytes + cc * 16;
-    *reinterpret_cast<uint4*>(kp + dst) = *reinterpret_cast<const uint4*>(p.k_new + src);
+    uint4 kq = *reinterpret_cast<const uint4*>(p.k_new + src);
+    if (ROPE) {
+      int fr, hr, wr;
+      rope_position(p, lo - p.pos0 + r, fr, hr, wr);
+      T* e = reinterpret_cast<T*>(&kq);
+#pragma unroll
+      for (int i = 0; i < VEC / 2; ++i) {
+        const int j = cc * (VEC / 2) + i;                      // complex pair of the head
+        double2 w;
+        if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
+        else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
+        else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
+        const double xr = static_cast<double>(to_f32<T>(e[2 * i])), xi = static_cast<double>(to_f32<T>(e[2 * i + 1]));
+        // float64 product, then float64 -> float32 -> T, as view_as_real(...).type_as(x) does
+        e[2 * i] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
+        e[2 * i + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
+      }
+    }
+    *reinterpret_cast<uint4*>(kp + dst) = kq;
     *reinterpret_cast<uint4*>(vp + dst) = *reinterpret_cast<const uint4*>(p.v_new + src);
   }
   __syncthreads();
@@ -319,13 +358,13 @@ __global__ void block_range_kernel(int64_t* __restrict__ table, int32_t* __restr
 
 using namespace nsa;
 
-extern "C" int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2],
-                                int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
-                                void* v_pool, int32_t page_tokens, int32_t* block_table,
-                                int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
-                                int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
-                                void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
-                                void* stream) {
+static int cache_append_impl(const void* k_new, const void* v_new, const int64_t kv_stride[2],
+                             int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                             void* v_pool, int32_t page_tokens, int32_t* block_table,
+                             int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
+                             int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
+                             void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
+                             const nsa_rope* rope, void* stream) {
   NSA_REQUIRE(S >= 0 && pos0 >= 0 && H > 0 && D > 0 && page_tokens > 0 && max_blocks > 0, NSA_ERR_INVALID,
               "cache_append: bad size");
   NSA_REQUIRE(dtype == NSA_BF16 || dtype == NSA_F16, NSA_ERR_UNSUPPORTED, "cache_append: bf16 / fp16 only");
@@ -346,14 +385,59 @@ extern "C" int nsa_cache_append(const void* k_new, const void* v_new, const int6
                  S, pos0, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
                  static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
                  static_cast<char*>(k_pooled), static_cast<char*>(v_pooled), status};
+  if (rope != nullptr) {
+    NSA_REQUIRE(rope->freqs_f && rope->freqs_h && rope->freqs_w, NSA_ERR_INVALID, "cache_append_rope: null frequency table");
+    NSA_REQUIRE(rope->c_f >= 0 && rope->c_h >= 0 && rope->c_w >= 0 && 2 * (rope->c_f + rope->c_h + rope->c_w) == D,
+                NSA_ERR_INVALID, "cache_append_rope: c_f + c_h + c_w must be D / 2");
+    NSA_REQUIRE(rope->pool_f > 0 && rope->pool_h > 0 && rope->pool_w > 0 && rope->grid_h > 0 && rope->grid_w > 0 &&
+                    rope->grid_h % rope->pool_h == 0 && rope->grid_w % rope->pool_w == 0 && rope->start_frame >= 0,
+                NSA_ERR_INVALID, "cache_append_rope: bad grid / pooling window");
+    NSA_REQUIRE(S % (static_cast<int64_t>(rope->grid_h) * rope->grid_w * rope->pool_f) == 0, NSA_ERR_INVALID,
+                "cache_append_rope: S must be whole groups of pool_f frames of grid_h x grid_w tokens");
+    p.rope_f = static_cast<const double2*>(rope->freqs_f); p.rope_h = static_cast<const double2*>(rope->freqs_h);
+    p.rope_w = static_cast<const double2*>(rope->freqs_w);
+    p.c_f = rope->c_f; p.c_h = rope->c_h; p.c_w = rope->c_w;
+    p.grid_h = rope->grid_h; p.grid_w = rope->grid_w; p.pool_f = rope->pool_f; p.pool_h = rope->pool_h;
+    p.pool_w = rope->pool_w; p.start_frame = rope->start_frame;
+  }
   const int cpr = D * esz / 16, rp = 128 / cpr;
   const size_t smem = 2 * static_cast<size_t>(rp) * D * sizeof(float);
   const dim3 grid(n_touched_blocks, H);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(p);
-  else cache_append_kernel<__half><<<grid, 128, smem, s>>>(p);
+  if (rope != nullptr) {
+    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, true><<<grid, 128, smem, s>>>(p);
+    else cache_append_kernel<__half, true><<<grid, 128, smem, s>>>(p);
+  } else {
+    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, false><<<grid, 128, smem, s>>>(p);
+    else cache_append_kernel<__half, false><<<grid, 128, smem, s>>>(p);
+  }
   NSA_LAUNCH_OK("cache_append_kernel");
   return NSA_OK;
+}
+
+extern "C" int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2],
+                                int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                                void* v_pool, int32_t page_tokens, int32_t* block_table,
+                                int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
+                                int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
+                                void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
+                                void* stream) {
+  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, H, D, k_pool, v_pool, page_tokens, block_table,
+                           max_blocks, new_pages, n_touched_blocks, page_owner, page_stamp, epoch, k_pooled,
+                           v_pooled, status, dtype, nullptr, stream);
+}
+
+extern "C" int nsa_cache_append_rope(const void* k_new, const void* v_new, const int64_t kv_stride[2],
+                                     int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                                     void* v_pool, int32_t page_tokens, int32_t* block_table,
+                                     int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
+                                     int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
+                                     void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
+                                     const nsa_rope* rope, void* stream) {
+  NSA_REQUIRE(rope != nullptr, NSA_ERR_INVALID, "cache_append_rope: rope is null");
+  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, H, D, k_pool, v_pool, page_tokens, block_table,
+                           max_blocks, new_pages, n_touched_blocks, page_owner, page_stamp, epoch, k_pooled,
+                           v_pooled, status, dtype, rope, stream);
 }
 
 extern "C" size_t nsa_cache_dedup_workspace_bytes(int64_t n_keys) {

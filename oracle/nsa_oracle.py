@@ -339,6 +339,38 @@ def merge_partials(outs: List[torch.Tensor], lses: List[torch.Tensor]):
 
 
 # --------------------------------------------------------------------------------------
+# rotary embedding of a key chunk in the reordered token order
+# --------------------------------------------------------------------------------------
+def rope_params(max_seq_len: int, dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """complex128 [max_seq_len, dim/2] table (models/transformers/wan_model.py:37-43)."""
+    freqs = torch.outer(torch.arange(max_seq_len),
+                        1.0 / torch.pow(theta, torch.arange(0, dim, 2).to(torch.float64).div(dim)))
+    return torch.polar(torch.ones_like(freqs), freqs)
+
+
+def reorder_rope_apply(x: torch.Tensor, grid, freqs: torch.Tensor, start_frame: int = 0, pool=(1, 1, 1)):
+    """One sample of causal_reorder_rope_apply (models/transformers/causal_wan_nsa_model.py:72-105):
+    x [S, H, D] with S = f*h*w tokens in the order (f h w fs hs ws) of the pooling windows; the
+    frame / row / column parts of the table multiply the complex pairs in float64."""
+    f, h, w = grid
+    pf, ph, pw = pool
+    S, H, D = x.shape
+    assert S == f * h * w and f % pf == 0 and h % ph == 0 and w % pw == 0
+    c = D // 2
+    parts = freqs.split([c - 2 * (c // 3), c // 3, c // 3], dim=1)
+    t = torch.arange(S)
+    ws = t % pw; t = t // pw
+    hs = t % ph; t = t // ph
+    fs = t % pf; t = t // pf
+    wo = t % (w // pw); t = t // (w // pw)
+    ho = t % (h // ph); t = t // (h // ph)
+    fr, hr, wr = t * pf + fs, ho * ph + hs, wo * pw + ws
+    fac = torch.cat([parts[0][start_frame + fr], parts[1][hr], parts[2][wr]], dim=1)      # [S, c]
+    xc = torch.view_as_complex(x.to(torch.float64).reshape(S, H, c, 2))
+    return torch.view_as_real(xc * fac[:, None, :]).flatten(2).type_as(x)
+
+
+# --------------------------------------------------------------------------------------
 # gate + sum of the three branches (a16)
 # --------------------------------------------------------------------------------------
 def gate_combine(g_logits: torch.Tensor, o_cmp, o_slc, o_swa, gate_mode: str = "sigmoid"):

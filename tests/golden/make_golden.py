@@ -104,6 +104,40 @@ def case_lru(MMCache, seed, heads, cap, n_ids, n_touch):
                 meta=np.array([heads, cap, n_ids, n_touch]))
 
 
+def _reference_function(path, name):
+    """Executes one top-level function of a reference module from its source text (the module
+    itself imports packages that are not installed here)."""
+    import re
+    from einops import rearrange
+    src = open(path).read()
+    m = re.search(r"^def %s\(.*?(?=^(?:def |class |@))" % name, src, re.S | re.M)
+    ns = {"torch": torch, "rearrange": rearrange}
+    exec(m.group(0), ns)
+    return ns[name]
+
+
+def case_rope(ref_root):
+    """causal_reorder_rope_apply on small bf16 chunks: plain and pooled token order."""
+    base = os.path.join(ref_root, "src", "omnimem", "models", "transformers")
+    rope_apply = _reference_function(os.path.join(base, "causal_wan_nsa_model.py"), "causal_reorder_rope_apply")
+    rope_params = _reference_function(os.path.join(base, "wan_model.py"), "rope_params")
+    D, H = 32, 2
+    c = D // 2
+    freqs = torch.cat([rope_params(64, D - 4 * (D // 6)), rope_params(64, 2 * (D // 6)), rope_params(64, 2 * (D // 6))],
+                      dim=1)                                  # the layout WanModel builds (wan_model.py)
+    assert freqs.shape[1] == c
+    out = {"freqs": torch.view_as_real(freqs).numpy()}
+    g = torch.Generator().manual_seed(21)
+    for tag, (f, h, w), pool, start in (("plain", (2, 4, 6), (1, 1, 1), 3), ("pooled", (2, 4, 6), (2, 2, 2), 5)):
+        x = torch.randn(1, f * h * w, H, D, generator=g).to(torch.bfloat16)
+        y = rope_apply(x, torch.tensor([[f, h, w]]), freqs, start_frame=start, pool_f=pool[0], pool_h=pool[1],
+                       pool_w=pool[2])
+        out[f"{tag}_x"] = x[0].float().numpy()
+        out[f"{tag}_y"] = y[0].float().numpy()
+        out[f"{tag}_meta"] = np.array([f, h, w, *pool, start])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (its src/ is imported)")
@@ -128,6 +162,7 @@ def main():
                                           select_attention_torch_chunk, 16, 2, 64, 256, 2, 64,
                                           3, 32, 16, 64, False)
     out["lru"] = case_lru(MMCache, 17, 3, 4, 9, 200)
+    out["rope"] = case_rope(args.reference)
     for name, d in out.items():
         path = os.path.join(HERE, f"{name}.npz")
         np.savez_compressed(path, **d)

@@ -72,6 +72,8 @@ def test_struct_layouts_match_the_header():
     # nsa_kv_source: int32, 2 ptr, 2x3 int64, int64, ptr, 2 int32, 2 ptr, int64
     assert C.sizeof(_lib.KVSource) == 8 + 16 + 48 + 8 + 8 + 8 + 16 + 8 + 8
     assert C.sizeof(_lib.TopkMask) == 12 * 4
+    # nsa_rope: 3 pointers, 9 int32 (padded to 8 bytes)
+    assert C.sizeof(_lib.Rope) == 24 + 40
 
 
 def test_bad_arguments_return_a_status_not_a_crash():

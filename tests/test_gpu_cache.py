@@ -179,3 +179,38 @@ def test_pool_exhaustion_sets_status(dev):
     cache.append(k[:64], k[:64])            # needs 2 more pages, nothing may be evicted
     with pytest.raises(NSABackendError, match="exhausted"):
         cache.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pool", [(1, 1, 1), (2, 2, 2)])
+def test_append_with_rotary_embedding_matches_rope_then_append(dev, pool):
+    """Keys given without RoPE and embedded on the way into the pages == keys embedded by the
+    reference's function (oracle restatement, pinned to it by a golden vector) and appended plainly."""
+    from omnimem_b200.cache import RopeSpec
+    H, D = 3, 128
+    f, h, w = 4, 4, 6                                   # 96 tokens per group of two frames
+    freqs = torch.cat([O.rope_params(1024, D - 4 * (D // 6)), O.rope_params(1024, 2 * (D // 6)),
+                       O.rope_params(1024, 2 * (D // 6))], dim=1)
+    g = torch.Generator().manual_seed(4)
+    plain = _mk(dev, H=H, D=D, pages=64, max_blocks=16, host_tier=False)
+    fused = _mk(dev, H=H, D=D, pages=64, max_blocks=16, host_tier=False)
+    # a first chunk of 32 tokens without RoPE so that the embedded chunks start inside a page
+    k0 = torch.randn(32, H, D, generator=g).to(torch.bfloat16)
+    plain.append(k0.to(dev), k0.to(dev))
+    fused.append(k0.to(dev), k0.to(dev))
+    start = 0
+    for _ in range(2):
+        S = f * h * w
+        k = torch.randn(S, H, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(S, H, D, generator=g).to(torch.bfloat16)
+        k_roped = O.reorder_rope_apply(k, (f, h, w), freqs, start, pool)
+        plain.append(k_roped.to(dev), v.to(dev))
+        fused.append(k.to(dev), v.to(dev), rope=RopeSpec(freqs, (h, w), start, pool))
+        start += f
+    Kp, Vp = _dense_from_cache(plain)
+    Kf, Vf = _dense_from_cache(fused)
+    assert torch.equal(Kp, Kf) and torch.equal(Vp, Vf)
+    assert torch.equal(plain.pooled_keys(), fused.pooled_keys())
+    fused.check_status()
+    with pytest.raises(Exception):
+        fused.append(k[:50].to(dev), v[:50].to(dev), rope=RopeSpec(freqs, (h, w), start, pool))   # not whole frames

@@ -217,3 +217,20 @@ def test_gate_combine_matches_the_written_out_formula():
             assert torch.allclose(got, want, atol=1e-12)
     with pytest.raises(NotImplementedError):
         O.gate_combine(gl, *o, "tanh")
+
+
+def test_rope_matches_the_reference_function(golden):
+    """oracle.reorder_rope_apply against vectors produced by the reference's own
+    causal_reorder_rope_apply (tests/golden/make_golden.py, case_rope): bit-exact in bf16."""
+    g = golden("rope")
+    freqs = torch.view_as_complex(torch.as_tensor(g["freqs"]).double().contiguous())
+    for tag in ("plain", "pooled"):
+        f, h, w, pf, ph, pw, start = (int(v) for v in g[f"{tag}_meta"])
+        x = torch.as_tensor(g[f"{tag}_x"]).to(torch.bfloat16)
+        want = torch.as_tensor(g[f"{tag}_y"]).to(torch.bfloat16)
+        got = O.reorder_rope_apply(x, (f, h, w), freqs, start, (pf, ph, pw))
+        assert torch.equal(got, want), tag
+    # the table builder restates rope_params
+    d = 32
+    table = torch.cat([O.rope_params(64, d - 4 * (d // 6)), O.rope_params(64, 2 * (d // 6)), O.rope_params(64, 2 * (d // 6))], 1)
+    assert torch.equal(torch.view_as_real(table), torch.view_as_real(freqs))
