@@ -44,12 +44,15 @@ __device__ __forceinline__ void gates_of_row(const GateParams& p, int64_t row, f
 // reference's tensors are (g has the activations' dtype).
 template <typename T>
 __global__ void gate_combine_fwd_kernel(const GateParams p) {
-  const int cpr = p.D / 8;
+  const uint32_t cpr = static_cast<uint32_t>(p.D / 8);
   const int64_t total = p.rows * cpr;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = i / cpr;
-    const int cc = static_cast<int>(i - row * cpr);
+  {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    // rows * cpr fits 32 bits for every launch the host makes (checked there): 32-bit division
+    const uint32_t iu = static_cast<uint32_t>(i);
+    const int64_t row = iu / cpr;
+    const int cc = static_cast<int>(iu - static_cast<uint32_t>(row) * cpr);
     float s[3];
     bool inside[3];
     gates_of_row<T>(p, row, s, inside);
@@ -158,7 +161,8 @@ extern "C" int nsa_gate_combine(const void* g_logits, const void* o_cmp, const v
   p.o[0] = static_cast<const char*>(o_cmp); p.o[1] = static_cast<const char*>(o_slc); p.o[2] = static_cast<const char*>(o_swa);
   p.x = static_cast<char*>(x); p.rows = rows; p.D = D; p.softmax = softmax;
   const int64_t total = rows * (D / 8);
-  const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(cdiv64(total, 256), 1 << 20));
+  NSA_REQUIRE(total <= 0xffffffffll, NSA_ERR_INVALID, "gate_combine: too many rows");
+  const unsigned blocks = static_cast<unsigned>(cdiv64(total, 256));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == NSA_BF16) gate_combine_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(p);
   else gate_combine_fwd_kernel<__half><<<blocks, 256, 0, s>>>(p);
