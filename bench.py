@@ -334,7 +334,11 @@ def run_gpu(args):
         dom = max((n for n in per if n in work), key=lambda n: per[n])
         roof = dict(kernels[dom])
         roof.pop("ms")
-        roof.update(kernel=dom, traffic=None, peak_source=pk["source"] + " (burst)",
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, from the ncu
+        # captures summarised under profiles/ (sel_fwd_tc_config2.md, sel_bwd_tc_config2.md)
+        ncu_traffic = {"sel_fwd": 193.1e6 + 11.0e6, "sel_bwd_dq": 222.5e6 + 11.9e6, "sel_bwd_dkv": 206.7e6 + 159.4e6}
+        roof.update(kernel=dom, traffic=ncu_traffic.get(dom), traffic_unit="bytes per launch (ncu capture)",
+                    peak_source=pk["source"] + " (burst)",
                     note="achieved = algorithmic work of the kernel / mean CUDA-event time of its launches "
                          "(eager pass, launches queued behind a spin kernel so the brackets exclude host latency)")
         value = world * flops_step * args.steps / (ms_total * 1e-3) / 1e12
