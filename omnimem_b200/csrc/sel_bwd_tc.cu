@@ -24,6 +24,14 @@ namespace nsa {
 
 int device_status_address(int32_t** out);
 
+#ifdef NSA_TC_TRACE
+// Debug build only: clock64 stamps of thread block (0,0,0); [0][..] MMA issuers, [1][..] row thread 0.
+__device__ long long g_trace_dq[2][512];
+#define TRACE(role, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512) g_trace_dq[role][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, slot) do { } while (0)
+#endif
+
 namespace {
 
 using namespace tc;
@@ -81,6 +89,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
   const int64_t bhm = (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
 
+  if (threadIdx.x == 0) TRACE(1, 0);
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&qdo_full, 1);
@@ -154,6 +163,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const uint32_t tm = tmem_base_s;
   volatile int* abort = &s_abort;
   const int nb = s_nb;
+  if (threadIdx.x == 0) TRACE(1, 1);
 
   if (warp == 4) {
     // ======================= TMA producer =======================
@@ -202,6 +212,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                                      (t == 0 || mbar_wait(&sdp_free, (t - 1) & 1, abort)));    // S / dP of step t-1 were read
         if (!ok) break;
         tc_fence_after();
+        TRACE(0, 8 + t * 8 + 0);
         const uint64_t dK = smem_desc(smem_u32(sK + st * kTile), 16, 1024), dV = smem_desc(smem_u32(sV + st * kTile), 16, 1024);
         if (el) {
 #pragma unroll
@@ -218,6 +229,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           umma_commit(&v_empty[st]);
         }
         __syncwarp();
+        TRACE(0, 8 + t * 8 + 1);
       }
     }
   } else if (warp == 6) {
@@ -230,6 +242,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const int st = t & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(&ds_full, t & 1, abort))) break;
         tc_fence_after();
+        TRACE(0, 8 + t * 8 + 2);
         // K tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as N
         const uint64_t dKmn = smem_desc(smem_u32(sK + st * kTile), 8192, 1024);
         if (el) {
@@ -241,6 +254,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           if (t == nb - 1) umma_commit(&dq_final);
         }
         __syncwarp();
+        TRACE(0, 8 + t * 8 + 3);
       }
     }
   } else if (warp < 4) {
@@ -289,9 +303,12 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const float nl1 = r1 < n_q ? -(p.lse[bhm + r1] * kLog2e - lg) : -INFINITY;
       const float sl = p.scale_log2;
       bool ok = true;
+      if (threadIdx.x == 0) TRACE(1, 2);
       for (int t = 0; t < nb; ++t) {
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full, t & 1, abort));
         if (!ok) break;
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
         tc_fence_after();
         uint32_t x[32], y[32];
         tmem_ld_16x256b_x8_nowait(tm + lane_base + kColS, x);
@@ -303,6 +320,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&sdp_free);
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
         // x[4i], x[4i+1]: row r0, keys 8i+cq, +1;  x[4i+2], x[4i+3]: row r1.  Afterwards x[2i], x[2i+1]
         // hold the packed dS of (r0, r1) for key block i.
         if (nv == 64) {
@@ -327,6 +345,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             x[2 * i + 1] = pack2<__nv_bfloat16>(d10, d11);
           }
         }
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 3);
         if (!__all_sync(0xffffffffu, ds_ok)) {
           ok = __all_sync(0xffffffffu, mbar_wait(&ds_free, (t - 1) & 1, abort));
           if (!ok) break;
@@ -337,7 +356,9 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           stmatrix_x4(aDS + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
         fence_async_smem();                           // make the rows visible to the tensor core's reads
         mbar_arrive(&ds_full);
+        if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 4);
       }
+      if (threadIdx.x == 0) TRACE(1, 3);
       // ---- epilogue: dQ fragments -> bf16 -> swizzled staging tile (the dead Q tile) -> TMA tile stores
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_final, 0, abort));
       if (ok) {
@@ -369,9 +390,11 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     }
   }
 
+  if (threadIdx.x == 0) TRACE(1, 4);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, kTmemCols);
+  if (threadIdx.x == 0) TRACE(1, 5);
   if (threadIdx.x == 0 && s_abort) atomicExch(p.status, NSA_ERR_CUDA);
 }
 
@@ -426,3 +449,10 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
 }
 
 }  // namespace nsa
+
+#ifdef NSA_TC_TRACE
+extern "C" int nsa_debug_trace_dq(long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_dq, sizeof(long long) * 2 * 512));
+  return NSA_OK;
+}
+#endif
