@@ -29,8 +29,8 @@
 namespace nsa {
 
 int device_status_address(int32_t** out);
-int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
-                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
+int make_tile_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                   CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
 
 #ifdef NSA_TC_TRACE
 // Debug build only: clock64 stamps of thread block 0; [0] MMA issuers, [1] row thread 0, [2] producer, [3] epilogue.
@@ -45,12 +45,14 @@ namespace {
 using namespace tc;
 
 constexpr int kThreads = 512;
-constexpr int kStages = 3;               // Q / dO ring
+constexpr int kStages = 4;               // Q / dO ring
 constexpr uint32_t kKVBytes = 32768;     // K tile 16 KiB + V tile 16 KiB
 constexpr uint32_t kQdOBytes = 32768;    // Q 16 KiB + dO 16 KiB per stage
 constexpr uint32_t kPdSBytes = 16384;    // P 8 KiB + dS 8 KiB per buffer
-constexpr uint32_t kOutBytes = 32768;    // epilogue staging: dV tile 16 KiB + dK tile 16 KiB
-constexpr uint32_t kSmemTiles = 2 * kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes + kOutBytes;
+// The epilogue stages the item's dV and dK tiles (16 KiB each) in the ring stage of the item's
+// LAST step: that stage is dead once the last products have run, and handing it back to the
+// producer a little later costs less than a staging buffer that would take a ring stage away.
+constexpr uint32_t kSmemTiles = 2 * kKVBytes + kStages * kQdOBytes + 2 * kPdSBytes;
 
 // TMEM columns: S / dP double buffered (64 columns each), accumulators double buffered
 __device__ __forceinline__ uint32_t col_s(int buf) { return buf * 128; }
@@ -73,7 +75,12 @@ struct TcDkvParams {
   int32_t* counter;          // zeroed before the launch: next work item to hand out
 };
 
-struct Item { int b, h, blk, beg, n_ent, row, g0; bool active; };   // g0: first bucket entry (query group)
+constexpr int kItemGroups = 16;          // bucket entries the scheduler copies into the item
+struct Item {
+  int b, h, blk, beg, n_ent, row;
+  bool active;
+  int g[kItemGroups];                    // the bucket's first entries (query groups); later ones are read from global memory
+};
 
 // Decodes work item i (block fastest, then head, then batch) and its bucket.
 __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
@@ -93,24 +100,8 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
     if (page < 0) it.n_ent = 0;
   }
   it.active = it.n_ent > 0;
-  it.g0 = 0;
   return it;
 }
-// Work items are handed out through a global counter (buckets differ a lot in length, a static
-// split leaves thread blocks idle).  The producer takes the ticket, decodes the item and
-// publishes it in a 4-deep shared-memory ring that the other roles follow; n_ent = -1 ends it.
-__device__ __forceinline__ Item fetch_item(const TcDkvParams& p, int64_t n_items) {
-  const int64_t t = atomicAdd(p.counter, 1);
-  if (t < n_items) {
-    Item it = get_item(p, t);
-    if (it.active)
-      it.g0 = p.groups[(static_cast<int64_t>(it.b) * p.H + it.h) * p.MG * p.T + it.beg];
-    return it;
-  }
-  Item it{0, 0, 0, 0, -1, 0, 0, false};
-  return it;
-}
-
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -123,14 +114,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint8_t* sKV = tiles;                               // [buffer]{ K [2][64][128 B], V [2][64][128 B] }, item i in buffer i & 1
   uint8_t* sQdO = tiles + 2 * kKVBytes;               // [stage]{ Q [2][64][128 B], dO [2][64][128 B] }
   uint8_t* sPdS = sQdO + kStages * kQdOBytes;         // [buffer]{ P [64 q][128 B], dS [64 q][128 B] } swizzled
-  uint8_t* sOut = sPdS + 2 * kPdSBytes;               // { dV, dK }[2][64 keys][128 B] swizzled, for the tile stores
 
   __shared__ uint64_t kv_full[2], kv_empty[2], qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
       pds_free[2], acc_full[2], acc_free[2];
   __shared__ uint64_t sched_full[4], sched_empty[4];
   __shared__ Item s_items[4];
-  __shared__ float2 s_meta[kStages][64];              // per row of the stage's group: LSE * log2(e) (+inf = no row), delta
-  __shared__ int s_nkv[kStages];                      // visible keys of the stage's step
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
@@ -148,7 +136,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 387); }
-    for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 2); mbar_init(&qdo_empty[i], 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
       mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 128);
@@ -170,90 +158,61 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int64_t bucket_row = static_cast<int64_t>(p.MG) * p.T;
 
   if (warp == 8) {
-    // ======================= producer (whole warp; lane 0 issues the copies) =======================
-    uint32_t ic = 0, sc = 0;
-    bool ok = true;
-    for (uint32_t n = 0; ok; ++n) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
-      if (!ok) break;
-      const Item it = s_items[n & 3];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sched_empty[n & 3]);
-      if (it.n_ent < 0) break;
-      if (!it.active) continue;
-      TRACE(2, 16 + sc * 4 + 0);
-      const int kb = ic & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty[kb], ((ic >> 1) & 1) ^ 1, abort));
-      if (!ok) break;
-      TRACE(2, 16 + sc * 4 + 1);
-      if (lane == 0) {
-        uint8_t* kvb = sKV + kb * kKVBytes;
-        mbar_expect_tx(&kv_full[kb], kKVBytes);
-        for (int dh = 0; dh < 2; ++dh) {
+    // ======================= producer (one lane) =======================
+    // Issues copies and nothing else: the item and its bucket entries come from the scheduler's
+    // ring, so no global load sits between two copies.
+    if (lane == 0) {
+      uint32_t ic = 0, sc = 0;
+      bool ok = true;
+      for (uint32_t n = 0; ok; ++n) {
+        ok = mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort);
+        if (!ok) break;
+        const Item* it = &s_items[n & 3];
+        const int n_ent = it->n_ent;
+        if (n_ent <= 0) {
+          mbar_arrive(&sched_empty[n & 3]);
+          if (n_ent < 0) break;
+          continue;
+        }
+        const int ib = it->b, ih = it->h, irow = it->row;
+        TRACE(2, 16 + sc * 4 + 0);
+        const int kb = ic & 1;
+        ok = mbar_wait(&kv_empty[kb], ((ic >> 1) & 1) ^ 1, abort);
+        if (!ok) break;
+        TRACE(2, 16 + sc * 4 + 1);
+        {
+          uint8_t* kvb = sKV + kb * kKVBytes;
+          mbar_expect_tx(&kv_full[kb], kKVBytes);
           if (p.paged) {
-            tma_load_2d(kvb + dh * 8192, &mapK, dh * 64, it.row, &kv_full[kb]);
-            tma_load_2d(kvb + 16384 + dh * 8192, &mapV, dh * 64, it.row, &kv_full[kb]);
+            tma_load_3d(kvb, &mapK, 0, irow, 0, &kv_full[kb]);
+            tma_load_3d(kvb + 16384, &mapV, 0, irow, 0, &kv_full[kb]);
           } else {
-            tma_load_4d(kvb + dh * 8192, &mapK, dh * 64, it.h, it.row, it.b, &kv_full[kb]);
-            tma_load_4d(kvb + 16384 + dh * 8192, &mapV, dh * 64, it.h, it.row, it.b, &kv_full[kb]);
+            tma_load_5d(kvb, &mapK, 0, ih, irow, 0, ib, &kv_full[kb]);
+            tma_load_5d(kvb + 16384, &mapV, 0, ih, irow, 0, ib, &kv_full[kb]);
           }
         }
-      }
-      const int32_t* bucket = p.groups + (static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg;
-      const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
-      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
-      const int64_t bh = (static_cast<int64_t>(it.b) * p.H + it.h) * p.M;
-      // Bucket entries are read two steps ahead and the rows' LSE / delta (two rows per lane) one
-      // step ahead, so that none of these dependent global loads delays the copies of a step.
-      auto load_rows = [&](int g, float2 (&mt)[2]) {
-        const int64_t m0 = static_cast<int64_t>(g) * p.G;
-        const int nq = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int r = lane + 32 * k;
-          mt[k].x = r < nq ? p.lse[bh + m0 + r] * kLog2e : INFINITY;
-          mt[k].y = r < nq ? p.delta[bh + m0 + r] : 0.f;
-        }
-      };
-      int g_cur = it.g0, g_next = it.n_ent > 1 ? bucket[1] : 0;
-      float2 mt_cur[2], mt_next[2];
-      load_rows(g_cur, mt_cur);
-      for (int t = 0; t < it.n_ent; ++t, ++sc) {
-        const int st = sc % kStages, ph = (sc / kStages) & 1;
-        const int g = g_cur;
-        const int g_after = (t + 2 < it.n_ent) ? bucket[t + 2] : 0;
-        if (t + 1 < it.n_ent) load_rows(g_next, mt_next);
-        const int64_t m0 = static_cast<int64_t>(g) * p.G;
-        ok = __all_sync(0xffffffffu, mbar_wait(&qdo_empty[st], ph ^ 1, abort));
-        if (!ok) break;
-        TRACE(2, 16 + sc * 4 + 2);
-        if (lane == 0) {
+        const int32_t* bucket = p.groups + (static_cast<int64_t>(ib) * p.H + ih) * bucket_row + it->beg;
+        for (int t = 0; t < n_ent; ++t, ++sc) {
+          const int st = sc % kStages, ph = (sc / kStages) & 1;
+          const int g = t < kItemGroups ? it->g[t] : bucket[t];
+          const int m0 = g * p.G;
+          TRACE(2, 16 + sc * 4 + 3);
+          ok = mbar_wait(&qdo_empty[st], ph ^ 1, abort);
+          if (!ok) break;
+          TRACE(2, 16 + sc * 4 + 2);
           uint8_t* dq = sQdO + st * kQdOBytes;
           mbar_expect_tx(&qdo_full[st], kQdOBytes);
-          for (int dh = 0; dh < 2; ++dh) {
-            tma_load_4d(dq + dh * 8192, &mapQ, dh * 64, it.h, static_cast<int>(m0), it.b, &qdo_full[st]);
-            tma_load_4d(dq + 16384 + dh * 8192, &mapDO, dh * 64, it.h, static_cast<int>(m0), it.b, &qdo_full[st]);
-          }
-          int nkv = n_blk;
-          if (p.causal) {
-            const int64_t lim = (m0 / p.chunk_size + 1) * p.chunk_size - t0;
-            if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
-          }
-          s_nkv[st] = nkv;
+          tma_load_5d(dq, &mapQ, 0, ih, m0, 0, ib, &qdo_full[st]);
+          tma_load_5d(dq + 16384, &mapDO, 0, ih, m0, 0, ib, &qdo_full[st]);
         }
-        s_meta[st][lane] = mt_cur[0];
-        s_meta[st][lane + 32] = mt_cur[1];
-        mt_cur[0] = mt_next[0]; mt_cur[1] = mt_next[1];
-        g_cur = g_next; g_next = g_after;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&qdo_full[st]);
+        mbar_arrive(&sched_empty[n & 3]);              // the item's bucket entries are no longer needed
+        ++ic;
       }
-      ++ic;
-    }
-    if (*abort && lane == 0) {
-      // consumers have stopped: wait (bounded) for the copies still in flight
-      for (uint32_t u = (ic > 2 ? ic - 2 : 0); u < ic; ++u) mbar_wait(&kv_full[u & 1], (u >> 1) & 1, abort);
-      for (uint32_t u = (sc > kStages ? sc - kStages : 0); u < sc; ++u) mbar_wait(&qdo_full[u % kStages], (u / kStages) & 1, abort);
+      if (*abort) {
+        // consumers have stopped: wait (bounded) for the copies still in flight
+        for (uint32_t u = (ic > 2 ? ic - 2 : 0); u < ic; ++u) mbar_wait(&kv_full[u & 1], (u >> 1) & 1, abort);
+        for (uint32_t u = (sc > kStages ? sc - kStages : 0); u < sc; ++u) mbar_wait(&qdo_full[u % kStages], (u / kStages) & 1, abort);
+      }
     }
   } else if (warp == 9) {
     // ======================= MMA issuer 1: S and dP of every step =======================
@@ -339,7 +298,8 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               umma_ss(tdk, desc_advance(dQmn, kk * 2048), desc_advance(dDS, kk * 2048), idesc_second, kk > 0 ? 1u : acc0);
-            umma_commit(&qdo_empty[st]);
+            // the stage of the item's last step goes to the epilogue, which hands it back
+            if (t != n_ent - 1) umma_commit(&qdo_empty[st]);
             umma_commit(&pds_free[pb]);
             if (t == n_ent - 1) umma_commit(&acc_full[acc]);
           }
@@ -350,18 +310,36 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       }
     }
   } else if (warp == 11) {
-    // ======================= scheduler =======================
-    // Takes tickets from the global counter, decodes each item (bucket bounds, page, first
-    // group) and publishes it in the 4-deep ring the other roles follow; the three dependent
-    // global loads behind one item are paid here, several items ahead of the copies.
-    if (lane == 0) {
-      for (uint32_t n = 0;; ++n) {
-        const Item it = fetch_item(p, n_items);
-        if (!mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort)) break;
-        s_items[n & 3] = it;
-        mbar_arrive(&sched_full[n & 3]);
-        if (it.n_ent < 0) break;
+    // ======================= scheduler (whole warp) =======================
+    // Takes tickets from the global counter (buckets differ a lot in length, a static split
+    // leaves thread blocks idle), decodes each item (bucket bounds, page) and copies the bucket's
+    // first entries, one per lane; publishes it in the 4-deep ring the other roles follow, so the
+    // dependent global loads behind one item are paid here, several items ahead of the copies.
+    // The ticket of the next item is taken while the current one is decoded; n_ent = -1 ends it.
+    int tk = lane == 0 ? atomicAdd(p.counter, 1) : 0;
+    for (uint32_t n = 0;; ++n) {
+      tk = __shfl_sync(0xffffffffu, tk, 0);
+      const bool live = tk < n_items;
+      int tk_next = 0;
+      if (lane == 0 && live) tk_next = atomicAdd(p.counter, 1);
+      Item it{0, 0, 0, 0, -1, 0, false, {}};
+      int gl = 0;
+      if (live) {
+        it = get_item(p, tk);
+        if (lane < it.n_ent && lane < kItemGroups)
+          gl = p.groups[(static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg + lane];
       }
+      if (!__all_sync(0xffffffffu, mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort))) break;
+      Item* slot = &s_items[n & 3];
+      if (lane == 0) {
+        slot->b = it.b; slot->h = it.h; slot->blk = it.blk; slot->beg = it.beg;
+        slot->n_ent = it.n_ent; slot->row = it.row; slot->active = it.active;
+      }
+      if (lane < kItemGroups) slot->g[lane] = gl;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sched_full[n & 3]);
+      if (it.n_ent < 0) break;
+      tk = tk_next;
     }
   } else if (warp < 4 || warp >= 12) {
     // ======================= row arithmetic: P and dS on accumulator fragments =======================
@@ -383,13 +361,36 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     for (uint32_t n = 0; ok; ++n) {
       ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
       if (!ok) break;
-      const int n_ent = s_items[n & 3].n_ent;
-      mbar_arrive(&sched_empty[n & 3]);
-      if (n_ent < 0) break;
+      const Item* it = &s_items[n & 3];
+      const int n_ent = it->n_ent;
+      if (n_ent <= 0) {
+        mbar_arrive(&sched_empty[n & 3]);
+        if (n_ent < 0) break;
+        continue;
+      }
+      const int64_t bh = (static_cast<int64_t>(it->b) * p.H + it->h) * p.M;
+      const int32_t* bucket = p.groups + (static_cast<int64_t>(it->b) * p.H + it->h) * bucket_row + it->beg;
+      const int64_t t0 = static_cast<int64_t>(it->blk) * 64;
+      const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
       for (int t = 0; t < n_ent; ++t, ++sc) {
-        const int st = sc % kStages, sb = sc & 1, ph = (sc >> 1) & 1;
+        const int sb = sc & 1, ph = (sc >> 1) & 1;
         if (sb != grp) continue;
         if (tracer) TRACE(1, 16 + sc * 8 + 0);
+        // This thread's two rows of the step's query group: LSE * log2(e) (+inf = no such row) and
+        // delta, and the step's visible key count; the loads fly while S and dP are computed.
+        const int g = t < kItemGroups ? it->g[t] : bucket[t];
+        const int64_t m_first = static_cast<int64_t>(g) * p.G;
+        const int nq = static_cast<int>(p.M - m_first < p.G ? p.M - m_first : p.G);
+        float2 m0, m1;
+        m0.x = r0 < nq ? p.lse[bh + m_first + r0] * kLog2e : INFINITY;
+        m0.y = r0 < nq ? p.delta[bh + m_first + r0] : 0.f;
+        m1.x = r1 < nq ? p.lse[bh + m_first + r1] * kLog2e : INFINITY;
+        m1.y = r1 < nq ? p.delta[bh + m_first + r1] : 0.f;
+        int nkv = n_blk;
+        if (p.causal) {
+          const int64_t lim = (static_cast<int64_t>(static_cast<uint32_t>(m_first) / static_cast<uint32_t>(p.chunk_size)) + 1) * p.chunk_size - t0;
+          if (lim < nkv) nkv = static_cast<int>(lim < 0 ? 0 : lim);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[sb], ph, abort));
         if (!ok) break;
         if (tracer) TRACE(1, 16 + sc * 8 + 1);
@@ -397,8 +398,6 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         uint32_t x[32], y[32];
         tmem_ld_16x256b_x8_nowait(tm + lane_base + col_s(sb), x);
         tmem_ld_16x256b_x8_nowait(tm + lane_base + col_dp(sb), y);
-        const float2 m0 = s_meta[st][r0], m1 = s_meta[st][r1];
-        const int nkv = s_nkv[st];
         // the buffer's previous P / dS (two steps ago) must have been consumed: normally long true,
         // so poll once here, where the round trip hides behind the TMEM load
         const bool pds_ok = mbar_try(&pds_free[sb], ph ^ 1);
@@ -460,12 +459,13 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_arrive(&pds_full[sb]);
         if (tracer) TRACE(1, 16 + sc * 8 + 4);
       }
+      if (ok) mbar_arrive(&sched_empty[n & 3]);        // the item's bucket entries are no longer needed
     }
   } else if (warp < 8) {
     // ======================= epilogue (warps 4-7): one head-dim lane per thread =======================
     const int te = threadIdx.x - 128;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t ic = 0;
+    uint32_t ic = 0, sc = 0;
     bool ok = true;
     for (uint32_t n = 0; ok; ++n) {
       ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
@@ -491,9 +491,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (!ok) break;
       if (te == 0) TRACE(3, 16 + ic * 4 + 1);
       tc_fence_after();
-      // the staging tiles are free once the previous item's tile stores have read them
-      if (te == 0) bulk_wait_read_all();
-      named_barrier(3, 128);
+      // acc_full also says that every product reading the last step's Q / dO stage has run:
+      // the stage now holds { dV, dK }[2][64 keys][128 B] swizzled, for the tile stores
+      sc += static_cast<uint32_t>(it.n_ent);
+      const int st_last = static_cast<int>((sc - 1) % kStages);
+      uint8_t* sOut = sQdO + st_last * kQdOBytes;
       // Accumulator fragments (16 head-dim lanes x 64 keys per load) are packed to bf16 pairs of
       // adjacent keys and stored TRANSPOSED, 8 x 8 at a time, into the [key][head dim] tiles.
 #pragma unroll
@@ -527,11 +529,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       named_barrier(3, 128);
       if (te == 0) {
         const int tok = static_cast<int>(t0);
-        for (int dh = 0; dh < 2; ++dh) {
-          tma_store_4d(&mapDV, sOut + dh * 8192, dh * 64, it.h, tok, it.b);
-          tma_store_4d(&mapDK, sOut + 16384 + dh * 8192, dh * 64, it.h, tok, it.b);
-        }
+        tma_store_5d(&mapDV, sOut, 0, it.h, tok, 0, it.b);
+        tma_store_5d(&mapDK, sOut + 16384, 0, it.h, tok, 0, it.b);
         bulk_commit_group();
+        bulk_wait_read_all();                          // the stores have read the stage: back to the producer
+        mbar_arrive(&qdo_empty[st_last]);
         TRACE(3, 16 + ic * 4 + 2);
       }
       ++ic;
@@ -564,14 +566,14 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   if (encode_tiled_fn() == nullptr) return NSA_OK;
   CUtensorMap mapQ, mapDO, mapK, mapV, mapDK, mapDV;
   int rc;
-  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
-  if ((rc = make_qkv_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
+  if ((rc = make_tile_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  if ((rc = make_tile_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
   {
-    // dK / dV are contiguous [B, N, H, 128]: the same 64 x 64 boxes as the loads, used for tile stores
+    // dK / dV are contiguous [B, N, H, 128]: the same tile boxes as the loads, used for tile stores
     const int64_t N = kv->n_tokens;
     const int64_t st[4] = {N * H * 128, static_cast<int64_t>(H) * 128, 128, 1};
-    if ((rc = make_qkv_maps(dk, st, nullptr, B, N, H, &mapDK, nullptr, nullptr))) return rc;
-    if ((rc = make_qkv_maps(dv, st, nullptr, B, N, H, &mapDV, nullptr, nullptr))) return rc;
+    if ((rc = make_tile_maps(dk, st, nullptr, B, N, H, &mapDK, nullptr, nullptr))) return rc;
+    if ((rc = make_tile_maps(dv, st, nullptr, B, N, H, &mapDV, nullptr, nullptr))) return rc;
   }
   TcDkvParams p;
   p.groups = groups; p.offsets = offsets; p.lse = lse; p.delta = delta;

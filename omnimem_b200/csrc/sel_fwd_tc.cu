@@ -517,6 +517,37 @@ int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* k
   return NSA_OK;
 }
 
+// Maps whose box is a whole 64-row x 128-column tile of one head, landing in shared memory as
+// the two 64-column halves one after the other ([half][row][64], each half 128-byte swizzled):
+// the head dimension is split into (64, 2) and the half index is placed ABOVE the row dimension.
+// Dense tensors [B,M,H,128]: coordinates (0, head, row, 0, batch); paged K/V [rows,128]:
+// coordinates (0, row, 0).  One copy instruction per tile instead of two.
+int make_tile_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                   CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV) {
+  int rc;
+  const uint32_t box5[5] = {64, 1, 64, 2, 1};
+  auto dense = [&](CUtensorMap* map, const void* base, const int64_t* stride, int64_t rows) {
+    const uint64_t dims[5] = {64, static_cast<uint64_t>(H), static_cast<uint64_t>(rows), 2, static_cast<uint64_t>(B)};
+    const uint64_t st[4] = {static_cast<uint64_t>(stride[2]) * 2, static_cast<uint64_t>(stride[1]) * 2, 128,
+                            B > 1 ? static_cast<uint64_t>(stride[0]) * 2 : static_cast<uint64_t>(stride[1]) * 2 * rows};
+    return tc::make_bf16_map(map, base, 5, dims, st, box5);
+  };
+  if (q != nullptr && (rc = dense(mapQ, q, q_stride, M))) return rc;
+  if (kv == nullptr) return NSA_OK;
+  if (kv->mode == NSA_KV_DENSE) {
+    if ((rc = dense(mapK, kv->k, kv->k_stride, kv->n_tokens))) return rc;
+    if ((rc = dense(mapV, kv->v, kv->v_stride, kv->n_tokens))) return rc;
+  } else {
+    const uint64_t rows = kv->num_pages > 0 ? static_cast<uint64_t>(kv->num_pages) * 64 : (1ull << 31);
+    const uint64_t dims[3] = {64, rows, 2};
+    const uint64_t st[2] = {256, 128};
+    const uint32_t box[3] = {64, 64, 2};
+    if ((rc = tc::make_bf16_map(mapK, kv->k, 3, dims, st, box))) return rc;
+    if ((rc = tc::make_bf16_map(mapV, kv->v, 3, dims, st, box))) return rc;
+  }
+  return NSA_OK;
+}
+
 // 4-D map of a [B,M,H,128] bf16 tensor whose box holds `box_rows` rows of one head (64 columns):
 // for tile stores of a query group shorter than 64 rows, which must not touch the next group.
 int make_rows_map(const void* q, const int64_t* q_stride, int B, int64_t M, int H, int box_rows, CUtensorMap* map) {
