@@ -169,26 +169,20 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // ======================= TMA producer =======================
     if (lane == 0 && nb > 0) {
       mbar_expect_tx(&qdo_full, 2 * kTile);
-      for (int dh = 0; dh < 2; ++dh) {
-        tma_load_4d(sQ + dh * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
-        tma_load_4d(sDO + dh * 8192, &mapDO, dh * 64, h, static_cast<int>(m0), b, &qdo_full);
-      }
+      tma_load_5d(sQ, &mapQ, 0, h, static_cast<int>(m0), 0, b, &qdo_full);
+      tma_load_5d(sDO, &mapDO, 0, h, static_cast<int>(m0), 0, b, &qdo_full);
       int t = 0;
       for (; t < nb; ++t) {
         const int st = t & 1, ph = (t >> 1) & 1;
         const int row = s_row[t];
         if (!mbar_wait(&k_empty[st], ph ^ 1, abort)) break;
         mbar_expect_tx(&k_full[st], kTile);
-        for (int dh = 0; dh < 2; ++dh) {
-          if (p.paged) tma_load_2d(sK + st * kTile + dh * 8192, &mapK, dh * 64, row, &k_full[st]);
-          else tma_load_4d(sK + st * kTile + dh * 8192, &mapK, dh * 64, h, row, b, &k_full[st]);
-        }
+        if (p.paged) tma_load_3d(sK + st * kTile, &mapK, 0, row, 0, &k_full[st]);
+        else tma_load_5d(sK + st * kTile, &mapK, 0, h, row, 0, b, &k_full[st]);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) { ++t; break; }
         mbar_expect_tx(&v_full[st], kTile);
-        for (int dh = 0; dh < 2; ++dh) {
-          if (p.paged) tma_load_2d(sV + st * kTile + dh * 8192, &mapV, dh * 64, row, &v_full[st]);
-          else tma_load_4d(sV + st * kTile + dh * 8192, &mapV, dh * 64, h, row, b, &v_full[st]);
-        }
+        if (p.paged) tma_load_3d(sV + st * kTile, &mapV, 0, row, 0, &v_full[st]);
+        else tma_load_5d(sV + st * kTile, &mapV, 0, h, row, 0, b, &v_full[st]);
       }
       if (*abort) {
         // the other roles have stopped consuming: wait (bounded) for the copies still in flight
@@ -400,8 +394,8 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 
 }  // namespace
 
-int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
-                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
+int make_tile_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
+                   CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV);
 int make_rows_map(const void* q, const int64_t* q_stride, int B, int64_t M, int H, int box_rows, CUtensorMap* map);
 
 // Launches the tensor-core dQ kernel when it covers the call (*launched = true).
@@ -424,8 +418,8 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
   if (encode_tiled_fn() == nullptr) return NSA_OK;
   CUtensorMap mapQ, mapDO, mapK, mapV, mapDQ;
   int rc;
-  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
-  if ((rc = make_qkv_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
+  if ((rc = make_tile_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  if ((rc = make_tile_maps(d_out, do_stride, nullptr, B, M, H, &mapDO, nullptr, nullptr))) return rc;
   // the store box holds G rows: a group shorter than 64 rows must not write into the next group
   if ((rc = make_rows_map(dq, dq_stride, B, M, H, G, &mapDQ))) return rc;
   TcDqParams p;

@@ -210,23 +210,19 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // ======================= TMA producer =======================
     if (lane == 0) {
       mbar_expect_tx(&q_full, kTile);
-      for (int dh = 0; dh < 2; ++dh) tma_load_4d(sQ + dh * 8192, &mapQ, dh * 64, h, static_cast<int>(m0), b, &q_full);
+      tma_load_5d(sQ, &mapQ, 0, h, static_cast<int>(m0), 0, b, &q_full);
       int t = 0;
       for (; t < nb; ++t) {
         const int st = t & 1, ph = (t >> 1) & 1;
         const int row = s_row[t];
         if (!mbar_wait(&k_empty[st], ph ^ 1, abort)) break;
         mbar_expect_tx(&k_full[st], kTile);
-        for (int dh = 0; dh < 2; ++dh) {
-          if (p.paged) tma_load_2d(sK + st * kTile + dh * 8192, &mapK, dh * 64, row, &k_full[st]);
-          else tma_load_4d(sK + st * kTile + dh * 8192, &mapK, dh * 64, h, row, b, &k_full[st]);
-        }
+        if (p.paged) tma_load_3d(sK + st * kTile, &mapK, 0, row, 0, &k_full[st]);
+        else tma_load_5d(sK + st * kTile, &mapK, 0, h, row, 0, b, &k_full[st]);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) { ++t; break; }
         mbar_expect_tx(&v_full[st], kTile);
-        for (int dh = 0; dh < 2; ++dh) {
-          if (p.paged) tma_load_2d(sV + st * kTile + dh * 8192, &mapV, dh * 64, row, &v_full[st]);
-          else tma_load_4d(sV + st * kTile + dh * 8192, &mapV, dh * 64, h, row, b, &v_full[st]);
-        }
+        if (p.paged) tma_load_3d(sV + st * kTile, &mapV, 0, row, 0, &v_full[st]);
+        else tma_load_5d(sV + st * kTile, &mapV, 0, h, row, 0, b, &v_full[st]);
       }
       if (*abort) {
         // the other roles have stopped consuming: wait (bounded) for the copies still in flight
@@ -483,40 +479,6 @@ int device_status_address(int32_t** out) {
   return NSA_OK;
 }
 
-// Tensor maps of the tensor-core kernels: a [B,M,H,128] bf16 query-like tensor as a 4-D map
-// (box = 64 columns x 64 rows of one head) and, when `kv` is given, K and V either as 4-D maps of
-// the dense tensors or as 2-D maps over the page pool [num_pages*64, 128].
-int make_qkv_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int B, int64_t M, int H,
-                  CUtensorMap* mapQ, CUtensorMap* mapK, CUtensorMap* mapV) {
-  int rc;
-  const uint32_t box4[4] = {64, 1, 64, 1};
-  {
-    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), static_cast<uint64_t>(M), static_cast<uint64_t>(B)};
-    const uint64_t st[3] = {static_cast<uint64_t>(q_stride[2]) * 2, static_cast<uint64_t>(q_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(q_stride[0]) * 2 : static_cast<uint64_t>(q_stride[1]) * 2 * M};
-    if ((rc = tc::make_bf16_map(mapQ, q, 4, dims, st, box4))) return rc;
-  }
-  if (kv == nullptr) return NSA_OK;
-  if (kv->mode == NSA_KV_DENSE) {
-    const uint64_t N = static_cast<uint64_t>(kv->n_tokens);
-    const uint64_t dims[4] = {128, static_cast<uint64_t>(H), N, static_cast<uint64_t>(B)};
-    const uint64_t sk[3] = {static_cast<uint64_t>(kv->k_stride[2]) * 2, static_cast<uint64_t>(kv->k_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(kv->k_stride[0]) * 2 : static_cast<uint64_t>(kv->k_stride[1]) * 2 * N};
-    const uint64_t sv[3] = {static_cast<uint64_t>(kv->v_stride[2]) * 2, static_cast<uint64_t>(kv->v_stride[1]) * 2,
-                            B > 1 ? static_cast<uint64_t>(kv->v_stride[0]) * 2 : static_cast<uint64_t>(kv->v_stride[1]) * 2 * N};
-    if ((rc = tc::make_bf16_map(mapK, kv->k, 4, dims, sk, box4))) return rc;
-    if ((rc = tc::make_bf16_map(mapV, kv->v, 4, dims, sv, box4))) return rc;
-  } else {
-    const uint64_t rows = kv->num_pages > 0 ? static_cast<uint64_t>(kv->num_pages) * 64 : (1ull << 31);
-    const uint64_t dims[2] = {128, rows};
-    const uint64_t st[1] = {256};
-    const uint32_t box[2] = {64, 64};
-    if ((rc = tc::make_bf16_map(mapK, kv->k, 2, dims, st, box))) return rc;
-    if ((rc = tc::make_bf16_map(mapV, kv->v, 2, dims, st, box))) return rc;
-  }
-  return NSA_OK;
-}
-
 // Maps whose box is a whole 64-row x 128-column tile of one head, landing in shared memory as
 // the two 64-column halves one after the other ([half][row][64], each half 128-byte swizzled):
 // the head dimension is split into (64, 2) and the half index is placed ABOVE the row dimension.
@@ -581,7 +543,7 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
     return NSA_OK;
   CUtensorMap mapQ, mapK, mapV, mapO;
   int rc;
-  if ((rc = make_qkv_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
+  if ((rc = make_tile_maps(q, q_stride, kv, B, M, H, &mapQ, &mapK, &mapV))) return rc;
   // the store box holds G rows: a group shorter than 64 rows must not write into the next group
   if ((rc = make_rows_map(out, out_stride, B, M, H, G, &mapO))) return rc;
 
