@@ -7,18 +7,19 @@
 // SM) take items from a global counter.  A step is ONE bucket entry (one query group against
 // the item's block); most buckets hold one to three entries, so small steps in a deep pipeline
 // beat wide ones.  Roles, pipelined across steps and across items:
-//   warp 8   producer: K, V tile of the item (TMA); per step the Q and dO rows of the group
-//            into a four-stage ring (TMA), plus each row's LSE and delta and the step's visible
-//            key count into the same stage (the whole warp loads them, two rows per lane)
-//   warp 11  scheduler: item tickets from the global counter, decoded a few items ahead
+//   warp 11  scheduler: item tickets from the global counter, decoded a few items ahead and
+//            published, with the bucket's first entries, in a small ring the other roles follow
+//   warp 8   producer (one lane): nothing but copies - the K, V tile of the item and, per step,
+//            the Q and dO rows of the group into a four-stage ring, one TMA copy per tile
 //   warp 9   MMA issuer 1, per step:  S = Q K^T, dP = dO V^T          (M=64, N=64, K=128)
 //   warp 10  MMA issuer 2, per step:  dV^T += dO^T P,  dK^T += Q^T dS  (M=128 = head dim, N=64 keys, K=64 rows)
 //   warps 0-3 and 12-15  row arithmetic on the accumulator fragments (16 rows x 64 keys per warp;
 //            the first group takes the even steps, the second the odd ones):
 //            P = exp2(S c - LSE), dS = P (dP - delta) scale, stored as bf16 with stmatrix into
-//            the 128-byte-swizzled shared-memory tiles the second products read
-//   warps 4-7  epilogue: one head-dim lane per thread, read dV^T / dK^T from TMEM and store the
-//            transposed tile; items with an empty bucket are zero-filled here
+//            the 128-byte-swizzled shared-memory tiles the second products read; each thread
+//            loads its rows' LSE and delta itself while S and dP are being computed
+//   warps 4-7  epilogue: read dV^T / dK^T from TMEM, transpose into the ring stage of the item's
+//            last step and store the two tiles with TMA; items with an empty bucket are zero-filled here
 // S/dP, the P/dS tiles and the dV^T/dK^T accumulators are double buffered.
 #include "sel_common.cuh"
 #include "tc_common.cuh"
@@ -36,6 +37,8 @@ int make_tile_maps(const void* q, const int64_t* q_stride, const nsa_kv_source* 
 // Debug build only: clock64 stamps of thread block 0; [0] MMA issuers, [1] row thread 0, [2] producer, [3] epilogue.
 __device__ long long g_trace_dkv[4][1024];
 #define TRACE(role, slot) do { if (blockIdx.x == 0 && (slot) < 1024) g_trace_dkv[role][slot] = clock64(); } while (0)
+__device__ unsigned long long g_trace_dkv_span[256][2];   // per thread block: globaltimer at start and end
+__device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #else
 #define TRACE(role, slot) do { } while (0)
 #endif
@@ -75,6 +78,7 @@ struct TcDkvParams {
   int32_t* counter;          // zeroed before the launch: next work item to hand out
 };
 
+constexpr uint32_t kSched = 4;           // items the scheduler may run ahead of the slowest role
 constexpr int kItemGroups = 16;          // bucket entries the scheduler copies into the item
 struct Item {
   int b, h, blk, beg, n_ent, row;
@@ -117,11 +121,14 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   __shared__ uint64_t kv_full[2], kv_empty[2], qdo_full[kStages], qdo_empty[kStages], sdp_full[2], sdp_free[2], pds_full[2],
       pds_free[2], acc_full[2], acc_free[2];
-  __shared__ uint64_t sched_full[4], sched_empty[4];
-  __shared__ Item s_items[4];
+  __shared__ uint64_t sched_full[kSched], sched_empty[kSched];
+  __shared__ Item s_items[kSched];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
+#ifdef NSA_TC_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_dkv_span[blockIdx.x][0] = global_ns();
+#endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
     // The host sizes the dynamic segment as the tiles plus the padding up to the next 1 KiB
@@ -135,7 +142,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   }
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int i = 0; i < 4; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 387); }
+    for (int i = 0; i < kSched; ++i) { mbar_init(&sched_full[i], 1); mbar_init(&sched_empty[i], 387); }
     for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
@@ -165,12 +172,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
-        ok = mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort);
+        ok = mbar_wait(&sched_full[n % kSched], (n / kSched) & 1, abort);
         if (!ok) break;
-        const Item* it = &s_items[n & 3];
+        const Item* it = &s_items[n % kSched];
         const int n_ent = it->n_ent;
         if (n_ent <= 0) {
-          mbar_arrive(&sched_empty[n & 3]);
+          mbar_arrive(&sched_empty[n % kSched]);
           if (n_ent < 0) break;
           continue;
         }
@@ -205,7 +212,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tma_load_5d(dq, &mapQ, 0, ih, m0, 0, ib, &qdo_full[st]);
           tma_load_5d(dq + 16384, &mapDO, 0, ih, m0, 0, ib, &qdo_full[st]);
         }
-        mbar_arrive(&sched_empty[n & 3]);              // the item's bucket entries are no longer needed
+        mbar_arrive(&sched_empty[n % kSched]);              // the item's bucket entries are no longer needed
         ++ic;
       }
       if (*abort) {
@@ -223,23 +230,39 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const uint32_t el = elect_one();
       uint32_t ic = 0, sc = 0;
       bool ok = true;
+      // A wait on a barrier whose phase is long complete still costs a round trip of a few hundred
+      // cycles, and this warp has up to four of them per step.  So the barriers of the NEXT step
+      // (and, on an item's last step, of the next item) are tested before this step's products
+      // are issued and the answers read afterwards: a phase seen complete stays complete until
+      // this warp itself has used it.
+      bool have_sched = false, have_kv = false, have_step = false;
       for (uint32_t n = 0; ok; ++n) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort))) break;
-        const int n_ent = s_items[n & 3].n_ent;
+        if (!have_sched && !__all_sync(0xffffffffu, mbar_wait(&sched_full[n % kSched], (n / kSched) & 1, abort))) break;
+        have_sched = false;
+        const int n_ent = s_items[n % kSched].n_ent;
         __syncwarp();
-        if (el) mbar_arrive(&sched_empty[n & 3]);
+        if (el) mbar_arrive(&sched_empty[n % kSched]);
         if (n_ent < 0) break;
         if (n_ent == 0) continue;
-        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[ic & 1], (ic >> 1) & 1, abort))) break;
+        if (!have_kv && !__all_sync(0xffffffffu, mbar_wait(&kv_full[ic & 1], (ic >> 1) & 1, abort))) break;
+        have_kv = false;
         const uint32_t aKV = smem_u32(sKV + (ic & 1) * kKVBytes);
         const uint64_t dK = smem_desc(aKV, 16, 1024), dV = smem_desc(aKV + 16384, 16, 1024);
         for (int t = 0; t < n_ent; ++t, ++sc) {
           const int st = sc % kStages, sb = sc & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort) &&
-                                       mbar_wait(&sdp_free[sb], ((sc >> 1) & 1) ^ 1, abort));
-          if (!ok) break;
+          if (!have_step) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[st], (sc / kStages) & 1, abort) &&
+                                         mbar_wait(&sdp_free[sb], ((sc >> 1) & 1) ^ 1, abort));
+            if (!ok) break;
+          }
           TRACE(0, 16 + sc * 8 + 2);
           tc_fence_after();
+          const uint32_t sn = sc + 1, icn = ic + 1, nn = n + 1;
+          const bool last = t == n_ent - 1;
+          const bool nxt_q = mbar_test(&qdo_full[sn % kStages], (sn / kStages) & 1);
+          const bool nxt_s = mbar_test(&sdp_free[sn & 1], ((sn >> 1) & 1) ^ 1);
+          const bool nxt_kv = last && mbar_test(&kv_full[icn & 1], (icn >> 1) & 1);
+          const bool nxt_it = last && mbar_test(&sched_full[nn % kSched], (nn / kSched) & 1);
           const uint32_t aQ = smem_u32(sQdO + st * kQdOBytes);
           const uint64_t dQ = smem_desc(aQ, 16, 1024), dDO = smem_desc(aQ + 16384, 16, 1024);
           const uint32_t ts = tm + col_s(sb), tdp = tm + col_dp(sb);
@@ -253,9 +276,14 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
               umma_ss(tdp, desc_advance(dDO, (kk >> 2) * 8192 + (kk & 3) * 32),
                       desc_advance(dV, (kk >> 2) * 8192 + (kk & 3) * 32), idesc_first, kk > 0 ? 1u : 0u);
             umma_commit(&sdp_full[sb]);
-            if (t == n_ent - 1) umma_commit(&kv_empty[ic & 1]);
+            if (last) umma_commit(&kv_empty[ic & 1]);
           }
           __syncwarp();
+          have_step = __all_sync(0xffffffffu, nxt_q && nxt_s);
+          if (last) {
+            have_kv = __all_sync(0xffffffffu, nxt_kv);
+            have_sched = __all_sync(0xffffffffu, nxt_it);
+          }
           TRACE(0, 16 + sc * 8 + 3);
         }
         ++ic;
@@ -271,10 +299,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       uint32_t ic = 0, sc = 0;
       bool ok = true;
       for (uint32_t n = 0; ok; ++n) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort))) break;
-        const int n_ent = s_items[n & 3].n_ent;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sched_full[n % kSched], (n / kSched) & 1, abort))) break;
+        const int n_ent = s_items[n % kSched].n_ent;
         __syncwarp();
-        if (el) mbar_arrive(&sched_empty[n & 3]);
+        if (el) mbar_arrive(&sched_empty[n % kSched]);
         if (n_ent < 0) break;
         if (n_ent == 0) continue;
         const int acc = ic & 1;
@@ -313,7 +341,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     // ======================= scheduler (whole warp) =======================
     // Takes tickets from the global counter (buckets differ a lot in length, a static split
     // leaves thread blocks idle), decodes each item (bucket bounds, page) and copies the bucket's
-    // first entries, one per lane; publishes it in the 4-deep ring the other roles follow, so the
+    // first entries, one per lane; publishes it in the ring the other roles follow, so the
     // dependent global loads behind one item are paid here, several items ahead of the copies.
     // The ticket of the next item is taken while the current one is decoded; n_ent = -1 ends it.
     int tk = lane == 0 ? atomicAdd(p.counter, 1) : 0;
@@ -329,15 +357,15 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (lane < it.n_ent && lane < kItemGroups)
           gl = p.groups[(static_cast<int64_t>(it.b) * p.H + it.h) * bucket_row + it.beg + lane];
       }
-      if (!__all_sync(0xffffffffu, mbar_wait(&sched_empty[n & 3], ((n >> 2) & 1) ^ 1, abort))) break;
-      Item* slot = &s_items[n & 3];
+      if (!__all_sync(0xffffffffu, mbar_wait(&sched_empty[n % kSched], ((n / kSched) & 1) ^ 1, abort))) break;
+      Item* slot = &s_items[n % kSched];
       if (lane == 0) {
         slot->b = it.b; slot->h = it.h; slot->blk = it.blk; slot->beg = it.beg;
         slot->n_ent = it.n_ent; slot->row = it.row; slot->active = it.active;
       }
       if (lane < kItemGroups) slot->g[lane] = gl;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sched_full[n & 3]);
+      if (lane == 0) mbar_arrive(&sched_full[n % kSched]);
       if (it.n_ent < 0) break;
       tk = tk_next;
     }
@@ -359,12 +387,12 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint32_t sc = 0;
     bool ok = true;
     for (uint32_t n = 0; ok; ++n) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n % kSched], (n / kSched) & 1, abort));
       if (!ok) break;
-      const Item* it = &s_items[n & 3];
+      const Item* it = &s_items[n % kSched];
       const int n_ent = it->n_ent;
       if (n_ent <= 0) {
-        mbar_arrive(&sched_empty[n & 3]);
+        mbar_arrive(&sched_empty[n % kSched]);
         if (n_ent < 0) break;
         continue;
       }
@@ -459,7 +487,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_arrive(&pds_full[sb]);
         if (tracer) TRACE(1, 16 + sc * 8 + 4);
       }
-      if (ok) mbar_arrive(&sched_empty[n & 3]);        // the item's bucket entries are no longer needed
+      if (ok) mbar_arrive(&sched_empty[n % kSched]);        // the item's bucket entries are no longer needed
     }
   } else if (warp < 8) {
     // ======================= epilogue (warps 4-7): one head-dim lane per thread =======================
@@ -468,10 +496,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint32_t ic = 0, sc = 0;
     bool ok = true;
     for (uint32_t n = 0; ok; ++n) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n & 3], (n >> 2) & 1, abort));
+      ok = __all_sync(0xffffffffu, mbar_wait(&sched_full[n % kSched], (n / kSched) & 1, abort));
       if (!ok) break;
-      const Item it = s_items[n & 3];
-      mbar_arrive(&sched_empty[n & 3]);
+      const Item it = s_items[n % kSched];
+      mbar_arrive(&sched_empty[n % kSched]);
       if (it.n_ent < 0) break;
       const int64_t t0 = static_cast<int64_t>(it.blk) * 64;
       const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
@@ -544,6 +572,9 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+#ifdef NSA_TC_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 256) g_trace_dkv_span[blockIdx.x][1] = global_ns();
+#endif
   if (threadIdx.x == 0 && s_abort) atomicExch(p.status, NSA_ERR_CUDA);
 }
 
@@ -605,6 +636,10 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
 }  // namespace nsa
 
 #ifdef NSA_TC_TRACE
+extern "C" int nsa_debug_trace_dkv_span(unsigned long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_dkv_span, sizeof(unsigned long long) * 512));
+  return NSA_OK;
+}
 extern "C" int nsa_debug_trace_dkv(long long* out) {
   NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_dkv, sizeof(long long) * 4 * 1024));
   return NSA_OK;
