@@ -146,8 +146,8 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     for (int i = 0; i < kStages; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 128);
-      mbar_init(&pds_full[i], 128); mbar_init(&pds_free[i], 1);
+      mbar_init(&sdp_full[i], 1); mbar_init(&sdp_free[i], 256);
+      mbar_init(&pds_full[i], 256); mbar_init(&pds_free[i], 1);
       mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 128);
     }
     fence_barrier_init();
@@ -371,10 +371,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   } else if (warp < 4 || warp >= 12) {
     // ======================= row arithmetic: P and dS on accumulator fragments =======================
-    // Two groups of four warps: warps 0-3 take the even steps, warps 12-15 the odd ones (S/dP and
-    // P/dS are double buffered by step parity, so the groups never share a buffer).
+    // Two groups of four warps share every step: warps 0-3 take keys 0-31, warps 12-15 keys 32-63,
+    // which halves the time from S / dP to P / dS, a link of the chain that bounds a ring stage's life.
     // Warp w (of its group) owns rows 16w .. 16w+15 of the step's query group (TMEM lanes 32w ..
-    // 32w+15 of an M=64 accumulator); thread t holds rows 16w + t/4 and + 8, keys 8i + 2(t%4), +1.
+    // 32w+15 of an M=64 accumulator); thread t holds rows 16w + t/4 and + 8, keys 32 grp + 8i + 2(t%4), +1.
     const int grp = warp >= 12 ? 1 : 0, w4 = warp & 3;
     const bool tracer = threadIdx.x == 0;
     const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
@@ -402,7 +402,6 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const int n_blk = static_cast<int>(p.n_tokens - t0 < 64 ? p.n_tokens - t0 : 64);
       for (int t = 0; t < n_ent; ++t, ++sc) {
         const int sb = sc & 1, ph = (sc >> 1) & 1;
-        if (sb != grp) continue;
         if (tracer) TRACE(1, 16 + sc * 8 + 0);
         // This thread's two rows of the step's query group: LSE * log2(e) (+inf = no such row) and
         // delta, and the step's visible key count; the loads fly while S and dP are computed.
@@ -423,9 +422,9 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!ok) break;
         if (tracer) TRACE(1, 16 + sc * 8 + 1);
         tc_fence_after();
-        uint32_t x[32], y[32];
-        tmem_ld_16x256b_x8_nowait(tm + lane_base + col_s(sb), x);
-        tmem_ld_16x256b_x8_nowait(tm + lane_base + col_dp(sb), y);
+        uint32_t x[16], y[16];
+        tmem_ld_16x256b_x4_nowait(tm + lane_base + col_s(sb) + 32 * grp, x);
+        tmem_ld_16x256b_x4_nowait(tm + lane_base + col_dp(sb) + 32 * grp, y);
         // the buffer's previous P / dS (two steps ago) must have been consumed: normally long true,
         // so poll once here, where the round trip hides behind the TMEM load
         const bool pds_ok = mbar_try(&pds_free[sb], ph ^ 1);
@@ -434,11 +433,11 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         mbar_arrive(&sdp_free[sb]);
         const float sl = p.scale_log2, sc_ = p.scale;
         const float nl0 = -m0.x, nl1 = -m1.x, nd0 = -m0.y * sc_, nd1 = -m1.y * sc_;
-        // x[4i], x[4i+1]: row r0, keys 8i+cq, +1;  x[4i+2], x[4i+3]: row r1, same keys.  Afterwards
-        // x[2i], x[2i+1] hold the packed P of (r0, r1) for key block i, y[2i], y[2i+1] the packed dS.
+        // x[4i], x[4i+1]: row r0, keys 32 grp + 8i + cq, +1;  x[4i+2], x[4i+3]: row r1, same keys.
+        // Afterwards x[2i], x[2i+1] hold the packed P of (r0, r1) for key block i, y[2i], y[2i+1] the packed dS.
         if (nkv == 64) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const float p00 = fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0));
             const float p01 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0));
             const float p10 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, nl1));
@@ -454,8 +453,8 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = 8 * i + cq;
+          for (int i = 0; i < 4; ++i) {
+            const int c = 32 * grp + 8 * i + cq;
             const float p00 = (c < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0)) : 0.f;
             const float p01 = (c + 1 < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0)) : 0.f;
             const float p10 = (c < nkv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, nl1)) : 0.f;
@@ -478,8 +477,8 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (tracer) TRACE(1, 16 + sc * 8 + 3);
         const uint32_t aP = smem_u32(sPdS + sb * kPdSBytes) + st_row * 128;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4);
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t off = static_cast<uint32_t>(((4 * grp + 2 * q + st_chunk) ^ (st_row & 7)) << 4);
           stmatrix_x4(aP + off, x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
           stmatrix_x4(aP + 8192 + off, y[4 * q], y[4 * q + 1], y[4 * q + 2], y[4 * q + 3]);
         }
