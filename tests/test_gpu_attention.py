@@ -89,7 +89,8 @@ def test_tensor_core_kernel_agrees_with_general_kernel(dev, monkeypatch):
     ops = _ops()
     for seed, M, N, T, chunk, causal in ((41, 256, 4096, 16, 256, False), (42, 200, 1000, 5, 100, True),
                                           (43, 150, 3000, 1, 150, False), (44, 4680, 6000, 7, 1560, True),
-                                          (45, 128, 64 * 1500, 8, 128, False)):   # long runs of unselected blocks
+                                          (45, 128, 64 * 1500, 8, 128, False),    # long runs of unselected blocks
+                                          (46, 3072, 384, 4, 3072, False)):       # 32 query groups per block bucket
         q, k, v, do, ids = _rand_case(seed, 1, M, N, 3, 128, T, 64, 64, chunk, causal)
         ids[0, 0, 0, T // 2:] = -1
         args = (q.to(dev), ops.DenseKV(k.to(dev), v.to(dev)), ids.to(dev), 64, chunk, 128 ** -0.5, causal, 64)
