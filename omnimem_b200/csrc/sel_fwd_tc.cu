@@ -2,16 +2,18 @@
 // the page geometry: bf16, D = 128, 64-token blocks, query groups of up to 64 rows, K/V read
 // from a dense [B,N,H,D] tensor or straight from the fixed-page pool through the block table.
 //
-// One thread block per (batch, query group, head), TWO thread blocks resident per SM (about 97 KiB
+// One thread block per (batch, query group, head), TWO thread blocks resident per SM (96 KiB
 // of tiles and 256 TMEM columns each), so that the list-building prologue and the store epilogue
 // of one block run beside the main loop of the other.  A step is ONE selected block (64 keys):
-//   warp 4  producer: block list (ballot compaction), Q once, K and V tiles through two-stage rings (TMA);
+//   warp 4  producer: block list (ballot compaction), Q once, K tiles through a three-stage and V tiles
+//           through a two-stage ring (TMA), K one step ahead of V;
 //   warp 5  issues S = Q K^T (M=64, N=64, K=128) into a double-buffered TMEM tile, so the scores of
 //           step t+1 are computed while the softmax of step t runs;
 //   warps 0-3  online softmax on the accumulator fragments (16 rows x 64 keys per warp, the four
-//           threads of a quad share a row); P goes as bf16 through stmatrix into a swizzled,
-//           double-buffered shared tile;
-//   warp 6  issues O += P V (M=64, N=128, K=64; the V tile is read MN-major in place).
+//           threads of a quad share a row); P never leaves TMEM: the packed bf16 pairs of the
+//           fragment are stored (tcgen05.st.16x128b) over the first 32 of S(t)'s 64 columns;
+//   warp 6  issues O += P V (M=64, N=128, K=64) with P as the A operand read from TMEM and the V
+//           tile read MN-major in place; S(t+2) is issued once P V of step t has run.
 // O stays in TMEM across steps; it is rescaled only when a row's running maximum grows by more than
 // 2^8 (the reference maximum is otherwise kept, which is exact because P and the row sum use the
 // same reference).  The epilogue normalises the O fragments, stages them with stmatrix in the dead
@@ -76,12 +78,13 @@ using namespace tc;
 constexpr int kTcThreads = 224;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTile = 16384;              // 64 rows x 256 bytes, as two 64-column halves of 8 KiB
-constexpr uint32_t kSmemTiles = kTile + 2 * kTile + 2 * kTile + 2 * 8192;   // Q, K x2, V x2, P x2
+constexpr int kKStages = 3;
+constexpr uint32_t kSmemTiles = kTile + kKStages * kTile + 2 * kTile;   // Q, K x3, V x2
 constexpr float kRescaleGap = 8.f;             // log2 units
 constexpr uint32_t kTmemCols = 256;            // per thread block; two blocks share an SM's 512
 
 // TMEM columns
-constexpr uint32_t kColS = 0;      // 2 x 64 fp32 score columns (double buffered)
+constexpr uint32_t kColS = 0;      // 2 x 64 fp32 score columns (double buffered); P(t) is packed over the first 32 of S(t)'s
 constexpr uint32_t kColO = 128;    // 128
 
 struct TcFwdParams {
@@ -116,11 +119,10 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = tiles;                   // [2][64][128 B]; reused as the output staging tile by the epilogue
-  uint8_t* sK = tiles + kTile;           // 2 stages
-  uint8_t* sV = tiles + 3 * kTile;       // 2 stages
-  uint8_t* sP = tiles + 5 * kTile;       // 2 x [64 q][128 B] swizzled
+  uint8_t* sK = tiles + kTile;                     // kKStages stages
+  uint8_t* sV = tiles + (1 + kKStages) * kTile;    // 2 stages
 
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_free[2], p_full[2], p_free[2],
+  __shared__ uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2], s_full[2], p_full[2], p_free[2],
       pv_done, o_final;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
@@ -137,11 +139,11 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     s_abort = 0;
     mbar_init(&q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+      mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128); mbar_init(&p_free[i], 1);
     }
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     mbar_init(&pv_done, 1);
     mbar_init(&o_final, 1);
     fence_barrier_init();
@@ -211,25 +213,32 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (lane == 0) {
       mbar_expect_tx(&q_full, kTile);
       tma_load_5d(sQ, &mapQ, 0, h, static_cast<int>(m0), 0, b, &q_full);
-      int t = 0;
-      for (; t < nb; ++t) {
+      // K runs one step ahead of V: K(t+1) is asked for before V(t), so that a K tile is in flight
+      // while the step before it still holds both V stages
+      int kt = 0, vt = 0;                             // copies issued so far
+      auto load_k = [&](int t) {
+        const int ks = t % kKStages;
+        if (!mbar_wait(&k_empty[ks], ((t / kKStages) & 1) ^ 1, abort)) return false;
+        mbar_expect_tx(&k_full[ks], kTile);
+        if (p.paged) tma_load_3d(sK + ks * kTile, &mapK, 0, s_row[t], 0, &k_full[ks]);
+        else tma_load_5d(sK + ks * kTile, &mapK, 0, h, s_row[t], 0, b, &k_full[ks]);
+        ++kt;
+        return true;
+      };
+      bool okp = load_k(0);
+      for (int t = 0; okp && t < nb; ++t) {
+        if (t + 1 < nb && !(okp = load_k(t + 1))) break;
         const int st = t & 1, ph = (t >> 1) & 1;
-        const int row = s_row[t];
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort)) break;
-        mbar_expect_tx(&k_full[st], kTile);
-        if (p.paged) tma_load_3d(sK + st * kTile, &mapK, 0, row, 0, &k_full[st]);
-        else tma_load_5d(sK + st * kTile, &mapK, 0, h, row, 0, b, &k_full[st]);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) { ++t; break; }
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) break;
         mbar_expect_tx(&v_full[st], kTile);
-        if (p.paged) tma_load_3d(sV + st * kTile, &mapV, 0, row, 0, &v_full[st]);
-        else tma_load_5d(sV + st * kTile, &mapV, 0, h, row, 0, b, &v_full[st]);
+        if (p.paged) tma_load_3d(sV + st * kTile, &mapV, 0, s_row[t], 0, &v_full[st]);
+        else tma_load_5d(sV + st * kTile, &mapV, 0, h, s_row[t], 0, b, &v_full[st]);
+        ++vt;
       }
       if (*abort) {
         // the other roles have stopped consuming: wait (bounded) for the copies still in flight
-        for (int u = (t > 2 ? t - 2 : 0); u < t; ++u) {
-          mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort);
-          mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
-        }
+        for (int u = (kt > kKStages ? kt - kKStages : 0); u < kt; ++u) mbar_wait(&k_full[u % kKStages], (u / kKStages) & 1, abort);
+        for (int u = (vt > 2 ? vt - 2 : 0); u < vt; ++u) mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
         mbar_wait(&q_full, 0, abort);
       }
     }
@@ -242,12 +251,14 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     TRACE(0, 0);
     for (int t = 0; ok && t < nb; ++t) {
       const int st = t & 1, ph = (t >> 1) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&k_full[st], ph, abort) &&
-                                   (t < 2 || mbar_wait(&s_free[st], ((t - 2) >> 1) & 1, abort)));   // S(t-2) was read
+      // P(t-2) lives in the columns of S(t-2): they are free once P V of step t-2 has run
+      const int ks = t % kKStages;
+      ok = __all_sync(0xffffffffu, mbar_wait(&k_full[ks], (t / kKStages) & 1, abort) &&
+                                   (t < 2 || mbar_wait(&p_free[st], ((t - 2) >> 1) & 1, abort)));
       if (!ok) break;
       tc_fence_after();
       TRACE(0, 8 + t * 8 + 0);
-      const uint64_t dK = smem_desc(smem_u32(sK + st * kTile), 16, 1024);
+      const uint64_t dK = smem_desc(smem_u32(sK + ks * kTile), 16, 1024);
       if (el) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -255,7 +266,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           umma_ss(tm + kColS + st * 64, desc_advance(dQ, off), desc_advance(dK, off), idesc, kk > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
+        umma_commit(&k_empty[ks]);
       }
       __syncwarp();
       TRACE(0, 8 + t * 8 + 1);
@@ -269,13 +280,12 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       if (!__all_sync(0xffffffffu, mbar_wait(&v_full[st], ph, abort) && mbar_wait(&p_full[st], ph, abort))) break;
       tc_fence_after();
       TRACE(0, 8 + t * 8 + 2);
-      const uint64_t dP = smem_desc(smem_u32(sP + st * 8192), 16, 1024);
       // V tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as N
       const uint64_t dVmn = smem_desc(smem_u32(sV + st * kTile), 8192, 1024);
       if (el) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tm + kColO, desc_advance(dP, kk * 32), desc_advance(dVmn, kk * 2048), idesc, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tm + kColO, tm + kColS + st * 64 + kk * 8, desc_advance(dVmn, kk * 2048), idesc, (t > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(&p_free[st]);
         umma_commit(&pv_done);
@@ -307,12 +317,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       uint32_t x[32];
       tmem_ld_16x256b_x8_nowait(tm + lane_base + kColS + sb * 64, x);
       const int nv = s_nvis[t];
-      // the P tile of step t-2 must have been consumed before it is overwritten: normally long true,
-      // so poll once here, where the round trip hides behind the TMEM load
-      const bool p_ok = t < 2 || mbar_try(&p_free[sb], ((t - 2) >> 1) & 1);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&s_free[sb]);
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
       // running maxima on the unscaled scores (the scale is positive)
       float t0 = -INFINITY, t1 = -INFINITY;
@@ -334,10 +339,6 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       t1 = quad_max(t1) * sl;
       const bool need0 = t0 > m_0 + kRescaleGap, need1 = t1 > m_1 + kRescaleGap;   // true at the first step (m = -inf)
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 3);
-      if (!__all_sync(0xffffffffu, p_ok)) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&p_free[sb], ((t - 2) >> 1) & 1, abort));
-        if (!ok) break;
-      }
       if (__any_sync(0xffffffffu, need0 || need1)) {
         const float n0 = need0 ? t0 : m_0, n1 = need1 ? t1 : m_1;
         if (t > 0) {
@@ -404,11 +405,10 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         l_1 += a1;
       }
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 5);
-      const uint32_t aP = smem_u32(sP + sb * 8192) + st_row * 128;
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        stmatrix_x4(aP + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
-      fence_async_smem();                           // make the rows visible to the tensor core's reads
+      // P stays in TMEM, packed over the first 32 of S(t)'s 64 columns, as the A operand of P V
+      tmem_st_16x128b_x8_nowait(tm + lane_base + kColS + sb * 64, x);
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(&p_full[sb]);
       if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 6);
     }

@@ -220,6 +220,16 @@ __device__ __forceinline__ void tmem_st_16x256b_x8_nowait(uint32_t taddr, const 
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
+// 16 lanes x 32 columns; thread t writes r[2j] to (lane base + t/4, column 4j + t%4) and r[2j+1] to the
+// same column of lane base + t/4 + 8: with bf16 pairs in the registers this is exactly the packed form of an
+// accumulator fragment (tmem_ld_16x256b), i.e. the A operand of a following MMA that reads A from TMEM
+// (for M = 64 the A rows sit in the same lanes as the accumulator rows: 0-15, 32-47, 64-79, 96-111).
+__device__ __forceinline__ void tmem_st_16x128b_x8_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 // Four 8x8 b16 matrices from accumulator-layout registers (thread t: row t/4, columns 2(t%4), +1 of
 // each matrix); thread l supplies the address of row l%8 of matrix l/8.
 __device__ __forceinline__ void stmatrix_x4(uint32_t smem_addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
