@@ -36,8 +36,8 @@ METRIC = "nsa_selection_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = ("config2: bf16 NSA selection fwd+bwd, B=1 H=12 D=128, Q=4680 (3 latent frames), "
             "KV=32760 (21 frames) in 64-token blocks, top-16 per 64-query group")
-# kernels launched by one step: pool(q), pool(k), score, select, fwd, inverted index, dq, dkv
-LAUNCHES_PER_STEP = 8
+# kernels launched by one step: pool(q), pool(k), score, select, fwd, inverted index, dq, counter reset, dkv
+LAUNCHES_PER_STEP = 9
 
 
 def peaks():
@@ -355,7 +355,7 @@ def run_gpu(args):
                     "overlap": "upload of step s+1 and download of step s-1 run beside the kernels of step s"},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps,
             "launch": "eager (one Python call per kernel)" if args.no_graph else
-                      "the step's kernels captured once and replayed as one CUDA graph; `kernels` times are from an eager pass",
+                      "the step's kernels captured once and replayed as one CUDA graph, kernel-to-kernel edges as programmatic dependent launches; `kernels` times are from an eager pass",
             "clocks": clocks, "roofline": roof, "kernels": kernels,
         }
         if sharded is not None:

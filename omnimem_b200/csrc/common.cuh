@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 
 #include <cstdarg>
 #include <cstdint>
@@ -88,6 +89,40 @@ template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u)
 }
 template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+
+// ---- programmatic dependent launch --------------------------------------------------
+// A kernel launched with launch_chained() may become resident while the kernel before it in the
+// stream is still running: its thread blocks start as soon as every block of the predecessor has
+// called chain_release() (or exited) and room is free, run whatever needs no result of the
+// predecessor (barrier set-up, TMEM allocation, descriptor prefetch) and stop at chain_wait(),
+// which returns when the predecessor has completed and its writes are visible.  Both
+// instructions do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// OMNIMEM_B200_CHAINED_LAUNCH=0 launches the ordinary way.
+inline bool chained_launch_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("OMNIMEM_B200_CHAINED_LAUNCH");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // ---- async copies, ldmatrix, mma.sync -----------------------------------------------

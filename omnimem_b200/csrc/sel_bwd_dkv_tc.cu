@@ -108,6 +108,14 @@ __device__ __forceinline__ Item get_item(const TcDkvParams& p, int64_t i) {
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Zeroes the scheduling counter as a kernel, so that the launch chain dQ kernel -> this -> dK/dV
+// kernel stays a chain of kernels (a memset between two kernels would end the early start).
+__global__ void zero_counter_kernel(int32_t* counter) {
+  chain_release();
+  chain_wait();                                // completes only after the kernel before it: the next kernel's wait relies on that
+  *counter = 0;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapDO,
                       const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
@@ -159,6 +167,7 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  chain_wait();                                // everything above needs no result of the kernels before this one
   const uint32_t tm = tmem_base_s;
   volatile int* abort = &s_abort;
   const int64_t n_items = static_cast<int64_t>(p.B) * p.H * p.NS;
@@ -614,7 +623,6 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   p.scale = scale; p.scale_log2 = scale * kLog2e;
   if ((rc = device_status_address(&p.status))) return rc;
   p.counter = counter;
-  NSA_CUDA_OK(cudaMemsetAsync(counter, 0, sizeof(int32_t), stream));
   int dev = 0, sms = 0;
   NSA_CUDA_OK(cudaGetDevice(&dev));
   NSA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -626,7 +634,8 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   NSA_CUDA_OK(cudaFuncGetAttributes(&fa, sel_bwd_dkv_tc_kernel));
   const size_t smem = kSmemTiles + (1024 - fa.sharedSizeBytes % 1024) % 1024;
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  sel_bwd_dkv_tc_kernel<<<grid, kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, mapDK, mapDV, p);
+  NSA_CUDA_OK(launch_chained(zero_counter_kernel, dim3(1), dim3(1), 0, stream, counter));
+  NSA_CUDA_OK(launch_chained(sel_bwd_dkv_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, mapQ, mapDO, mapK, mapV, mapDK, mapDV, p));
   NSA_LAUNCH_OK("sel_bwd_dkv_tc_kernel");
   *launched = true;
   return NSA_OK;

@@ -89,6 +89,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
   const int64_t bhm = (static_cast<int64_t>(b) * p.H + h) * p.M + m0;
 
+  chain_release();
   if (threadIdx.x == 0) TRACE(1, 0);
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -106,6 +107,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapDO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
+  chain_wait();                                // everything above needs no result of the kernel before this one
   // ---- row warps start the loads for delta = sum_d O dO right away: thread j takes query row j / 2,
   // head dims [64 (j & 1), +64)
   const int drow_q = threadIdx.x >> 1, dhalf = threadIdx.x & 1;
@@ -436,7 +438,8 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  sel_bwd_dq_tc_kernel<<<dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), kThreads, smem, stream>>>(mapQ, mapDO, mapK, mapV, mapDQ, p);
+  NSA_CUDA_OK(launch_chained(sel_bwd_dq_tc_kernel, dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), dim3(kThreads), smem, stream,
+                             mapQ, mapDO, mapK, mapV, mapDQ, p));
   NSA_LAUNCH_OK("sel_bwd_dq_tc_kernel");
   *launched = true;
   return NSA_OK;

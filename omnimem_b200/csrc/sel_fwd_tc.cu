@@ -134,6 +134,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
   const int q_chunk = static_cast<int>(m0 / p.chunk_size);
 
+  chain_release();
   if (threadIdx.x == 0) TRACE(1, 0);
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -152,6 +153,7 @@ sel_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
+  chain_wait();                                // everything above needs no result of the kernel before this one
   // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by warp 4
   if (warp == 4) {
     int base = 0;
@@ -562,7 +564,8 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  sel_fwd_tc_kernel<<<dim3(static_cast<unsigned>(MG), H, B), kTcThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p);
+  NSA_CUDA_OK(launch_chained(sel_fwd_tc_kernel, dim3(static_cast<unsigned>(MG), H, B), dim3(kTcThreads), smem, stream, mapQ, mapK, mapV,
+                             mapO, p));
   NSA_LAUNCH_OK("sel_fwd_tc_kernel");
   *launched = true;
   return NSA_OK;

@@ -20,6 +20,8 @@ struct PoolParams {
 
 template <typename T>
 __global__ void __launch_bounds__(128) pool_rows_kernel(const PoolParams p) {
+  chain_release();
+  chain_wait();
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float s_part[];                  // [rp][D]
   const int64_t c = blockIdx.x;
@@ -134,6 +136,8 @@ constexpr int kScoreMmaRows = 64;
 
 template <typename T>
 __global__ void __launch_bounds__(128) score_mma_kernel(const ScoreParams p) {
+  chain_release();
+  chain_wait();
   extern __shared__ __align__(16) char s_raw[];
   const int PITCH = p.D + 8;
   T* sK = reinterpret_cast<T*>(s_raw);                  // [64][PITCH]
@@ -191,7 +195,7 @@ int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(2 * kScoreCols) * (sp.D + 8) * sizeof(T);
   NSA_CUDA_OK(cudaFuncSetAttribute(score_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const dim3 grid(static_cast<unsigned>(cdiv64(sp.NC, kScoreCols)), cdiv(sp.MG, kScoreMmaRows), sp.H * B);
-  score_mma_kernel<T><<<grid, 128, smem, s>>>(sp);
+  NSA_CUDA_OK(launch_chained(score_mma_kernel<T>, grid, dim3(128), smem, s, sp));
   NSA_LAUNCH_OK("score_mma_kernel");
   return NSA_OK;
 }
@@ -360,6 +364,8 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
 // the lane that owned it clears the key and rebuilds its own maximum with a reduction tree.
 template <int ITEMS, bool MERGE>
 __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (row >= rows) return;
@@ -448,9 +454,9 @@ template <bool MERGE>
 int launch_select(const SelectParams& sel, int64_t rows, cudaStream_t s) {
   const unsigned blocks4 = static_cast<unsigned>(cdiv64(rows, 4));
   if (sel.NC <= 512) {
-    select_warp_kernel<16, MERGE><<<blocks4, 128, 0, s>>>(sel, rows);
+    NSA_CUDA_OK(launch_chained(select_warp_kernel<16, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
   } else if (sel.NC <= 1024) {
-    select_warp_kernel<32, MERGE><<<blocks4, 128, 0, s>>>(sel, rows);
+    NSA_CUDA_OK(launch_chained(select_warp_kernel<32, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
   } else {
     const size_t ksmem = sel.NC * 8 <= 64 * 1024 ? static_cast<size_t>(sel.NC) * 8 : 0;
     NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<MERGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
@@ -485,7 +491,7 @@ int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
   const int lpr = p.D / vec;
   const int rp = 128 / lpr;
   const size_t smem = static_cast<size_t>(rp) * p.D * sizeof(float);
-  pool_rows_kernel<T><<<dim3(static_cast<unsigned>(NB), H, B), 128, smem, s>>>(p);
+  NSA_CUDA_OK(launch_chained(pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB), H, B), dim3(128), smem, s, p));
   NSA_LAUNCH_OK("pool_rows_kernel");
   return NSA_OK;
 }
