@@ -101,17 +101,19 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// OMNIMEM_B200_CHAINED_LAUNCH=0 launches the ordinary way.
-inline bool chained_launch_enabled() {
-  static const bool on = [] {
+// OMNIMEM_B200_CHAINED_LAUNCH is a bit mask of the launch sites that use it (1: pooling, scoring and
+// selection, 2: forward, 4: dQ, 8: dK/dV with its counter reset); 0 launches everything the ordinary way.
+constexpr int kChainSmall = 1, kChainFwd = 2, kChainDq = 4, kChainDkv = 8;
+inline int chained_launch_mask() {
+  static const int mask = [] {
     const char* e = getenv("OMNIMEM_B200_CHAINED_LAUNCH");
-    return !(e != nullptr && e[0] == '0');
+    return e != nullptr ? atoi(e) : 15;
   }();
-  return on;
+  return mask;
 }
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                  Args&&... args) {
+inline cudaError_t launch_chained(int site, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -121,7 +123,7 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  cfg.numAttrs = (chained_launch_mask() & site) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -634,8 +634,8 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   NSA_CUDA_OK(cudaFuncGetAttributes(&fa, sel_bwd_dkv_tc_kernel));
   const size_t smem = kSmemTiles + (1024 - fa.sharedSizeBytes % 1024) % 1024;
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  NSA_CUDA_OK(launch_chained(zero_counter_kernel, dim3(1), dim3(1), 0, stream, counter));
-  NSA_CUDA_OK(launch_chained(sel_bwd_dkv_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, mapQ, mapDO, mapK, mapV, mapDK, mapDV, p));
+  NSA_CUDA_OK(launch_chained(kChainDkv, zero_counter_kernel, dim3(1), dim3(1), 0, stream, counter));
+  NSA_CUDA_OK(launch_chained(kChainDkv, sel_bwd_dkv_tc_kernel, dim3(grid), dim3(kThreads), smem, stream, mapQ, mapDO, mapK, mapV, mapDK, mapDV, p));
   NSA_LAUNCH_OK("sel_bwd_dkv_tc_kernel");
   *launched = true;
   return NSA_OK;

@@ -438,7 +438,7 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  NSA_CUDA_OK(launch_chained(sel_bwd_dq_tc_kernel, dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), dim3(kThreads), smem, stream,
+  NSA_CUDA_OK(launch_chained(kChainDq, sel_bwd_dq_tc_kernel, dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), dim3(kThreads), smem, stream,
                              mapQ, mapDO, mapK, mapV, mapDQ, p));
   NSA_LAUNCH_OK("sel_bwd_dq_tc_kernel");
   *launched = true;

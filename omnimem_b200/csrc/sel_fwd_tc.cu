@@ -564,7 +564,7 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   NSA_CUDA_OK(cudaFuncSetAttribute(sel_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  NSA_CUDA_OK(launch_chained(sel_fwd_tc_kernel, dim3(static_cast<unsigned>(MG), H, B), dim3(kTcThreads), smem, stream, mapQ, mapK, mapV,
+  NSA_CUDA_OK(launch_chained(kChainFwd, sel_fwd_tc_kernel, dim3(static_cast<unsigned>(MG), H, B), dim3(kTcThreads), smem, stream, mapQ, mapK, mapV,
                              mapO, p));
   NSA_LAUNCH_OK("sel_fwd_tc_kernel");
   *launched = true;

@@ -195,7 +195,7 @@ int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(2 * kScoreCols) * (sp.D + 8) * sizeof(T);
   NSA_CUDA_OK(cudaFuncSetAttribute(score_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const dim3 grid(static_cast<unsigned>(cdiv64(sp.NC, kScoreCols)), cdiv(sp.MG, kScoreMmaRows), sp.H * B);
-  NSA_CUDA_OK(launch_chained(score_mma_kernel<T>, grid, dim3(128), smem, s, sp));
+  NSA_CUDA_OK(launch_chained(kChainSmall, score_mma_kernel<T>, grid, dim3(128), smem, s, sp));
   NSA_LAUNCH_OK("score_mma_kernel");
   return NSA_OK;
 }
@@ -454,9 +454,9 @@ template <bool MERGE>
 int launch_select(const SelectParams& sel, int64_t rows, cudaStream_t s) {
   const unsigned blocks4 = static_cast<unsigned>(cdiv64(rows, 4));
   if (sel.NC <= 512) {
-    NSA_CUDA_OK(launch_chained(select_warp_kernel<16, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
+    NSA_CUDA_OK(launch_chained(kChainSmall, select_warp_kernel<16, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
   } else if (sel.NC <= 1024) {
-    NSA_CUDA_OK(launch_chained(select_warp_kernel<32, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
+    NSA_CUDA_OK(launch_chained(kChainSmall, select_warp_kernel<32, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
   } else {
     const size_t ksmem = sel.NC * 8 <= 64 * 1024 ? static_cast<size_t>(sel.NC) * 8 : 0;
     NSA_CUDA_OK(cudaFuncSetAttribute(select_kernel<MERGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
@@ -491,7 +491,7 @@ int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
   const int lpr = p.D / vec;
   const int rp = 128 / lpr;
   const size_t smem = static_cast<size_t>(rp) * p.D * sizeof(float);
-  NSA_CUDA_OK(launch_chained(pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB), H, B), dim3(128), smem, s, p));
+  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB), H, B), dim3(128), smem, s, p));
   NSA_LAUNCH_OK("pool_rows_kernel");
   return NSA_OK;
 }
