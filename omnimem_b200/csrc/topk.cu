@@ -358,10 +358,10 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
   }
 }
 
-// Rows with at most 32*ITEMS candidates: one warp per row, candidates in registers, no block-wide
-// barrier.  Same keys and order as select_kernel.  Per round the warp's best key is found with two
-// warp reductions (max of the score half, then max of the id half among the lanes that hold it);
-// the lane that owned it clears the key and rebuilds its own maximum with a reduction tree.
+// Rows with at most 32*ITEMS candidates: one warp per row, no block-wide barrier.  Same keys and
+// order as select_kernel.  Every lane sorts its ITEMS keys once; per round the warp's best key is
+// found with two warp reductions (max of the score half, then max of the id half among the lanes
+// that hold it) and the lane that owned it steps to its next key.
 template <int ITEMS, bool MERGE>
 __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
   chain_release();
@@ -414,19 +414,38 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     }
     keys[i] = k;
   }
-  auto lane_max = [&]() -> unsigned long long {
-    unsigned long long t[ITEMS];
+  // Each lane sorts its own keys once, largest first (bitonic network, all indices compile-time
+  // constants, so the keys stay in registers), and parks the list in shared memory; a lane that
+  // owns a round's winner then only steps to its next key.
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) t[i] = keys[i];
+  for (int k = 2; k <= ITEMS; k <<= 1)
 #pragma unroll
-    for (int w = ITEMS / 2; w >= 1; w >>= 1)
+    for (int j = k >> 1; j > 0; j >>= 1)
 #pragma unroll
-      for (int i = 0; i < w; ++i) t[i] = t[i] > t[i + w] ? t[i] : t[i + w];
-    return t[0];
-  };
-  unsigned long long local = lane_max();
+      for (int i = 0; i < ITEMS; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long x = keys[i], y = keys[l];
+          const bool sw = ((i & k) == 0) ? (x < y) : (x > y);
+          keys[i] = sw ? y : x;
+          keys[l] = sw ? x : y;
+        }
+      }
+  __shared__ unsigned long long s_sorted[4][ITEMS][32];   // [warp][rank][lane]: conflict-free for a warp
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) s_sorted[warp][i][lane] = keys[i];
+  unsigned long long local = keys[0];
+  int next = 1;
   int32_t* oi = p.out_idx + row * p.topk;
   float* os = p.out_scores ? p.out_scores + row * p.topk : nullptr;
+  // winners are kept one per lane (round r in lane r % 32) and written 32 at a time
+  unsigned long long mine = 0ull;
+  auto flush = [&](int first, int n) {
+    if (lane < n) {
+      oi[first + lane] = key_id(mine);
+      if (os) os[first + lane] = key_score(mine);
+    }
+  };
   int r = 0;
   for (; r < p.topk; ++r) {
     const uint32_t lhi = static_cast<uint32_t>(local >> 32), llo = static_cast<uint32_t>(local);
@@ -434,16 +453,14 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     if (bhi == 0u) break;                                  // the score half of a real key is never 0
     const uint32_t blo = __reduce_max_sync(0xffffffffu, lhi == bhi ? llo : 0u);
     const unsigned long long best = (static_cast<unsigned long long>(bhi) << 32) | blo;
-    if (lane == 0) {
-      oi[r] = key_id(best);
-      if (os) os[r] = key_score(best);
-    }
+    if (lane == (r & 31)) mine = best;
+    if ((r & 31) == 31) flush(r - 31, 32);
     if (local == best) {            // keys are unique: exactly one lane owns the winner
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) keys[i] = keys[i] == best ? 0ull : keys[i];
-      local = lane_max();
+      local = next < ITEMS ? s_sorted[warp][next][lane] : 0ull;
+      ++next;
     }
   }
+  flush(r & ~31, r & 31);
   for (int i = r + lane; i < p.topk; i += 32) {
     oi[i] = -1;
     if (os) os[i] = -INFINITY;
