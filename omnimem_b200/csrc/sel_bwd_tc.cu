@@ -1,19 +1,25 @@
 // Selection attention backward, dQ half, on tcgen05 / TMEM / TMA for the page geometry
 // (bf16, D = 128, 64-token blocks, query groups of up to 64 rows, dense or paged K/V).
 //
-// One thread block per (batch, query group, head), TWO thread blocks resident per SM (about
-// 105 KiB of tiles and 256 TMEM columns each): the block-list / delta prologue and the store
-// epilogue of one block run beside the main loop of the other, and the tensor pipe always has a
-// second queue to draw from.  A step is ONE selected block (64 keys):
-//     S  = Q  K^T           (M=64, N=64, K=128)    recomputed scores           warp 5 issues
-//     dP = dO V^T           (M=64, N=64, K=128)                                warp 5 issues
-//     dS = exp2(S c - LSE + log2 scale) (dP - delta)   on accumulator fragments, stored as bf16
-//          with stmatrix into a swizzled shared tile                           warps 0-3
-//     dQ += dS K            (M=64, N=128, K=64; K tile read MN-major in place) warp 6 issues
+// One thread block per (batch, query group, head), TWO thread blocks resident per SM (104 KiB of
+// tiles and 256 TMEM columns each): the block-list / delta prologue and the store epilogue of one
+// block run beside the main loop of the other, and the tensor pipe always has a second queue to
+// draw from.  A step is ONE selected block (64 keys):
+//     S    = Q  K^T         (M=64, N=64, K=128)    Q is the A operand read from TMEM  warp 5 issues
+//     dP   = dO V^T         (M=64, N=64, K=128)                                       warp 5 issues
+//     dS   = exp2(S c - LSE + log2 scale) (dP - delta)   on accumulator fragments, stored as bf16
+//            with stmatrix into a swizzled shared tile                                warps 0-3
+//     dQ^T += K^T dS^T      (M=128 head dims, N=64 rows, K=64 keys; the K tile is read MN-major
+//            in place as A, dS K-major as B)                                          warp 6 issues
+// Accumulating dQ transposed takes 64 TMEM columns instead of 128; the 64 columns saved hold Q,
+// which the row warps move from its landing tile into TMEM in the prologue (tcgen05.st.16x128b),
+// so S reads only K from shared memory and the landing tile becomes a third K stage - a K tile
+// is held from S(t) to dQ(t), two stages left the copy of K(t+2) on the path every other step.
 // Warp 4 builds the list of visible selected blocks and issues every TMA copy (Q and dO once,
-// K and V per step through two-stage rings).  delta = sum_d(O dO) is reduced in the prologue and
-// stored for the dK/dV kernel.  The epilogue packs the dQ fragments to bf16, stages them with
-// stmatrix in the (dead) Q tile and writes them with TMA tile stores.
+// K through a three-stage, V through a two-stage ring).  delta = sum_d(O dO) is reduced in the
+// prologue and stored for the dK/dV kernel.  The epilogue packs the dQ^T fragments to bf16 and
+// stores them transposed (stmatrix.trans) into the first K stage, dead by then, from where TMA
+// tile stores write them.
 #include "sel_common.cuh"
 #include "tc_common.cuh"
 
@@ -39,11 +45,13 @@ using namespace tc;
 constexpr int kThreads = 224;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTile = 16384;                 // 64 rows x 256 bytes, as two 64-column halves of 8 KiB
-constexpr uint32_t kSmemTiles = 2 * kTile + 2 * kTile + 2 * kTile + 8192;   // Q, dO, K x2, V x2, dS
+constexpr int kKStages = 3;
+constexpr uint32_t kSmemTiles = kTile + kKStages * kTile + 2 * kTile + 8192;   // dO, K x3, V x2, dS
 
-constexpr uint32_t kColS = 0;      // 64
-constexpr uint32_t kColDP = 64;    // 64
-constexpr uint32_t kColDQ = 128;   // 128
+constexpr uint32_t kColS = 0;      // 64: S (M=64 rows x 64 keys, fp32)
+constexpr uint32_t kColDP = 64;    // 64: dP
+constexpr uint32_t kColDQ = 128;   // 64: dQ^T (M=128 head dims x 64 rows, fp32)
+constexpr uint32_t kColQ = 192;    // 64: Q as the A operand of S (64 rows x 128 bf16, two per column)
 constexpr uint32_t kTmemCols = 256;
 
 struct TcDqParams {
@@ -70,13 +78,16 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                      const __grid_constant__ CUtensorMap mapDQ, const TcDqParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = tiles;                   // [2][64][128 B]; reused as the dQ staging tile by the epilogue
-  uint8_t* sDO = tiles + kTile;
-  uint8_t* sK = tiles + 2 * kTile;       // 2 stages
-  uint8_t* sV = tiles + 4 * kTile;       // 2 stages
-  uint8_t* sDS = tiles + 6 * kTile;      // [64 q][128 B] swizzled
+  uint8_t* sDO = tiles;                                 // [2][64][128 B]
+  uint8_t* sK = tiles + kTile;                          // kKStages stages; the last one first receives Q (moved to TMEM
+                                                        // in the prologue), the first one is the epilogue's dQ staging tile
+  uint8_t* sV = tiles + (1 + kKStages) * kTile;         // 2 stages
+  uint8_t* sDS = tiles + (3 + kKStages) * kTile;        // [64 q][128 B] swizzled
+  uint8_t* sQ = sK + (kKStages - 1) * kTile;            // landing tile of Q
+  uint8_t* sOut = sK;                                   // dQ staging tile
 
-  __shared__ uint64_t qdo_full, k_full[2], k_empty[2], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full, ds_free, dq_final;
+  __shared__ uint64_t qdo_full, q_moved, k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full,
+      ds_free, dq_final;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
   __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
@@ -94,10 +105,9 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-    }
+    mbar_init(&q_moved, 128);
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     mbar_init(&sdp_full, 1); mbar_init(&sdp_free, 128);
     mbar_init(&ds_full, 128); mbar_init(&ds_free, 1);
     mbar_init(&dq_final, 1);
@@ -176,11 +186,14 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       int t = 0;
       for (; t < nb; ++t) {
         const int st = t & 1, ph = (t >> 1) & 1;
+        const int ks = t % kKStages, kph = (t / kKStages) & 1;
         const int row = s_row[t];
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort)) break;
-        mbar_expect_tx(&k_full[st], kTile);
-        if (p.paged) tma_load_3d(sK + st * kTile, &mapK, 0, row, 0, &k_full[st]);
-        else tma_load_5d(sK + st * kTile, &mapK, 0, h, row, 0, b, &k_full[st]);
+        // the last K stage held Q until the row warps moved it to TMEM
+        if (t == kKStages - 1 && !mbar_wait(&q_moved, 0, abort)) break;
+        if (!mbar_wait(&k_empty[ks], kph ^ 1, abort)) break;
+        mbar_expect_tx(&k_full[ks], kTile);
+        if (p.paged) tma_load_3d(sK + ks * kTile, &mapK, 0, row, 0, &k_full[ks]);
+        else tma_load_5d(sK + ks * kTile, &mapK, 0, h, row, 0, b, &k_full[ks]);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort)) { ++t; break; }
         mbar_expect_tx(&v_full[st], kTile);
         if (p.paged) tma_load_3d(sV + st * kTile, &mapV, 0, row, 0, &v_full[st]);
@@ -188,10 +201,8 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
       if (*abort) {
         // the other roles have stopped consuming: wait (bounded) for the copies still in flight
-        for (int u = (t > 2 ? t - 2 : 0); u < t; ++u) {
-          mbar_wait(&k_full[u & 1], (u >> 1) & 1, abort);
-          mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
-        }
+        for (int u = (t > kKStages ? t - kKStages : 0); u < t; ++u) mbar_wait(&k_full[u % kKStages], (u / kKStages) & 1, abort);
+        for (int u = (t > 2 ? t - 2 : 0); u < t; ++u) mbar_wait(&v_full[u & 1], (u >> 1) & 1, abort);
         mbar_wait(&qdo_full, 0, abort);
       }
     }
@@ -200,21 +211,23 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     if (nb > 0) {
       constexpr uint32_t idesc = instr_desc_bf16(64, 64, 0, 0);        // both operands K-major
       const uint32_t el = elect_one();
-      const uint64_t dQ = smem_desc(smem_u32(sQ), 16, 1024), dDO = smem_desc(smem_u32(sDO), 16, 1024);
-      bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort));
+      const uint64_t dDO = smem_desc(smem_u32(sDO), 16, 1024);
+      // dO has landed (qdo_full) and Q sits in TMEM (q_moved)
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort) && mbar_wait(&q_moved, 0, abort));
       for (int t = 0; ok && t < nb; ++t) {
         const int st = t & 1, ph = (t >> 1) & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(&k_full[st], ph, abort) && mbar_wait(&v_full[st], ph, abort) &&
+        const int ks = t % kKStages;
+        ok = __all_sync(0xffffffffu, mbar_wait(&k_full[ks], (t / kKStages) & 1, abort) && mbar_wait(&v_full[st], ph, abort) &&
                                      (t == 0 || mbar_wait(&sdp_free, (t - 1) & 1, abort)));    // S / dP of step t-1 were read
         if (!ok) break;
         tc_fence_after();
         TRACE(0, 8 + t * 8 + 0);
-        const uint64_t dK = smem_desc(smem_u32(sK + st * kTile), 16, 1024), dV = smem_desc(smem_u32(sV + st * kTile), 16, 1024);
+        const uint64_t dK = smem_desc(smem_u32(sK + ks * kTile), 16, 1024), dV = smem_desc(smem_u32(sV + st * kTile), 16, 1024);
         if (el) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = (kk >> 2) * 8192 + (kk & 3) * 32;
-            umma_ss(tm + kColS, desc_advance(dQ, off), desc_advance(dK, off), idesc, kk > 0 ? 1u : 0u);
+            umma_ts(tm + kColS, tm + kColQ + kk * 8, desc_advance(dK, off), idesc, kk > 0 ? 1u : 0u);   // A = Q from TMEM
           }
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -231,21 +244,22 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   } else if (warp == 6) {
     // ======================= MMA issuer 2: dQ += dS K =======================
     if (nb > 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(64, 128, 0, 1);       // A (dS) K-major, B (K tile) MN-major
+      // dQ^T += K^T dS^T: the accumulator is (128 head dims) x (64 rows) and takes 64 TMEM columns instead of 128
+      constexpr uint32_t idesc = instr_desc_bf16(128, 64, 1, 0);       // A (K tile, head dim as M) MN-major, B (dS) K-major
       const uint32_t el = elect_one();
       const uint64_t dDS = smem_desc(smem_u32(sDS), 16, 1024);
       for (int t = 0; t < nb; ++t) {
-        const int st = t & 1;
+        const int ks = t % kKStages;
         if (!__all_sync(0xffffffffu, mbar_wait(&ds_full, t & 1, abort))) break;
         tc_fence_after();
         TRACE(0, 8 + t * 8 + 2);
-        // K tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as N
-        const uint64_t dKmn = smem_desc(smem_u32(sK + st * kTile), 8192, 1024);
+        // K tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as M
+        const uint64_t dKmn = smem_desc(smem_u32(sK + ks * kTile), 8192, 1024);
         if (el) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tm + kColDQ, desc_advance(dDS, kk * 32), desc_advance(dKmn, kk * 2048), idesc, (t > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&k_empty[st]);
+            umma_ss(tm + kColDQ, desc_advance(dKmn, kk * 2048), desc_advance(dDS, kk * 32), idesc, (t > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&k_empty[ks]);
           umma_commit(&ds_free);
           if (t == nb - 1) umma_commit(&dq_final);
         }
@@ -298,7 +312,26 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const float nl0 = r0 < n_q ? -(p.lse[bhm + r0] * kLog2e - lg) : -INFINITY;
       const float nl1 = r1 < n_q ? -(p.lse[bhm + r1] * kLog2e - lg) : -INFINITY;
       const float sl = p.scale_log2;
-      bool ok = true;
+      // ---- Q from its landing tile into TMEM, in the layout of an M=64 A operand: row r in the lane of
+      // accumulator row r, head dims 2c, 2c+1 in column c.  With tcgen05.st.16x128b a thread supplies, per
+      // four-column block j, the word (row r0, column 4j + t%4) and the same column of row r1.
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort));
+      if (ok) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const uint8_t* box = sQ + hf * 8192;
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            w[2 * j] = *reinterpret_cast<const uint32_t*>(box + r0 * 128 + ((j ^ (r0 & 7)) << 4) + 4 * (lane & 3));
+            w[2 * j + 1] = *reinterpret_cast<const uint32_t*>(box + r1 * 128 + ((j ^ (r1 & 7)) << 4) + 4 * (lane & 3));
+          }
+          tmem_st_16x128b_x8_nowait(tm + lane_base + kColQ + hf * 32, w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      mbar_arrive(&q_moved);
       if (threadIdx.x == 0) TRACE(1, 2);
       for (int t = 0; t < nb; ++t) {
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 0);
@@ -355,16 +388,22 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 4);
       }
       if (threadIdx.x == 0) TRACE(1, 3);
-      // ---- epilogue: dQ fragments -> bf16 -> swizzled staging tile (the dead Q tile) -> TMA tile stores
+      // ---- epilogue: dQ^T fragments (16 head-dim lanes x 64 rows per load) -> bf16 pairs of adjacent rows,
+      // stored TRANSPOSED 8 x 8 at a time into the swizzled [row][head dim] staging tile (the first K stage,
+      // dead once every product has run) -> TMA tile stores
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_final, 0, abort));
       if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int dh = 0; dh < 2; ++dh) {
+        for (int lh = 0; lh < 2; ++lh) {                   // lanes 0-15 and 16-31 of this warp's quadrant
           uint32_t x[32];
-          tmem_ld_16x256b_x8_nowait(tm + lane_base + kColDQ + dh * 64, x);
+          tmem_ld_16x256b_x8_nowait(tm + lane_base + (static_cast<uint32_t>(lh * 16) << 16) + kColDQ, x);
           tmem_ld_wait();
-          const uint32_t aO = smem_u32(sQ) + dh * 8192 + st_row * 128;
+          // x[4i], x[4i+1]: head dim D0 + lane/4, rows 8i + 2(lane%4), +1;  x[4i+2], x[4i+3]: head dim + 8
+          const int D0 = warp * 32 + lh * 16;
+          const int dsel = D0 + ((lane >> 3) & 1) * 8;     // head dims of the matrix this lane addresses
+          const uint32_t boxa = smem_u32(sOut + (dsel >> 6) * 8192);
+          const uint32_t dchunk = static_cast<uint32_t>((dsel & 63) >> 3);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int i0 = 2 * q, i1 = 2 * q + 1;
@@ -372,14 +411,16 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             const uint32_t b0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0 + 2]), __uint_as_float(x[4 * i0 + 3]));
             const uint32_t a1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1]), __uint_as_float(x[4 * i1 + 1]));
             const uint32_t b1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1 + 2]), __uint_as_float(x[4 * i1 + 3]));
-            stmatrix_x4(aO + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), a0, b0, a1, b1);
+            // matrices: (rows 8 i0.., dims D0..), (rows 8 i0.., dims D0+8..), (rows 8 i1.., D0..), (rows 8 i1.., D0+8..)
+            const int qrow = 8 * (2 * q + (lane >> 4)) + (lane & 7);
+            stmatrix_x4_trans(boxa + qrow * 128 + ((dchunk ^ static_cast<uint32_t>(qrow & 7)) << 4), a0, b0, a1, b1);
           }
         }
         fence_async_smem();
       }
       named_barrier(1, 128);
       if (ok && threadIdx.x == 0) {
-        for (int dh = 0; dh < 2; ++dh) tma_store_4d(&mapDQ, sQ + dh * 8192, dh * 64, h, static_cast<int>(m0), b);
+        for (int dh = 0; dh < 2; ++dh) tma_store_4d(&mapDQ, sOut + dh * 8192, dh * 64, h, static_cast<int>(m0), b);
         bulk_commit_group();
         bulk_wait_all();
       }
