@@ -336,7 +336,7 @@ def run_gpu(args):
         roof.pop("ms")
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, from the ncu
         # captures summarised under profiles/ (sel_fwd_tc_config2.md, sel_bwd_tc_config2.md)
-        ncu_traffic = {"sel_fwd": 193.0e6 + 10.7e6, "sel_bwd_dq": 222.5e6 + 11.9e6, "sel_bwd_dkv": 206.7e6 + 158.0e6}
+        ncu_traffic = {"sel_fwd": 193.0e6 + 10.7e6, "sel_bwd_dq": 222.3e6 + 14.4e6, "sel_bwd_dkv": 206.7e6 + 158.0e6}
         roof.update(kernel=dom, traffic=ncu_traffic.get(dom), traffic_unit="bytes per launch (ncu capture)",
                     peak_source=pk["source"] + " (burst)",
                     note="achieved = algorithmic work of the kernel / mean CUDA-event time of its launches "
