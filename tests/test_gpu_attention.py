@@ -73,6 +73,8 @@ GEOMS = [
     (6, 1, 180, 600, 2, 128, 4, 60, 60, 180, True),        # 60/60
     (7, 1, 99, 700, 2, 64, 6, 100, 33, 99, False),         # block longer than a tile, odd group
     (8, 1, 130, 390, 2, 128, 20, 13, 10, 130, True),       # many small blocks packed into tiles
+    (9, 2, 192, 640, 2, 128, 4, 64, 64, 192, True),        # the page geometry with a batch dimension
+    (10, 3, 100, 300, 2, 128, 3, 64, 50, 100, False),      # batch of 3, 50-query groups, ragged last block
 ]
 
 
@@ -176,6 +178,14 @@ def test_strided_inputs(dev):
     out, lse = ops.sel_fwd(qd[..., D:2 * D], ops.DenseKV(kvd[..., :D], kvd[..., D:]), ids.to(dev), bs, 128, D ** -0.5, True, G)
     o_ref, _ = O.selection_fwd(q.float(), k.float(), v.float(), ids, bs, 128, None, True, G)
     assert_close_bf16(out, o_ref, "strided out")
+    # backward with strided q / k / v / dO (views into wider tensors)
+    big_do = torch.randn(B, M, H, 2 * D, generator=g).to(torch.bfloat16)
+    dod = big_do.to(dev)
+    dq, dk, dv = ops.sel_bwd(qd[..., D:2 * D], ops.DenseKV(kvd[..., :D], kvd[..., D:]), ids.to(dev), out, lse,
+                             dod[..., D:], bs, 128, D ** -0.5, True, G)
+    dq_c, dk_c, dv_c = ops.sel_bwd(qd[..., D:2 * D].contiguous(), ops.DenseKV(kvd[..., :D].contiguous(), kvd[..., D:].contiguous()),
+                                   ids.to(dev), out, lse, dod[..., D:].contiguous(), bs, 128, D ** -0.5, True, G)
+    assert torch.equal(dq, dq_c) and torch.equal(dk, dk_c) and torch.equal(dv, dv_c), "strided backward differs from contiguous"
 
 
 def test_dkdv_bit_reproducible(dev):
