@@ -42,7 +42,10 @@ typedef enum nsa_dtype { NSA_BF16 = 0, NSA_F16 = 1, NSA_F32 = 2 } nsa_dtype;
 typedef enum nsa_kv_mode {
   NSA_KV_DENSE = 0, /* k/v [B,N,H,D] with element strides (common.cuh:158-190 DenseKV)   */
   NSA_KV_PAGED = 1, /* fixed-page pool + int32 block table [H][max_blocks] -> page or -1;
-                       the B200-native replacement of the int64 pointer tables            */
+                       the B200-native replacement of the int64 pointer tables.  Whole pages
+                       are read: the rows of a partly filled page behind the block's last
+                       token get probability 0, but must hold finite values (0 x NaN = NaN
+                       in the P V and dS K products) - zero the pool once at allocation   */
   NSA_KV_PTR = 2    /* int64 byte-address tables [B,MG,H,T] laid out like block_indices, 0 =
                        skip, whole blocks only (common.cuh:193-215 PtrKV); block_indices is
                        ignored by the forward in this mode                                */

@@ -69,8 +69,11 @@ class BlockKVCache:
         self.num_pages, self.max_blocks = num_pages, max_blocks
         self.dtype, self.device = dtype, dev
         self.protect_blocks = protect_blocks
-        self.k_pool = torch.empty(num_pages, page_tokens, head_dim, dtype=dtype, device=dev)
-        self.v_pool = torch.empty_like(self.k_pool)
+        # Zero-filled, not empty: the rows of a partly filled page behind the block's last token are
+        # read by the attention kernels (their keys get probability 0, but 0 x NaN would still be NaN
+        # in the P V and dS K products), so the pool must never hold non-finite bit patterns.
+        self.k_pool = torch.zeros(num_pages, page_tokens, head_dim, dtype=dtype, device=dev)
+        self.v_pool = torch.zeros_like(self.k_pool)
         self.block_table = torch.full((num_heads, max_blocks), -1, dtype=torch.int32, device=dev)
         self.page_owner = torch.full((num_pages,), -1, dtype=torch.int32, device=dev)
         self.page_stamp = torch.zeros(num_pages, dtype=torch.int64, device=dev)
@@ -81,8 +84,8 @@ class BlockKVCache:
         self.host_k = self.host_v = None
         if host_tier:
             # one fixed slot per (head, block); pinned memory is addressable from the device
-            self.host_k = torch.empty(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
-            self.host_v = torch.empty(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
+            self.host_k = torch.zeros(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
+            self.host_v = torch.zeros(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
         self.n_tokens = 0
         self.epoch = 0
         self._pages_used = 0            # high-water mark of pages handed out while the pool fills

@@ -317,8 +317,10 @@ sel_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int acc = ic & 1;
         for (int t = 0; t < n_ent; ++t, ++sc) {
           const int st = sc % kStages, pb = sc & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(&pds_full[pb], (sc >> 1) & 1, abort) &&
-                                       (t > 0 || mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)));
+          // the accumulator of two items ago is normally long drained: ask first, so that the round
+          // trip of that wait passes while P / dS are still being written
+          ok = __all_sync(0xffffffffu, (t > 0 || mbar_wait(&acc_free[acc], ((ic >> 1) & 1) ^ 1, abort)) &&
+                                       mbar_wait(&pds_full[pb], (sc >> 1) & 1, abort));
           if (!ok) break;
           TRACE(0, 16 + sc * 8 + 5);
           tc_fence_after();
