@@ -78,6 +78,20 @@ def test_paged_attention_equals_dense(dev):
     assert torch.equal(out, dense)                       # same kernel, same tiles: bit-identical
 
 
+def test_pools_start_zero_filled(dev):
+    """The kernels read whole pages; rows behind a block's last token must be finite (0 x NaN = NaN in
+    P V and dS K), so the pools are zero-filled at allocation even when the allocator hands back
+    memory that held non-finite bit patterns."""
+    poison = torch.full((64, 64, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+    del poison                                            # back to the caching allocator, still NaN
+    cache = _mk(dev, H=2, pages=64, max_blocks=16, host_tier=False)
+    assert int(torch.count_nonzero(cache.k_pool)) == 0 and int(torch.count_nonzero(cache.v_pool)) == 0
+    g = torch.Generator().manual_seed(31)
+    k = torch.randn(100, 2, 128, generator=g).to(torch.bfloat16).to(dev)     # second block holds 36 of 64 tokens
+    cache.append(k, k)
+    assert bool(torch.isfinite(cache.k_pool.float()).all()) and bool(torch.isfinite(cache.v_pool.float()).all())
+
+
 def test_paged_backward_equals_dense(dev):
     """dQ, dK, dV with K/V read from the page pool through the block table: the same kernels and
     the same tiles as with dense tensors, so the gradients are bit-identical (B = 1, the pool
