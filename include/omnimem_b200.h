@@ -132,15 +132,31 @@ int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_stride[3], con
                             int64_t NC, int32_t topk, float scale, const nsa_topk_mask* mask,
                             int32_t* out_idx, float* out_scores, int32_t dtype, void* stream);
 
-/* Fused block-compressed key scoring: pools the raw keys k [B,N,H,D] block by block
- * (writes k_pooled_out [B,NC,H,D] contiguous when not NULL), scores them against
- * q_pooled and selects, reading K exactly once.  Same outputs as nsa_topk.
- * Replaces pooling + topk_cuda of the two citations above in one pass over K. */
+/* Fused block-compressed key scoring: ONE kernel pools the raw keys k [B,N,H,D] block by block
+ * (each key is read exactly once; the pooled keys go to k_pooled_out [B,NC,H,D] contiguous, which
+ * must not be NULL) and scores them against q_pooled on the spot; a selection kernel follows as a
+ * programmatic dependent.  Same outputs, bit for bit, as nsa_pool_rows + nsa_topk.  16-bit
+ * operands with D in {16, 32, 64, 128, 256} and 16-byte aligned rows take the fused kernel; every
+ * other call runs pooling, scoring and selection as three kernels.
+ * Replaces pooling + topk_cuda of the two citations above (the score tile + merge of
+ * topk.cu:296-439) in one pass over K. */
 int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
                         const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
                         int64_t N, int32_t topk, float scale, const nsa_topk_mask* mask,
                         void* k_pooled_out, int32_t* out_idx, float* out_scores, void* workspace,
                         size_t workspace_bytes, int32_t dtype, void* stream);
+
+/* The whole block selection from the RAW tensors: pools the queries q [B,M,H,D] in groups of
+ * mask->q_group_size (-> q_pooled_out [B,MG,H,D] contiguous, MG = ceil(M / q_group_size)), then
+ * runs nsa_pool_score_topk, whose fused kernel pools K while the query pooling is still running.
+ * Workspace: nsa_topk_workspace_bytes(B, MG, H, ceil(N / mask->block_size)).
+ * Replaces, in one call, the query-group pooling of nsa/ops/index_topk.py:72-79, the key pooling
+ * of models/transformers/causal_wan_nsa_model.py:408-409 and topk_cuda (topk.cu:664-808). */
+int nsa_select_blocks(const void* q, const int64_t q_stride[3], const void* k,
+                      const int64_t k_stride[3], int32_t B, int64_t M, int32_t H, int32_t D, int64_t N,
+                      int32_t topk, float scale, const nsa_topk_mask* mask, void* q_pooled_out,
+                      void* k_pooled_out, int32_t* out_idx, float* out_scores, void* workspace,
+                      size_t workspace_bytes, int32_t dtype, void* stream);
 
 /* Merge R candidate lists (idx/scores [R][rows][T], global ids) into the global top-k with
  * the same order rule.  New for block-sharded KV; the order rule is topk.cu:100-102 and the
@@ -228,11 +244,18 @@ int nsa_sel_bwd_dkv_ptr(const void* q, const int64_t q_stride[3], const int64_t*
                         int32_t H, int32_t D, int32_t T, int32_t block_size, int32_t group_size,
                         float scale, int32_t dtype, void* stream);
 
-/* Merge R attention partials over disjoint key sets/* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
+/* Merge R attention partials over disjoint key sets: outs [R][B,M,H,D] (dtype),
  * lses float [R][B,H,M] -> out, lse.  O = sum_r exp(lse_r - lse) O_r.  New for
  * block-sharded KV (no counterpart: the reference never splits one row's keys). */
 int nsa_merge_partials(const void* outs, const float* lses, int32_t R, int32_t B, int64_t M,
                        int32_t H, int32_t D, void* out, float* lse, int32_t dtype, void* stream);
+
+/* nsa_merge_partials over packed rows, for a row-split exchange: a row is the partial output of
+ * one query token for all heads (H*D elements of `dtype`) followed by its H log-sum-exps (fp32),
+ * H*D*2 + H*4 bytes rounded up to a multiple of 16.  parts [R][rows] rows (a rank's share of the rows, one copy
+ * from every rank) -> merged [rows] rows of the same format.  New for block-sharded KV. */
+int nsa_merge_packed_rows(const void* parts, int32_t R, int64_t rows, int32_t H, int32_t D, void* merged,
+                          int32_t dtype, void* stream);
 
 /* Three-branch gate + sum that consumes the selection output
  * (models/transformers/causal_wan_nsa_model.py:378-386, 541-546):
@@ -272,7 +295,10 @@ int nsa_build_ptr_table(const int32_t* block_indices, const int64_t idx_stride[4
  * stay on the device (n_dev pointers), so no call needs a host synchronisation. */
 
 /* Append S new tokens (k_new/v_new [S,H,D]; kv_stride = element strides of (s, h)) at
- * absolute token position pos0.  A touched block that has no page takes
+ * absolute token position pos0 <= n_tokens, the number of tokens the cache holds before the call
+ * (pos0 < n_tokens rewrites tokens in place; the blocks it touches must be resident or receive a
+ * page whose rows outside the rewritten range already hold the block's data).  A touched block
+ * that has no page takes
  * new_pages[h*n_touched_blocks + j] (device int32; e.g. fresh page ids or the victims list).
  * Writes the tokens with 16-byte stores, stamps the pages with `epoch`, and recomputes the
  * pooled key / value of every touched block over the tokens it now holds (v_pooled may be
@@ -280,7 +306,7 @@ int nsa_build_ptr_table(const int32_t* block_indices, const int64_t idx_stride[4
  * pooled-cache append of models/transformers/causal_wan_nsa_model.py:479-504, and
  * block_range_kernel (block_kv_range.cu:13-37). */
 int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2], int64_t S,
-                     int64_t pos0, int32_t H, int32_t D, void* k_pool, void* v_pool,
+                     int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool, void* v_pool,
                      int32_t page_tokens, int32_t* block_table, int32_t max_blocks,
                      const int32_t* new_pages, int32_t n_touched_blocks, int32_t* page_owner,
                      int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
@@ -308,30 +334,33 @@ typedef struct nsa_rope {
  * causal_reorder_rope_apply + update_cache + the pooled-cache append
  * (causal_wan_nsa_model.py:72-105, 479-504; cache.py:478-502). */
 int nsa_cache_append_rope(const void* k_new, const void* v_new, const int64_t kv_stride[2], int64_t S,
-                          int64_t pos0, int32_t H, int32_t D, void* k_pool, void* v_pool,
+                          int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool, void* v_pool,
                           int32_t page_tokens, int32_t* block_table, int32_t max_blocks,
                           const int32_t* new_pages, int32_t n_touched_blocks, int32_t* page_owner,
                           int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
                           int32_t* status, int32_t dtype, const nsa_rope* rope, void* stream);
 
-/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
+/* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
  * unique keys (cid*H + h)*bpc + loc (cid = bid / bpc, loc = bid % bpc): out_unique[0] = count
  * (may exceed cap), out_unique[1..cap] keys.  `stamp` is a persistent int32 [H*max_blocks]
  * scratch of the cache; epoch32 >= 1 must differ from call to call.  With a block_table
  * (needs bpc == max_blocks, so key = h*max_blocks + bid): resident pages among the keys get
  * page_stamp = epoch (the LRU touch) and out_missing (may be NULL) receives, in the same
- * format, the keys whose block has no page.
+ * format, the keys whose block has no page; `counters` (device int64 [4], may be NULL) then
+ * receives counters[0] += keys found resident (LRU hits), counters[1] += keys without a page
+ * (misses) - the hit / miss counts of MMCache (models/cache.py:156-163, 673-699, 713-716).
  * Replaces dedup_run (block_kv_dedup.cu:16-120; block_kv_ops.h:26-31) and the host LRU touch
  * loop of nsa/ops/selection/padded_ptr/wrapper.py:253-362. */
 size_t nsa_cache_dedup_workspace_bytes(int64_t n_keys);
 int nsa_cache_dedup_touch(const int32_t* block_indices, int64_t n_entries, int32_t H, int32_t T,
                           int32_t max_blocks, int32_t bpc, int32_t* stamp, int32_t epoch32,
                           const int32_t* block_table, int64_t* page_stamp, int64_t epoch,
-                          int32_t* out_unique, int32_t* out_missing, int32_t cap,
+                          int32_t* out_unique, int32_t* out_missing, int32_t cap, int64_t* counters,
                           void* workspace, size_t workspace_bytes, void* stream);
 
-/* The n least recently used pages, ascending (stamp, page): owned, owner's block id below
- * protect_from_bid, and not stamped with the current epoch.  n = *n_dev when n_dev != NULL
+/* n pages to (re)use: free pages first (ascending page id), then the least recently used owned
+ * pages, ascending (stamp, page): owner's block id below protect_from_bid and not stamped with
+ * the current epoch.  n = *n_dev when n_dev != NULL
  * (clamped to cap), else the host value n.  Sets *status = NSA_ERR_EXHAUSTED and pads with
  * -1 when fewer pages qualify.  Replaces the OrderedDict pop of
  * MMCache.lru_touch_per_head (models/cache.py:673-699). */
@@ -347,13 +376,16 @@ int nsa_cache_select_victims(const int32_t* page_owner, const int64_t* page_stam
  *   direction 1 (fetch): slot of keys[1+i] -> pages[i]; then block_table[key] = page,
  *                        owner and stamp set.  keys is a count-first list as written by
  *                        nsa_cache_dedup_touch (out_missing).
- * n = *n_dev when n_dev != NULL (grid sized by cap), else n.
+ * n = *n_dev when n_dev != NULL (grid sized by cap), else n.  `counters` (device int64 [4], may
+ * be NULL): counters[2] += pages evicted, counters[3] += pages fetched (bytes moved = pages x
+ * 2 x page_bytes).
  * Replaces gather_publish_clear (block_kv_gather.cu:13-45) and the copies of
  * MMCache.flush_offload (models/cache.py:1032-1142). */
 int nsa_cache_move_pages(int32_t direction, const int32_t* pages, const int32_t* keys, int32_t n,
                          const int32_t* n_dev, int32_t cap, void* k_pool, void* v_pool,
                          int64_t page_bytes, void* host_k, void* host_v, int32_t* block_table,
-                         int32_t* page_owner, int64_t* page_stamp, int64_t epoch, void* stream);
+                         int32_t* page_owner, int64_t* page_stamp, int64_t epoch, int64_t* counters,
+                         void* stream);
 
 /* The reference's K1 and K2 entry points with their own contracts (block_kv_ops.h:12-24):
  * desc int64 SoA [src_k|src_v|dst_k|dst_v|pub_k|pub_v] x n_fetch then clear x n_clear;

@@ -60,6 +60,8 @@ PROTOTYPES = {
                                        C.POINTER(TopkMask), _vp, _vp, _i32, _vp]),
     "nsa_pool_score_topk": (_i32, [_vp, _S3, _vp, _S3, _i32, _i32, _i32, _i32, _i64, _i32, _f32,
                                    C.POINTER(TopkMask), _vp, _vp, _vp, _vp, _sz, _i32, _vp]),
+    "nsa_select_blocks": (_i32, [_vp, _S3, _vp, _S3, _i32, _i64, _i32, _i32, _i64, _i32, _f32,
+                                 C.POINTER(TopkMask), _vp, _vp, _vp, _vp, _vp, _sz, _i32, _vp]),
     "nsa_merge_candidates": (_i32, [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),
     "nsa_sel_fwd": (_i32, [_vp, _S3, C.POINTER(KVSource), _vp, _S3, _vp, _S3, _vp, _i32, _i64, _i32,
                            _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32, _vp]),
@@ -75,6 +77,7 @@ PROTOTYPES = {
     "nsa_sel_bwd_dkv": (_i32, [_vp, _S3, C.POINTER(KVSource), _vp, _vp, _vp, _vp, _vp, _S3, _vp, _vp,
                                _i32, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _sz, _i32, _vp]),
     "nsa_merge_partials": (_i32, [_vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),
+    "nsa_merge_packed_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _i32, _vp]),
     "nsa_sel_bwd_dkv_ptr": (_i32, [_vp, _S3, _vp, _vp, _vp, _vp, _S3, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _i64,
                                    _i64, _vp, _vp, _i64, _vp, _vp, _vp, _S3, _i32, _i64, _i32, _i32, _i32, _i32, _i32,
                                    _f32, _i32, _vp]),
@@ -82,16 +85,16 @@ PROTOTYPES = {
     "nsa_gate_combine_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "nsa_build_ptr_table": (_i32, [_vp, _S3, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64,
                                    _i32, _i64, _vp, _vp, _vp]),
-    "nsa_cache_append": (_i32, [_vp, _vp, _S3, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
+    "nsa_cache_append": (_i32, [_vp, _vp, _S3, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
                                 _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _vp]),
-    "nsa_cache_append_rope": (_i32, [_vp, _vp, _S3, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
+    "nsa_cache_append_rope": (_i32, [_vp, _vp, _S3, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
                                      _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, C.POINTER(Rope), _vp]),
     "nsa_cache_dedup_workspace_bytes": (_sz, [_i64]),
     "nsa_cache_dedup_touch": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _i64,
-                                     _vp, _vp, _i32, _vp, _sz, _vp]),
+                                     _vp, _vp, _i32, _vp, _vp, _sz, _vp]),
     "nsa_cache_select_victims": (_i32, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp]),
     "nsa_cache_move_pages": (_i32, [_i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp,
-                                    _vp, _vp, _i64, _vp]),
+                                    _vp, _vp, _i64, _vp, _vp]),
     "nsa_gather_publish_clear": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, C.POINTER(C.c_int64), _vp]),
     "nsa_block_range": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32,
                                _i32, _i32, _vp]),

@@ -86,9 +86,12 @@ class BlockKVCache:
             # one fixed slot per (head, block); pinned memory is addressable from the device
             self.host_k = torch.zeros(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
             self.host_v = torch.zeros(num_heads * max_blocks, page_tokens, head_dim, dtype=dtype, pin_memory=True)
+        # LRU statistics kept on the device (MMCache's hit / miss counters, models/cache.py:156-163,
+        # 713-716): [0] selected blocks found resident, [1] selected blocks that had no page,
+        # [2] pages evicted, [3] pages fetched back from the host tier
+        self.counters = torch.zeros(4, dtype=torch.int64, device=dev)
         self.n_tokens = 0
         self.epoch = 0
-        self._pages_used = 0            # high-water mark of pages handed out while the pool fills
         self._evicted_any = False
         self.page_bytes = page_tokens * head_dim * self.k_pool.element_size()
         self._dtype_code = ops._dtype(self.k_pool)
@@ -118,9 +121,22 @@ class BlockKVCache:
             self.status.zero_()
             raise NSABackendError(f"block cache: device status {st} (page pool exhausted)")
 
-    def _select_victims(self, n: int, n_dev: Optional[torch.Tensor], cap: int) -> torch.Tensor:
+    def stats(self) -> dict:
+        """Synchronising read of the LRU counters (the role of MMCache.lru_hit_rate_overall,
+        models/cache.py:713-716): hits and misses count unique selected (head, block) pairs per
+        `touch`; bytes moved are whole pages, K and V."""
+        hits, misses, evicted, fetched = (int(x) for x in self.counters.tolist())
+        total = hits + misses
+        return {"hits": hits, "misses": misses, "hit_rate": hits / total if total else 0.0,
+                "pages_evicted": evicted, "pages_fetched": fetched,
+                "bytes_to_host": evicted * 2 * self.page_bytes if self.host_k is not None else 0,
+                "bytes_from_host": fetched * 2 * self.page_bytes}
+
+    def _select_victims(self, n: int, n_dev: Optional[torch.Tensor], cap: int, protect_from: Optional[int] = None
+                        ) -> torch.Tensor:
         victims = torch.full((max(cap, 1),), -1, dtype=torch.int32, device=self.device)
-        protect_from = max(self.n_blocks - self.protect_blocks, 0)
+        if protect_from is None:
+            protect_from = max(self.n_blocks - self.protect_blocks, 0)
         call("nsa_cache_select_victims", self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.num_pages,
              self.max_blocks, protect_from, self.epoch, n, None if n_dev is None else n_dev.data_ptr(), cap,
              victims.data_ptr(), self.status.data_ptr(), self._stream())
@@ -131,7 +147,28 @@ class BlockKVCache:
              None if n_dev is None else n_dev.data_ptr(), cap, self.k_pool.data_ptr(), self.v_pool.data_ptr(),
              self.page_bytes, None if self.host_k is None else self.host_k.data_ptr(),
              None if self.host_v is None else self.host_v.data_ptr(), self.block_table.data_ptr(),
-             self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.epoch, self._stream())
+             self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.epoch, self.counters.data_ptr(),
+             self._stream())
+
+    def _make_resident(self, ids: torch.Tensor, T: int, count: bool, protect_from: Optional[int] = None):
+        """Stamp the pages of the listed blocks with the current epoch and bring the ones that have
+        no page back from the host tier, evicting (free pages first, then least recently used)
+        to make room - all on the device.  ids: flat int32 in [.., H, T] order."""
+        cap = min(ids.numel(), self.H * self.max_blocks)
+        uniq = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
+        miss = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
+        wsb = _lib.load().nsa_cache_dedup_workspace_bytes(self.H * self.max_blocks)
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=self.device)
+        call("nsa_cache_dedup_touch", ids.data_ptr(), ids.numel(), self.H, T, self.max_blocks, self.max_blocks,
+             self._stamp32.data_ptr(), self.epoch, self.block_table.data_ptr(), self.page_stamp.data_ptr(),
+             self.epoch, uniq.data_ptr(), miss.data_ptr(), cap, self.counters.data_ptr() if count else None,
+             ws.data_ptr(), wsb, self._stream())
+        if self._evicted_any and self.host_k is not None:
+            n_dev = miss[:1]
+            victims = self._select_victims(0, n_dev, cap, protect_from)
+            self._move(0, victims, None, 0, n_dev, cap)
+            self._move(1, victims, miss, 0, n_dev, cap)
+        return uniq, miss
 
     # ------------------------------------------------------------------------------- append
     def append(self, k_new: torch.Tensor, v_new: torch.Tensor, pos0: Optional[int] = None,
@@ -139,7 +176,11 @@ class BlockKVCache:
         """Write k_new / v_new [S,H,D] at token position pos0 (default: the end).  Re-writing
         existing positions is allowed (each denoising step of a chunk overwrites the chunk).
         With `rope` the keys are given WITHOUT their rotary embedding and receive it on the way
-        into the pages (causal_reorder_rope_apply, causal_wan_nsa_model.py:72-105)."""
+        into the pages (causal_reorder_rope_apply, causal_wan_nsa_model.py:72-105).
+
+        Blocks the call touches are never chosen as victims for the pages it needs, and a touched
+        block that was evicted earlier comes back from the host tier before it is rewritten, so a
+        rewrite that covers part of a block keeps the rest of it."""
         S = k_new.shape[0]
         if S == 0:
             return
@@ -155,25 +196,27 @@ class BlockKVCache:
             raise NSABackendError(f"token {pos0 + S - 1} is past the block table ({self.max_blocks} blocks)")
         n_touched = last - first + 1
         n_new = max(0, last + 1 - self.n_blocks)            # blocks that have never had a page
+        n_exist = n_touched - n_new                         # touched blocks that were appended before
         self.epoch += 1
+        # pages for this call may only come from blocks in front of the ones it touches
+        protect_from = max(min(first, self.n_blocks - self.protect_blocks), 0)
         with torch.cuda.device(self.device):
+            if n_exist and self._evicted_any:
+                if self.host_k is None:
+                    raise NSABackendError("rewriting blocks after evictions needs the host tier (a dropped block "
+                                          "cannot be completed again)")
+                ids = torch.arange(first, first + n_exist, dtype=torch.int32, device=self.device).repeat_interleave(self.H)
+                self._make_resident(ids, 1, count=False, protect_from=protect_from)
             new_pages = torch.full((self.H, n_touched), -1, dtype=torch.int32, device=self.device)
             need = n_new * self.H
             if need:
-                fresh = min(need, self.num_pages - self._pages_used)
-                ids = []
-                if fresh:
-                    ids.append(torch.arange(self._pages_used, self._pages_used + fresh, dtype=torch.int32,
-                                            device=self.device))
-                    self._pages_used += fresh
-                if need > fresh:
-                    victims = self._select_victims(need - fresh, None, need - fresh)
-                    self._move(0, victims, None, need - fresh, None, need - fresh)
-                    ids.append(victims)
+                pages = self._select_victims(need, None, need, protect_from)
+                self._move(0, pages, None, need, None, need)          # free pages pass through untouched
+                new_pages[:, n_exist:] = pages.view(self.H, n_new)
+                if self.n_blocks * self.H + need > self.num_pages:
                     self._evicted_any = True
-                new_pages[:, n_touched - n_new:] = torch.cat(ids).view(self.H, n_new)
             args = (k_new.data_ptr(), v_new.data_ptr(),
-                    (C.c_int64 * 3)(k_new.stride(0), k_new.stride(1), 0), S, pos0, self.H, self.D,
+                    (C.c_int64 * 3)(k_new.stride(0), k_new.stride(1), 0), S, pos0, self.n_tokens, self.H, self.D,
                     self.k_pool.data_ptr(), self.v_pool.data_ptr(), self.page_tokens, self.block_table.data_ptr(),
                     self.max_blocks, new_pages.data_ptr(), n_touched, self.page_owner.data_ptr(),
                     self.page_stamp.data_ptr(), self.epoch, self.k_pooled.data_ptr(), self.v_pooled.data_ptr(),
@@ -192,21 +235,19 @@ class BlockKVCache:
         ids = block_indices.contiguous().view(-1)
         T = block_indices.shape[-1]
         self.epoch += 1
-        cap = min(ids.numel(), self.H * self.max_blocks)
         with torch.cuda.device(self.device):
-            uniq = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
-            miss = torch.empty(1 + cap, dtype=torch.int32, device=self.device)
-            wsb = _lib.load().nsa_cache_dedup_workspace_bytes(self.H * self.max_blocks)
-            ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=self.device)
-            call("nsa_cache_dedup_touch", ids.data_ptr(), ids.numel(), self.H, T, self.max_blocks, self.max_blocks,
-                 self._stamp32.data_ptr(), self.epoch, self.block_table.data_ptr(), self.page_stamp.data_ptr(),
-                 self.epoch, uniq.data_ptr(), miss.data_ptr(), cap, ws.data_ptr(), wsb, self._stream())
-            if self._evicted_any and self.host_k is not None:
-                n_dev = miss[:1]
-                victims = self._select_victims(0, n_dev, cap)
-                self._move(0, victims, None, 0, n_dev, cap)
-                self._move(1, victims, miss, 0, n_dev, cap)
+            uniq, miss = self._make_resident(ids, T, count=True)
         return (uniq, miss) if return_lists else None
+
+    def evict_all(self) -> None:
+        """Move every resident page to the host tier and free it (the block cache's form of
+        MMCache.flush_offload with nothing protected, models/cache.py:1032-1142)."""
+        if self.host_k is None:
+            raise NSABackendError("evict_all needs the host tier")
+        with torch.cuda.device(self.device):
+            pages = torch.arange(self.num_pages, dtype=torch.int32, device=self.device)
+            self._move(0, pages, None, self.num_pages, None, self.num_pages)
+        self._evicted_any = True
 
     def selection_attention(self, q: torch.Tensor, block_indices: torch.Tensor, scale: Optional[float] = None,
                             group_size: int = 64, return_lse: bool = False):
@@ -225,7 +266,7 @@ class BlockKVCache:
         self.page_stamp.zero_()
         self._stamp32.zero_()
         self.status.zero_()
+        self.counters.zero_()
         self.n_tokens = 0
         self.epoch = 0
-        self._pages_used = 0
         self._evicted_any = False

@@ -17,6 +17,7 @@ struct AppendParams {
   const char* k_new; const char* v_new;
   int64_t s_stride, h_stride;      // elements
   int64_t S, pos0;
+  int64_t n_tokens_before;         // tokens the cache held before this call (a rewrite may end before them)
   int H, D, page_tokens, max_blocks, n_touched;
   char* k_pool; char* v_pool;
   int32_t* block_table; const int32_t* new_pages;
@@ -105,8 +106,10 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     *reinterpret_cast<uint4*>(vp + dst) = *reinterpret_cast<const uint4*>(p.v_new + src);
   }
   __syncthreads();
-  // pooled key / value over the tokens the block now holds (rows [0, n_present))
-  const int n_present = static_cast<int>(hi - blk0);
+  // pooled key / value over the tokens the block now holds (rows [0, n_present)): a rewrite that
+  // ends inside the block leaves the tokens behind it in place
+  const int64_t held = min(p.n_tokens_before, blk0 + p.page_tokens);
+  const int n_present = static_cast<int>(max(hi, held) - blk0);
   const int rp = blockDim.x / cpr;
   const int col = threadIdx.x % cpr, r0 = threadIdx.x / cpr;
   float ak[VEC], av[VEC];
@@ -168,8 +171,11 @@ __global__ void __launch_bounds__(kTileKeys) dedup_count_kernel(const int32_t* _
 }
 
 // single block: exclusive scan of the tile counts; writes totals to out_unique[0] / out_missing[0]
+// counters (may be null): [0] += unique blocks found resident (hits), [1] += unique blocks without
+// a page (misses) - the device form of the hit / miss counts of MMCache.lru_touch_per_head
+// (models/cache.py:156-163, 673-699)
 __global__ void dedup_scan_kernel(int32_t* __restrict__ counts, int n_tiles, int32_t* out_unique,
-                                  int32_t* out_missing) {
+                                  int32_t* out_missing, int64_t* counters) {
   if (threadIdx.x != 0) return;
   int a = 0, b = 0;
   for (int t = 0; t < n_tiles; ++t) {
@@ -179,6 +185,7 @@ __global__ void dedup_scan_kernel(int32_t* __restrict__ counts, int n_tiles, int
   }
   out_unique[0] = a;
   if (out_missing) out_missing[0] = b;
+  if (counters) { counters[0] += a - b; counters[1] += b; }
 }
 
 __global__ void __launch_bounds__(kTileKeys) dedup_compact_kernel(
@@ -204,8 +211,9 @@ __global__ void __launch_bounds__(kTileKeys) dedup_compact_kernel(
 }
 
 // ------------------------------------------------------------------------- victim selection
-// Single block.  Picks the n least-recently-used pages: owner >= 0, owner's block id below
-// protect_from_bid, stamp < epoch (not touched by the current call); order (stamp, page) asc.
+// Single block.  Picks n pages to (re)use: free pages first (owner < 0, ascending page id), then
+// the least recently used owned pages: owner's block id below protect_from_bid, stamp < epoch (not
+// touched by the current call), order (stamp, page) ascending.
 __global__ void __launch_bounds__(1024) select_victims_kernel(
     const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp, int num_pages,
     int max_blocks, int protect_from_bid, int64_t epoch, int n_host, const int32_t* __restrict__ n_dev,
@@ -216,11 +224,11 @@ __global__ void __launch_bounds__(1024) select_victims_kernel(
   if (n > cap) n = cap;
   auto key_at = [&](int pg) -> unsigned long long {
     const int owner = page_owner[pg];
-    if (owner < 0) return ~0ull;
+    if (owner < 0) return static_cast<unsigned long long>(pg);        // free: before every owned page
     if (owner % max_blocks >= protect_from_bid) return ~0ull;
     const int64_t st = page_stamp[pg];
     if (st >= epoch) return ~0ull;
-    return (static_cast<unsigned long long>(st) << 24) | static_cast<unsigned>(pg);
+    return (static_cast<unsigned long long>(st + 1) << 24) | static_cast<unsigned>(pg);
   };
   auto scan_above = [&](unsigned long long bound, bool any) {
     unsigned long long best = ~0ull;
@@ -261,6 +269,7 @@ struct MoveParams {
   char* k_pool; char* v_pool; int64_t page_bytes;
   char* host_k; char* host_v;  // slot of key = base + key * page_bytes (device-mapped pinned memory)
   int32_t* block_table; int32_t* page_owner; int64_t* page_stamp; int64_t epoch;
+  unsigned long long* counters;  // may be null: [2] += pages evicted, [3] += pages fetched
 };
 
 template <bool FETCH>
@@ -282,6 +291,7 @@ __global__ void __launch_bounds__(256) move_pages_kernel(const MoveParams p) {
       p.page_owner[page] = key;
       p.page_stamp[page] = p.epoch;
       p.block_table[key] = page;
+      if (p.counters) atomicAdd(p.counters + 3, 1ull);
     }
   } else {
     const int key = p.page_owner[page];
@@ -295,6 +305,7 @@ __global__ void __launch_bounds__(256) move_pages_kernel(const MoveParams p) {
     if (threadIdx.x == 0) {
       p.block_table[key] = -1;
       p.page_owner[page] = -1;
+      if (p.counters) atomicAdd(p.counters + 2, 1ull);
     }
   }
 }
@@ -359,7 +370,7 @@ __global__ void block_range_kernel(int64_t* __restrict__ table, int32_t* __restr
 using namespace nsa;
 
 static int cache_append_impl(const void* k_new, const void* v_new, const int64_t kv_stride[2],
-                             int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                             int64_t S, int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool,
                              void* v_pool, int32_t page_tokens, int32_t* block_table,
                              int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
                              int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
@@ -367,6 +378,9 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
                              const nsa_rope* rope, void* stream) {
   NSA_REQUIRE(S >= 0 && pos0 >= 0 && H > 0 && D > 0 && page_tokens > 0 && max_blocks > 0, NSA_ERR_INVALID,
               "cache_append: bad size");
+  NSA_REQUIRE(n_tokens >= 0 && pos0 <= n_tokens, NSA_ERR_INVALID,
+              "cache_append: pos0 = %lld would leave a gap behind the %lld tokens the cache holds",
+              static_cast<long long>(pos0), static_cast<long long>(n_tokens));
   NSA_REQUIRE(dtype == NSA_BF16 || dtype == NSA_F16, NSA_ERR_UNSUPPORTED, "cache_append: bf16 / fp16 only");
   if (S == 0) return NSA_OK;
   const int esz = 2;
@@ -382,7 +396,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
               NSA_ERR_LAYOUT, "cache_append: new K/V rows must be 16-byte aligned");
   NSA_REQUIRE(H <= 65535, NSA_ERR_INVALID, "cache_append: H must be <= 65535");
   AppendParams p{static_cast<const char*>(k_new), static_cast<const char*>(v_new), kv_stride[0], kv_stride[1],
-                 S, pos0, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
+                 S, pos0, n_tokens, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
                  static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
                  static_cast<char*>(k_pooled), static_cast<char*>(v_pooled), status};
   if (rope != nullptr) {
@@ -416,26 +430,26 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
 }
 
 extern "C" int nsa_cache_append(const void* k_new, const void* v_new, const int64_t kv_stride[2],
-                                int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                                int64_t S, int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool,
                                 void* v_pool, int32_t page_tokens, int32_t* block_table,
                                 int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
                                 int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
                                 void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
                                 void* stream) {
-  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, H, D, k_pool, v_pool, page_tokens, block_table,
+  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, n_tokens, H, D, k_pool, v_pool, page_tokens, block_table,
                            max_blocks, new_pages, n_touched_blocks, page_owner, page_stamp, epoch, k_pooled,
                            v_pooled, status, dtype, nullptr, stream);
 }
 
 extern "C" int nsa_cache_append_rope(const void* k_new, const void* v_new, const int64_t kv_stride[2],
-                                     int64_t S, int64_t pos0, int32_t H, int32_t D, void* k_pool,
+                                     int64_t S, int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool,
                                      void* v_pool, int32_t page_tokens, int32_t* block_table,
                                      int32_t max_blocks, const int32_t* new_pages, int32_t n_touched_blocks,
                                      int32_t* page_owner, int64_t* page_stamp, int64_t epoch,
                                      void* k_pooled, void* v_pooled, int32_t* status, int32_t dtype,
                                      const nsa_rope* rope, void* stream) {
   NSA_REQUIRE(rope != nullptr, NSA_ERR_INVALID, "cache_append_rope: rope is null");
-  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, H, D, k_pool, v_pool, page_tokens, block_table,
+  return cache_append_impl(k_new, v_new, kv_stride, S, pos0, n_tokens, H, D, k_pool, v_pool, page_tokens, block_table,
                            max_blocks, new_pages, n_touched_blocks, page_owner, page_stamp, epoch, k_pooled,
                            v_pooled, status, dtype, rope, stream);
 }
@@ -448,7 +462,7 @@ extern "C" int nsa_cache_dedup_touch(const int32_t* block_indices, int64_t n_ent
                                      int32_t T, int32_t max_blocks, int32_t bpc, int32_t* stamp, int32_t epoch32,
                                      const int32_t* block_table, int64_t* page_stamp, int64_t epoch,
                                      int32_t* out_unique, int32_t* out_missing, int32_t cap,
-                                     void* workspace, size_t workspace_bytes, void* stream) {
+                                     int64_t* counters, void* workspace, size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(n_entries >= 0 && H > 0 && T > 0 && max_blocks > 0 && cap >= 0, NSA_ERR_INVALID, "cache_dedup: bad size");
   NSA_REQUIRE(stamp && out_unique, NSA_ERR_INVALID, "cache_dedup: null pointer");
   NSA_REQUIRE(bpc > 0 && max_blocks % bpc == 0, NSA_ERR_INVALID, "cache_dedup: bpc must divide max_blocks");
@@ -470,7 +484,7 @@ extern "C" int nsa_cache_dedup_touch(const int32_t* block_indices, int64_t n_ent
   }
   dedup_count_kernel<<<n_tiles, kTileKeys, 0, s>>>(stamp, epoch32, block_table, n_keys, counts);
   NSA_LAUNCH_OK("dedup_count_kernel");
-  dedup_scan_kernel<<<1, 32, 0, s>>>(counts, n_tiles, out_unique, out_missing);
+  dedup_scan_kernel<<<1, 32, 0, s>>>(counts, n_tiles, out_unique, out_missing, block_table ? counters : nullptr);
   NSA_LAUNCH_OK("dedup_scan_kernel");
   dedup_compact_kernel<<<n_tiles, kTileKeys, 0, s>>>(stamp, epoch32, block_table, n_keys, counts, page_stamp,
                                                      epoch, out_unique, out_missing, cap);
@@ -497,7 +511,7 @@ extern "C" int nsa_cache_move_pages(int32_t direction, const int32_t* pages, con
                                     int32_t n, const int32_t* n_dev, int32_t cap, void* k_pool,
                                     void* v_pool, int64_t page_bytes, void* host_k, void* host_v,
                                     int32_t* block_table, int32_t* page_owner, int64_t* page_stamp,
-                                    int64_t epoch, void* stream) {
+                                    int64_t epoch, int64_t* counters, void* stream) {
   NSA_REQUIRE(direction == 0 || direction == 1, NSA_ERR_INVALID, "cache_move_pages: direction must be 0 or 1");
   NSA_REQUIRE(n >= 0 && cap >= 0 && page_bytes > 0 && page_bytes % 16 == 0, NSA_ERR_INVALID, "cache_move_pages: bad size");
   NSA_REQUIRE(pages && k_pool && v_pool && block_table && page_owner && page_stamp, NSA_ERR_INVALID,
@@ -506,7 +520,8 @@ extern "C" int nsa_cache_move_pages(int32_t direction, const int32_t* pages, con
   const int grid = n_dev ? cap : n;
   if (grid == 0) return NSA_OK;
   MoveParams p{pages, keys, n, n_dev, static_cast<char*>(k_pool), static_cast<char*>(v_pool), page_bytes,
-               static_cast<char*>(host_k), static_cast<char*>(host_v), block_table, page_owner, page_stamp, epoch};
+               static_cast<char*>(host_k), static_cast<char*>(host_v), block_table, page_owner, page_stamp, epoch,
+               reinterpret_cast<unsigned long long*>(counters)};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (direction == 1) move_pages_kernel<true><<<grid, 256, 0, s>>>(p);
   else move_pages_kernel<false><<<grid, 256, 0, s>>>(p);

@@ -50,6 +50,54 @@ __global__ void merge_partials_kernel(const char* __restrict__ outs, const float
   }
 }
 
+// The same merge over PACKED rows, for the row-split exchange of the block-sharded forward: a row
+// holds the partial output of one query token for all heads (H*D elements) followed by its H
+// log-sum-exps as fp32, padded to a multiple of 16 bytes; `parts` is [R][rows] such rows (what one rank receives from the all-to-all:
+// its share of the rows from every rank), `merged` [rows] rows in the same format.
+template <typename T>
+__global__ void merge_packed_rows_kernel(const char* __restrict__ parts, int R, int64_t rows, int H, int D,
+                                         int64_t row_bytes, char* __restrict__ merged) {
+  const int cpr = D / 8;
+  const int64_t total = rows * H * cpr;
+  const int64_t part_bytes = rows * row_bytes;
+  const int64_t lse_off = static_cast<int64_t>(H) * D * sizeof(T);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % cpr);
+    const int64_t rh = i / cpr;
+    const int h = static_cast<int>(rh % H);
+    const int64_t row = rh / H;
+    const char* base = parts + row * row_bytes;
+    float w[kMaxParts];
+    float mx = -INFINITY;
+    for (int r = 0; r < R; ++r) {
+      w[r] = *reinterpret_cast<const float*>(base + r * part_bytes + lse_off + h * 4);
+      mx = fmaxf(mx, w[r]);
+    }
+    float den = 0.f;
+    for (int r = 0; r < R; ++r) { w[r] = (w[r] == -INFINITY) ? 0.f : __expf(w[r] - mx); den += w[r]; }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int r = 0; r < R; ++r) {
+      if (w[r] == 0.f) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(base + r * part_bytes + (static_cast<int64_t>(h) * D) * sizeof(T) + cc * 16);
+      const T* e8 = reinterpret_cast<const T*>(&v);
+      const float wr = w[r] * inv;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += wr * to_f32<T>(e8[e]);
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) oe[e] = from_f32<T>(acc[e]);
+    char* orow = merged + row * row_bytes;
+    *reinterpret_cast<uint4*>(orow + (static_cast<int64_t>(h) * D) * sizeof(T) + cc * 16) = o;
+    if (cc == 0) *reinterpret_cast<float*>(orow + lse_off + h * 4) = den > 0.f ? mx + logf(den) : -INFINITY;
+  }
+}
+
 __global__ void build_ptr_table_kernel(const int32_t* __restrict__ ids, int64_t i_sb, int64_t i_sg,
                                        int64_t i_sh, int64_t i_st, const int64_t* __restrict__ base_k,
                                        const int64_t* __restrict__ base_v,
@@ -107,6 +155,28 @@ extern "C" int nsa_merge_partials(const void* outs, const float* lses, int32_t R
     merge_partials_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const char*>(outs), lses, R, B, M, H, D,
                                                          static_cast<char*>(out), lse);
   NSA_LAUNCH_OK("merge_partials_kernel");
+  return NSA_OK;
+}
+
+extern "C" int nsa_merge_packed_rows(const void* parts, int32_t R, int64_t rows, int32_t H, int32_t D,
+                                     void* merged, int32_t dtype, void* stream) {
+  NSA_REQUIRE(R >= 1 && R <= kMaxParts, NSA_ERR_INVALID, "merge_packed_rows: R must be in [1,%d]", kMaxParts);
+  NSA_REQUIRE(rows >= 0 && H > 0 && D > 0 && D % 8 == 0, NSA_ERR_INVALID, "merge_packed_rows: bad size");
+  NSA_REQUIRE(dtype == NSA_BF16 || dtype == NSA_F16, NSA_ERR_UNSUPPORTED, "merge_packed_rows: bf16 / fp16 only");
+  const int64_t row_bytes = static_cast<int64_t>(align_up(static_cast<size_t>(H) * D * 2 + static_cast<size_t>(H) * 4, 16));
+  const int64_t total = rows * H * (D / 8);
+  if (total == 0) return NSA_OK;
+  NSA_REQUIRE(parts && merged && aligned16(parts) && aligned16(merged), NSA_ERR_INVALID,
+              "merge_packed_rows: null or misaligned pointer");
+  const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == NSA_BF16)
+    merge_packed_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const char*>(parts), R, rows, H, D, row_bytes,
+                                                                   static_cast<char*>(merged));
+  else
+    merge_packed_rows_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const char*>(parts), R, rows, H, D, row_bytes,
+                                                            static_cast<char*>(merged));
+  NSA_LAUNCH_OK("merge_packed_rows_kernel");
   return NSA_OK;
 }
 

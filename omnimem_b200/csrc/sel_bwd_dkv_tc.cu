@@ -602,6 +602,7 @@ int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_
   const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
   if (env != nullptr && std::string(env) == "general") return NSA_OK;
   if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || H == 1) return NSA_OK;
+  if (!(scale > 0.f)) return NSA_OK;   // the kernel folds log2(scale) into the exponent
   if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
   if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
   if (encode_tiled_fn() == nullptr) return NSA_OK;

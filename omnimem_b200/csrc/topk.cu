@@ -20,8 +20,10 @@ struct PoolParams {
 
 template <typename T>
 __global__ void __launch_bounds__(128) pool_rows_kernel(const PoolParams p) {
-  chain_release();
+  // wait first, release second: a kernel chained behind this one starts only when every kernel in
+  // front of this one has completed, so it may read their results before its own chain_wait()
   chain_wait();
+  chain_release();
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float s_part[];                  // [rp][D]
   const int64_t c = blockIdx.x;
@@ -197,6 +199,138 @@ int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
   const dim3 grid(static_cast<unsigned>(cdiv64(sp.NC, kScoreCols)), cdiv(sp.MG, kScoreMmaRows), sp.H * B);
   NSA_CUDA_OK(launch_chained(kChainSmall, score_mma_kernel<T>, grid, dim3(128), smem, s, sp));
   NSA_LAUNCH_OK("score_mma_kernel");
+  return NSA_OK;
+}
+
+// ------------------------------------------------------------------- fused pooling + scoring
+// One thread block pools kFusedCols consecutive key blocks of one (batch, head) - the HBM-bound part:
+// every key is read exactly once, 16 bytes per load, eight loads in flight per thread - keeps the
+// rounded pooled keys in shared memory (and writes them out), and scores them against ALL pooled
+// query rows of the head with the same m16n8k16 products, in the same order, as score_mma_kernel,
+// so the scores carry the same bits.  The pooled queries (MG x D, a few KB per head) come from L2.
+// With early_k the keys are pooled BEFORE the wait on the kernel in front (which then must be one
+// that releases its dependents only after its own wait: the query-group pooling launched by
+// nsa_select_blocks), so that pooling the queries costs no time of its own.
+constexpr int kFusedCols = 8;
+
+struct PoolScoreParams {
+  PoolParams pool;                                   // raw keys -> pooled keys [B,NC,H,D]
+  const char* q; int64_t q_sb, q_sg, q_sh;           // pooled queries [B,MG,H,D]
+  float* scores;                                     // [B,H,MG,NC]
+  int MG, H;
+  int64_t NC;
+  float scale;
+  int early_k;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p) {
+  constexpr int VEC = 8;                              // 16-bit elements per 16-byte load
+  constexpr int UNROLL = 8;
+  extern __shared__ __align__(16) char s_raw[];
+  const int D = p.pool.D, PITCH = D + 8;
+  const int lpr = D / VEC, rp = 128 / lpr;
+  float* s_part = reinterpret_cast<float*>(s_raw);                      // [rp][D]
+  T* sK = reinterpret_cast<T*>(s_raw + static_cast<size_t>(rp) * D * sizeof(float));   // [8][PITCH] pooled keys
+  T* sQ = sK + kFusedCols * PITCH;                                      // [64][PITCH] pooled queries
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kFusedCols;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int ncol = static_cast<int>(p.NC - c0 < kFusedCols ? p.NC - c0 : kFusedCols);
+  const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
+  if (!p.early_k) chain_wait();
+  chain_release();
+
+  for (int j = 0; j < kFusedCols; ++j) {
+    if (j >= ncol) {                                  // columns past the last key block score nothing
+      for (int d = threadIdx.x; d < D; d += blockDim.x) sK[j * PITCH + d] = from_f32<T>(0.f);
+      continue;
+    }
+    const int64_t n0 = (c0 + j) * p.pool.size;
+    const int n = static_cast<int>(p.pool.N - n0 < p.pool.size ? p.pool.N - n0 : p.pool.size);
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    const char* base = p.pool.x + (b * p.pool.x_sb + n0 * p.pool.x_sn + h * p.pool.x_sh) * sizeof(T) + col * 16;
+    const int64_t row_bytes = p.pool.x_sn * sizeof(T);
+    for (int r = r0; r < n; r += UNROLL * rp) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int rr = r + u * rp;
+        v[u] = rr < n ? *reinterpret_cast<const uint4*>(base + rr * row_bytes) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        if (r + u * rp < n) {                         // rows in ascending order, as pool_rows_kernel adds them
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+        }
+      }
+    }
+    __syncthreads();                                  // s_part of the previous key block has been read
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_part[r0 * D + col * VEC + i] = acc[i];
+    __syncthreads();
+    const float inv = 1.f / static_cast<float>(n);
+    T* orow = reinterpret_cast<T*>(p.pool.out + (b * p.pool.o_sb + (c0 + j) * p.pool.o_sn + h * p.pool.o_sh) * sizeof(T));
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float sum = 0.f;
+      for (int r = 0; r < rp; ++r) sum += s_part[r * D + d];
+      const T kq = from_f32<T>(sum * inv);
+      orow[d] = kq;
+      sK[j * PITCH + d] = kq;
+    }
+  }
+  if (p.early_k) chain_wait();                        // the pooled queries come from the kernel in front
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
+  const int cpr = D / 8;
+  for (int g0 = 0; g0 < p.MG; g0 += kScoreMmaRows) {
+    const int nrow = min(kScoreMmaRows, p.MG - g0);
+    __syncthreads();                                  // sK complete / sQ of the previous tile consumed
+    for (int i = threadIdx.x; i < kScoreMmaRows * cpr; i += blockDim.x) {
+      const int r = i / cpr, cc = i - r * cpr;
+      const char* qsrc = p.q + (b * p.q_sb + (g0 + r) * p.q_sg + h * p.q_sh) * 2 + cc * 16;
+      cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? qsrc : p.q, r < nrow ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    if (warp * 16 < nrow) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const T* qa = sQ + (warp * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8;
+      const T* kb = sK + gid * PITCH + t4 * 2;
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, qa + kk * 16);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8);
+        mma16816<T>(acc, a, b0, b1);
+      }
+      float* out = p.scores + ((static_cast<int64_t>(b) * p.H + h) * p.MG + g0) * p.NC + c0;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + gid + 8 * r;
+        if (row < nrow) {
+          const int cc = 2 * t4;
+          if (cc < ncol) out[static_cast<int64_t>(row) * p.NC + cc] = acc[2 * r] * p.scale + 0.f;
+          if (cc + 1 < ncol) out[static_cast<int64_t>(row) * p.NC + cc + 1] = acc[2 * r + 1] * p.scale + 0.f;
+        }
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_pool_score(const PoolScoreParams& p, int B, cudaStream_t s) {
+  const int D = p.pool.D, rp = 128 / (D / 8);
+  const size_t smem = static_cast<size_t>(rp) * D * sizeof(float) +
+                      static_cast<size_t>(kFusedCols + kScoreMmaRows) * (D + 8) * sizeof(T);
+  NSA_CUDA_OK(cudaFuncSetAttribute(pool_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const dim3 grid(static_cast<unsigned>(cdiv64(p.NC, kFusedCols)), p.H, B);
+  NSA_CUDA_OK(launch_chained(kChainSmall, pool_score_kernel<T>, grid, dim3(128), smem, s, p));
+  NSA_LAUNCH_OK("pool_score_kernel");
   return NSA_OK;
 }
 
@@ -502,6 +636,16 @@ int fill_mask(const nsa_topk_mask* in, int MG, int64_t NC_global, Mask* m) {
   return NSA_OK;
 }
 
+// The mask of a call over NC local columns.  The teacher-forcing layout splits the GLOBAL key
+// blocks into a clean and a noisy half; a shard (id_stride > 1) does not know the global count
+// (ragged shards would disagree on it), so that combination is rejected.
+int fill_mask_checked(const nsa_topk_mask* in, int MG, int64_t NC, Mask* m) {
+  NSA_REQUIRE(in != nullptr, NSA_ERR_INVALID, "topk: mask is null");
+  NSA_REQUIRE(!(in->tf_mask && in->id_stride > 1), NSA_ERR_UNSUPPORTED,
+              "topk: tf_mask cannot be combined with block-sharded ids (id_stride > 1)");
+  return fill_mask(in, MG, NC, m);
+}
+
 template <typename T>
 int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
   const int vec = 16 / static_cast<int>(sizeof(T));
@@ -628,18 +772,19 @@ extern "C" int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const v
   NSA_REQUIRE(workspace && workspace_bytes >= nsa_topk_workspace_bytes(B, MG, H, NC), NSA_ERR_WORKSPACE,
               "topk: workspace too small");
   Mask m;
-  const int64_t nc_global = mask ? mask->id_base + NC * static_cast<int64_t>(mask->id_stride > 0 ? mask->id_stride : 1) : NC;
-  if ((rc = fill_mask(mask, MG, mask && mask->id_stride > 1 ? nc_global : NC, &m))) return rc;
+  if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
   return run_score_select(q_pooled, q_stride, k_pooled, k_stride, B, MG, H, D, NC, topk, scale, m,
                           out_idx, out_scores, static_cast<float*>(workspace), dtype, s);
 }
 
-extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
-                                   const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H,
-                                   int32_t D, int64_t N, int32_t topk, float scale,
-                                   const nsa_topk_mask* mask, void* k_pooled_out, int32_t* out_idx,
-                                   float* out_scores, void* workspace, size_t workspace_bytes,
-                                   int32_t dtype, void* stream) {
+// Pooling of the raw keys + scoring + selection.  Fused (one pass over K, scores written once) when
+// the operands are 16-bit with a head dim the mma tiles cover; otherwise pooling, scoring and
+// selection run as three kernels.  early_k: see pool_score_kernel.
+static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], const void* k,
+                             const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D, int64_t N,
+                             int32_t topk, float scale, const nsa_topk_mask* mask, void* k_pooled_out,
+                             int32_t* out_idx, float* out_scores, void* workspace, size_t workspace_bytes,
+                             int32_t dtype, int early_k, void* stream) {
   NSA_REQUIRE(mask != nullptr && mask->block_size > 0, NSA_ERR_INVALID, "pool_score_topk: mask / block_size");
   NSA_REQUIRE(N >= 0, NSA_ERR_INVALID, "pool_score_topk: N < 0");
   const int64_t NC = cdiv64(N, mask->block_size);
@@ -650,13 +795,65 @@ extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[
   if (rows == 0 && (NC == 0 || !k_pooled_out)) return NSA_OK;
   NSA_REQUIRE(k_pooled_out != nullptr, NSA_ERR_INVALID, "pool_score_topk: k_pooled_out is null");
   const int64_t ps[3] = {NC * H * D, static_cast<int64_t>(H) * D, D};
-  if (NC > 0) {
-    if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
+  const bool pow2_lanes = D == 16 || D == 32 || D == 64 || D == 128 || D == 256;
+  const bool fused = rows > 0 && NC > 0 && dtype != NSA_F32 && pow2_lanes && NC <= 0x7fffffff && q_pooled && k &&
+                     aligned16(q_pooled) && (q_stride[0] * 2) % 16 == 0 && (q_stride[1] * 2) % 16 == 0 &&
+                     (q_stride[2] * 2) % 16 == 0 && aligned16(k) && (k_stride[0] * 2) % 16 == 0 &&
+                     (k_stride[1] * 2) % 16 == 0 && (k_stride[2] * 2) % 16 == 0;
+  if (!fused) {
+    if (NC > 0) {
+      if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
+    }
+    if (rows == 0) return NSA_OK;
+    if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+    return nsa_topk(q_pooled, q_stride, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx,
+                    out_scores, workspace, workspace_bytes, dtype, stream);
   }
-  if (rows == 0) return NSA_OK;
-  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
-  return nsa_topk(q_pooled, q_stride, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx,
-                  out_scores, workspace, workspace_bytes, dtype, stream);
+  NSA_REQUIRE(workspace && workspace_bytes >= nsa_topk_workspace_bytes(B, MG, H, NC), NSA_ERR_WORKSPACE,
+              "pool_score_topk: workspace too small");
+  Mask m;
+  if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
+  PoolScoreParams p{};
+  p.pool = PoolParams{static_cast<const char*>(k), k_stride[0], k_stride[1], k_stride[2],
+                      static_cast<char*>(k_pooled_out), ps[0], ps[1], ps[2], N, D, mask->block_size};
+  p.q = static_cast<const char*>(q_pooled); p.q_sb = q_stride[0]; p.q_sg = q_stride[1]; p.q_sh = q_stride[2];
+  p.scores = static_cast<float*>(workspace); p.MG = MG; p.H = H; p.NC = NC; p.scale = scale; p.early_k = early_k;
+  rc = dtype == NSA_BF16 ? launch_pool_score<__nv_bfloat16>(p, B, s) : launch_pool_score<__half>(p, B, s);
+  if (rc) return rc;
+  SelectParams sel{};
+  sel.scores = p.scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
+  sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
+  sel.mask = m;
+  return launch_select<false>(sel, rows, s);
+}
+
+extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
+                                   const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H,
+                                   int32_t D, int64_t N, int32_t topk, float scale,
+                                   const nsa_topk_mask* mask, void* k_pooled_out, int32_t* out_idx,
+                                   float* out_scores, void* workspace, size_t workspace_bytes,
+                                   int32_t dtype, void* stream) {
+  return pool_score_select(q_pooled, q_stride, k, k_stride, B, MG, H, D, N, topk, scale, mask, k_pooled_out,
+                           out_idx, out_scores, workspace, workspace_bytes, dtype, 0, stream);
+}
+
+extern "C" int nsa_select_blocks(const void* q, const int64_t q_stride[3], const void* k,
+                                 const int64_t k_stride[3], int32_t B, int64_t M, int32_t H, int32_t D,
+                                 int64_t N, int32_t topk, float scale, const nsa_topk_mask* mask,
+                                 void* q_pooled_out, void* k_pooled_out, int32_t* out_idx, float* out_scores,
+                                 void* workspace, size_t workspace_bytes, int32_t dtype, void* stream) {
+  NSA_REQUIRE(mask != nullptr && mask->q_group_size > 0, NSA_ERR_INVALID, "select_blocks: mask / q_group_size");
+  NSA_REQUIRE(M >= 0 && cdiv64(M, mask->q_group_size) <= 0x7fffffff, NSA_ERR_INVALID, "select_blocks: bad M");
+  NSA_REQUIRE(q_pooled_out != nullptr || M == 0, NSA_ERR_INVALID, "select_blocks: q_pooled_out is null");
+  const int32_t MG = static_cast<int32_t>(cdiv64(M, mask->q_group_size));
+  const int64_t qs[3] = {static_cast<int64_t>(MG) * H * D, static_cast<int64_t>(H) * D, D};
+  int rc;
+  if (M > 0 && (rc = nsa_pool_rows(q, q_stride, q_pooled_out, qs, B, M, H, D, mask->q_group_size, dtype, stream))) return rc;
+  // the kernel in front of the fused one is the query pooling just launched, which releases its
+  // dependents only after its own wait: everything older in the stream, K included, is complete by
+  // the time the fused kernel starts, so it may pool K before it waits for the pooled queries
+  return pool_score_select(q_pooled_out, qs, k, k_stride, B, MG, H, D, N, topk, scale, mask, k_pooled_out, out_idx,
+                           out_scores, workspace, workspace_bytes, dtype, M > 0 ? 1 : 0, stream);
 }
 
 extern "C" int nsa_merge_candidates(const int32_t* idx, const float* scores, int32_t R, int64_t rows,
@@ -730,8 +927,7 @@ extern "C" int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_str
   if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
   NSA_REQUIRE(q_pooled && k_pooled, NSA_ERR_INVALID, "topk_static_scratch: null pointer");
   Mask m;
-  if ((rc = fill_mask(mask, MG, mask && mask->id_stride > 1 ? mask->id_base + NC * static_cast<int64_t>(mask->id_stride) : NC, &m)))
-    return rc;
+  if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
   float* scratch = nullptr;
   if ((rc = nsa::static_scratch_address(&scratch))) return rc;
   // Every score the selection reads is written by the scoring kernel of the same call, so nothing

@@ -50,16 +50,15 @@ def parallel_nsa_topk(
         q = _ops.pool_rows(q, G)
     if causal and not allow_ragged:
         assert chunk_size % block_size == 0
-    rows = q.shape[1]
     if tf_mask:
-        rows_per_chunk = chunk_size // G
-        assert rows % (2 * rows_per_chunk) == 0, (
-            f"tf_mask=True requires T ({rows}) divisible by 2*chunk_size ({2 * rows_per_chunk}); "
-            f"Q must be laid out as [clean | noisy] with equal halves.")
-        kchunk_blocks = chunk_size // block_size
-        assert k.shape[1] % (2 * kchunk_blocks) == 0, (
-            f"tf_mask=True requires TC ({k.shape[1]}) divisible by 2 * (chunk_size_k/block_size) "
-            f"({2 * kchunk_blocks}); K layout must be [clean | noisy] with equal halves.")
+        # teacher forcing: pooled rows and key blocks both come as [clean | noisy] halves of whole
+        # chunks (messages of reference index_topk.py:86-97)
+        for what, have, per_chunk, unit, side in (
+                ("T", q.shape[1], chunk_size // G, "2*chunk_size", "Q must be laid out as"),
+                ("TC", k.shape[1], chunk_size // block_size, "2 * (chunk_size_k/block_size)", "K layout must be")):
+            if have % (2 * per_chunk):
+                raise AssertionError(f"tf_mask=True requires {what} ({have}) divisible by {unit} ({2 * per_chunk}); "
+                                     f"{side} [clean | noisy] with equal halves.")
     sc = scale if scale is not None else K ** -0.5
     return _ops.topk(q, k, block_counts, sc, block_size, chunk_size, chunk_size, causal,
                      ex_win=exclude_window_chunks, ex_sink=exclude_sink_chunks,
@@ -88,9 +87,11 @@ def parallel_nsa_topk_grouped_heads(
                                  chunk_size=chunk_size, causal=causal, group_size=group_size,
                                  tf_mask=tf_mask, **topk_kwargs)
     hpg = H // num_kv_head_groups
-    # head pooling first, then query pooling, each rounded to the input dtype (reference order)
-    q_grouped = q.view(B, T, num_kv_head_groups, hpg, K).mean(dim=3)
-    k_grouped = k.view(B, TC, num_kv_head_groups, hpg, K).mean(dim=3)
+    # head pooling first, then query pooling, each rounded to the input dtype (reference order).
+    # The heads of a group are neighbouring rows of the [B*T*H, K] matrix, so the row-pooling
+    # kernel does it (fp32 sum, one rounding), like the mean over dim 3 of the 5-D view.
+    q_grouped = _ops.pool_rows(q.reshape(1, B * T * H, 1, K), hpg).view(B, T, num_kv_head_groups, K)
+    k_grouped = _ops.pool_rows(k.reshape(1, B * TC * H, 1, K), hpg).view(B, TC, num_kv_head_groups, K)
     idx = parallel_nsa_topk(q=q_grouped, k=k_grouped, block_counts=block_counts, block_size=block_size,
                             chunk_size=chunk_size, causal=causal, group_size=group_size, tf_mask=tf_mask,
                             **topk_kwargs)
@@ -100,10 +101,10 @@ def parallel_nsa_topk_grouped_heads(
 
 def should_use_selection_attention(seq_len, chunk_size, exclude_window_chunks, exclude_sink_chunks,
                                    causal=True):
-    total_chunks = math.ceil(seq_len / chunk_size)
-    if causal:
-        max_visible = total_chunks
-        excluded = min(exclude_sink_chunks, max_visible) + min(exclude_window_chunks, max_visible)
-        return max_visible - excluded > 0
-    excluded = exclude_window_chunks + exclude_sink_chunks
-    return total_chunks - excluded > 0
+    """False when the sink and window exclusions hide every chunk, so the caller can return zeros
+    for the selection branch without a launch (reference index_topk.py:165-176).  Under the causal
+    rule an exclusion cannot hide more chunks than exist; without it the two counts simply add."""
+    n_chunks = math.ceil(seq_len / chunk_size)
+    sink, window = exclude_sink_chunks, exclude_window_chunks
+    hidden = min(sink, n_chunks) + min(window, n_chunks) if causal else sink + window
+    return n_chunks > hidden

@@ -18,39 +18,46 @@ def _debug_checks_enabled() -> bool:
     return os.environ.get("OMNIMEM_NSA_DEBUG", "0") not in ("", "0", "false", "False")
 
 
-def _validate_common(q, k, v, block_indices, block_size, chunk_size, group_size, causal, allow_ragged=False):
+def _fail(kind, text):
+    raise kind(text)
+
+
+def _check_arguments(q, k, v, block_indices, block_size, chunk_size, group_size, causal, allow_ragged):
+    """The reference facade's argument contract (selection/__init__.py:16-44), with its exception
+    types and messages, checked shape first, values last; the id range check costs one host
+    synchronisation, as it does there.  Returns the number of key blocks."""
     B, M, H, D = q.shape
-    N = k.shape[1]
-    G = group_size
-    assert k.shape == (B, N, H, D), f"expected k {(B, N, H, D)}, got {tuple(k.shape)}"
-    assert v.shape == (B, N, H, D), f"expected v {(B, N, H, D)}, got {tuple(v.shape)}"
-    assert D >= 16, f"expected D >= 16, but got {D}"
-    if not allow_ragged:
-        assert M % G == 0, f"M ({M}) must be divisible by group_size ({G})"
-    MG = -(-M // G)
-    assert block_indices.dim() == 4 and block_indices.shape[:3] == (B, MG, H), (
-        f"Expected block_indices {(B, MG, H, '*')}, got {tuple(block_indices.shape)}")
+    N, G = k.shape[1], group_size
+    kv_shape = (B, N, H, D)
+    for name, t in (("k", k), ("v", v)):
+        if tuple(t.shape) != kv_shape:
+            _fail(AssertionError, f"expected {name} {kv_shape}, got {tuple(t.shape)}")
+    if D < 16:
+        _fail(AssertionError, f"expected D >= 16, but got {D}")
+    if M % G and not allow_ragged:
+        _fail(AssertionError, f"M ({M}) must be divisible by group_size ({G})")
+    rows = (M + G - 1) // G
+    if block_indices.dim() != 4 or tuple(block_indices.shape[:3]) != (B, rows, H):
+        _fail(AssertionError, f"Expected block_indices {(B, rows, H, '*')}, got {tuple(block_indices.shape)}")
     if chunk_size <= 0:
-        raise ValueError(f"chunk_size must be > 0, got {chunk_size}")
-    if causal and G > 1 and not allow_ragged:
-        assert chunk_size % G == 0, (
-            f"causal + group requires chunk_size ({chunk_size}) divisible by group_size ({G})")
+        _fail(ValueError, f"chunk_size must be > 0, got {chunk_size}")
+    if causal and G > 1 and chunk_size % G and not allow_ragged:
+        _fail(AssertionError, f"causal + group requires chunk_size ({chunk_size}) divisible by group_size ({G})")
     if block_indices.shape[-1] == 0:
-        raise ValueError("top_idx last dim T must be > 0")
-    num_blocks = math.ceil(N / block_size)
-    valid_mask = block_indices >= 0                     # one host sync per call, as the reference
-    if valid_mask.any() and torch.any(block_indices[valid_mask] >= num_blocks):
-        raise ValueError(
-            f"top_idx out of range: expected in [-1, {num_blocks - 1}] "
-            f"but got [{block_indices.min()}, {block_indices.max()}]")
-    return num_blocks
+        _fail(ValueError, "top_idx last dim T must be > 0")
+    n_blocks = math.ceil(N / block_size)
+    if block_indices.numel():
+        lo, hi = (int(x) for x in torch.aminmax(block_indices))
+        if hi >= n_blocks:
+            _fail(ValueError, f"top_idx out of range: expected in [-1, {n_blocks - 1}] but got [{lo}, {hi}]")
+    return n_blocks
 
 
-def _debug_check_unique(block_indices):
-    ids = block_indices.to(torch.int64)
-    sorted_ids, _ = ids.sort(dim=-1)
-    dup = (sorted_ids[..., 1:] == sorted_ids[..., :-1]) & (sorted_ids[..., 1:] >= 0)
-    if dup.any():
+def _check_no_duplicates(block_indices):
+    """OMNIMEM_NSA_DEBUG: a row must not list a valid block twice (selection/__init__.py:47-53)."""
+    ordered = block_indices.to(torch.int64).sort(dim=-1).values
+    same = ordered.diff(dim=-1) == 0
+    if bool((same & (ordered[..., 1:] >= 0)).any()):
         raise ValueError("duplicate valid block ids within a row are not allowed (OMNIMEM_NSA_DEBUG)")
 
 
@@ -91,17 +98,21 @@ def selection_attention(q, k, v, block_indices, block_count, block_size, chunk_s
 
     ``variant``, ``allow_tf32`` and ``bwd_method`` are validated like the reference and
     otherwise ignored: there is one forward and one (atomics-free) backward."""
-    if variant not in ('one-pass', 'two-pass'):
-        raise ValueError(f"Invalid variant: {variant!r}, expected 'one-pass' or 'two-pass'")
-    if group_size < 1:
-        raise ValueError(f"Invalid group_size: {group_size}, expected >= 1")
-    if variant == 'one-pass':
-        raise NotImplementedError(f"{variant=} is not supported")
-    if bwd_method not in ('auto', 'mask', 'inverted'):
-        raise ValueError(f"Unknown bwd_method '{bwd_method}', expected 'auto', 'inverted' or 'mask'")
-    _validate_common(q, k, v, block_indices, block_size, chunk_size, group_size, causal, allow_ragged)
+    # option checks in the reference's order, with its exception types and messages (:70-77)
+    problems = (
+        (variant not in ('one-pass', 'two-pass'), ValueError,
+         f"Invalid variant: {variant!r}, expected 'one-pass' or 'two-pass'"),
+        (group_size < 1, ValueError, f"Invalid group_size: {group_size}, expected >= 1"),
+        (variant == 'one-pass', NotImplementedError, f"{variant=} is not supported"),
+        (bwd_method not in ('auto', 'mask', 'inverted'), ValueError,
+         f"Unknown bwd_method '{bwd_method}', expected 'auto', 'inverted' or 'mask'"),
+    )
+    for bad, kind, text in problems:
+        if bad:
+            _fail(kind, text)
+    _check_arguments(q, k, v, block_indices, block_size, chunk_size, group_size, causal, allow_ragged)
     if _debug_checks_enabled():
-        _debug_check_unique(block_indices)
+        _check_no_duplicates(block_indices)
     if block_indices.dtype != torch.int32:
         block_indices = block_indices.to(torch.int32)
     return SelectionAttentionB200.apply(q, k, v, block_indices, block_size, chunk_size, scale, causal,

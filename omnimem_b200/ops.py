@@ -135,6 +135,37 @@ def pool_score_topk(q_pooled: torch.Tensor, k: torch.Tensor, topk: int, scale: f
     return (out, kp, scores) if return_scores else (out, kp)
 
 
+def select_blocks(q: torch.Tensor, k: torch.Tensor, topk: int, scale: float, block_size: int, group_size: int,
+                  chunk_size: int, chunk_size_k: int, causal: bool, ex_win: int = 0, ex_sink: int = 0,
+                  prog_excl: bool = False, tf_mask: bool = False, q_chunk_offset: int = 0,
+                  return_scores: bool = False):
+    """Block selection from the raw tensors in one call: q [B,M,H,D] pooled per query group, k
+    [B,N,H,D] pooled per key block and scored in the same pass, top-k per (group, head).
+    Returns (idx int32 [B,MG,H,topk], q_pooled, k_pooled[, scores])."""
+    _require_cuda(q, k)
+    if q.dtype != k.dtype:
+        raise NSABackendError(f"select_blocks: q and k must share a dtype, got {q.dtype} vs {k.dtype}")
+    B, M, H, D = q.shape
+    N = k.shape[1]
+    q, k = _rows16(q), _rows16(k)
+    MG = (M + group_size - 1) // group_size
+    NC = (N + block_size - 1) // block_size
+    dev = k.device
+    qp = torch.empty(B, MG, H, D, dtype=q.dtype, device=dev)
+    kp = torch.empty(B, NC, H, D, dtype=k.dtype, device=dev)
+    out = torch.empty(B, MG, H, topk, dtype=torch.int32, device=dev)
+    scores = torch.empty(B, MG, H, topk, dtype=torch.float32, device=dev) if return_scores else None
+    m = _mask(block_size, chunk_size, chunk_size_k, group_size, q_chunk_offset, ex_win, ex_sink,
+              causal, tf_mask, prog_excl)
+    with torch.cuda.device(dev):
+        wsb = _lib.load().nsa_topk_workspace_bytes(B, MG, H, NC)
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+        call("nsa_select_blocks", q.data_ptr(), strides3(q), k.data_ptr(), strides3(k), B, M, H, D, N,
+             _i32(topk, "topk"), float(scale), C.byref(m), qp.data_ptr(), kp.data_ptr(), out.data_ptr(),
+             _ptr(scores), ws.data_ptr(), wsb, _dtype(k), _stream(k))
+    return (out, qp, kp, scores) if return_scores else (out, qp, kp)
+
+
 def merge_candidates(idx: torch.Tensor, scores: torch.Tensor, topk: int):
     """idx / scores [R, ..., T] (global ids, -1 = none) -> merged ([..., topk], [..., topk])."""
     _require_cuda(idx, scores)
@@ -214,12 +245,17 @@ class PtrKV:
 
 # ------------------------------------------------------------------------- selection attention
 def sel_fwd(q: torch.Tensor, kv, block_indices: Optional[torch.Tensor], block_size: int,
-            chunk_size: int, scale: float, causal: bool, group_size: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(out [B,M,H,D] in q.dtype, lse fp32 [B,H,M])."""
+            chunk_size: int, scale: float, causal: bool, group_size: int,
+            out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(out [B,M,H,D] in q.dtype, lse fp32 [B,H,M]).  `out` may be given: a [B,M,H,D] tensor or
+    view (innermost stride 1, 16-byte aligned rows) that the kernel writes in place."""
     _require_cuda(q, block_indices)
     B, M, H, D = q.shape
     q = _rows16(q)
-    out = torch.empty(B, M, H, D, dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty(B, M, H, D, dtype=q.dtype, device=q.device)
+    elif out.shape != q.shape or out.dtype != q.dtype or _rows16(out) is not out:
+        raise NSABackendError("sel_fwd: `out` must have q's shape and dtype, unit innermost stride and 16-byte aligned rows")
     lse = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
     table = kv.ptr_k if isinstance(kv, PtrKV) else block_indices
     if table.dim() != 4:
@@ -295,6 +331,26 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor):
     return out, lse
 
 
+def packed_row_elems(H: int, D: int) -> int:
+    """Elements (of a 16-bit dtype) of one packed row: H*D outputs, H fp32 log-sum-exps, and padding
+    to a multiple of 16 bytes."""
+    return (H * D + 2 * H + 7) // 8 * 8
+
+
+def merge_packed_rows(parts: torch.Tensor, H: int, D: int) -> torch.Tensor:
+    """parts [R, rows, packed_row_elems(H, D)] (16-bit dtype; elements [H*D, H*D + 2*H) of a row are
+    H fp32 log-sum-exps) -> merged [rows, ...] in the same format: attention partials over disjoint
+    key sets merged exactly, row by row."""
+    _require_cuda(parts)
+    if parts.dim() != 3 or parts.shape[-1] != packed_row_elems(H, D) or not parts.is_contiguous():
+        raise NSABackendError("merge_packed_rows: parts must be contiguous [R, rows, packed_row_elems(H, D)]")
+    R, rows, _ = parts.shape
+    merged = torch.empty(rows, parts.shape[-1], dtype=parts.dtype, device=parts.device)
+    with torch.cuda.device(parts.device):
+        call("nsa_merge_packed_rows", parts.data_ptr(), R, rows, H, D, merged.data_ptr(), _dtype(parts), _stream(parts))
+    return merged
+
+
 def build_ptr_table(block_indices, base_k, base_v, n_blocks_per_head, batch_stride: int,
                     blocks_per_chunk: int, in_chunk_block_bytes: int):
     """Block id -> int64 byte address tables (0 = invalid / not resident)."""
@@ -356,7 +412,7 @@ def dedup_run(block_indices_flat: torch.Tensor, stamp: torch.Tensor, out: torch.
         ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
         call("nsa_cache_dedup_touch", block_indices_flat.data_ptr(), block_indices_flat.numel(), heads, t, mb,
              bpc, stamp.data_ptr(), _i32(epoch, "epoch"), None, None, 0, out.data_ptr(), None, _i32(cap, "cap"),
-             ws.data_ptr(), wsb, _stream(stamp))
+             None, ws.data_ptr(), wsb, _stream(stamp))
 
 
 def sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: int, scale: float,

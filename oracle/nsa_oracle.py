@@ -531,9 +531,10 @@ def dedup_keys(block_indices: torch.Tensor, heads: int, mb: int) -> torch.Tensor
 class EpochLRUPagePool:
     """Host model of the device page pool's policy, page ids included, for parity tests of
     the cache kernels.  The LRU clock is an epoch counter bumped once per append / touch call;
-    victims are the owned, unprotected pages not stamped in the current epoch, in ascending
-    (stamp, page id) order.  With one key touched per epoch this is exactly the OrderedDict
-    LRU of cache.py:673-699 (`LRUBlockCacheModel`)."""
+    a page for a new or returning block is a free page (lowest id first) or, when none is free,
+    the owned, unprotected page not stamped in the current epoch with the lowest (stamp, page id).
+    With one key touched per epoch and one pool per head this is exactly the OrderedDict LRU of
+    cache.py:673-699 (`LRUBlockCacheModel`); tests replay the reference's own trace through it."""
 
     def __init__(self, num_heads: int, num_pages: int, max_blocks: int, page_tokens: int,
                  protect_blocks: int = 0):
@@ -544,18 +545,21 @@ class EpochLRUPagePool:
         self.stamp = [0] * num_pages
         self.n_tokens = 0
         self.epoch = 0
-        self.used = 0
         self.host = set()               # keys whose K/V were saved to the host tier
         self.evicted_any = False
+        self.hits = self.misses = self.pages_evicted = self.pages_fetched = 0
+        self.last_evicted = []          # keys evicted by the latest call
 
     @property
     def n_blocks(self):
         return -(-self.n_tokens // self.PT)
 
-    def _victims(self, n):
-        protect_from = max(self.n_blocks - self.protect, 0)
-        cand = [(self.stamp[p], p) for p in range(self.P)
-                if self.owner[p] >= 0 and self.owner[p] % self.MB < protect_from and self.stamp[p] < self.epoch]
+    def _victims(self, n, protect_from=None):
+        if protect_from is None:
+            protect_from = max(self.n_blocks - self.protect, 0)
+        cand = [(0, p) for p in range(self.P) if self.owner[p] < 0]
+        cand += [(self.stamp[p] + 1, p) for p in range(self.P)
+                 if self.owner[p] >= 0 and self.owner[p] % self.MB < protect_from and self.stamp[p] < self.epoch]
         cand.sort()
         out = [p for _, p in cand[:n]]
         return out + [-1] * (n - len(out))
@@ -566,25 +570,49 @@ class EpochLRUPagePool:
                 continue
             key = self.owner[p]
             self.host.add(key)
+            self.last_evicted.append(key)
+            self.pages_evicted += 1
             del self.table[key]
             self.owner[p] = -1
+
+    def _make_resident(self, uniq, count, protect_from=None):
+        miss = [k for k in uniq if k not in self.table]
+        if count:
+            self.hits += len(uniq) - len(miss)
+            self.misses += len(miss)
+        for k in uniq:
+            if k in self.table:
+                self.stamp[self.table[k]] = self.epoch
+        if self.evicted_any and miss:
+            v = self._victims(len(miss), protect_from)
+            self._evict(v)
+            for k, p in zip(miss, v):
+                if p < 0:
+                    continue
+                self.table[k] = p
+                self.owner[p] = k
+                self.stamp[p] = self.epoch
+                self.pages_fetched += 1
+        return miss
 
     def append(self, S, pos0=None):
         pos0 = self.n_tokens if pos0 is None else pos0
         first, last = pos0 // self.PT, (pos0 + S - 1) // self.PT
         n_touched = last - first + 1
         n_new = max(0, last + 1 - self.n_blocks)
+        n_exist = n_touched - n_new
         self.epoch += 1
+        self.last_evicted = []
+        protect_from = max(min(first, self.n_blocks - self.protect), 0)
+        if n_exist and self.evicted_any:
+            keys = sorted(h * self.MB + bid for h in range(self.H) for bid in range(first, first + n_exist))
+            self._make_resident(keys, False, protect_from)
         ids = []
         need = n_new * self.H
         if need:
-            fresh = min(need, self.P - self.used)
-            ids += list(range(self.used, self.used + fresh))
-            self.used += fresh
-            if need > fresh:
-                v = self._victims(need - fresh)
-                self._evict(v)
-                ids += v
+            ids = self._victims(need, protect_from)
+            self._evict(ids)
+            if self.n_blocks * self.H + need > self.P:
                 self.evicted_any = True
         for h in range(self.H):
             for j in range(n_touched):
@@ -592,7 +620,7 @@ class EpochLRUPagePool:
                 key = h * self.MB + bid
                 page = self.table.get(key, -1)
                 if page < 0:
-                    jn = j - (n_touched - n_new)
+                    jn = j - n_exist
                     page = ids[h * n_new + jn] if jn >= 0 else -1
                     if page >= 0:
                         self.table[key] = page
@@ -601,21 +629,15 @@ class EpochLRUPagePool:
                     self.stamp[page] = self.epoch
         self.n_tokens = max(self.n_tokens, pos0 + S)
 
+    def evict_all(self):
+        self.last_evicted = []
+        self._evict(list(range(self.P)))
+        self.evicted_any = True
+
     def touch(self, block_indices):
         """block_indices [1,MG,H,T]; returns (unique keys, missing keys), both ascending."""
         self.epoch += 1
+        self.last_evicted = []
         uniq = [int(x) for x in dedup_keys(block_indices, self.H, self.MB).tolist()]
-        miss = [k for k in uniq if k not in self.table]
-        for k in uniq:
-            if k in self.table:
-                self.stamp[self.table[k]] = self.epoch
-        if self.evicted_any and miss:
-            v = self._victims(len(miss))
-            self._evict(v)
-            for k, p in zip(miss, v):
-                if p < 0:
-                    continue
-                self.table[k] = p
-                self.owner[p] = k
-                self.stamp[p] = self.epoch
+        miss = self._make_resident(uniq, True)
         return uniq, miss

@@ -16,6 +16,18 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_terminal_summary(terminalreporter):
+    """One line per output / gradient comparison of the run: the measured errors beside the limits."""
+    from tests.helpers import PARITY_LOG
+    if not PARITY_LOG:
+        return
+    tr = terminalreporter
+    tr.section("measured parity errors (max abs / mean abs vs limit; largest reference magnitude)")
+    for what, mx, mean, ref, lim_max, lim_mean in PARITY_LOG:
+        tr.write_line(f"PARITY {what}: max_abs {mx:.3e} (limit {lim_max:.1e})  mean_abs {mean:.3e} "
+                      f"(limit {lim_mean:.1e})  max|ref| {ref:.3g}")
+
+
 def load_golden(name):
     """Load tests/golden/<name>.npz; keys ending in _bf16 hold bf16 bit patterns and are
     returned as torch.bfloat16 tensors under the key without the suffix."""

@@ -138,6 +138,25 @@ def case_rope(ref_root):
     return out
 
 
+def case_early_out(ref_root):
+    """Truth table of should_use_selection_attention (nsa/ops/index_topk.py:165-176) over a grid of
+    sequence lengths (in tokens, chunk 10: whole and ragged chunk counts) and exclusion counts."""
+    import math
+    path = os.path.join(ref_root, "src", "omnimem", "nsa", "ops", "index_topk.py")
+    src = open(path).read()
+    body = src[src.index("def should_use_selection_attention("):]
+    ns = {"math": math}
+    exec(body, ns)
+    fn = ns["should_use_selection_attention"]
+    rows = []
+    for seq_len in (1, 9, 10, 11, 20, 35, 40, 70):
+        for ex_win in range(0, 5):
+            for ex_sink in range(0, 4):
+                for causal in (False, True):
+                    rows.append([seq_len, 10, ex_win, ex_sink, int(causal), int(bool(fn(seq_len, 10, ex_win, ex_sink, causal)))])
+    return {"table": np.array(rows, dtype=np.int64)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (its src/ is imported)")
@@ -163,6 +182,7 @@ def main():
                                           3, 32, 16, 64, False)
     out["lru"] = case_lru(MMCache, 17, 3, 4, 9, 200)
     out["rope"] = case_rope(args.reference)
+    out["early_out"] = case_early_out(args.reference)
     for name, d in out.items():
         path = os.path.join(HERE, f"{name}.npz")
         np.savez_compressed(path, **d)

@@ -29,8 +29,29 @@ def merge_candidates(idx, scores, topk):
     return O.merge_candidates(list(idx), list(scores), topk)
 
 
-def sel_fwd(q, kv, block_indices, block_size, chunk_size, scale, causal, group_size):
-    return O.selection_fwd(q, kv.k, kv.v, block_indices, block_size, chunk_size, scale, causal, group_size)
+def sel_fwd(q, kv, block_indices, block_size, chunk_size, scale, causal, group_size, out=None):
+    o, lse = O.selection_fwd(q.float(), kv.k.float(), kv.v.float(), block_indices, block_size, chunk_size, scale,
+                             causal, group_size)
+    if out is not None:
+        out.copy_(o)
+        return out, lse
+    return o.to(q.dtype), lse
+
+
+def packed_row_elems(H, D):
+    return (H * D + 2 * H + 7) // 8 * 8
+
+
+def merge_packed_rows(parts, H, D):
+    """[R, rows, H*D + 2*H] packed rows (16-bit outputs, fp32 log-sum-exps in the tail) -> [rows, ...]."""
+    R, rows, _ = parts.shape
+    outs = [parts[r, :, :H * D].reshape(1, rows, H, D).float() for r in range(R)]
+    lses = [parts[r, :, H * D:H * D + 2 * H].contiguous().view(torch.float32).t().unsqueeze(0) for r in range(R)]
+    out, lse = O.merge_partials(outs, lses)
+    merged = torch.empty(rows, parts.shape[-1], dtype=parts.dtype)
+    merged[:, :H * D] = out.reshape(rows, H * D).to(parts.dtype)
+    merged[:, H * D:H * D + 2 * H].view(torch.float32).copy_(lse[0].t())
+    return merged
 
 
 def merge_partials(outs, lses):

@@ -212,6 +212,113 @@ def test_lru_eviction_and_fetch_follow_the_policy_model(dev):
     assert model.evicted_any and len(model.host) > 0
 
 
+def test_block_cache_replays_the_reference_lru_trace(dev, golden):
+    """The device cache against the reference itself: the trace of MMCache.lru_touch_per_head
+    (models/cache.py:673-699; tests/golden/lru.npz) replayed through BlockKVCache.touch, one
+    (head, block) id per call, one pool of `cap` pages per head, every block starting in the host
+    tier.  The block each touch evicts, the final LRU order, the hit count and the data that comes
+    back from the host tier must be the reference's."""
+    d = golden("lru")
+    heads, cap, n_ids, n_touch = d["meta"].tolist()
+    g = torch.Generator().manual_seed(8)
+    caches, data = [], []
+    for _ in range(heads):
+        c = _mk(dev, H=1, D=128, pages=cap, max_blocks=n_ids, pt=64, host_tier=True)
+        K = torch.randn(n_ids * 64, 1, 128, generator=g).to(torch.bfloat16)
+        for b in range(n_ids):
+            c.append(K[b * 64:(b + 1) * 64].to(dev), K[b * 64:(b + 1) * 64].to(dev))
+        c.evict_all()
+        c.counters.zero_()
+        assert int((c.block_table >= 0).sum()) == 0
+        caches.append(c)
+        data.append(K)
+    for (h, cid), ev in zip(d["trace"].tolist(), d["evicted"].tolist()):
+        c = caches[h]
+        before = set(torch.nonzero(c.block_table[0] >= 0).view(-1).tolist())
+        c.touch(torch.tensor([[[[cid]]]], dtype=torch.int32, device=dev))
+        after = set(torch.nonzero(c.block_table[0] >= 0).view(-1).tolist())
+        gone = sorted(before - after)
+        assert gone == ([ev] if ev >= 0 else []), f"touch ({h}, {cid}) evicted {gone}, the reference evicted {ev}"
+        assert cid in after
+    hits = 0
+    for h, c in enumerate(caches):
+        c.check_status()
+        order = [x for x in d["final_order"][h].tolist() if x >= 0]
+        tab, st = c.block_table[0].cpu(), c.page_stamp.cpu()
+        resident = sorted((b for b in range(n_ids) if tab[b] >= 0), key=lambda b: int(st[tab[b]]))
+        assert resident == order
+        for b in resident:                       # the pages hold what was appended, back from the host
+            assert torch.equal(c.k_pool[int(tab[b])].cpu(), data[h][b * 64:(b + 1) * 64, 0])
+        s = c.stats()
+        hits += s["hits"]
+        assert s["pages_fetched"] == s["misses"] and s["bytes_from_host"] == s["misses"] * 2 * 64 * 128 * 2
+    assert hits == int(d["hits"][0])
+
+
+def _block_of(cache, K, h, b):
+    """K rows of block b of head h as the cache holds them (the block must be resident)."""
+    page = int(cache.block_table[h, b])
+    assert page >= 0
+    return cache.k_pool[page].cpu()
+
+
+def test_rewrite_of_an_evicted_partly_filled_block_keeps_its_rows(dev):
+    """A tiny pool: the tail block is evicted by a selection, then an append rewrites part of it.
+    The block comes back from the host tier first, keeps the rows the append does not cover, is
+    not chosen as a victim for the call's own pages, and its pooled key covers every row it holds."""
+    g = torch.Generator().manual_seed(21)
+    H, D, PT, MB, P = 2, 128, 64, 16, 8
+    cache = _mk(dev, H=H, D=D, pages=P, max_blocks=MB, pt=PT, host_tier=True)
+    model = O.EpochLRUPagePool(H, P, MB, PT)
+    K = torch.randn(MB * PT, H, D, generator=g).to(torch.bfloat16)
+
+    def same_state():
+        tab = cache.block_table.cpu().view(-1)
+        for key in range(H * MB):
+            assert int(tab[key]) == model.table.get(key, -1), f"key {key}"
+        assert cache.page_owner.cpu().tolist() == model.owner
+
+    def ids_of(blocks):
+        return torch.tensor(blocks, dtype=torch.int32).view(1, 1, 1, -1).expand(1, 1, H, -1).contiguous()
+
+    cache.append(K[:256].to(dev), K[:256].to(dev)); model.append(256)            # blocks 0-3: pool full
+    cache.append(K[256:356].to(dev), K[256:356].to(dev)); model.append(100)      # blocks 4, 5 (36 rows): evicts 0, 1
+    same_state()
+    for blocks in ([0, 2], [0, 1, 3]):                                           # the second one evicts blocks 4 and 5
+        cache.touch(ids_of(blocks).to(dev)); model.touch(ids_of(blocks))
+        same_state()
+    assert int(cache.block_table[0, 5]) < 0 and int(cache.block_table[1, 5]) < 0
+    # rewrite tokens 330..379: rows 10..59 of block 5, whose rows 0..9 live in the host tier
+    new = torch.randn(50, H, D, generator=g).to(torch.bfloat16)
+    cache.append(new.to(dev), new.to(dev), pos0=330); model.append(50, 330)
+    same_state()
+    cache.check_status()
+    want = torch.cat([K[320:330], new])                                          # 60 rows of block 5
+    for h in range(H):
+        got = _block_of(cache, K, h, 5)
+        assert torch.equal(got[:60], want[:, h]), "rows of the rewritten block"
+    pooled = O.pool_rows(want.unsqueeze(0), 64)[0, 0]                            # [H, D] mean of the 60 rows
+    got = cache.k_pooled[:, 5].cpu()
+    assert ((got.float() - pooled.float()).abs() <= 2 ** -7 * pooled.float().abs() + 1e-6).all()
+    # a rewrite that ends inside the block leaves the pooled key over all 60 rows
+    new2 = torch.randn(5, H, D, generator=g).to(torch.bfloat16)
+    cache.append(new2.to(dev), new2.to(dev), pos0=325); model.append(5, 325)
+    want[5:10] = new2
+    pooled = O.pool_rows(want.unsqueeze(0), 64)[0, 0]
+    got = cache.k_pooled[:, 5].cpu()
+    assert ((got.float() - pooled.float()).abs() <= 2 ** -7 * pooled.float().abs() + 1e-6).all()
+    # every other block still holds its data: bring them back one at a time
+    for b in range(5):
+        cache.touch(ids_of([b]).to(dev)); model.touch(ids_of([b]))
+        for h in range(H):
+            assert torch.equal(_block_of(cache, K, h, b), K[b * PT:(b + 1) * PT, h]), f"block {b}"
+    same_state()
+    cache.check_status()
+    s = cache.stats()
+    assert (s["hits"], s["misses"], s["pages_evicted"], s["pages_fetched"]) == (
+        model.hits, model.misses, model.pages_evicted, model.pages_fetched)
+
+
 def ops_sel(cache, q, ids):
     from omnimem_b200 import ops
     return ops.sel_fwd(q, cache.kv_source(), ids, cache.page_tokens, 1, q.shape[-1] ** -0.5, False, 64)

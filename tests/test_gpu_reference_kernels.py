@@ -1,0 +1,73 @@
+"""The reference's own CUDA operators, rebuilt for sm_100a, as second judge: top-k ids, selection
+forward and backward of this library against torch.ops.omnimem_nsa.{topk, sel_fwd, sel_bwd} of the
+reference (src/omnimem/nsa/cuda_backend/csrc) on the same seeded inputs, at geometries the
+reference accepts.  The reference library runs in a child process (both register the same
+operator names); the tests skip where the prebuilt library is absent."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from oracle import ref_cuda_runner as R
+from tests.helpers import assert_close_bf16, assert_topk_parity, grad_max_abs, masked_scores
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _reference_outputs(case):
+    if not R.available():
+        pytest.skip("oracle/_ref/omnimem_nsa_ref.so is not built (python -m oracle.build_ref)")
+    with tempfile.TemporaryDirectory() as tmp:
+        out = os.path.join(tmp, "ref.pt")
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "ref_cuda_runner.py"), "--case", case, "--out", out],
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, f"reference operators failed on {case}:\n{r.stdout[-2000:]}\n{r.stderr[-2000:]}"
+        return torch.load(out)
+
+
+@pytest.mark.parametrize("case", ["small_6464", "small_3015", "full_causal_6464", "divisible_6464", "native_3015"])
+def test_against_the_reference_cuda_operators(dev, case):
+    from omnimem_b200 import ops
+    ref = _reference_outputs(case)
+    c, q, k, v, do = R.make_case(case)
+    B, M, N, H, D, T, bs, G = (c[x] for x in ("B", "M", "N", "H", "D", "T", "bs", "G"))
+    scale = D ** -0.5
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, do))
+    # pooled operands: the kernel's means are the torch expressions' means
+    qp, kp = ops.pool_rows(qd, G), ops.pool_rows(kd, bs)
+    assert torch.equal(qp.cpu(), ref["q_pooled"]) and torch.equal(kp.cpu(), ref["k_pooled"])
+    # ids: exact except where a score lies within the tie band of the k-th score; both lists in
+    # (score desc, id asc) order with -1 padding
+    idx, *_ = ops.select_blocks(qd, kd, T, scale, bs, G, c["chunk"], c["chunk"], c["causal"], ex_win=c["ex_win"],
+                                ex_sink=c["ex_sink"], prog_excl=c["prog"], q_chunk_offset=c["q_off"])
+    mask_kw = dict(block_size=bs, chunk_size=c["chunk"], chunk_size_k=c["chunk"], causal=c["causal"],
+                   ex_win=c["ex_win"], ex_sink=c["ex_sink"], prog_excl=c["prog"], q_chunk_offset=c["q_off"],
+                   q_group_size=G)
+    s = masked_scores(ref["q_pooled"], ref["k_pooled"], scale, **mask_kw)
+    differing = assert_topk_parity(idx, s, T)
+    differing_ref = assert_topk_parity(ref["idx"], s, T)
+    rows = B * (M // G) * H
+    same_rows = (idx.cpu() == ref["idx"]).all(-1).float().mean().item()
+    print(f"PARITY-IDS {case}: rows {rows}, identical to the reference {same_rows:.4f}, rows with a tie-band "
+          f"difference vs the exact scores: ours {differing}, reference {differing_ref}")
+    assert same_rows >= 0.97
+    # attention on the REFERENCE's ids, so that forward and backward are compared on identical work
+    ids = ref["idx"].to(dev)
+    a_chunk, a_causal = (c["chunk"], True) if c.get("attn_causal") else (1, False)
+    out, lse = ops.sel_fwd(qd, ops.DenseKV(kd, vd), ids, bs, a_chunk, scale, a_causal, G)
+    assert_close_bf16(out, ref["out"], f"{case} out vs reference CUDA")
+    fin = torch.isfinite(ref["lse"])
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    assert torch.allclose(lse.cpu()[fin], ref["lse"][fin], atol=2e-3, rtol=1e-4)
+    # backward from the reference's out / lse, as its autograd function does
+    dq, dk, dv = ops.sel_bwd(qd, ops.DenseKV(kd, vd), ids, ref["out"].to(dev), ref["lse"].to(dev), dod, bs, a_chunk,
+                             scale, a_causal, G)
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert_close_bf16(got, ref[name], f"{case} {name} vs reference CUDA", max_abs=2 * grad_max_abs(ref[name].float()),
+                          mean_abs=4e-3)

@@ -69,6 +69,40 @@ def test_world_size_one(dev):
         dist.destroy_process_group()
 
 
+def test_without_a_process_group(dev):
+    """No torch.distributed initialised: one rank, no exchange (the N=1 point of the config-5 leg)."""
+    from omnimem_b200 import ops
+    from omnimem_b200.sharded import ShardedSelection
+    q, k, v = _case(seed=6)
+    sh = ShardedSelection()
+    assert (sh.rank, sh.world) == (0, 1)
+    out, lse, idx = sh.forward(q.to(dev), k.to(dev), v.to(dev), 8, 64, 64, 100, True, q_chunk_offset=30)
+    want, _, _ = ops.select_blocks(q.to(dev), k.to(dev), 8, 128 ** -0.5, 64, 64, 100, 100, True, q_chunk_offset=30)
+    assert torch.equal(idx, want)
+    o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), idx.cpu(), 64, 1, None, False, 64)
+    assert_close_bf16(out, o_ref, "single rank out")
+
+
+def test_packed_row_merge_equals_the_plain_merge(dev):
+    """The merge over packed rows (a token's H x D outputs followed by its H log-sum-exps), which the
+    row-split exchange uses, against nsa_merge_partials on the same partials: bit for bit."""
+    from omnimem_b200 import ops
+    g = torch.Generator().manual_seed(7)
+    R, M, H, D = 5, 77, 3, 128
+    outs = torch.randn(R, 1, M, H, D, generator=g).to(torch.bfloat16).to(dev)
+    lses = torch.randn(R, 1, H, M, generator=g).to(dev)
+    lses[1, :, :, ::3] = float("-inf")
+    lses[:, :, 1, 5] = float("-inf")                     # a row no part has seen
+    want_o, want_l = ops.merge_partials(outs, lses)
+    row = ops.packed_row_elems(H, D)
+    packed = torch.empty(R, M, row, dtype=torch.bfloat16, device=dev)
+    packed[:, :, :H * D] = outs.view(R, M, H * D)
+    packed[:, :, H * D:H * D + 2 * H].view(torch.float32).copy_(lses[:, 0].transpose(1, 2))
+    merged = ops.merge_packed_rows(packed, H, D)
+    assert torch.equal(merged[:, :H * D].view(1, M, H, D), want_o)
+    assert torch.equal(merged[:, H * D:H * D + 2 * H].view(torch.float32).t().unsqueeze(0), want_l)
+
+
 def test_nccl_ranks_match_single_device():
     world = min(torch.cuda.device_count(), 4)
     if world < 2:

@@ -174,6 +174,80 @@ def test_pool_score_topk_equals_two_step(dev):
     assert torch.equal(kp, kp2) and torch.equal(idx, idx2) and torch.equal(sc, sc2)
 
 
+@pytest.mark.parametrize("case", [
+    # M, N, H, D, block, group, topk, chunk, causal, q_off, dtype
+    (4680, 32760, 12, 128, 64, 64, 16, 1560, True, 18, torch.bfloat16),    # the Wan layer shape, ragged tails
+    (300, 1000, 3, 64, 30, 15, 16, 300, True, 2, torch.bfloat16),          # reference-native 30/15 blocks, D=64
+    (130, 64 * 21 + 5, 2, 128, 64, 64, 4, 64, False, 0, torch.float16),    # fp16, 22 key blocks: a short last tile
+    (70, 900, 2, 256, 64, 64, 3, 10 ** 6, False, 0, torch.bfloat16),       # D=256
+    (64, 64 * 3, 1, 32, 64, 1, 2, 64, True, 2, torch.bfloat16),            # one query per row, three key blocks
+])
+def test_fused_pool_score_select_equals_the_separate_kernels(dev, case):
+    """The fused kernel (keys pooled and scored in one pass) and the whole-selection entry point
+    (queries pooled too) against pool_rows + topk: pooled operands, ids and scores bit for bit."""
+    M, N, H, D, bs, G, T, chunk, causal, q_off, dtype = case
+    g = torch.Generator().manual_seed(M + N)
+    q = torch.randn(1, M, H, D, generator=g).to(dtype).to(dev)
+    k = torch.randn(1, N, H, D, generator=g).to(dtype).to(dev)
+    ops = _ops()
+    qp = ops.pool_rows(q, G) if G > 1 else q
+    kp = ops.pool_rows(k, bs)
+    want_i, want_s = ops.topk(qp, kp, T, D ** -0.5, bs, chunk, chunk, causal, q_chunk_offset=q_off, q_group_size=G,
+                              return_scores=True)
+    idx, kp2, sc = ops.pool_score_topk(qp, k, T, D ** -0.5, bs, chunk, chunk, causal, q_chunk_offset=q_off,
+                                       q_group_size=G, return_scores=True)
+    assert torch.equal(kp2, kp), "pooled keys of the fused kernel"
+    assert torch.equal(idx, want_i) and torch.equal(sc, want_s)
+    idx, qp3, kp3, sc = ops.select_blocks(q, k, T, D ** -0.5, bs, G, chunk, chunk, causal, q_chunk_offset=q_off,
+                                          return_scores=True)
+    assert torch.equal(qp3, qp) and torch.equal(kp3, kp)
+    assert torch.equal(idx, want_i) and torch.equal(sc, want_s)
+    # strided keys (a slice of a wider tensor): rows stay 16-byte aligned, no copy is made
+    wide = torch.randn(1, N, H, 2 * D, generator=torch.Generator().manual_seed(3)).to(dtype).to(dev)
+    wide[..., :D] = k
+    idx, _, kp4 = ops.select_blocks(q, wide[..., :D], T, D ** -0.5, bs, G, chunk, chunk, causal, q_chunk_offset=q_off)
+    assert torch.equal(kp4, kp) and torch.equal(idx, want_i)
+
+
+def test_tf_mask_is_rejected_for_sharded_ids(dev):
+    from omnimem_b200 import NSABackendError
+    q = torch.randn(1, 8, 2, 64).to(torch.bfloat16).to(dev)
+    k = torch.randn(1, 8, 2, 64).to(torch.bfloat16).to(dev)
+    with pytest.raises(NSABackendError, match="tf_mask"):
+        _ops().topk(q, k, 2, 1.0, 8, 16, 16, True, tf_mask=True, id_base=1, id_stride=3)
+
+
+def test_head_group_pooling_before_selection(dev):
+    """num_kv_head_groups < H: heads are averaged per group first (rounded to the input dtype), the
+    queries per group second, and every head of a group receives the group's ids
+    (nsa/ops/index_topk.py:108-162)."""
+    from omnimem_b200.nsa.ops import parallel_nsa_topk, parallel_nsa_topk_grouped_heads
+    g = torch.Generator().manual_seed(13)
+    B, M, NC, H, D, G, T, NG = 2, 256, 40, 12, 128, 64, 8, 4
+    q = torch.randn(B, M, H, D, generator=g).to(torch.bfloat16)
+    k = separated_keys(B, NC, H, D, g)
+    idx = parallel_nsa_topk_grouped_heads(q.to(dev), k.to(dev), NG, T, 64, 128, causal=True, group_size=G)
+    assert idx.shape == (B, M // G, H, T)
+    hpg = H // NG
+    qg = q.view(B, M, NG, hpg, D).mean(3)                   # the reference's expressions, on the CPU
+    kg = k.view(B, NC, NG, hpg, D).mean(3)
+    # the kernel's head means: the reference's values up to the last bit of a 1/3 in fp32
+    qg_d = _ops().pool_rows(q.to(dev).reshape(1, B * M * H, 1, D), hpg).view(B, M, NG, D)
+    kg_d = _ops().pool_rows(k.to(dev).reshape(1, B * NC * H, 1, D), hpg).view(B, NC, NG, D)
+    for a, b in ((qg_d.cpu(), qg), (kg_d.cpu(), kg)):
+        assert (a == b).float().mean() > 0.99
+        assert ((a.float() - b.float()).abs() <= 2 ** -7 * b.float().abs() + 1e-6).all()
+    qg, kg = qg_d.cpu(), kg_d.cpu()
+    want = parallel_nsa_topk(qg_d, kg_d, T, 64, None, 128, True, group_size=G)
+    assert torch.equal(idx.view(B, M // G, NG, hpg, T), want.unsqueeze(3).expand(-1, -1, -1, hpg, -1))
+    qp = O.pool_rows(qg, G)
+    s = masked_scores(qp, kg, D ** -0.5, block_size=64, chunk_size=128, chunk_size_k=128, causal=True, q_group_size=G)
+    assert_topk_parity(want, s, T)
+    # all heads in their own group: the plain path
+    same = parallel_nsa_topk_grouped_heads(q.to(dev), k.to(dev), H, T, 64, 128, causal=True, group_size=G)
+    assert torch.equal(same, parallel_nsa_topk(q.to(dev), k.to(dev), T, 64, None, 128, True, group_size=G))
+
+
 def test_topk_many_blocks_uses_global_path(dev):
     g = torch.Generator().manual_seed(10)
     NC = 9000                                           # more keys than fit the shared-memory key cache

@@ -77,6 +77,41 @@ def test_lru_model_matches_reference_mmcache(golden):
     assert m.hits == int(d["hits"][0])
 
 
+def test_page_pool_model_replays_the_reference_lru_trace(golden):
+    """The policy model the device cache is compared with, pinned to the reference: the trace of
+    MMCache.lru_touch_per_head (models/cache.py:673-699) replayed through one page pool per head
+    (capacity = the LRU size, every block starting in the host tier) evicts the same ids in the
+    same order, ends with the same LRU order and counts the same hits."""
+    d = golden("lru")
+    heads, cap, n_ids, n_touch = d["meta"].tolist()
+    pools = []
+    for _ in range(heads):
+        m = O.EpochLRUPagePool(1, cap, n_ids, 64)
+        m.n_tokens = n_ids * 64
+        m.evict_all()
+        pools.append(m)
+    for (h, cid), ev in zip(d["trace"].tolist(), d["evicted"].tolist()):
+        m = pools[h]
+        m.touch(torch.tensor([[[[cid]]]], dtype=torch.int32))
+        got = m.last_evicted[0] if m.last_evicted else -1
+        assert got == ev and len(m.last_evicted) <= 1
+    for h, m in enumerate(pools):
+        order = [x for x in d["final_order"][h].tolist() if x >= 0]
+        resident = sorted(m.table, key=lambda k: m.stamp[m.table[k]])
+        assert resident == order
+    assert sum(m.hits for m in pools) == int(d["hits"][0])
+
+
+def test_early_out_matches_the_reference_truth_table(golden):
+    """should_use_selection_attention against the table the reference's own function produced
+    (nsa/ops/index_topk.py:165-176): host integer logic, no device involved."""
+    from omnimem_b200.nsa.ops.index_topk import should_use_selection_attention
+    table = golden("early_out")["table"].tolist()
+    assert len(table) == 8 * 5 * 4 * 2
+    for seq_len, chunk, ex_win, ex_sink, causal, want in table:
+        assert bool(should_use_selection_attention(seq_len, chunk, ex_win, ex_sink, bool(causal))) == bool(want)
+
+
 def _visible_bruteforce(g, c, bs, cs, csk, causal, ex_win, ex_sink, prog, off, G):
     q_cid = (g * G) // cs + off
     k_cid = (c * bs) // csk

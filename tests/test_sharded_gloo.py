@@ -29,15 +29,18 @@ def _worker(rank, world, port, case, ret):
         from tests import oracle_ops
         M, N, H, D, T, bs, G, chunk, causal, q_off = case
         g = torch.Generator().manual_seed(77)
-        q = torch.randn(1, M, H, D, generator=g)
-        k = torch.randn(1, N, H, D, generator=g)
-        v = torch.randn(1, N, H, D, generator=g)
+        # bf16 tensors: the partial outputs cross the ranks as packed 16-bit rows
+        q = torch.randn(1, M, H, D, generator=g).to(torch.bfloat16)
+        k = torch.randn(1, N, H, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(1, N, H, D, generator=g).to(torch.bfloat16)
         sh = ShardedSelection(ops=oracle_ops)
         out, lse, idx = sh.forward(q, shard_kv(k, bs, rank, world), shard_kv(v, bs, rank, world), T, bs, G, chunk,
                                    causal, q_chunk_offset=q_off)
         full_idx = O.parallel_nsa_topk(q, O.pool_rows(k, bs), T, bs, None, chunk, causal, G, q_chunk_offset=q_off)
-        o_ref, l_ref = O.selection_fwd(q, k, v, full_idx, bs, 1, None, False, G)
-        ok = torch.equal(idx, full_idx) and torch.allclose(out, o_ref, atol=1e-5) and torch.allclose(lse, l_ref, atol=1e-5)
+        o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), full_idx, bs, 1, None, False, G)
+        # partials are rounded to bf16 before the merge (2^-9 relative each), the log-sum-exps stay fp32
+        ok = (torch.equal(idx, full_idx) and out.shape == o_ref.shape and lse.shape == l_ref.shape
+              and torch.allclose(out.float(), o_ref, atol=1.5e-2) and torch.allclose(lse, l_ref, atol=1e-4))
         gathered = [None] * world
         dist.all_gather_object(gathered, (bool(ok), idx.sum().item()))
         if rank == 0:
