@@ -470,6 +470,8 @@ def run_gpu(args):
     del d, res_host, slots
     torch.cuda.empty_cache()
     sharded = None if args.no_extras else run_sharded(args, dist, dev, rank, world)
+    torch.cuda.empty_cache()
+    roll = None if args.no_extras else run_rollout(args, dist, dev, rank, world)
 
     if rank == 0:
         per = {}
@@ -525,6 +527,8 @@ def run_gpu(args):
         }
         if sharded is not None:
             line["sharded"] = sharded
+        if roll is not None:
+            line["rollout"] = roll
         if world == 1 and not args.no_extras:
             line["gpu_baseline"] = gpu_baseline(per)
         if world == 1 and not args.no_cpu_baseline:
@@ -671,6 +675,40 @@ def run_sharded(args, dist, dev, rank, world):
     return res
 
 
+def run_rollout(args, dist, dev, rank, world, long_video=False):
+    """Configs 3 / 4: the causal rollout of the Wan2.1-1.3B-shaped model (random bf16 weights,
+    synthetic conditioning) with every self-attention on the NSA path; one independent rollout per
+    GPU.  Latent frames per second = frames / wall time of the denoising loop, max over ranks."""
+    from omnimem_b200 import rollout as R
+    shape = R.WanShape()
+    if long_video:
+        plan = R.RolloutPlan(latent_frames=241, cache_cap_frames=48, new_prompt_every=40, seed=rank)
+    else:
+        plan = R.RolloutPlan(seed=rank)
+    if args.rollout_layers:
+        shape.num_layers = args.rollout_layers
+    model, caches = R.build(shape, plan, dev, seed=1000 + rank)
+    warm = R.RolloutPlan(**{**plan.__dict__, "latent_frames": 2 * plan.frames_per_chunk, "new_prompt_every": None})
+    R.rollout(model, caches, warm, dev)                                  # warm-up: two chunks
+    res = R.rollout(model, caches, plan, dev)
+    t = torch.tensor([res.seconds], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs = t.item()
+    mem = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    out = {"workload": ("config4: 241 latent frames in 3-frame chunks, block cache capped at 48 frames per layer, "
+                        "a fresh conditioning tensor every 40 frames" if long_video else
+                        "config3: 21 latent frames (480x832, 81 frames) in 3-frame chunks, 4 denoising steps + 1 cache-write forward per chunk"),
+           "model": f"Wan2.1-T2V-1.3B shape, {shape.num_layers} blocks, dim {shape.dim}, {shape.num_heads} heads, ffn {shape.ffn_dim}, random bf16 weights",
+           "attention": "cmp + swa + selection (top-16 of 64-token blocks per 64-query group), all three on the selection forward kernel",
+           "latent_frames_per_second": round(world * plan.latent_frames / secs, 3), "seconds": round(secs, 3),
+           "forwards": res.forwards, "ms_per_forward": round(secs * 1e3 / res.forwards, 2),
+           "rollouts": world, "cache": res.cache, "gpu_mem_gib": round(mem, 1), "device_status_clean": True}
+    del model, caches
+    torch.cuda.empty_cache()
+    return out
+
+
 # ------------------------------------------------------------------------------ CPU reference
 def cpu_pass(O, t, groups=None):
     """The oracle's restatement of the same step on host tensors; `groups` limits the pass to a
@@ -740,6 +778,32 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_rollout_only(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the GPU arm has no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    res = run_rollout(args, dist, dev, rank, world, long_video=args.workload == "rollout-long")
+    if rank == 0:
+        line = {"metric": "wan_causal_rollout_latent_frames_per_second", "value": res["latent_frames_per_second"],
+                "unit": "latent frames/s", "n_gpus": world, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic", "config": {"workload": res["workload"], "model": res["model"]},
+                "rollout": res, "clocks": sampler.stop()}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -749,6 +813,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the isolated HBM / cache kernel timings, the config-5 leg and the reference-GPU baseline")
+    ap.add_argument("--workload", default="selection", choices=["selection", "rollout", "rollout-long"],
+                    help="selection: the op-level step (default, with the rollout of config 3 as an extra); rollout / "
+                         "rollout-long: only the rollout of config 3 / config 4, as a line of its own")
+    ap.add_argument("--rollout-layers", type=int, default=0, help="fewer transformer blocks than 30 (for quick runs)")
     ap.add_argument("--passes", type=int, default=0, help="passes of K steps in the timed region (default: about 2 s worth)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--kernels-only", action="store_true",
@@ -756,6 +824,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "selection":
+        run_rollout_only(args)
     else:
         run_gpu(args)
 

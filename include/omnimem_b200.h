@@ -340,6 +340,12 @@ int nsa_cache_append_rope(const void* k_new, const void* v_new, const int64_t kv
                           int64_t* page_stamp, int64_t epoch, void* k_pooled, void* v_pooled,
                           int32_t* status, int32_t dtype, const nsa_rope* rope, void* stream);
 
+/* The same rotary embedding for a chunk of queries: x [S,H,D] (x_stride = element strides of (s, h))
+ * -> out [S,H,D] contiguous, float64 products rounded like the reference.  Replaces
+ * causal_reorder_rope_apply on the query side (causal_wan_nsa_model.py:72-105, 463-466). */
+int nsa_rope_apply(const void* x, const int64_t x_stride[2], int64_t S, int32_t H, int32_t D, void* out,
+                   int32_t dtype, const nsa_rope* rope, void* stream);
+
 /* Selected (head, block) pairs of a flattened [B,MG,H,T] id table -> strictly ascending
  * unique keys (cid*H + h)*bpc + loc (cid = bid / bpc, loc = bid % bpc): out_unique[0] = count
  * (may exceed cap), out_unique[1..cap] keys.  `stamp` is a persistent int32 [H*max_blocks]

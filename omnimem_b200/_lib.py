@@ -89,6 +89,7 @@ PROTOTYPES = {
                                 _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, _vp]),
     "nsa_cache_append_rope": (_i32, [_vp, _vp, _S3, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _vp, _i32,
                                      _vp, _i32, _vp, _vp, _i64, _vp, _vp, _vp, _i32, C.POINTER(Rope), _vp]),
+    "nsa_rope_apply": (_i32, [_vp, _S3, _i64, _i32, _i32, _vp, _i32, C.POINTER(Rope), _vp]),
     "nsa_cache_dedup_workspace_bytes": (_sz, [_i64]),
     "nsa_cache_dedup_touch": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _vp, _vp, _i64,
                                      _vp, _vp, _i32, _vp, _vp, _sz, _vp]),

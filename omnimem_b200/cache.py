@@ -58,6 +58,21 @@ class RopeSpec:
         return s
 
 
+def rope_apply(x: torch.Tensor, rope: RopeSpec) -> torch.Tensor:
+    """Rotary embedding of a chunk of queries x [S,H,D] (bf16 / fp16) -> a new contiguous tensor;
+    the query-side use of causal_reorder_rope_apply (causal_wan_nsa_model.py:72-105, 463-466)."""
+    if not x.is_cuda or x.dim() != 3:
+        raise NSABackendError("rope_apply: x must be a CUDA tensor [S,H,D]")
+    x = ops._rows16(x)
+    S, H, D = x.shape
+    out = torch.empty(S, H, D, dtype=x.dtype, device=x.device)
+    spec = rope.struct(x.device, D)
+    with torch.cuda.device(x.device):
+        call("nsa_rope_apply", x.data_ptr(), (C.c_int64 * 3)(x.stride(0), x.stride(1), 0), S, H, D, out.data_ptr(),
+             ops._dtype(x), C.byref(spec), torch.cuda.current_stream(x.device).cuda_stream)
+    return out
+
+
 class BlockKVCache:
     def __init__(self, num_heads: int, head_dim: int, num_pages: int, max_blocks: int,
                  page_tokens: int = 64, dtype: torch.dtype = torch.bfloat16, device="cuda",
@@ -270,3 +285,37 @@ class BlockKVCache:
         self.n_tokens = 0
         self.epoch = 0
         self._evicted_any = False
+
+
+class BlockKVStore:
+    """One BlockKVCache per transformer layer: the block-level store that the reference's
+    selection_attention_block_store expects behind ``kv_cache.block_store``
+    (padded_ptr/block_wrapper.py:51-85) and that its repository does not ship."""
+
+    def __init__(self, num_layers: int, num_heads: int, head_dim: int, num_pages: int, max_blocks: int,
+                 page_tokens: int = 64, dtype: torch.dtype = torch.bfloat16, device="cuda", host_tier: bool = True,
+                 protect_blocks: int = 0):
+        self.layers = [BlockKVCache(num_heads, head_dim, num_pages, max_blocks, page_tokens, dtype, device, host_tier,
+                                    protect_blocks) for _ in range(num_layers)]
+        self.block_tokens, self.head_dim, self.num_heads = page_tokens, head_dim, num_heads
+
+    @property
+    def block_store(self):
+        return self
+
+    def layer(self, layer_idx: int) -> BlockKVCache:
+        return self.layers[layer_idx]
+
+    def reset(self) -> None:
+        for c in self.layers:
+            c.reset()
+
+    def stats(self) -> dict:
+        total = {}
+        for c in self.layers:
+            for k, v in c.stats().items():
+                if k != "hit_rate":
+                    total[k] = total.get(k, 0) + v
+        n = total.get("hits", 0) + total.get("misses", 0)
+        total["hit_rate"] = total.get("hits", 0) / n if n else 0.0
+        return total

@@ -80,50 +80,82 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
   char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes;
   const int cpr = p.D / VEC;
   const int nrows = static_cast<int>(hi - lo);
-  for (int c = threadIdx.x; c < nrows * cpr; c += blockDim.x) {
-    const int r = c / cpr, cc = c - r * cpr;
-    const int64_t src = ((lo - p.pos0 + r) * p.s_stride + h * p.h_stride) * sizeof(T) + cc * 16;
-    const int64_t dst = (lo - blk0 + r) * row_bytes + cc * 16;
-    uint4 kq = *reinterpret_cast<const uint4*>(p.k_new + src);
-    if (ROPE) {
-      int fr, hr, wr;
-      rope_position(p, lo - p.pos0 + r, fr, hr, wr);
-      T* e = reinterpret_cast<T*>(&kq);
-#pragma unroll
-      for (int i = 0; i < VEC / 2; ++i) {
-        const int j = cc * (VEC / 2) + i;                      // complex pair of the head
-        double2 w;
-        if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
-        else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
-        else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
-        const double xr = static_cast<double>(to_f32<T>(e[2 * i])), xi = static_cast<double>(to_f32<T>(e[2 * i + 1]));
-        // float64 product, then float64 -> float32 -> T, as view_as_real(...).type_as(x) does
-        e[2 * i] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
-        e[2 * i + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
-      }
-    }
-    *reinterpret_cast<uint4*>(kp + dst) = kq;
-    *reinterpret_cast<uint4*>(vp + dst) = *reinterpret_cast<const uint4*>(p.v_new + src);
-  }
-  __syncthreads();
-  // pooled key / value over the tokens the block now holds (rows [0, n_present)): a rewrite that
-  // ends inside the block leaves the tokens behind it in place
-  const int64_t held = min(p.n_tokens_before, blk0 + p.page_tokens);
-  const int n_present = static_cast<int>(max(hi, held) - blk0);
   const int rp = blockDim.x / cpr;
   const int col = threadIdx.x % cpr, r0 = threadIdx.x / cpr;
+  const int64_t held = min(p.n_tokens_before, blk0 + p.page_tokens);
+  const int n_present = static_cast<int>(max(hi, held) - blk0);   // rows the block holds after this call
+  // When the call writes every row the block holds (the common case: a chunk covers whole blocks),
+  // the pooled sums are taken from the rows on their way through the registers; otherwise the page is
+  // read back below.  A thread copies rows r0, r0 + rp, ... of its 16-byte column, the pooling order.
+  const bool whole = lo == blk0 && nrows == n_present;
   float ak[VEC], av[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) ak[i] = av[i] = 0.f;
+  constexpr int UNROLL = 4;
   if (r0 < rp) {
-    for (int r = r0; r < n_present; r += rp) {
-      const uint4 a = *reinterpret_cast<const uint4*>(kp + r * row_bytes + col * 16);
-      const uint4 b = *reinterpret_cast<const uint4*>(vp + r * row_bytes + col * 16);
-      const T* ea = reinterpret_cast<const T*>(&a);
-      const T* eb = reinterpret_cast<const T*>(&b);
+    const char* ksrc = p.k_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
+    const char* vsrc = p.v_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
+    const int64_t src_row = p.s_stride * sizeof(T);
+    char* kdst = kp + (lo - blk0) * row_bytes + col * 16;
+    char* vdst = vp + (lo - blk0) * row_bytes + col * 16;
+    for (int rb = r0; rb < nrows; rb += UNROLL * rp) {
+      uint4 kq[UNROLL], vq[UNROLL];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) { ak[i] += to_f32<T>(ea[i]); av[i] += to_f32<T>(eb[i]); }
+      for (int u = 0; u < UNROLL; ++u) {                 // all loads of the batch first
+        const int r = rb + u * rp;
+        if (r < nrows) {
+          kq[u] = *reinterpret_cast<const uint4*>(ksrc + r * src_row);
+          vq[u] = *reinterpret_cast<const uint4*>(vsrc + r * src_row);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int r = rb + u * rp;
+        if (r >= nrows) continue;
+        if (ROPE) {
+          int fr, hr, wr;
+          rope_position(p, lo - p.pos0 + r, fr, hr, wr);
+          T* e = reinterpret_cast<T*>(&kq[u]);
+#pragma unroll
+          for (int i = 0; i < VEC / 2; ++i) {
+            const int j = col * (VEC / 2) + i;                   // complex pair of the head
+            double2 w;
+            if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
+            else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
+            else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
+            const double xr = static_cast<double>(to_f32<T>(e[2 * i])), xi = static_cast<double>(to_f32<T>(e[2 * i + 1]));
+            // float64 product, then float64 -> float32 -> T, as view_as_real(...).type_as(x) does
+            e[2 * i] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
+            e[2 * i + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
+          }
+        }
+        *reinterpret_cast<uint4*>(kdst + r * row_bytes) = kq[u];
+        *reinterpret_cast<uint4*>(vdst + r * row_bytes) = vq[u];
+        if (whole) {
+          const T* ea = reinterpret_cast<const T*>(&kq[u]);
+          const T* eb = reinterpret_cast<const T*>(&vq[u]);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) { ak[i] += to_f32<T>(ea[i]); av[i] += to_f32<T>(eb[i]); }
+        }
+      }
     }
+  }
+  if (!whole) {
+    __syncthreads();
+    // pooled key / value over the tokens the block now holds (rows [0, n_present)): a rewrite that
+    // covers part of the block leaves the other tokens in place
+    if (r0 < rp) {
+      for (int r = r0; r < n_present; r += rp) {
+        const uint4 a = *reinterpret_cast<const uint4*>(kp + r * row_bytes + col * 16);
+        const uint4 b = *reinterpret_cast<const uint4*>(vp + r * row_bytes + col * 16);
+        const T* ea = reinterpret_cast<const T*>(&a);
+        const T* eb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { ak[i] += to_f32<T>(ea[i]); av[i] += to_f32<T>(eb[i]); }
+      }
+    }
+  }
+  if (r0 < rp) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       s_part[r0 * p.D + col * VEC + i] = ak[i];
@@ -139,6 +171,38 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
     for (int r = 0; r < rp; ++r) { sk += s_part[r * p.D + d]; sv += s_part[(rp + r) * p.D + d]; }
     ok[d] = from_f32<T>(sk * inv);
     if (p.v_pooled) ov[d] = from_f32<T>(sv * inv);
+  }
+}
+
+// Rotary embedding of a chunk of QUERIES (same rule and rounding as the keys above): one thread per
+// 16-byte piece of a row, x [S,H,D] by stride -> out [S,H,D] contiguous.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_apply_kernel(const AppendParams p, char* __restrict__ out) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int cpr = p.D / VEC;
+  const int64_t total = p.S * p.H * cpr;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % cpr);
+    const int64_t sh = i / cpr;
+    const int h = static_cast<int>(sh % p.H);
+    const int64_t t = sh / p.H;
+    uint4 q = *reinterpret_cast<const uint4*>(p.k_new + (t * p.s_stride + h * p.h_stride) * sizeof(T) + cc * 16);
+    int fr, hr, wr;
+    rope_position(p, t, fr, hr, wr);
+    T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+    for (int k = 0; k < VEC / 2; ++k) {
+      const int j = cc * (VEC / 2) + k;
+      double2 w;
+      if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
+      else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
+      else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
+      const double xr = static_cast<double>(to_f32<T>(e[2 * k])), xi = static_cast<double>(to_f32<T>(e[2 * k + 1]));
+      e[2 * k] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
+      e[2 * k + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
+    }
+    *reinterpret_cast<uint4*>(out + ((t * p.H + h) * static_cast<int64_t>(p.D)) * sizeof(T) + cc * 16) = q;
   }
 }
 
@@ -261,6 +325,97 @@ __global__ void __launch_bounds__(1024) select_victims_kernel(
   }
 }
 
+// The same selection without a rescan per victim.  The scan kernel above costs milliseconds when
+// a new chunk needs a page for every (head, block) it brings (888 pages out of 14040 at a 48-frame
+// cap); this one finds the n-th smallest key by radix selection (eight passes over the pool, one
+// byte of the 64-bit key each, histogram in shared memory), gathers the n keys that do not exceed
+// it into shared memory, sorts them there (bitonic) and writes them out in ascending order: tens
+// of microseconds whatever n is.  n is limited by the shared-memory list to kSelectMax victims.
+constexpr int kSelectMax = 16384;
+
+__device__ __forceinline__ unsigned long long victim_key(const int32_t* __restrict__ page_owner,
+                                                         const int64_t* __restrict__ page_stamp, int pg,
+                                                         int max_blocks, int protect_from_bid, int64_t epoch) {
+  const int owner = page_owner[pg];
+  if (owner < 0) return static_cast<unsigned long long>(pg);           // free: before every owned page
+  if (owner % max_blocks >= protect_from_bid) return ~0ull;
+  const int64_t st = page_stamp[pg];
+  if (st >= epoch) return ~0ull;
+  return (static_cast<unsigned long long>(st + 1) << 24) | static_cast<unsigned>(pg);
+}
+
+__global__ void __launch_bounds__(1024) select_victims_radix_kernel(
+    const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp, int num_pages,
+    int max_blocks, int protect_from_bid, int64_t epoch, int n_host, const int32_t* __restrict__ n_dev,
+    int cap, int32_t* __restrict__ victims, int32_t* status) {
+  extern __shared__ unsigned long long s_list[];            // the selected keys, padded to a power of two
+  __shared__ unsigned int s_hist[256];
+  __shared__ unsigned long long s_prefix;
+  __shared__ int s_remaining, s_count, s_total;
+  int n = n_dev ? *n_dev : n_host;
+  if (n > cap) n = cap;
+  if (n > kSelectMax) n = kSelectMax;                       // the host sends larger requests to the scan kernel
+  if (n <= 0) return;
+  if (threadIdx.x == 0) { s_prefix = 0ull; s_remaining = n; s_count = 0; s_total = 0; }
+  // ---- the n-th smallest key, one byte at a time from the top
+  for (int byte = 7; byte >= 0; --byte) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0u;
+    __syncthreads();
+    const unsigned long long prefix = s_prefix;
+    for (int pg = threadIdx.x; pg < num_pages; pg += blockDim.x) {
+      const unsigned long long k = victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch);
+      if (k == ~0ull) continue;
+      if (byte == 7 || (k >> (8 * (byte + 1))) == prefix) atomicAdd(&s_hist[(k >> (8 * byte)) & 255u], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int remaining = s_remaining, digit = 255;
+      unsigned int seen = 0u;
+      for (int d = 0; d < 256; ++d) {
+        if (seen + s_hist[d] >= static_cast<unsigned>(remaining)) { digit = d; break; }
+        seen += s_hist[d];
+      }
+      if (byte == 7) { unsigned int tot = 0u; for (int d = 0; d < 256; ++d) tot += s_hist[d]; s_total = static_cast<int>(tot); }
+      // fewer candidates than asked for: the loop ran off the end (digit 255, every candidate taken)
+      s_remaining = remaining - static_cast<int>(seen);
+      s_prefix = (prefix << 8) | static_cast<unsigned long long>(digit);
+    }
+    __syncthreads();
+  }
+  const int total = s_total;
+  const int take = total < n ? total : n;                   // keys that exist
+  const unsigned long long threshold = total < n ? ~0ull - 1ull : s_prefix;
+  // ---- gather the keys up to the threshold (exactly `take` of them: keys are unique), sort, write
+  int n_pow2 = 2;
+  while (n_pow2 < take) n_pow2 <<= 1;
+  for (int i = threadIdx.x; i < n_pow2; i += blockDim.x) s_list[i] = ~0ull;
+  __syncthreads();
+  for (int pg = threadIdx.x; pg < num_pages; pg += blockDim.x) {
+    const unsigned long long k = victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch);
+    if (k != ~0ull && k <= threshold) {
+      const int pos = atomicAdd(&s_count, 1);
+      if (pos < n_pow2) s_list[pos] = k;
+    }
+  }
+  __syncthreads();
+  for (int k = 2; k <= n_pow2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n_pow2; i += blockDim.x) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long a = s_list[i], b = s_list[l];
+          const bool ascending = (i & k) == 0;
+          if ((a > b) == ascending) { s_list[i] = b; s_list[l] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    victims[i] = i < take ? static_cast<int32_t>(s_list[i] & 0xffffffu) : -1;
+  if (threadIdx.x == 0 && take < n) atomicExch(status, NSA_ERR_EXHAUSTED);
+}
+
 // ----------------------------------------------------------------------------- page movement
 struct MoveParams {
   const int32_t* pages;        // [n] page per move (evict: the victim; fetch: the destination)
@@ -369,6 +524,23 @@ __global__ void block_range_kernel(int64_t* __restrict__ table, int32_t* __restr
 
 using namespace nsa;
 
+static int set_rope(const nsa_rope* rope, int64_t S, int32_t D, AppendParams* p) {
+  NSA_REQUIRE(rope->freqs_f && rope->freqs_h && rope->freqs_w, NSA_ERR_INVALID, "rope: null frequency table");
+  NSA_REQUIRE(rope->c_f >= 0 && rope->c_h >= 0 && rope->c_w >= 0 && 2 * (rope->c_f + rope->c_h + rope->c_w) == D,
+              NSA_ERR_INVALID, "rope: c_f + c_h + c_w must be D / 2");
+  NSA_REQUIRE(rope->pool_f > 0 && rope->pool_h > 0 && rope->pool_w > 0 && rope->grid_h > 0 && rope->grid_w > 0 &&
+                  rope->grid_h % rope->pool_h == 0 && rope->grid_w % rope->pool_w == 0 && rope->start_frame >= 0,
+              NSA_ERR_INVALID, "rope: bad grid / pooling window");
+  NSA_REQUIRE(S % (static_cast<int64_t>(rope->grid_h) * rope->grid_w * rope->pool_f) == 0, NSA_ERR_INVALID,
+              "rope: S must be whole groups of pool_f frames of grid_h x grid_w tokens");
+  p->rope_f = static_cast<const double2*>(rope->freqs_f); p->rope_h = static_cast<const double2*>(rope->freqs_h);
+  p->rope_w = static_cast<const double2*>(rope->freqs_w);
+  p->c_f = rope->c_f; p->c_h = rope->c_h; p->c_w = rope->c_w;
+  p->grid_h = rope->grid_h; p->grid_w = rope->grid_w; p->pool_f = rope->pool_f; p->pool_h = rope->pool_h;
+  p->pool_w = rope->pool_w; p->start_frame = rope->start_frame;
+  return NSA_OK;
+}
+
 static int cache_append_impl(const void* k_new, const void* v_new, const int64_t kv_stride[2],
                              int64_t S, int64_t pos0, int64_t n_tokens, int32_t H, int32_t D, void* k_pool,
                              void* v_pool, int32_t page_tokens, int32_t* block_table,
@@ -400,19 +572,8 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
                  static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
                  static_cast<char*>(k_pooled), static_cast<char*>(v_pooled), status};
   if (rope != nullptr) {
-    NSA_REQUIRE(rope->freqs_f && rope->freqs_h && rope->freqs_w, NSA_ERR_INVALID, "cache_append_rope: null frequency table");
-    NSA_REQUIRE(rope->c_f >= 0 && rope->c_h >= 0 && rope->c_w >= 0 && 2 * (rope->c_f + rope->c_h + rope->c_w) == D,
-                NSA_ERR_INVALID, "cache_append_rope: c_f + c_h + c_w must be D / 2");
-    NSA_REQUIRE(rope->pool_f > 0 && rope->pool_h > 0 && rope->pool_w > 0 && rope->grid_h > 0 && rope->grid_w > 0 &&
-                    rope->grid_h % rope->pool_h == 0 && rope->grid_w % rope->pool_w == 0 && rope->start_frame >= 0,
-                NSA_ERR_INVALID, "cache_append_rope: bad grid / pooling window");
-    NSA_REQUIRE(S % (static_cast<int64_t>(rope->grid_h) * rope->grid_w * rope->pool_f) == 0, NSA_ERR_INVALID,
-                "cache_append_rope: S must be whole groups of pool_f frames of grid_h x grid_w tokens");
-    p.rope_f = static_cast<const double2*>(rope->freqs_f); p.rope_h = static_cast<const double2*>(rope->freqs_h);
-    p.rope_w = static_cast<const double2*>(rope->freqs_w);
-    p.c_f = rope->c_f; p.c_h = rope->c_h; p.c_w = rope->c_w;
-    p.grid_h = rope->grid_h; p.grid_w = rope->grid_w; p.pool_f = rope->pool_f; p.pool_h = rope->pool_h;
-    p.pool_w = rope->pool_w; p.start_frame = rope->start_frame;
+    const int rc = set_rope(rope, S, D, &p);
+    if (rc) return rc;
   }
   const int cpr = D * esz / 16, rp = 128 / cpr;
   const size_t smem = 2 * static_cast<size_t>(rp) * D * sizeof(float);
@@ -452,6 +613,29 @@ extern "C" int nsa_cache_append_rope(const void* k_new, const void* v_new, const
   return cache_append_impl(k_new, v_new, kv_stride, S, pos0, n_tokens, H, D, k_pool, v_pool, page_tokens, block_table,
                            max_blocks, new_pages, n_touched_blocks, page_owner, page_stamp, epoch, k_pooled,
                            v_pooled, status, dtype, rope, stream);
+}
+
+extern "C" int nsa_rope_apply(const void* x, const int64_t x_stride[2], int64_t S, int32_t H, int32_t D, void* out,
+                              int32_t dtype, const nsa_rope* rope, void* stream) {
+  NSA_REQUIRE(S >= 0 && H > 0 && D > 0, NSA_ERR_INVALID, "rope_apply: bad size");
+  NSA_REQUIRE(dtype == NSA_BF16 || dtype == NSA_F16, NSA_ERR_UNSUPPORTED, "rope_apply: bf16 / fp16 only");
+  NSA_REQUIRE((D * 2) % 16 == 0, NSA_ERR_UNSUPPORTED, "rope_apply: head dim %d", D);
+  NSA_REQUIRE(rope != nullptr, NSA_ERR_INVALID, "rope_apply: rope is null");
+  if (S == 0) return NSA_OK;
+  NSA_REQUIRE(x && out && aligned16(x) && aligned16(out) && (x_stride[0] * 2) % 16 == 0 && (x_stride[1] * 2) % 16 == 0,
+              NSA_ERR_LAYOUT, "rope_apply: rows must be 16-byte aligned");
+  AppendParams p{};
+  p.k_new = static_cast<const char*>(x); p.s_stride = x_stride[0]; p.h_stride = x_stride[1];
+  p.S = S; p.H = H; p.D = D;
+  int rc;
+  if ((rc = set_rope(rope, S, D, &p))) return rc;
+  const int64_t total = S * H * (D * 2 / 16);
+  const int blocks = static_cast<int>(cdiv64(total, 256) < 148 * 16 ? cdiv64(total, 256) : 148 * 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == NSA_BF16) rope_apply_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(p, static_cast<char*>(out));
+  else rope_apply_kernel<__half><<<blocks, 256, 0, s>>>(p, static_cast<char*>(out));
+  NSA_LAUNCH_OK("rope_apply_kernel");
+  return NSA_OK;
 }
 
 extern "C" size_t nsa_cache_dedup_workspace_bytes(int64_t n_keys) {
@@ -501,6 +685,20 @@ extern "C" int nsa_cache_select_victims(const int32_t* page_owner, const int64_t
   NSA_REQUIRE(page_owner && page_stamp && victims && status, NSA_ERR_INVALID, "cache_select_victims: null pointer");
   NSA_REQUIRE(n_dev != nullptr || n <= cap, NSA_ERR_INVALID, "cache_select_victims: n > cap");
   if (cap == 0 || (!n_dev && n == 0)) return NSA_OK;
+  // test hook: OMNIMEM_B200_VICTIMS_KERNEL=scan keeps the rescanning kernel for every pool size
+  const char* env = getenv("OMNIMEM_B200_VICTIMS_KERNEL");
+  const bool scan_only = env != nullptr && env[0] == 's';
+  const int n_max = n_dev ? cap : n;                        // the most victims this call can ask for
+  if (n_max <= kSelectMax && !scan_only) {
+    int n_pow2 = 2;
+    while (n_pow2 < n_max) n_pow2 <<= 1;
+    const size_t smem = static_cast<size_t>(n_pow2) * sizeof(unsigned long long);
+    NSA_CUDA_OK(cudaFuncSetAttribute(select_victims_radix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectMax * 8));
+    select_victims_radix_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
+        page_owner, page_stamp, num_pages, max_blocks, protect_from_bid, epoch, n, n_dev, cap, victims, status);
+    NSA_LAUNCH_OK("select_victims_radix_kernel");
+    return NSA_OK;
+  }
   select_victims_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
       page_owner, page_stamp, num_pages, max_blocks, protect_from_bid, epoch, n, n_dev, cap, victims, status);
   NSA_LAUNCH_OK("select_victims_kernel");

@@ -204,14 +204,15 @@ int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
 
 // ------------------------------------------------------------------- fused pooling + scoring
 // One thread block pools kFusedCols consecutive key blocks of one (batch, head) - the HBM-bound part:
-// every key is read exactly once, 16 bytes per load, eight loads in flight per thread - keeps the
+// every key is read exactly once, 16 bytes per load, eight to sixteen loads in flight per thread - keeps the
 // rounded pooled keys in shared memory (and writes them out), and scores them against ALL pooled
 // query rows of the head with the same m16n8k16 products, in the same order, as score_mma_kernel,
 // so the scores carry the same bits.  The pooled queries (MG x D, a few KB per head) come from L2.
 // With early_k the keys are pooled BEFORE the wait on the kernel in front (which then must be one
 // that releases its dependents only after its own wait: the query-group pooling launched by
 // nsa_select_blocks), so that pooling the queries costs no time of its own.
-constexpr int kFusedCols = 8;
+constexpr int kFusedCols = 4;       // key blocks per thread block (columns 4..7 of the n8 score tile stay zero)
+constexpr int kFusedQRows = 32;     // pooled query rows staged per pass
 
 struct PoolScoreParams {
   PoolParams pool;                                   // raw keys -> pooled keys [B,NC,H,D]
@@ -224,7 +225,7 @@ struct PoolScoreParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p) {
+__global__ void __launch_bounds__(128, 8) pool_score_kernel(const PoolScoreParams p) {
   constexpr int VEC = 8;                              // 16-bit elements per 16-byte load
   constexpr int UNROLL = 8;
   extern __shared__ __align__(16) char s_raw[];
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p
   const int lpr = D / VEC, rp = 128 / lpr;
   float* s_part = reinterpret_cast<float*>(s_raw);                      // [rp][D]
   T* sK = reinterpret_cast<T*>(s_raw + static_cast<size_t>(rp) * D * sizeof(float));   // [8][PITCH] pooled keys
-  T* sQ = sK + kFusedCols * PITCH;                                      // [64][PITCH] pooled queries
+  T* sQ = sK + 8 * PITCH;                                               // [kFusedQRows][PITCH] pooled queries
   const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kFusedCols;
   const int h = blockIdx.y, b = blockIdx.z;
   const int ncol = static_cast<int>(p.NC - c0 < kFusedCols ? p.NC - c0 : kFusedCols);
@@ -240,32 +241,52 @@ __global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p
   if (!p.early_k) chain_wait();
   chain_release();
 
+  const int64_t row_bytes = p.pool.x_sn * sizeof(T);
+  const char* head_base = p.pool.x + (b * p.pool.x_sb + h * p.pool.x_sh) * sizeof(T) + col * 16;
+  // the first UNROLL rows this thread owns of key block j (rows r0, r0 + rp, ...), all loads in flight at once
+  auto issue = [&](int j, uint4 (&v)[UNROLL]) -> int {
+    if (j >= ncol) return 0;
+    const int64_t n0 = (c0 + j) * p.pool.size;
+    const int n = static_cast<int>(p.pool.N - n0 < p.pool.size ? p.pool.N - n0 : p.pool.size);
+    const char* base = head_base + n0 * row_bytes;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int rr = r0 + u * rp;
+      v[u] = rr < n ? *reinterpret_cast<const uint4*>(base + rr * row_bytes) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    return n;
+  };
+  for (int i = threadIdx.x; i < (8 - kFusedCols) * PITCH; i += blockDim.x) sK[kFusedCols * PITCH + i] = from_f32<T>(0.f);
+
+  // Key blocks are pooled one after the other; a thread has its UNROLL rows of the block in flight at
+  // once (a whole 64 x 128 key block per thread block), and enough thread blocks fit an SM (the
+  // register bound below) to keep the memory system busy while others reduce or score.
+#pragma unroll 1
   for (int j = 0; j < kFusedCols; ++j) {
     if (j >= ncol) {                                  // columns past the last key block score nothing
       for (int d = threadIdx.x; d < D; d += blockDim.x) sK[j * PITCH + d] = from_f32<T>(0.f);
       continue;
     }
-    const int64_t n0 = (c0 + j) * p.pool.size;
-    const int n = static_cast<int>(p.pool.N - n0 < p.pool.size ? p.pool.N - n0 : p.pool.size);
+    uint4 v[UNROLL];
+    const int n = issue(j, v);
     float acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-    const char* base = p.pool.x + (b * p.pool.x_sb + n0 * p.pool.x_sn + h * p.pool.x_sh) * sizeof(T) + col * 16;
-    const int64_t row_bytes = p.pool.x_sn * sizeof(T);
-    for (int r = r0; r < n; r += UNROLL * rp) {
-      uint4 v[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int rr = r + u * rp;
-        v[u] = rr < n ? *reinterpret_cast<const uint4*>(base + rr * row_bytes) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < UNROLL; ++u) {
+      if (r0 + u * rp < n) {                          // rows in ascending order, as pool_rows_kernel adds them
+        const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
       }
+    }
+    if (n > UNROLL * rp) {                            // key blocks longer than one batch of loads
+      const char* base = head_base + (c0 + j) * p.pool.size * row_bytes;
+      for (int r = r0 + UNROLL * rp; r < n; r += rp) {
+        const uint4 w = *reinterpret_cast<const uint4*>(base + r * row_bytes);
+        const T* e = reinterpret_cast<const T*>(&w);
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        if (r + u * rp < n) {                         // rows in ascending order, as pool_rows_kernel adds them
-          const T* e = reinterpret_cast<const T*>(&v[u]);
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
-        }
+        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
       }
     }
     __syncthreads();                                  // s_part of the previous key block has been read
@@ -286,10 +307,10 @@ __global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
   const int cpr = D / 8;
-  for (int g0 = 0; g0 < p.MG; g0 += kScoreMmaRows) {
-    const int nrow = min(kScoreMmaRows, p.MG - g0);
-    __syncthreads();                                  // sK complete / sQ of the previous tile consumed
-    for (int i = threadIdx.x; i < kScoreMmaRows * cpr; i += blockDim.x) {
+  for (int g0 = 0; g0 < p.MG; g0 += kFusedQRows) {
+    const int nrow = min(kFusedQRows, p.MG - g0);
+    __syncthreads();                                  // sK complete / sQ of the previous pass consumed
+    for (int i = threadIdx.x; i < kFusedQRows * cpr; i += blockDim.x) {
       const int r = i / cpr, cc = i - r * cpr;
       const char* qsrc = p.q + (b * p.q_sb + (g0 + r) * p.q_sg + h * p.q_sh) * 2 + cc * 16;
       cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? qsrc : p.q, r < nrow ? 16 : 0);
@@ -297,7 +318,7 @@ __global__ void __launch_bounds__(128) pool_score_kernel(const PoolScoreParams p
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
-    if (warp * 16 < nrow) {
+    if (warp * 16 < nrow) {                           // two warps, 16 rows each
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       const T* qa = sQ + (warp * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8;
       const T* kb = sK + gid * PITCH + t4 * 2;
@@ -326,7 +347,7 @@ template <typename T>
 int launch_pool_score(const PoolScoreParams& p, int B, cudaStream_t s) {
   const int D = p.pool.D, rp = 128 / (D / 8);
   const size_t smem = static_cast<size_t>(rp) * D * sizeof(float) +
-                      static_cast<size_t>(kFusedCols + kScoreMmaRows) * (D + 8) * sizeof(T);
+                      static_cast<size_t>(8 + kFusedQRows) * (D + 8) * sizeof(T);
   NSA_CUDA_OK(cudaFuncSetAttribute(pool_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const dim3 grid(static_cast<unsigned>(cdiv64(p.NC, kFusedCols)), p.H, B);
   NSA_CUDA_OK(launch_chained(kChainSmall, pool_score_kernel<T>, grid, dim3(128), smem, s, p));
@@ -419,6 +440,9 @@ struct SelectParams {
   int32_t* out_idx;       // [rows][topk]
   float* out_scores;      // may be null
   Mask mask;
+  int seg_cols;           // MASKED, first stage of long rows: columns per segment (0 = the whole row);
+  int n_seg;              //   warp w takes segment w % n_seg of row w / n_seg and writes its list to
+                          //   out_idx / out_scores laid out [n_seg][rows][topk]
 };
 
 template <bool MERGE>
@@ -501,8 +525,13 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
   chain_release();
   chain_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
-  if (row >= rows) return;
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  const int n_seg = (!MERGE && p.seg_cols > 0) ? p.n_seg : 1;
+  if (unit >= rows * n_seg) return;
+  const int64_t row = unit / n_seg;
+  const int seg = static_cast<int>(unit - row * n_seg);
+  const int64_t c_off = static_cast<int64_t>(seg) * p.seg_cols;          // 0 unless segmented
+  const int64_t NC = n_seg > 1 ? (p.NC - c_off < p.seg_cols ? p.NC - c_off : p.seg_cols) : p.NC;
   RowMask rm{};
   const float* srow;
   if (MERGE) {
@@ -513,12 +542,12 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     const int g = static_cast<int>(bg % p.MG);
     const int64_t b = bg / p.MG;
     rm = make_row_mask(p.mask, g);
-    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC;
+    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC + c_off;
   }
   // all loads first, unconditionally (clamped index), so that they are in flight together
   float vals[ITEMS];
   int cids[ITEMS];
-  const int64_t last = p.NC - 1;
+  const int64_t last = NC - 1;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     int64_t c = lane + 32 * i;
@@ -538,11 +567,11 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
   for (int i = 0; i < ITEMS; ++i) {
     const int64_t c = lane + 32 * i;
     unsigned long long k = 0ull;
-    if (c < p.NC) {
+    if (c < NC) {
       if (MERGE) {
         k = cids[i] < 0 ? 0ull : pack_key(vals[i], cids[i]);
       } else {
-        const int bid = p.mask.id_base + static_cast<int>(c) * p.mask.id_stride;
+        const int bid = p.mask.id_base + static_cast<int>(c_off + c) * p.mask.id_stride;
         k = visible(p.mask, rm, bid) ? pack_key(vals[i], bid) : 0ull;
       }
     }
@@ -570,8 +599,9 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
   for (int i = 0; i < ITEMS; ++i) s_sorted[warp][i][lane] = keys[i];
   unsigned long long local = keys[0];
   int next = 1;
-  int32_t* oi = p.out_idx + row * p.topk;
-  float* os = p.out_scores ? p.out_scores + row * p.topk : nullptr;
+  const int64_t out_row = n_seg > 1 ? static_cast<int64_t>(seg) * rows + row : row;
+  int32_t* oi = p.out_idx + out_row * p.topk;
+  float* os = p.out_scores ? p.out_scores + out_row * p.topk : nullptr;
   // winners are kept one per lane (round r in lane r % 32) and written 32 at a time
   unsigned long long mine = 0ull;
   auto flush = [&](int first, int n) {
@@ -601,9 +631,36 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
   }
 }
 
+constexpr int kSegCols = 1024;       // candidates one warp sorts in registers
+constexpr int kSegTopkMax = 64;      // largest top-k the two-stage selection of long rows is sized for
+
+size_t segment_workspace_bytes(int64_t rows, int64_t NC) {
+  if (NC <= kSegCols) return 0;
+  return align_up(static_cast<size_t>(cdiv64(NC, kSegCols)) * rows * kSegTopkMax * 8, 256);
+}
+
 template <bool MERGE>
-int launch_select(const SelectParams& sel, int64_t rows, cudaStream_t s) {
+int launch_select(const SelectParams& sel, int64_t rows, cudaStream_t s, void* seg_ws = nullptr) {
   const unsigned blocks4 = static_cast<unsigned>(cdiv64(rows, 4));
+  if (!MERGE && seg_ws != nullptr && sel.NC > kSegCols && sel.topk <= kSegTopkMax &&
+      cdiv64(sel.NC, kSegCols) * rows <= 0x7fffffff) {
+    // Long rows in two stages: one warp per (row, 1024-column segment) takes the segment's top-k
+    // (same keys, same order), then the per-segment lists of a row are merged like per-shard
+    // candidate lists.  Exact: the row's top-k is a subset of the union of the segments' top-k.
+    const int n_seg = static_cast<int>(cdiv64(sel.NC, kSegCols));
+    int32_t* cand_idx = static_cast<int32_t*>(seg_ws);
+    float* cand_val = reinterpret_cast<float*>(cand_idx + static_cast<int64_t>(n_seg) * rows * sel.topk);
+    SelectParams first = sel;
+    first.seg_cols = kSegCols; first.n_seg = n_seg; first.out_idx = cand_idx; first.out_scores = cand_val;
+    const unsigned blocks = static_cast<unsigned>(cdiv64(rows * n_seg, 4));
+    NSA_CUDA_OK(launch_chained(kChainSmall, select_warp_kernel<32, false>, dim3(blocks), dim3(128), 0, s, first, rows));
+    NSA_LAUNCH_OK("select kernel (segments)");
+    SelectParams merge{};
+    merge.scores = cand_val; merge.cand_ids = cand_idx; merge.NC = static_cast<int64_t>(n_seg) * sel.topk;
+    merge.MG = 1; merge.H = 1; merge.seg_len = sel.topk; merge.seg_stride = rows * sel.topk; merge.topk = sel.topk;
+    merge.out_idx = sel.out_idx; merge.out_scores = sel.out_scores;
+    return launch_select<true>(merge, rows, s);
+  }
   if (sel.NC <= 512) {
     NSA_CUDA_OK(launch_chained(kChainSmall, select_warp_kernel<16, MERGE>, dim3(blocks4), dim3(128), 0, s, sel, rows));
   } else if (sel.NC <= 1024) {
@@ -667,7 +724,8 @@ int check_rows16(const char* what, const void* ptr, const int64_t* stride, int e
 
 int run_score_select(const void* qp, const int64_t* qs, const void* kp, const int64_t* ks, int B,
                      int MG, int H, int D, int64_t NC, int topk, float scale, const Mask& m,
-                     int32_t* out_idx, float* out_scores, float* scores, int dtype, cudaStream_t s) {
+                     int32_t* out_idx, float* out_scores, float* scores, int dtype, cudaStream_t s,
+                     void* seg_ws = nullptr) {
   ScoreParams sp{static_cast<const char*>(qp), qs[0], qs[1], qs[2], static_cast<const char*>(kp),
                  ks[0], ks[1], ks[2], scores, MG, H, D, NC, scale};
   const size_t smem = (static_cast<size_t>(kScoreCols) * (D + 1) + static_cast<size_t>(kScoreRows) * D) * sizeof(float);
@@ -694,8 +752,7 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
   sel.scores = scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
   sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
   sel.mask = m;
-  return launch_select<false>(sel, static_cast<int64_t>(B) * MG * H, s);
-  return NSA_OK;
+  return launch_select<false>(sel, static_cast<int64_t>(B) * MG * H, s, seg_ws);
 }
 
 __global__ void fill_empty_kernel(int32_t* __restrict__ out_idx, float* __restrict__ out_scores, int64_t n) {
@@ -741,8 +798,12 @@ extern "C" int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out
   return launch_pool<float>(p, B, H, NB, s);
 }
 
-extern "C" size_t nsa_topk_workspace_bytes(int32_t B, int32_t MG, int32_t H, int64_t NC) {
+// scores [B,H,MG,NC] fp32, then (rows longer than 1024 columns) the per-segment candidate lists
+static size_t score_bytes(int32_t B, int32_t MG, int32_t H, int64_t NC) {
   return align_up(static_cast<size_t>(B) * MG * H * NC * sizeof(float), 256);
+}
+extern "C" size_t nsa_topk_workspace_bytes(int32_t B, int32_t MG, int32_t H, int64_t NC) {
+  return score_bytes(B, MG, H, NC) + segment_workspace_bytes(static_cast<int64_t>(B) * MG * H, NC);
 }
 
 static int topk_common_checks(int32_t B, int32_t MG, int32_t H, int32_t D, int64_t NC, int32_t topk,
@@ -773,8 +834,9 @@ extern "C" int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const v
               "topk: workspace too small");
   Mask m;
   if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
+  void* seg_ws = NC > kSegCols ? static_cast<char*>(workspace) + score_bytes(B, MG, H, NC) : nullptr;
   return run_score_select(q_pooled, q_stride, k_pooled, k_stride, B, MG, H, D, NC, topk, scale, m,
-                          out_idx, out_scores, static_cast<float*>(workspace), dtype, s);
+                          out_idx, out_scores, static_cast<float*>(workspace), dtype, s, seg_ws);
 }
 
 // Pooling of the raw keys + scoring + selection.  Fused (one pass over K, scores written once) when
@@ -824,7 +886,7 @@ static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], co
   sel.scores = p.scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
   sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
   sel.mask = m;
-  return launch_select<false>(sel, rows, s);
+  return launch_select<false>(sel, rows, s, NC > kSegCols ? static_cast<char*>(workspace) + score_bytes(B, MG, H, NC) : nullptr);
 }
 
 extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,

@@ -38,11 +38,10 @@ def _check(dev, q, k, v, do, ids, bs, chunk, causal, G, what):
     # oracle gradients use the kernel's own out / lse rounding of the forward as the reference does
     dq_r, dk_r, dv_r = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), bs, chunk,
                                        scale, causal, G)
-    n_sel = max(1.0, float(ids.shape[1] * ids.shape[-1]) / max(1, k.shape[1] // bs))
-    assert_close_bf16(dq, dq_r, f"{what} dq", max_abs=4e-2)
-    # dk / dv sum over every group that selected the block: scale the bound with that count
-    assert_close_bf16(dk, dk_r, f"{what} dk", max_abs=2e-2 * max(2.0, n_sel ** 0.5 * 2), mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
-    assert_close_bf16(dv, dv_r, f"{what} dv", max_abs=2e-2 * max(2.0, n_sel ** 0.5 * 2), mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
+    # gradients at the contract's tolerance for outputs AND gradients: max abs 2e-2, mean abs 2e-3
+    assert_close_bf16(dq, dq_r, f"{what} dq")
+    assert_close_bf16(dk, dk_r, f"{what} dk")
+    assert_close_bf16(dv, dv_r, f"{what} dv")
     return out, lse, dq, dk, dv
 
 
@@ -58,9 +57,9 @@ def test_golden_from_reference_naive(dev, golden, name):
     assert_close_bf16(out, d["out"], f"{name} out vs reference naive")
     dq, dk, dv = ops.sel_bwd(q.to(dev), ops.DenseKV(k.to(dev), v.to(dev)), ids.to(dev), out, lse, do.to(dev), bs,
                              chunk, scale, bool(causal), G)
-    assert_close_bf16(dq, d["dq"], f"{name} dq vs reference naive", max_abs=4e-2)
-    assert_close_bf16(dk, d["dk"], f"{name} dk vs reference naive", max_abs=6e-2, mean_abs=4e-3)
-    assert_close_bf16(dv, d["dv"], f"{name} dv vs reference naive", max_abs=6e-2, mean_abs=4e-3)
+    assert_close_bf16(dq, d["dq"], f"{name} dq vs reference naive")
+    assert_close_bf16(dk, d["dk"], f"{name} dk vs reference naive")
+    assert_close_bf16(dv, d["dv"], f"{name} dv vs reference naive")
 
 
 GEOMS = [
@@ -114,10 +113,10 @@ def test_tensor_core_kernel_agrees_with_general_kernel(dev, monkeypatch):
         monkeypatch.delenv("OMNIMEM_B200_BWD_KERNEL")
         dq_t, dl_t = ops.sel_bwd_dq(*bargs)
         assert torch.allclose(dl_t, dl_g, atol=2e-3, rtol=1e-3), f"delta (seed {seed})"
-        assert_close_bf16(dq_t, dq_g, f"tc vs general dq (seed {seed})", max_abs=3e-2, mean_abs=1.5e-3)
+        assert_close_bf16(dq_t, dq_g, f"tc vs general dq (seed {seed})", mean_abs=1.5e-3)
         dq_r, _, _ = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), 64, chunk, None,
                                      causal, 64)
-        assert_close_bf16(dq_t, dq_r, f"tc dq vs oracle (seed {seed})", max_abs=4e-2)
+        assert_close_bf16(dq_t, dq_r, f"tc dq vs oracle (seed {seed})")
         # dK / dV half: tensor-core kernel against the general kernel and the oracle
         NS = -(-N // 64)
         groups, offsets = ops.inverted_index(ids.to(dev), NS, 64, chunk, causal, 64)
@@ -131,12 +130,10 @@ def test_tensor_core_kernel_agrees_with_general_kernel(dev, monkeypatch):
         assert torch.equal(dk_t, dk_t2) and torch.equal(dv_t, dv_t2), "dk/dv not bit-reproducible"
         _, dk_r, dv_r = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), 64, chunk,
                                         None, causal, 64)
-        n_sel = max(1.0, float(ids.shape[1] * T) / NS)
-        bound = 2e-2 * max(2.0, n_sel ** 0.5 * 2)
-        assert_close_bf16(dk_t, dk_g, f"tc vs general dk (seed {seed})", max_abs=bound, mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
-        assert_close_bf16(dv_t, dv_g, f"tc vs general dv (seed {seed})", max_abs=bound, mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
-        assert_close_bf16(dk_t, dk_r, f"tc dk vs oracle (seed {seed})", max_abs=bound, mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
-        assert_close_bf16(dv_t, dv_r, f"tc dv vs oracle (seed {seed})", max_abs=bound, mean_abs=2e-3 * max(1.0, n_sel ** 0.5))
+        assert_close_bf16(dk_t, dk_g, f"tc vs general dk (seed {seed})")
+        assert_close_bf16(dv_t, dv_g, f"tc vs general dv (seed {seed})")
+        assert_close_bf16(dk_t, dk_r, f"tc dk vs oracle (seed {seed})")
+        assert_close_bf16(dv_t, dv_r, f"tc dv vs oracle (seed {seed})")
 
 
 def test_fp16(dev):
@@ -280,9 +277,9 @@ def test_facade_autograd_and_errors(dev):
     dq_r, dk_r, dv_r = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), 64, 128,
                                        None, True, 64)
     assert_close_bf16(out, o_ref, "facade out")
-    assert_close_bf16(qd.grad, dq_r, "facade dq", max_abs=4e-2)
-    assert_close_bf16(kd.grad, dk_r, "facade dk", max_abs=6e-2, mean_abs=4e-3)
-    assert_close_bf16(vd.grad, dv_r, "facade dv", max_abs=6e-2, mean_abs=4e-3)
+    assert_close_bf16(qd.grad, dq_r, "facade dq")
+    assert_close_bf16(kd.grad, dk_r, "facade dk")
+    assert_close_bf16(vd.grad, dv_r, "facade dv")
     with pytest.raises(ValueError, match="out of range"):
         selection_attention(qd, kd, vd, torch.full_like(ids, 99).to(dev), 4, 64, group_size=64)
     with pytest.raises(AssertionError, match="divisible"):
@@ -308,8 +305,8 @@ def test_config1_shape_fp32_tensors(dev):
                                    allow_ragged=True)
     assert out.dtype == torch.float32 and out.shape == q.shape
     o_ref, l_ref = O.selection_fwd(q, k, v, idx.cpu(), 64, 1, None, False, 64)
-    assert_close_bf16(out, o_ref, "config 1 out (fp32 tensors, bf16 operands)", max_abs=3e-2, mean_abs=3e-3)
-    assert torch.allclose(lse.cpu(), l_ref, atol=3e-2)
+    assert_close_bf16(out, o_ref, "config 1 out (fp32 tensors, bf16 operands)")
+    assert torch.allclose(lse.cpu(), l_ref, atol=1e-2)
 
 
 def test_torch_ops_namespace(dev):
@@ -359,7 +356,7 @@ def test_config2_full_size_properties(dev):
     assert torch.allclose(ml, lse, atol=1e-4)
     # property 2: linear in V
     out2, _ = ops.sel_fwd(qd, ops.DenseKV(kd, vd * 2), idx, bs, 1, D ** -0.5, False, G)
-    assert_close_bf16(out2, out.float() * 2, "linearity in V", max_abs=3.2e-2, mean_abs=4e-3)
+    assert_close_bf16(out2, out.float() * 2, "linearity in V")
     # property 3: sum over tokens of dV rows equals P^T dO column sums -> sum(dv) = sum over rows of dO weighted by 1
     dq, dk, dv = ops.sel_bwd(qd, kv, idx, out, lse, dod, bs, 1, D ** -0.5, False, G)
     assert torch.allclose(dv.float().sum((0, 1)), dod.float().sum((0, 1)), rtol=2e-2, atol=1.0)
@@ -372,7 +369,18 @@ def test_config2_full_size_properties(dev):
         assert torch.allclose(lse[:, :, m0:m1].cpu(), l_ref, atol=2e-3)
         dq_r, _, _ = O.selection_bwd(q[:, m0:m1].float(), k.float(), v.float(), ids_g, o_ref, l_ref,
                                      do[:, m0:m1].float(), bs, 1, None, False, G)
-        assert_close_bf16(dq[:, m0:m1], dq_r, f"group {grp} dq", max_abs=4e-2)
+        assert_close_bf16(dq[:, m0:m1], dq_r, f"group {grp} dq")
+    # the whole backward of three heads (first, middle, last) against the oracle: every dK / dV row of
+    # the 32760 tokens, summed over all the groups that selected its block, and all of dQ
+    hs = [0, 5, 11]
+    qh, kh, vh, doh = (t[:, :, hs].float() for t in (q, k, v, do))
+    ids_h = idx[:, :, hs].cpu()
+    o_ref, l_ref = O.selection_fwd(qh, kh, vh, ids_h, bs, 1, None, False, G)
+    dq_r, dk_r, dv_r = O.selection_bwd(qh, kh, vh, ids_h, o_ref, l_ref, doh, bs, 1, None, False, G)
+    assert_close_bf16(out[:, :, hs], o_ref, "config 2 out, heads 0/5/11")
+    assert_close_bf16(dq[:, :, hs], dq_r, "config 2 dq, heads 0/5/11")
+    assert_close_bf16(dk[:, :, hs], dk_r, "config 2 dk, heads 0/5/11")
+    assert_close_bf16(dv[:, :, hs], dv_r, "config 2 dv, heads 0/5/11")
     # top-k parity on the same pooled operands
     from tests.helpers import assert_topk_parity, masked_scores
     s = masked_scores(qp.cpu(), kp.cpu(), D ** -0.5, block_size=bs, chunk_size=frame, chunk_size_k=frame,

@@ -248,14 +248,21 @@ def test_head_group_pooling_before_selection(dev):
     assert torch.equal(same, parallel_nsa_topk(q.to(dev), k.to(dev), T, 64, None, 128, True, group_size=G))
 
 
-def test_topk_many_blocks_uses_global_path(dev):
+@pytest.mark.parametrize("topk,NC,causal", [(32, 9000, False), (100, 9000, False), (16, 16384, True), (16, 1025, True)])
+def test_topk_long_rows(dev, topk, NC, causal):
+    """Rows of more than 1024 key blocks: per-segment lists merged in a second stage (top-k up to 64)
+    or the block-wide kernel (larger top-k); 9000 keys do not fit the shared-memory key cache."""
     g = torch.Generator().manual_seed(10)
-    NC = 9000                                           # more keys than fit the shared-memory key cache
-    q = torch.randn(1, 3, 2, 64, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, 5, 2, 64, generator=g).to(torch.bfloat16)
     k = torch.randn(1, NC, 2, 64, generator=g).to(torch.bfloat16)
-    got = _ops().topk(q.to(dev), k.to(dev), 32, 0.125, 64, 10 ** 6, 10 ** 6, False)
-    s = masked_scores(q, k, 0.125, block_size=64, chunk_size=10 ** 6, chunk_size_k=10 ** 6, causal=False)
-    assert_topk_parity(got, s, 32)
+    chunk = 64 * 2000 if causal else 10 ** 6                # causal: queries of chunk 3 see the first four key chunks
+    got, sc = _ops().topk(q.to(dev), k.to(dev), topk, 0.125, 64, chunk, chunk, causal, q_chunk_offset=3 if causal else 0,
+                          q_group_size=64, return_scores=True)
+    s = masked_scores(q, k, 0.125, block_size=64, chunk_size=chunk, chunk_size_k=chunk, causal=causal,
+                      q_chunk_offset=3 if causal else 0, q_group_size=64)
+    assert_topk_parity(got, s, topk)
+    picked = torch.gather(s.permute(0, 2, 1, 3), -1, got.cpu().long().clamp_min(0))
+    assert torch.allclose(sc.cpu()[got.cpu() >= 0], picked[got.cpu() >= 0], atol=1e-5)
 
 
 def test_sharded_candidates_merge_to_global_topk(dev):
