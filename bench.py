@@ -696,6 +696,13 @@ def run_rollout(args, dist, dev, rank, world, long_video=False):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     secs = t.item()
     mem = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    # where a forward's time goes: a second, bracketed pass over the last chunks (the brackets cost
+    # launches of their own, so the sections add up to more than the timed forward)
+    breakdown = None
+    if rank == 0 and not long_video:
+        tm = R.SectionTimer()
+        prof = R.rollout(model, caches, plan, dev, timer=tm)
+        breakdown = tm.summary_ms(per=prof.forwards)
     out = {"workload": ("config4: 241 latent frames in 3-frame chunks, block cache capped at 48 frames per layer, "
                         "a fresh conditioning tensor every 40 frames" if long_video else
                         "config3: 21 latent frames (480x832, 81 frames) in 3-frame chunks, 4 denoising steps + 1 cache-write forward per chunk"),
@@ -704,6 +711,8 @@ def run_rollout(args, dist, dev, rank, world, long_video=False):
            "latent_frames_per_second": round(world * plan.latent_frames / secs, 3), "seconds": round(secs, 3),
            "forwards": res.forwards, "ms_per_forward": round(secs * 1e3 / res.forwards, 2),
            "rollouts": world, "cache": res.cache, "gpu_mem_gib": round(mem, 1), "device_status_clean": True}
+    if breakdown is not None:
+        out["ms_per_forward_by_section_bracketed"] = breakdown
     del model, caches
     torch.cuda.empty_cache()
     return out

@@ -48,11 +48,13 @@ __device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, 
 }
 
 template <typename T, bool ROPE>
-__global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(128, ROPE ? 6 : 7) cache_append_kernel(const AppendParams p) {
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float s_part[];          // [2][rp][D]
   __shared__ int s_page;
-  const int j = blockIdx.x, h = blockIdx.y;
+  // blockIdx.x = touched block * H + head: the H thread blocks that read the H pieces of the same
+  // source rows are neighbours in launch order (DRAM page locality of the [S, H, D] source)
+  const int j = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const int64_t first_block = p.pos0 / p.page_tokens;
   const int64_t bid = first_block + j;
   const int64_t key = static_cast<int64_t>(h) * p.max_blocks + bid;
@@ -91,7 +93,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const AppendParams p)
   float ak[VEC], av[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) ak[i] = av[i] = 0.f;
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = ROPE ? 2 : 4;
   if (r0 < rp) {
     const char* ksrc = p.k_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
     const char* vsrc = p.v_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
@@ -332,6 +334,7 @@ __global__ void __launch_bounds__(1024) select_victims_kernel(
 // it into shared memory, sorts them there (bitonic) and writes them out in ascending order: tens
 // of microseconds whatever n is.  n is limited by the shared-memory list to kSelectMax victims.
 constexpr int kSelectMax = 16384;
+constexpr int kBatch = 8;               // pages a thread examines per batch of loads
 
 __device__ __forceinline__ unsigned long long victim_key(const int32_t* __restrict__ page_owner,
                                                          const int64_t* __restrict__ page_stamp, int pg,
@@ -362,10 +365,19 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0u;
     __syncthreads();
     const unsigned long long prefix = s_prefix;
-    for (int pg = threadIdx.x; pg < num_pages; pg += blockDim.x) {
-      const unsigned long long k = victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch);
-      if (k == ~0ull) continue;
-      if (byte == 7 || (k >> (8 * (byte + 1))) == prefix) atomicAdd(&s_hist[(k >> (8 * byte)) & 255u], 1u);
+    for (int pg0 = threadIdx.x; pg0 < num_pages; pg0 += kBatch * blockDim.x) {
+      unsigned long long ks[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {                    // the batch's loads are independent: in flight together
+        const int pg = pg0 + u * blockDim.x;
+        ks[u] = pg < num_pages ? victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch) : ~0ull;
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const unsigned long long k = ks[u];
+        if (k == ~0ull) continue;
+        if (byte == 7 || (k >> (8 * (byte + 1))) == prefix) atomicAdd(&s_hist[(k >> (8 * byte)) & 255u], 1u);
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -390,11 +402,19 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
   while (n_pow2 < take) n_pow2 <<= 1;
   for (int i = threadIdx.x; i < n_pow2; i += blockDim.x) s_list[i] = ~0ull;
   __syncthreads();
-  for (int pg = threadIdx.x; pg < num_pages; pg += blockDim.x) {
-    const unsigned long long k = victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch);
-    if (k != ~0ull && k <= threshold) {
-      const int pos = atomicAdd(&s_count, 1);
-      if (pos < n_pow2) s_list[pos] = k;
+  for (int pg0 = threadIdx.x; pg0 < num_pages; pg0 += kBatch * blockDim.x) {
+    unsigned long long ks[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int pg = pg0 + u * blockDim.x;
+      ks[u] = pg < num_pages ? victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch) : ~0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      if (ks[u] != ~0ull && ks[u] <= threshold) {
+        const int pos = atomicAdd(&s_count, 1);
+        if (pos < n_pow2) s_list[pos] = ks[u];
+      }
     }
   }
   __syncthreads();
@@ -566,7 +586,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
               NSA_ERR_INVALID, "cache_append: null pointer");
   NSA_REQUIRE(aligned16(k_new) && aligned16(v_new) && (kv_stride[0] * esz) % 16 == 0 && (kv_stride[1] * esz) % 16 == 0,
               NSA_ERR_LAYOUT, "cache_append: new K/V rows must be 16-byte aligned");
-  NSA_REQUIRE(H <= 65535, NSA_ERR_INVALID, "cache_append: H must be <= 65535");
+  NSA_REQUIRE(static_cast<int64_t>(n_touched_blocks) * H <= 0x7fffffff, NSA_ERR_INVALID, "cache_append: too many blocks");
   AppendParams p{static_cast<const char*>(k_new), static_cast<const char*>(v_new), kv_stride[0], kv_stride[1],
                  S, pos0, n_tokens, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
                  static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
@@ -577,7 +597,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
   }
   const int cpr = D * esz / 16, rp = 128 / cpr;
   const size_t smem = 2 * static_cast<size_t>(rp) * D * sizeof(float);
-  const dim3 grid(n_touched_blocks, H);
+  const dim3 grid(static_cast<unsigned>(n_touched_blocks) * H);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (rope != nullptr) {
     if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, true><<<grid, 128, smem, s>>>(p);

@@ -16,6 +16,7 @@ struct PoolParams {
   char* out; int64_t o_sb, o_sn, o_sh;
   int64_t N;
   int D, size;
+  int H;
 };
 
 template <typename T>
@@ -26,8 +27,10 @@ __global__ void __launch_bounds__(128) pool_rows_kernel(const PoolParams p) {
   chain_release();
   constexpr int VEC = 16 / sizeof(T);
   extern __shared__ float s_part[];                  // [rp][D]
-  const int64_t c = blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // blockIdx.x = run * H + head: the H thread blocks that read the H pieces of the same rows are
+  // neighbours in launch order, so a DRAM page of a [.., H, D] row is used while it is open
+  const int64_t c = blockIdx.x / p.H;
+  const int h = blockIdx.x % p.H, b = blockIdx.z;
   const int lpr = p.D / VEC;                         // threads per row
   const int rp = blockDim.x / lpr;                   // rows in flight
   const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
@@ -234,8 +237,10 @@ __global__ void __launch_bounds__(128, 8) pool_score_kernel(const PoolScoreParam
   float* s_part = reinterpret_cast<float*>(s_raw);                      // [rp][D]
   T* sK = reinterpret_cast<T*>(s_raw + static_cast<size_t>(rp) * D * sizeof(float));   // [8][PITCH] pooled keys
   T* sQ = sK + 8 * PITCH;                                               // [kFusedQRows][PITCH] pooled queries
-  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kFusedCols;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // blockIdx.x = column group * H + head: the H thread blocks that read the H pieces of the same key
+  // rows are neighbours in launch order, so a DRAM page of a [.., H, D] row is used while it is open
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x / p.H) * kFusedCols;
+  const int h = blockIdx.x % p.H, b = blockIdx.z;
   const int ncol = static_cast<int>(p.NC - c0 < kFusedCols ? p.NC - c0 : kFusedCols);
   const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
   if (!p.early_k) chain_wait();
@@ -349,7 +354,7 @@ int launch_pool_score(const PoolScoreParams& p, int B, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(rp) * D * sizeof(float) +
                       static_cast<size_t>(8 + kFusedQRows) * (D + 8) * sizeof(T);
   NSA_CUDA_OK(cudaFuncSetAttribute(pool_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  const dim3 grid(static_cast<unsigned>(cdiv64(p.NC, kFusedCols)), p.H, B);
+  const dim3 grid(static_cast<unsigned>(cdiv64(p.NC, kFusedCols) * p.H), 1, B);
   NSA_CUDA_OK(launch_chained(kChainSmall, pool_score_kernel<T>, grid, dim3(128), smem, s, p));
   NSA_LAUNCH_OK("pool_score_kernel");
   return NSA_OK;
@@ -709,7 +714,7 @@ int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
   const int lpr = p.D / vec;
   const int rp = 128 / lpr;
   const size_t smem = static_cast<size_t>(rp) * p.D * sizeof(float);
-  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB), H, B), dim3(128), smem, s, p));
+  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB * H), 1, B), dim3(128), smem, s, p));
   NSA_LAUNCH_OK("pool_rows_kernel");
   return NSA_OK;
 }
@@ -789,9 +794,9 @@ extern "C" int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out
   if ((rc = check_rows16("pool_rows x", x, x_stride, esz))) return rc;
   NSA_REQUIRE(out != nullptr, NSA_ERR_INVALID, "pool_rows: out is null");
   PoolParams p{static_cast<const char*>(x), x_stride[0], x_stride[1], x_stride[2],
-               static_cast<char*>(out), out_stride[0], out_stride[1], out_stride[2], N, D, size};
+               static_cast<char*>(out), out_stride[0], out_stride[1], out_stride[2], N, D, size, H};
   const int64_t NB = cdiv64(N, size);
-  NSA_REQUIRE(NB <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
+  NSA_REQUIRE(NB * H <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == NSA_BF16) return launch_pool<__nv_bfloat16>(p, B, H, NB, s);
   if (dtype == NSA_F16) return launch_pool<__half>(p, B, H, NB, s);
@@ -859,7 +864,7 @@ static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], co
   const int64_t ps[3] = {NC * H * D, static_cast<int64_t>(H) * D, D};
   const bool pow2_lanes = D == 16 || D == 32 || D == 64 || D == 128 || D == 256;
   const bool fused = rows > 0 && NC > 0 && dtype != NSA_F32 && pow2_lanes && NC <= 0x7fffffff && q_pooled && k &&
-                     aligned16(q_pooled) && (q_stride[0] * 2) % 16 == 0 && (q_stride[1] * 2) % 16 == 0 &&
+                     cdiv64(NC, kFusedCols) * H <= 0x7fffffff && aligned16(q_pooled) && (q_stride[0] * 2) % 16 == 0 && (q_stride[1] * 2) % 16 == 0 &&
                      (q_stride[2] * 2) % 16 == 0 && aligned16(k) && (k_stride[0] * 2) % 16 == 0 &&
                      (k_stride[1] * 2) % 16 == 0 && (k_stride[2] * 2) % 16 == 0;
   if (!fused) {
@@ -877,7 +882,7 @@ static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], co
   if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
   PoolScoreParams p{};
   p.pool = PoolParams{static_cast<const char*>(k), k_stride[0], k_stride[1], k_stride[2],
-                      static_cast<char*>(k_pooled_out), ps[0], ps[1], ps[2], N, D, mask->block_size};
+                      static_cast<char*>(k_pooled_out), ps[0], ps[1], ps[2], N, D, mask->block_size, H};
   p.q = static_cast<const char*>(q_pooled); p.q_sb = q_stride[0]; p.q_sg = q_stride[1]; p.q_sh = q_stride[2];
   p.scores = static_cast<float*>(workspace); p.MG = MG; p.H = H; p.NC = NC; p.scale = scale; p.early_k = early_k;
   rc = dtype == NSA_BF16 ? launch_pool_score<__nv_bfloat16>(p, B, s) : launch_pool_score<__half>(p, B, s);

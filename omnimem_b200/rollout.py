@@ -71,6 +71,50 @@ class RolloutPlan:
     seed: int = 0
 
 
+class SectionTimer:
+    """CUDA-event brackets per named section of a layer, summed over layers and forwards - the role
+    of the reference's TripleAttnProfiler (utils/attn_profiler.py:10-133: cache, cmp, swa, slc_topk,
+    slc_attn).  Off by default: the brackets cost launches of their own."""
+
+    def __init__(self):
+        self.events = {}
+
+    class _Span:
+        def __init__(self, owner, name):
+            self.owner, self.name = owner, name
+
+        def __enter__(self):
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.b = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+        def __exit__(self, *exc):
+            self.b.record()
+            self.owner.events.setdefault(self.name, []).append((self.a, self.b))
+
+    def __call__(self, name):
+        return SectionTimer._Span(self, name)
+
+    def summary_ms(self, per: int = 1) -> dict:
+        """Total milliseconds per section divided by `per` (e.g. the number of forwards)."""
+        torch.cuda.synchronize()
+        return {k: round(sum(a.elapsed_time(b) for a, b in v) / per, 3) for k, v in self.events.items()}
+
+
+class _NoTimer:
+    def __call__(self, name):
+        return self
+
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_TIMER = _NoTimer()
+
+
 def rope_table(max_len: int, dim: int, theta: float = 10000.0) -> torch.Tensor:
     """complex128 [max_len, dim/2] (rope_params, wan_model.py:37-43)."""
     ang = torch.outer(torch.arange(max_len, dtype=torch.float64),
@@ -109,44 +153,56 @@ class NSASelfAttention(nn.Module):
         nn.init.normal_(self.g_proj.weight, mean=0.0, std=1e-3)     # gates start at 0.5 (initialize_gate, :164-168)
         nn.init.zeros_(self.g_proj.bias)
 
-    def forward(self, x, cache: BlockKVCache, rope: RopeSpec, start_token: int, timers=None):
+    def forward(self, x, cache: BlockKVCache, rope: RopeSpec, start_token: int, timer=_NO_TIMER):
         p = self.plan
         _, S, _ = x.shape
         H, D = self.h, self.hd
-        q = self.norm_q(self.q(x)).view(S, H, D)
-        k = self.norm_k(self.k(x)).view(S, H, D)
-        v = self.v(x).view(S, H, D)
-        g = self.g_proj(x).view(1, S, H, 3)
+        with timer("qkv_gate_proj"):
+            q = self.norm_q(self.q(x)).view(S, H, D)
+            k = self.norm_k(self.k(x)).view(S, H, D)
+            v = self.v(x).view(S, H, D)
+            g = self.g_proj(x).view(1, S, H, 3)
         scale = D ** -0.5
         # query rotary embedding; the keys receive theirs on the way into the pages, where they are also
         # pooled: one kernel replaces rope + four cache updates + two poolings of the reference layer
-        qr = rope_apply(q, rope).unsqueeze(0)
-        cache.append(k, v, pos0=start_token, rope=rope)
+        with timer("rope_q"):
+            qr = rope_apply(q, rope).unsqueeze(0)
+        with timer("cache_append"):
+            cache.append(k, v, pos0=start_token, rope=rope)
         nb = cache.n_blocks
         MG = -(-S // p.group)
         dev = x.device
         # compressed branch: attention over the pooled history, run by the selection forward over a
         # dense [1, nb, H, D] view of the pooled keys / values with every block listed
-        t_cmp = -(-nb // p.block)
-        ids_cmp = torch.arange(t_cmp, dtype=torch.int32, device=dev).expand(1, MG, H, t_cmp)
-        o_cmp, _ = ops.sel_fwd(qr, ops.DenseKV(cache.pooled_keys(), cache.pooled_values()), ids_cmp, p.block, 1, scale,
-                               False, p.group)
+        with timer("cmp"):
+            t_cmp = -(-nb // p.block)
+            ids_cmp = torch.arange(t_cmp, dtype=torch.int32, device=dev).expand(1, MG, H, t_cmp)
+            o_cmp, _ = ops.sel_fwd(qr, ops.DenseKV(cache.pooled_keys(), cache.pooled_values()), ids_cmp, p.block, 1,
+                                   scale, False, p.group)
         # sliding-window branch: the pages of the last window_chunks chunks through the block table
-        first_tok = max(0, start_token - (p.window_chunks - 1) * S)
-        first_blk = first_tok // p.block
-        ids_swa = torch.arange(first_blk, nb, dtype=torch.int32, device=dev).expand(1, MG, H, nb - first_blk)
-        o_swa, _ = ops.sel_fwd(qr, cache.kv_source(), ids_swa, p.block, 1, scale, False, p.group)
+        with timer("swa"):
+            first_tok = max(0, start_token - (p.window_chunks - 1) * S)
+            first_blk = first_tok // p.block
+            ids_swa = torch.arange(first_blk, nb, dtype=torch.int32, device=dev).expand(1, MG, H, nb - first_blk)
+            o_swa, _ = ops.sel_fwd(qr, cache.kv_source(), ids_swa, p.block, 1, scale, False, p.group)
         # selection branch
         q_chunk = start_token // S
         if p.progressive_exclude or should_use_selection_attention(nb * p.block, S, p.exclude_window_chunks, 0, causal=False):
-            qp = ops.pool_rows(qr, p.group)
-            idx = ops.topk(qp, cache.pooled_keys(), p.topk, scale, p.block, S, S, False, ex_win=p.exclude_window_chunks,
-                           prog_excl=p.progressive_exclude, q_chunk_offset=q_chunk, q_group_size=p.group)
-            o_slc = cache.selection_attention(qr, idx, scale=scale, group_size=p.group)
+            with timer("slc_topk"):
+                qp = ops.pool_rows(qr, p.group)
+                idx = ops.topk(qp, cache.pooled_keys(), p.topk, scale, p.block, S, S, False,
+                               ex_win=p.exclude_window_chunks, prog_excl=p.progressive_exclude,
+                               q_chunk_offset=q_chunk, q_group_size=p.group)
+            with timer("slc_touch_fetch"):
+                cache.touch(idx)
+            with timer("slc_attn"):
+                o_slc, _ = ops.sel_fwd(qr, cache.kv_source(), idx, p.block, 1, scale, False, p.group)
         else:
             o_slc = torch.zeros_like(qr)
-        y = ops.gate_combine(g, o_cmp, o_slc, o_swa)
-        return self.o(y.view(1, S, H * D))
+        with timer("gate_sum_oproj"):
+            y = ops.gate_combine(g, o_cmp, o_slc, o_swa)
+            out = self.o(y.view(1, S, H * D))
+        return out
 
 
 class CrossAttention(nn.Module):
@@ -178,14 +234,20 @@ class Block(nn.Module):
         self.ffn = nn.Sequential(nn.Linear(d, shape.ffn_dim), nn.GELU(approximate="tanh"), nn.Linear(shape.ffn_dim, d))
         self.modulation = nn.Parameter(torch.randn(1, 6, d) / d ** 0.5)
 
-    def forward(self, x, e0, context, cache, rope, start_token):
+    def forward(self, x, e0, context, cache, rope, start_token, timer=_NO_TIMER):
         e = (self.modulation.float() + e0).unbind(1)                 # six [1, dim] rows (fp32, as the reference)
         d = x.shape[-1]
-        h = (F.layer_norm(x.float(), (d,), eps=self.eps) * (1 + e[1]) + e[0]).to(x.dtype)
-        x = x + (self.self_attn(h, cache, rope, start_token).float() * e[2]).to(x.dtype)
-        x = x + self.cross_attn(self.norm3(x), context)
-        h = (F.layer_norm(x.float(), (d,), eps=self.eps) * (1 + e[4]) + e[3]).to(x.dtype)
-        return x + (self.ffn(h).float() * e[5]).to(x.dtype)
+        with timer("norm_modulation"):
+            h = (F.layer_norm(x.float(), (d,), eps=self.eps) * (1 + e[1]) + e[0]).to(x.dtype)
+        y = self.self_attn(h, cache, rope, start_token, timer)
+        with timer("norm_modulation"):
+            x = x + (y.float() * e[2]).to(x.dtype)
+        with timer("cross_attn"):
+            x = x + self.cross_attn(self.norm3(x), context)
+        with timer("ffn"):
+            h = (F.layer_norm(x.float(), (d,), eps=self.eps) * (1 + e[4]) + e[3]).to(x.dtype)
+            x = x + (self.ffn(h).float() * e[5]).to(x.dtype)
+        return x
 
 
 class CausalWanNSA(nn.Module):
@@ -206,7 +268,7 @@ class CausalWanNSA(nn.Module):
         self.freqs = torch.cat([rope_table(1024, hd - 4 * (hd // 6)), rope_table(1024, 2 * (hd // 6)),
                                 rope_table(1024, 2 * (hd // 6))], dim=1)
 
-    def forward(self, latents, t, context_embedded, start_frame, caches: List[BlockKVCache]):
+    def forward(self, latents, t, context_embedded, start_frame, caches: List[BlockKVCache], timer=_NO_TIMER):
         """latents [1, C, f, h, w]; t scalar timestep; returns the prediction in latent layout."""
         sh = self.shape
         x = self.patch_embedding(latents)
@@ -219,7 +281,7 @@ class CausalWanNSA(nn.Module):
         rope = RopeSpec(self.freqs, (gh, gw), start_frame, (1, 1, 1))
         start_token = start_frame * gh * gw
         for blk, cache in zip(self.blocks, caches):
-            x = blk(x, e0, context_embedded, cache, rope, start_token)
+            x = blk(x, e0, context_embedded, cache, rope, start_token, timer)
         m = (self.head_modulation.float() + e.float().unsqueeze(1)).unbind(1)
         x = (F.layer_norm(x.float(), (sh.dim,), eps=self.head_norm_eps) * (1 + m[1]) + m[0]).to(x.dtype)
         x = self.head(x)                                                # [1, S, out * pf*ph*pw]
@@ -262,8 +324,8 @@ class RolloutResult:
 
 
 @torch.no_grad()
-def rollout(model: CausalWanNSA, caches: List[BlockKVCache], plan: RolloutPlan, device, keep_latents: bool = False
-            ) -> RolloutResult:
+def rollout(model: CausalWanNSA, caches: List[BlockKVCache], plan: RolloutPlan, device, keep_latents: bool = False,
+            timer=_NO_TIMER) -> RolloutResult:
     """The denoising loop of CausalWanT2VPipeline.generate (pipeline_wan_causal.py:349-495): per chunk,
     len(timesteps) denoising forwards (each rewrites the chunk's K/V in the caches), then one forward
     of the clean chunk at t = 0 that leaves the final K/V behind.  Returns the wall time of the loop
@@ -293,7 +355,7 @@ def rollout(model: CausalWanNSA, caches: List[BlockKVCache], plan: RolloutPlan, 
         x0 = x_t
         for i, t in enumerate(plan.timesteps):
             sigma = t / 1000.0
-            v = model(x_t, t, context, start, caches)
+            v = model(x_t, t, context, start, caches, timer)
             forwards += 1
             x0 = (x_t.float() - sigma * v.float()).to(x_t.dtype)               # flow prediction -> clean estimate
             if i + 1 < len(plan.timesteps):
@@ -302,7 +364,7 @@ def rollout(model: CausalWanNSA, caches: List[BlockKVCache], plan: RolloutPlan, 
                 x_t = ((1.0 - s2) * x0.float() + s2 * eps.float()).to(x0.dtype)
         if latents is not None:
             latents[:, :, start:start + plan.frames_per_chunk] = x0
-        model(x0, 0.0, context, start, caches)                                 # cache-write forward on the clean chunk
+        model(x0, 0.0, context, start, caches, timer)                          # cache-write forward on the clean chunk
         forwards += 1
     torch.cuda.synchronize(device)
     dt = time.perf_counter() - t0

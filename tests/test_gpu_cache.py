@@ -338,11 +338,12 @@ def test_victim_selection_by_radix_select_equals_the_rescanning_kernel(dev, monk
     stamp = torch.randint(0, 40, (pages,), generator=g, dtype=torch.int64)
     protect_from, epoch = 1100, 37
     cap = max(n, 1)
+    owner_d, stamp_d = owner.to(dev), stamp.to(dev)
 
     def run():
         victims = torch.full((cap,), -7, dtype=torch.int32, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
-        _lib.call("nsa_cache_select_victims", owner.to(dev).data_ptr(), stamp.to(dev).data_ptr(), pages, MB, protect_from,
+        _lib.call("nsa_cache_select_victims", owner_d.data_ptr(), stamp_d.data_ptr(), pages, MB, protect_from,
                   epoch, n, None, cap, victims.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
         return victims.cpu().tolist(), int(status.item())

@@ -32,8 +32,8 @@ def test_nsa_layer_matches_the_oracle_over_four_chunks(dev):
     gh, gw, S, H = 4, 8, 96, shape.num_heads
     seen = {}
     layer.o.register_forward_pre_hook(lambda m, a: seen.__setitem__("y", a[0].detach()))
-    orig = cache.selection_attention
-    cache.selection_attention = lambda q, idx, **kw: (seen.__setitem__("idx", idx.detach().clone()), orig(q, idx, **kw))[1]
+    orig = cache.touch
+    cache.touch = lambda idx, **kw: (seen.__setitem__("idx", idx.detach().clone()), orig(idx, **kw))[1]
     K_hist, V_hist = [], []
     g = torch.Generator().manual_seed(4)
     with torch.no_grad():
