@@ -19,6 +19,7 @@ struct AppendParams {
   int64_t S, pos0;
   int64_t n_tokens_before;         // tokens the cache held before this call (a rewrite may end before them)
   int H, D, page_tokens, max_blocks, n_touched;
+  int hc;                          // heads per thread block of the append kernel
   char* k_pool; char* v_pool;
   int32_t* block_table; const int32_t* new_pages;
   int32_t* page_owner; int64_t* page_stamp; int64_t epoch;
@@ -47,18 +48,34 @@ __device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, 
   wr = wo * p.pool_w + ws;
 }
 
+// One thread block per (touched block, group of `hc` neighbouring heads).  A thread owns one 16-byte
+// column piece of one head and one quarter of the block's rows, so that the block reads CONTIGUOUS
+// pieces of the [S, H, D] source rows (hc x D elements each) and writes whole page rows; reading one
+// head's 256 bytes out of every source row left the DRAM pages half used.  The pooled key / value of
+// a block written as a whole come from the rows on their way through the registers; a block the call
+// covers only in part is read back from its page.  Sums are fp32: the rows of a quarter in ascending
+// order, then the four quarters in order.
+constexpr int kAppendSlices = 4;
+
 template <typename T, bool ROPE>
-__global__ void __launch_bounds__(128, ROPE ? 6 : 7) cache_append_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p) {
   constexpr int VEC = 16 / sizeof(T);
-  extern __shared__ float s_part[];          // [2][rp][D]
-  __shared__ int s_page;
-  // blockIdx.x = touched block * H + head: the H thread blocks that read the H pieces of the same
-  // source rows are neighbours in launch order (DRAM page locality of the [S, H, D] source)
-  const int j = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  constexpr int UNROLL = ROPE ? 2 : 4;
+  extern __shared__ float s_part[];          // [slices][hc][2][D] partial sums of K and V
+  __shared__ int s_page[64];
+  const int cpr = p.D / VEC;
+  const int j = blockIdx.x;
+  const int h0 = blockIdx.y * p.hc;
+  const int nh = p.H - h0 < p.hc ? p.H - h0 : p.hc;
+  const int per_slice = p.hc * cpr;
+  const int slice = threadIdx.x / per_slice, rem = threadIdx.x % per_slice;
+  const int hl = rem / cpr, col = rem % cpr;
+  const bool live = hl < nh;
+  const int h = h0 + hl;
   const int64_t first_block = p.pos0 / p.page_tokens;
   const int64_t bid = first_block + j;
   const int64_t key = static_cast<int64_t>(h) * p.max_blocks + bid;
-  if (threadIdx.x == 0) {
+  if (live && slice == 0 && col == 0) {
     int page = p.block_table[key];
     if (page < 0) {
       page = p.new_pages ? p.new_pages[static_cast<int64_t>(h) * p.n_touched + j] : -1;
@@ -70,69 +87,62 @@ __global__ void __launch_bounds__(128, ROPE ? 6 : 7) cache_append_kernel(const A
       }
     }
     if (page >= 0) p.page_stamp[page] = p.epoch;
-    s_page = page;
+    s_page[hl] = page;
   }
   __syncthreads();
-  const int page = s_page;
-  if (page < 0) return;
+  const int page = live ? s_page[hl] : -1;
   const int64_t blk0 = bid * p.page_tokens;
   const int64_t lo = max(p.pos0, blk0), hi = min(p.pos0 + p.S, blk0 + p.page_tokens);
-  const int64_t row_bytes = static_cast<int64_t>(p.D) * sizeof(T);
-  char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes;
-  char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes;
-  const int cpr = p.D / VEC;
-  const int nrows = static_cast<int>(hi - lo);
-  const int rp = blockDim.x / cpr;
-  const int col = threadIdx.x % cpr, r0 = threadIdx.x / cpr;
   const int64_t held = min(p.n_tokens_before, blk0 + p.page_tokens);
   const int n_present = static_cast<int>(max(hi, held) - blk0);   // rows the block holds after this call
-  // When the call writes every row the block holds (the common case: a chunk covers whole blocks),
-  // the pooled sums are taken from the rows on their way through the registers; otherwise the page is
-  // read back below.  A thread copies rows r0, r0 + rp, ... of its 16-byte column, the pooling order.
-  const bool whole = lo == blk0 && nrows == n_present;
+  const int row_lo = static_cast<int>(lo - blk0), row_hi = static_cast<int>(hi - blk0);
+  const bool whole = row_lo == 0 && row_hi == n_present;
+  const int rows_per_slice = (p.page_tokens + kAppendSlices - 1) / kAppendSlices;
+  const int s_begin = slice * rows_per_slice, s_end = min(s_begin + rows_per_slice, p.page_tokens);
+  const int64_t row_bytes = static_cast<int64_t>(p.D) * sizeof(T);
   float ak[VEC], av[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) ak[i] = av[i] = 0.f;
-  constexpr int UNROLL = ROPE ? 2 : 4;
-  if (r0 < rp) {
-    const char* ksrc = p.k_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
-    const char* vsrc = p.v_new + ((lo - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
+  if (page >= 0) {
+    char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
+    char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
+    // ---- copy the rows of this thread's quarter that the call writes
+    const int c_begin = max(s_begin, row_lo), c_end = min(s_end, row_hi);
     const int64_t src_row = p.s_stride * sizeof(T);
-    char* kdst = kp + (lo - blk0) * row_bytes + col * 16;
-    char* vdst = vp + (lo - blk0) * row_bytes + col * 16;
-    for (int rb = r0; rb < nrows; rb += UNROLL * rp) {
+    const char* ksrc = p.k_new + ((blk0 - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
+    const char* vsrc = p.v_new + ((blk0 - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
+    for (int rb = c_begin; rb < c_end; rb += UNROLL) {
       uint4 kq[UNROLL], vq[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {                 // all loads of the batch first
-        const int r = rb + u * rp;
-        if (r < nrows) {
-          kq[u] = *reinterpret_cast<const uint4*>(ksrc + r * src_row);
-          vq[u] = *reinterpret_cast<const uint4*>(vsrc + r * src_row);
+        if (rb + u < c_end) {
+          kq[u] = *reinterpret_cast<const uint4*>(ksrc + (rb + u) * src_row);
+          vq[u] = *reinterpret_cast<const uint4*>(vsrc + (rb + u) * src_row);
         }
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
-        const int r = rb + u * rp;
-        if (r >= nrows) continue;
+        const int r = rb + u;
+        if (r >= c_end) continue;
         if (ROPE) {
           int fr, hr, wr;
-          rope_position(p, lo - p.pos0 + r, fr, hr, wr);
+          rope_position(p, blk0 - p.pos0 + r, fr, hr, wr);
           T* e = reinterpret_cast<T*>(&kq[u]);
 #pragma unroll
           for (int i = 0; i < VEC / 2; ++i) {
-            const int j = col * (VEC / 2) + i;                   // complex pair of the head
+            const int jj = col * (VEC / 2) + i;                  // complex pair of the head
             double2 w;
-            if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
-            else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
-            else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
+            if (jj < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + jj];
+            else if (jj < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (jj - p.c_f)];
+            else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (jj - p.c_f - p.c_h)];
             const double xr = static_cast<double>(to_f32<T>(e[2 * i])), xi = static_cast<double>(to_f32<T>(e[2 * i + 1]));
             // float64 product, then float64 -> float32 -> T, as view_as_real(...).type_as(x) does
             e[2 * i] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
             e[2 * i + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
           }
         }
-        *reinterpret_cast<uint4*>(kdst + r * row_bytes) = kq[u];
-        *reinterpret_cast<uint4*>(vdst + r * row_bytes) = vq[u];
+        *reinterpret_cast<uint4*>(kp + r * row_bytes) = kq[u];
+        *reinterpret_cast<uint4*>(vp + r * row_bytes) = vq[u];
         if (whole) {
           const T* ea = reinterpret_cast<const T*>(&kq[u]);
           const T* eb = reinterpret_cast<const T*>(&vq[u]);
@@ -143,13 +153,16 @@ __global__ void __launch_bounds__(128, ROPE ? 6 : 7) cache_append_kernel(const A
     }
   }
   if (!whole) {
+    // pooled key / value over the rows the block now holds, [0, n_present): a rewrite that covers
+    // part of the block leaves the other rows in place, so read the page back (the rows this thread
+    // block just wrote are visible to it after the barrier)
     __syncthreads();
-    // pooled key / value over the tokens the block now holds (rows [0, n_present)): a rewrite that
-    // covers part of the block leaves the other tokens in place
-    if (r0 < rp) {
-      for (int r = r0; r < n_present; r += rp) {
-        const uint4 a = *reinterpret_cast<const uint4*>(kp + r * row_bytes + col * 16);
-        const uint4 b = *reinterpret_cast<const uint4*>(vp + r * row_bytes + col * 16);
+    if (page >= 0) {
+      const char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
+      const char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
+      for (int r = s_begin; r < min(s_end, n_present); ++r) {
+        const uint4 a = *reinterpret_cast<const uint4*>(kp + r * row_bytes);
+        const uint4 b = *reinterpret_cast<const uint4*>(vp + r * row_bytes);
         const T* ea = reinterpret_cast<const T*>(&a);
         const T* eb = reinterpret_cast<const T*>(&b);
 #pragma unroll
@@ -157,22 +170,30 @@ __global__ void __launch_bounds__(128, ROPE ? 6 : 7) cache_append_kernel(const A
       }
     }
   }
-  if (r0 < rp) {
+  if (slice < kAppendSlices) {
+    float* mine = s_part + (static_cast<int64_t>(slice) * p.hc + hl) * 2 * p.D + col * VEC;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      s_part[r0 * p.D + col * VEC + i] = ak[i];
-      s_part[(rp + r0) * p.D + col * VEC + i] = av[i];
-    }
+    for (int i = 0; i < VEC; ++i) { mine[i] = ak[i]; mine[p.D + i] = av[i]; }
   }
   __syncthreads();
-  const float inv = 1.f / static_cast<float>(n_present);
-  T* ok = reinterpret_cast<T*>(p.k_pooled + key * row_bytes);
-  T* ov = reinterpret_cast<T*>(p.v_pooled + key * row_bytes);
-  for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
-    float sk = 0.f, sv = 0.f;
-    for (int r = 0; r < rp; ++r) { sk += s_part[r * p.D + d]; sv += s_part[(rp + r) * p.D + d]; }
-    ok[d] = from_f32<T>(sk * inv);
-    if (p.v_pooled) ov[d] = from_f32<T>(sv * inv);
+  if (slice == 0 && page >= 0) {
+    const float inv = 1.f / static_cast<float>(n_present);
+    uint4 ok, ov;
+    T* ek = reinterpret_cast<T*>(&ok);
+    T* ev = reinterpret_cast<T*>(&ov);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float sk = 0.f, sv = 0.f;
+      for (int sl = 0; sl < kAppendSlices; ++sl) {
+        const float* part = s_part + (static_cast<int64_t>(sl) * p.hc + hl) * 2 * p.D + col * VEC;
+        sk += part[i];
+        sv += part[p.D + i];
+      }
+      ek[i] = from_f32<T>(sk * inv);
+      ev[i] = from_f32<T>(sv * inv);
+    }
+    *reinterpret_cast<uint4*>(p.k_pooled + key * row_bytes + col * 16) = ok;
+    if (p.v_pooled) *reinterpret_cast<uint4*>(p.v_pooled + key * row_bytes + col * 16) = ov;
   }
 }
 
@@ -365,7 +386,8 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0u;
     __syncthreads();
     const unsigned long long prefix = s_prefix;
-    for (int pg0 = threadIdx.x; pg0 < num_pages; pg0 += kBatch * blockDim.x) {
+    for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {     // block-uniform trip count
+      const int pg0 = base + threadIdx.x;
       unsigned long long ks[kBatch];
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {                    // the batch's loads are independent: in flight together
@@ -374,9 +396,13 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
       }
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
+        // one shared-memory atomic per distinct digit of the warp, not per page: the high bytes of the
+        // keys are all alike, and a warp's 32 increments of one counter would run one after the other
         const unsigned long long k = ks[u];
-        if (k == ~0ull) continue;
-        if (byte == 7 || (k >> (8 * (byte + 1))) == prefix) atomicAdd(&s_hist[(k >> (8 * byte)) & 255u], 1u);
+        const bool in = k != ~0ull && (byte == 7 || (k >> (8 * (byte + 1))) == prefix);
+        const unsigned digit = in ? static_cast<unsigned>((k >> (8 * byte)) & 255u) : 256u;
+        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        if (in && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&s_hist[digit], static_cast<unsigned>(__popc(peers)));
       }
     }
     __syncthreads();
@@ -402,7 +428,8 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
   while (n_pow2 < take) n_pow2 <<= 1;
   for (int i = threadIdx.x; i < n_pow2; i += blockDim.x) s_list[i] = ~0ull;
   __syncthreads();
-  for (int pg0 = threadIdx.x; pg0 < num_pages; pg0 += kBatch * blockDim.x) {
+  for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {
+    const int pg0 = base + threadIdx.x;
     unsigned long long ks[kBatch];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
@@ -411,9 +438,15 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      if (ks[u] != ~0ull && ks[u] <= threshold) {
-        const int pos = atomicAdd(&s_count, 1);
-        if (pos < n_pow2) s_list[pos] = ks[u];
+      const bool take_it = ks[u] != ~0ull && ks[u] <= threshold;
+      const unsigned takers = __ballot_sync(0xffffffffu, take_it);       // one counter update per warp
+      if (takers != 0u) {
+        const int lane = threadIdx.x & 31;
+        int first = 0;
+        if (lane == __ffs(takers) - 1) first = atomicAdd(&s_count, __popc(takers));
+        first = __shfl_sync(0xffffffffu, first, __ffs(takers) - 1);
+        const int pos = first + __popc(takers & ((1u << lane) - 1u));
+        if (take_it && pos < n_pow2) s_list[pos] = ks[u];
       }
     }
   }
@@ -588,23 +621,41 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
               NSA_ERR_LAYOUT, "cache_append: new K/V rows must be 16-byte aligned");
   NSA_REQUIRE(static_cast<int64_t>(n_touched_blocks) * H <= 0x7fffffff, NSA_ERR_INVALID, "cache_append: too many blocks");
   AppendParams p{static_cast<const char*>(k_new), static_cast<const char*>(v_new), kv_stride[0], kv_stride[1],
-                 S, pos0, n_tokens, H, D, page_tokens, max_blocks, n_touched_blocks, static_cast<char*>(k_pool),
+                 S, pos0, n_tokens, H, D, page_tokens, max_blocks, n_touched_blocks, H, static_cast<char*>(k_pool),
                  static_cast<char*>(v_pool), block_table, new_pages, page_owner, page_stamp, epoch,
                  static_cast<char*>(k_pooled), static_cast<char*>(v_pooled), status};
   if (rope != nullptr) {
     const int rc = set_rope(rope, S, D, &p);
     if (rc) return rc;
   }
-  const int cpr = D * esz / 16, rp = 128 / cpr;
-  const size_t smem = 2 * static_cast<size_t>(rp) * D * sizeof(float);
-  const dim3 grid(static_cast<unsigned>(n_touched_blocks) * H);
+  // heads per thread block: whole source rows when the touched blocks alone fill the GPU, else the
+  // heads are split (down to 512-byte pieces); 4 row quarters x hc heads x (D / 8) pieces <= 768 threads
+  const int cpr = D * esz / 16;
+  int hc = H;
+  const int min_hc = (512 + D * esz - 1) / (D * esz);
+  while (hc > min_hc && static_cast<int64_t>(n_touched_blocks) * cdiv(H, hc) < 148) hc = cdiv(hc, 2);
+  while (hc > 1 && kAppendSlices * hc * cpr > 768) hc = cdiv(hc, 2);
+  NSA_REQUIRE(kAppendSlices * hc * cpr <= 768 && hc <= 64, NSA_ERR_UNSUPPORTED, "cache_append: head dim %d too wide", D);
+  p.hc = hc;
+  const int threads = kAppendSlices * hc * cpr;
+  const size_t smem = static_cast<size_t>(kAppendSlices) * hc * 2 * D * sizeof(float);
+  const dim3 grid(static_cast<unsigned>(n_touched_blocks), cdiv(H, hc));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024) {
+    if (rope != nullptr) {
+      if (dtype == NSA_BF16) NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      else NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    } else {
+      if (dtype == NSA_BF16) NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      else NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+  }
   if (rope != nullptr) {
-    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, true><<<grid, 128, smem, s>>>(p);
-    else cache_append_kernel<__half, true><<<grid, 128, smem, s>>>(p);
+    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, true><<<grid, threads, smem, s>>>(p);
+    else cache_append_kernel<__half, true><<<grid, threads, smem, s>>>(p);
   } else {
-    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, false><<<grid, 128, smem, s>>>(p);
-    else cache_append_kernel<__half, false><<<grid, 128, smem, s>>>(p);
+    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, false><<<grid, threads, smem, s>>>(p);
+    else cache_append_kernel<__half, false><<<grid, threads, smem, s>>>(p);
   }
   NSA_LAUNCH_OK("cache_append_kernel");
   return NSA_OK;

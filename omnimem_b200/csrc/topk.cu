@@ -11,67 +11,84 @@ namespace nsa {
 namespace {
 
 // ---------------------------------------------------------------------------------- pooling
+// Mean over runs of `size` rows of x [B,N,H,D].  A thread owns one 16-byte column piece of a row of
+// one head and walks the run's rows with kPoolUnroll loads in flight; the threads of a block cover
+// `hc` neighbouring heads, so that a block reads CONTIGUOUS row pieces (whole rows when hc = H):
+// reading one head's 256 bytes out of every row, one thread block per head, left the DRAM pages
+// half used and capped these kernels near 0.55 of the copy bandwidth.  Sums are fp32, rows added in
+// ascending order, one rounding to the input dtype.
 struct PoolParams {
   const char* x; int64_t x_sb, x_sn, x_sh;
   char* out; int64_t o_sb, o_sn, o_sh;
   int64_t N;
   int D, size;
   int H;
+  int hc, hsplit;          // heads per thread block, thread blocks per run (hsplit = ceil(H / hc))
+  int vec_store;           // output rows are 16-byte addressable
 };
 
+constexpr int kPoolUnroll = 8;
+
 template <typename T>
-__global__ void __launch_bounds__(128) pool_rows_kernel(const PoolParams p) {
-  // wait first, release second: a kernel chained behind this one starts only when every kernel in
-  // front of this one has completed, so it may read their results before its own chain_wait()
-  chain_wait();
-  chain_release();
+__device__ __forceinline__ void pool_rows_body(const PoolParams& p, int64_t unit, int b) {
   constexpr int VEC = 16 / sizeof(T);
-  extern __shared__ float s_part[];                  // [rp][D]
-  // blockIdx.x = run * H + head: the H thread blocks that read the H pieces of the same rows are
-  // neighbours in launch order, so a DRAM page of a [.., H, D] row is used while it is open
-  const int64_t c = blockIdx.x / p.H;
-  const int h = blockIdx.x % p.H, b = blockIdx.z;
-  const int lpr = p.D / VEC;                         // threads per row
-  const int rp = blockDim.x / lpr;                   // rows in flight
-  const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
+  const int cpr = p.D / VEC;                                  // 16-byte pieces per head row
+  const int64_t c = unit / p.hsplit;
+  const int h0 = static_cast<int>(unit % p.hsplit) * p.hc;
+  const int nh = p.H - h0 < p.hc ? p.H - h0 : p.hc;
   const int64_t n0 = c * p.size;
   const int n = static_cast<int>(p.N - n0 < p.size ? p.N - n0 : p.size);
-  float acc[VEC];
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-  if (r0 < rp) {
+  const float inv = 1.f / static_cast<float>(n);
+  const int64_t row_bytes = p.x_sn * sizeof(T);
+  for (int item = threadIdx.x; item < nh * cpr; item += blockDim.x) {
+    const int h = h0 + item / cpr, col = item % cpr;
     const char* base = p.x + (b * p.x_sb + n0 * p.x_sn + h * p.x_sh) * sizeof(T) + col * 16;
-    const int64_t row_bytes = p.x_sn * sizeof(T);
-    int r = r0;
-    // four independent 16-byte loads in flight per thread
-    for (; r + 3 * rp < n; r += 4 * rp) {
-      uint4 v[4];
+    float acc[VEC];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(base + (r + u * rp) * row_bytes);
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int r = 0; r < n; r += kPoolUnroll) {
+      uint4 v[kPoolUnroll];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const T* e = reinterpret_cast<const T*>(&v[u]);
+      for (int u = 0; u < kPoolUnroll; ++u)
+        v[u] = r + u < n ? *reinterpret_cast<const uint4*>(base + (r + u) * row_bytes) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+      for (int u = 0; u < kPoolUnroll; ++u) {
+        if (r + u < n) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+        }
       }
     }
-    for (; r < n; r += rp) {
-      const uint4 v = *reinterpret_cast<const uint4*>(base + r * row_bytes);
-      const T* e = reinterpret_cast<const T*>(&v);
+    char* orow = p.out + (b * p.o_sb + c * p.o_sn + h * p.o_sh) * sizeof(T) + col * 16;
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
+    for (int i = 0; i < VEC; ++i) oe[i] = from_f32<T>(acc[i] * inv);
+    if (p.vec_store) {
+      *reinterpret_cast<uint4*>(orow) = o;
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) reinterpret_cast<T*>(orow)[i] = oe[i];
     }
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) s_part[r0 * p.D + col * VEC + i] = acc[i];
   }
-  __syncthreads();
-  const float inv = 1.f / static_cast<float>(n);
-  T* orow = reinterpret_cast<T*>(p.out + (b * p.o_sb + c * p.o_sn + h * p.o_sh) * sizeof(T));
-  for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
-    float s = 0.f;
-    for (int r = 0; r < rp; ++r) s += s_part[r * p.D + d];
-    orow[d] = from_f32<T>(s * inv);
-  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pool_rows_kernel(const PoolParams p) {
+  chain_release();
+  chain_wait();
+  pool_rows_body<T>(p, blockIdx.x, blockIdx.z);
+}
+
+// Two poolings in one launch (the query groups and the key blocks of one selection): thread blocks
+// [0, units_a) serve a, the rest b.
+template <typename T>
+__global__ void __launch_bounds__(256) pool_rows_pair_kernel(const PoolParams a, const PoolParams b, int64_t units_a) {
+  chain_release();
+  chain_wait();
+  if (static_cast<int64_t>(blockIdx.x) < units_a) pool_rows_body<T>(a, blockIdx.x, blockIdx.z);
+  else pool_rows_body<T>(b, blockIdx.x - units_a, blockIdx.z);
 }
 
 // ---------------------------------------------------------------------------------- scoring
@@ -202,161 +219,6 @@ int launch_score_mma(const ScoreParams& sp, int B, cudaStream_t s) {
   const dim3 grid(static_cast<unsigned>(cdiv64(sp.NC, kScoreCols)), cdiv(sp.MG, kScoreMmaRows), sp.H * B);
   NSA_CUDA_OK(launch_chained(kChainSmall, score_mma_kernel<T>, grid, dim3(128), smem, s, sp));
   NSA_LAUNCH_OK("score_mma_kernel");
-  return NSA_OK;
-}
-
-// ------------------------------------------------------------------- fused pooling + scoring
-// One thread block pools kFusedCols consecutive key blocks of one (batch, head) - the HBM-bound part:
-// every key is read exactly once, 16 bytes per load, eight to sixteen loads in flight per thread - keeps the
-// rounded pooled keys in shared memory (and writes them out), and scores them against ALL pooled
-// query rows of the head with the same m16n8k16 products, in the same order, as score_mma_kernel,
-// so the scores carry the same bits.  The pooled queries (MG x D, a few KB per head) come from L2.
-// With early_k the keys are pooled BEFORE the wait on the kernel in front (which then must be one
-// that releases its dependents only after its own wait: the query-group pooling launched by
-// nsa_select_blocks), so that pooling the queries costs no time of its own.
-constexpr int kFusedCols = 4;       // key blocks per thread block (columns 4..7 of the n8 score tile stay zero)
-constexpr int kFusedQRows = 32;     // pooled query rows staged per pass
-
-struct PoolScoreParams {
-  PoolParams pool;                                   // raw keys -> pooled keys [B,NC,H,D]
-  const char* q; int64_t q_sb, q_sg, q_sh;           // pooled queries [B,MG,H,D]
-  float* scores;                                     // [B,H,MG,NC]
-  int MG, H;
-  int64_t NC;
-  float scale;
-  int early_k;
-};
-
-template <typename T>
-__global__ void __launch_bounds__(128, 8) pool_score_kernel(const PoolScoreParams p) {
-  constexpr int VEC = 8;                              // 16-bit elements per 16-byte load
-  constexpr int UNROLL = 8;
-  extern __shared__ __align__(16) char s_raw[];
-  const int D = p.pool.D, PITCH = D + 8;
-  const int lpr = D / VEC, rp = 128 / lpr;
-  float* s_part = reinterpret_cast<float*>(s_raw);                      // [rp][D]
-  T* sK = reinterpret_cast<T*>(s_raw + static_cast<size_t>(rp) * D * sizeof(float));   // [8][PITCH] pooled keys
-  T* sQ = sK + 8 * PITCH;                                               // [kFusedQRows][PITCH] pooled queries
-  // blockIdx.x = column group * H + head: the H thread blocks that read the H pieces of the same key
-  // rows are neighbours in launch order, so a DRAM page of a [.., H, D] row is used while it is open
-  const int64_t c0 = static_cast<int64_t>(blockIdx.x / p.H) * kFusedCols;
-  const int h = blockIdx.x % p.H, b = blockIdx.z;
-  const int ncol = static_cast<int>(p.NC - c0 < kFusedCols ? p.NC - c0 : kFusedCols);
-  const int col = threadIdx.x % lpr, r0 = threadIdx.x / lpr;
-  if (!p.early_k) chain_wait();
-  chain_release();
-
-  const int64_t row_bytes = p.pool.x_sn * sizeof(T);
-  const char* head_base = p.pool.x + (b * p.pool.x_sb + h * p.pool.x_sh) * sizeof(T) + col * 16;
-  // the first UNROLL rows this thread owns of key block j (rows r0, r0 + rp, ...), all loads in flight at once
-  auto issue = [&](int j, uint4 (&v)[UNROLL]) -> int {
-    if (j >= ncol) return 0;
-    const int64_t n0 = (c0 + j) * p.pool.size;
-    const int n = static_cast<int>(p.pool.N - n0 < p.pool.size ? p.pool.N - n0 : p.pool.size);
-    const char* base = head_base + n0 * row_bytes;
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int rr = r0 + u * rp;
-      v[u] = rr < n ? *reinterpret_cast<const uint4*>(base + rr * row_bytes) : make_uint4(0u, 0u, 0u, 0u);
-    }
-    return n;
-  };
-  for (int i = threadIdx.x; i < (8 - kFusedCols) * PITCH; i += blockDim.x) sK[kFusedCols * PITCH + i] = from_f32<T>(0.f);
-
-  // Key blocks are pooled one after the other; a thread has its UNROLL rows of the block in flight at
-  // once (a whole 64 x 128 key block per thread block), and enough thread blocks fit an SM (the
-  // register bound below) to keep the memory system busy while others reduce or score.
-#pragma unroll 1
-  for (int j = 0; j < kFusedCols; ++j) {
-    if (j >= ncol) {                                  // columns past the last key block score nothing
-      for (int d = threadIdx.x; d < D; d += blockDim.x) sK[j * PITCH + d] = from_f32<T>(0.f);
-      continue;
-    }
-    uint4 v[UNROLL];
-    const int n = issue(j, v);
-    float acc[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (r0 + u * rp < n) {                          // rows in ascending order, as pool_rows_kernel adds them
-        const T* e = reinterpret_cast<const T*>(&v[u]);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
-      }
-    }
-    if (n > UNROLL * rp) {                            // key blocks longer than one batch of loads
-      const char* base = head_base + (c0 + j) * p.pool.size * row_bytes;
-      for (int r = r0 + UNROLL * rp; r < n; r += rp) {
-        const uint4 w = *reinterpret_cast<const uint4*>(base + r * row_bytes);
-        const T* e = reinterpret_cast<const T*>(&w);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] += to_f32<T>(e[i]);
-      }
-    }
-    __syncthreads();                                  // s_part of the previous key block has been read
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) s_part[r0 * D + col * VEC + i] = acc[i];
-    __syncthreads();
-    const float inv = 1.f / static_cast<float>(n);
-    T* orow = reinterpret_cast<T*>(p.pool.out + (b * p.pool.o_sb + (c0 + j) * p.pool.o_sn + h * p.pool.o_sh) * sizeof(T));
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-      float sum = 0.f;
-      for (int r = 0; r < rp; ++r) sum += s_part[r * D + d];
-      const T kq = from_f32<T>(sum * inv);
-      orow[d] = kq;
-      sK[j * PITCH + d] = kq;
-    }
-  }
-  if (p.early_k) chain_wait();                        // the pooled queries come from the kernel in front
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
-  const int cpr = D / 8;
-  for (int g0 = 0; g0 < p.MG; g0 += kFusedQRows) {
-    const int nrow = min(kFusedQRows, p.MG - g0);
-    __syncthreads();                                  // sK complete / sQ of the previous pass consumed
-    for (int i = threadIdx.x; i < kFusedQRows * cpr; i += blockDim.x) {
-      const int r = i / cpr, cc = i - r * cpr;
-      const char* qsrc = p.q + (b * p.q_sb + (g0 + r) * p.q_sg + h * p.q_sh) * 2 + cc * 16;
-      cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? qsrc : p.q, r < nrow ? 16 : 0);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    if (warp * 16 < nrow) {                           // two warps, 16 rows each
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      const T* qa = sQ + (warp * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8;
-      const T* kb = sK + gid * PITCH + t4 * 2;
-      for (int kk = 0; kk < D / 16; ++kk) {
-        uint32_t a[4];
-        ldmatrix_x4(a, qa + kk * 16);
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk * 16);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8);
-        mma16816<T>(acc, a, b0, b1);
-      }
-      float* out = p.scores + ((static_cast<int64_t>(b) * p.H + h) * p.MG + g0) * p.NC + c0;
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + gid + 8 * r;
-        if (row < nrow) {
-          const int cc = 2 * t4;
-          if (cc < ncol) out[static_cast<int64_t>(row) * p.NC + cc] = acc[2 * r] * p.scale + 0.f;
-          if (cc + 1 < ncol) out[static_cast<int64_t>(row) * p.NC + cc + 1] = acc[2 * r + 1] * p.scale + 0.f;
-        }
-      }
-    }
-  }
-}
-
-template <typename T>
-int launch_pool_score(const PoolScoreParams& p, int B, cudaStream_t s) {
-  const int D = p.pool.D, rp = 128 / (D / 8);
-  const size_t smem = static_cast<size_t>(rp) * D * sizeof(float) +
-                      static_cast<size_t>(8 + kFusedQRows) * (D + 8) * sizeof(T);
-  NSA_CUDA_OK(cudaFuncSetAttribute(pool_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  const dim3 grid(static_cast<unsigned>(cdiv64(p.NC, kFusedCols) * p.H), 1, B);
-  NSA_CUDA_OK(launch_chained(kChainSmall, pool_score_kernel<T>, grid, dim3(128), smem, s, p));
-  NSA_LAUNCH_OK("pool_score_kernel");
   return NSA_OK;
 }
 
@@ -525,30 +387,13 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
 // order as select_kernel.  Every lane sorts its ITEMS keys once; per round the warp's best key is
 // found with two warp reductions (max of the score half, then max of the id half among the lanes
 // that hold it) and the lane that owned it steps to its next key.
+// One warp selects one row (or one 1024-column segment of it): `srow` holds the row's scores (global
+// or shared memory), `sorted` is the warp's [ITEMS][32] scratch in shared memory.
 template <int ITEMS, bool MERGE>
-__global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
-  chain_release();
-  chain_wait();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + warp;
-  const int n_seg = (!MERGE && p.seg_cols > 0) ? p.n_seg : 1;
-  if (unit >= rows * n_seg) return;
-  const int64_t row = unit / n_seg;
-  const int seg = static_cast<int>(unit - row * n_seg);
-  const int64_t c_off = static_cast<int64_t>(seg) * p.seg_cols;          // 0 unless segmented
-  const int64_t NC = n_seg > 1 ? (p.NC - c_off < p.seg_cols ? p.NC - c_off : p.seg_cols) : p.NC;
-  RowMask rm{};
-  const float* srow;
-  if (MERGE) {
-    srow = p.scores + row * p.seg_len;
-  } else {
-    const int h = static_cast<int>(row % p.H);
-    const int64_t bg = row / p.H;
-    const int g = static_cast<int>(bg % p.MG);
-    const int64_t b = bg / p.MG;
-    rm = make_row_mask(p.mask, g);
-    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC + c_off;
-  }
+__device__ __forceinline__ void warp_select(const SelectParams& p, const float* srow, const RowMask& rm, int64_t NC,
+                                            int64_t c_off, int64_t row, int32_t* oi, float* os,
+                                            unsigned long long (*sorted)[32]) {
+  const int lane = threadIdx.x & 31;
   // all loads first, unconditionally (clamped index), so that they are in flight together
   float vals[ITEMS];
   int cids[ITEMS];
@@ -599,14 +444,10 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
           keys[l] = sw ? x : y;
         }
       }
-  __shared__ unsigned long long s_sorted[4][ITEMS][32];   // [warp][rank][lane]: conflict-free for a warp
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) s_sorted[warp][i][lane] = keys[i];
+  for (int i = 0; i < ITEMS; ++i) sorted[i][lane] = keys[i];      // [rank][lane]: conflict-free for a warp
   unsigned long long local = keys[0];
   int next = 1;
-  const int64_t out_row = n_seg > 1 ? static_cast<int64_t>(seg) * rows + row : row;
-  int32_t* oi = p.out_idx + out_row * p.topk;
-  float* os = p.out_scores ? p.out_scores + out_row * p.topk : nullptr;
   // winners are kept one per lane (round r in lane r % 32) and written 32 at a time
   unsigned long long mine = 0ull;
   auto flush = [&](int first, int n) {
@@ -625,7 +466,7 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     if (lane == (r & 31)) mine = best;
     if ((r & 31) == 31) flush(r - 31, 32);
     if (local == best) {            // keys are unique: exactly one lane owns the winner
-      local = next < ITEMS ? s_sorted[warp][next][lane] : 0ull;
+      local = next < ITEMS ? sorted[next][lane] : 0ull;
       ++next;
     }
   }
@@ -634,6 +475,128 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
     oi[i] = -1;
     if (os) os[i] = -INFINITY;
   }
+}
+
+template <int ITEMS, bool MERGE>
+__global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, int64_t rows) {
+  chain_release();
+  chain_wait();
+  const int warp = threadIdx.x >> 5;
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  const int n_seg = (!MERGE && p.seg_cols > 0) ? p.n_seg : 1;
+  if (unit >= rows * n_seg) return;
+  const int64_t row = unit / n_seg;
+  const int seg = static_cast<int>(unit - row * n_seg);
+  const int64_t c_off = static_cast<int64_t>(seg) * p.seg_cols;          // 0 unless segmented
+  const int64_t NC = n_seg > 1 ? (p.NC - c_off < p.seg_cols ? p.NC - c_off : p.seg_cols) : p.NC;
+  RowMask rm{};
+  const float* srow;
+  if (MERGE) {
+    srow = p.scores + row * p.seg_len;
+  } else {
+    const int h = static_cast<int>(row % p.H);
+    const int64_t bg = row / p.H;
+    const int g = static_cast<int>(bg % p.MG);
+    const int64_t b = bg / p.MG;
+    rm = make_row_mask(p.mask, g);
+    srow = p.scores + ((b * p.H + h) * p.MG + g) * p.NC + c_off;
+  }
+  __shared__ unsigned long long s_sorted[4][ITEMS][32];
+  const int64_t out_row = n_seg > 1 ? static_cast<int64_t>(seg) * rows + row : row;
+  warp_select<ITEMS, MERGE>(p, srow, rm, NC, c_off, row, p.out_idx + out_row * p.topk,
+                            p.out_scores ? p.out_scores + out_row * p.topk : nullptr, s_sorted[warp]);
+}
+
+// ------------------------------------------------------------------- fused scoring + selection
+// For rows of at most kFusedNC key blocks and 16-bit operands: one thread block per (batch, head,
+// kRowTile pooled query rows) stages the head's pooled keys in shared memory (up to kKeysPerRound
+// per round, one cp.async wave each), scores them with the same m16n8k16 products, in the same
+// order, as score_mma_kernel - the scores carry the same bits - keeps the scores in shared memory,
+// and each warp then selects one row.  No score buffer in global memory, one launch instead of two.
+constexpr int kRowTile = 8;
+constexpr int kFusedNC = 1024;
+constexpr int kKeysPerRound = 512;
+
+struct ScoreSelectParams {
+  ScoreParams sc;          // q, k pooled + strides, MG, H, D, NC, scale (scores pointer unused)
+  SelectParams sel;        // topk, out_idx, out_scores, mask (scores pointer unused)
+};
+
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(256) score_select_kernel(const ScoreSelectParams p) {
+  chain_release();
+  chain_wait();
+  extern __shared__ __align__(16) char s_raw[];
+  const int D = p.sc.D, PITCH = D + 8;
+  const int NC = static_cast<int>(p.sc.NC);
+  T* sQ = reinterpret_cast<T*>(s_raw);                                   // [16][PITCH], rows >= nrow zero
+  T* sK = sQ + 16 * PITCH;                                               // [kKeysPerRound][PITCH]
+  float* sS = reinterpret_cast<float*>(sK + kKeysPerRound * PITCH);      // [kRowTile][NC]
+  const int g0 = blockIdx.x * kRowTile;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int nrow = min(kRowTile, p.sc.MG - g0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
+  const int cpr = D / 8;
+  for (int i = threadIdx.x; i < 16 * cpr; i += blockDim.x) {
+    const int r = i / cpr, cc = i - r * cpr;
+    const char* src = p.sc.q + (b * p.sc.q_sb + (g0 + r) * p.sc.q_sg + h * p.sc.q_sh) * 2 + cc * 16;
+    cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? src : p.sc.q, r < nrow ? 16 : 0);
+  }
+  for (int k0 = 0; k0 < NC; k0 += kKeysPerRound) {
+    const int nk = min(kKeysPerRound, NC - k0);
+    const int nk8 = (nk + 7) & ~7;                                       // whole n8 slices, the tail zero-filled
+    if (k0 > 0) __syncthreads();                                         // the previous round's keys are consumed
+    for (int i = threadIdx.x; i < nk8 * cpr; i += blockDim.x) {
+      const int r = i / cpr, cc = i - r * cpr;
+      const char* src = p.sc.k + (b * p.sc.k_sb + static_cast<int64_t>(k0 + r) * p.sc.k_sc + h * p.sc.k_sh) * 2 + cc * 16;
+      cp_async16(sK + r * PITCH + cc * 8, r < nk ? src : p.sc.k, r < nk ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    const T* qa = sQ + (lane & 15) * PITCH + (lane >> 4) * 8;
+    for (int s8 = warp; s8 < nk8 / 8; s8 += 8) {                         // this warp's 8-key slices
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const T* kb = sK + (s8 * 8 + gid) * PITCH + t4 * 2;
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, qa + kk * 16);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8);
+        mma16816<T>(acc, a, b0, b1);
+      }
+      // rows gid (< kRowTile) of the m16 tile are the real ones; rows 8..15 are padding
+      const int c = k0 + s8 * 8 + 2 * t4;
+      if (c < NC) sS[gid * NC + c] = acc[0] * p.sc.scale + 0.f;
+      if (c + 1 < NC) sS[gid * NC + c + 1] = acc[1] * p.sc.scale + 0.f;
+    }
+  }
+  __syncthreads();                                                       // scores complete, key tile dead
+  if (warp < nrow) {
+    const int g = g0 + warp;
+    const RowMask rm = make_row_mask(p.sel.mask, g);
+    const int64_t row = (static_cast<int64_t>(b) * p.sc.MG + g) * p.sc.H + h;
+    unsigned long long (*sorted)[32] = reinterpret_cast<unsigned long long (*)[32]>(sK) + warp * ITEMS;
+    warp_select<ITEMS, false>(p.sel, sS + warp * NC, rm, NC, 0, row, p.sel.out_idx + row * p.sel.topk,
+                              p.sel.out_scores ? p.sel.out_scores + row * p.sel.topk : nullptr, sorted);
+  }
+}
+
+template <typename T>
+int launch_score_select(const ScoreSelectParams& p, int B, cudaStream_t s) {
+  const int D = p.sc.D;
+  const size_t smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * sizeof(T) +
+                      static_cast<size_t>(kRowTile) * p.sc.NC * sizeof(float);
+  const dim3 grid(cdiv(p.sc.MG, kRowTile), p.sc.H, B);
+  if (p.sc.NC <= 512) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 16>, grid, dim3(256), smem, s, p));
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 32>, grid, dim3(256), smem, s, p));
+  }
+  NSA_LAUNCH_OK("score_select_kernel");
+  return NSA_OK;
 }
 
 constexpr int kSegCols = 1024;       // candidates one warp sorts in registers
@@ -708,13 +671,27 @@ int fill_mask_checked(const nsa_topk_mask* in, int MG, int64_t NC, Mask* m) {
   return fill_mask(in, MG, NC, m);
 }
 
+// Heads per thread block: whole rows when there are enough runs to fill the GPU, otherwise the heads
+// are split over several blocks (down to 512-byte pieces) so that short tensors still spread out.
+void plan_pool(PoolParams* p, int64_t NB, int B, int esz) {
+  int hc = p->H;
+  const int min_hc = (512 + p->D * esz - 1) / (p->D * esz);
+  while (hc > min_hc && NB * B * cdiv(p->H, hc) < 2 * 148) hc = cdiv(hc, 2);
+  p->hc = hc;
+  p->hsplit = cdiv(p->H, hc);
+}
+inline int pool_threads(const PoolParams& p, int esz) {
+  const int items = p.hc * (p.D * esz / 16);
+  const int t = (items + 31) / 32 * 32;
+  return t < 32 ? 32 : (t > 256 ? 256 : t);
+}
+
 template <typename T>
-int launch_pool(const PoolParams& p, int B, int H, int64_t NB, cudaStream_t s) {
-  const int vec = 16 / static_cast<int>(sizeof(T));
-  const int lpr = p.D / vec;
-  const int rp = 128 / lpr;
-  const size_t smem = static_cast<size_t>(rp) * p.D * sizeof(float);
-  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_kernel<T>, dim3(static_cast<unsigned>(NB * H), 1, B), dim3(128), smem, s, p));
+int launch_pool(const PoolParams& p, int B, int64_t NB, cudaStream_t s) {
+  const int64_t units = NB * p.hsplit;
+  NSA_REQUIRE(units <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
+  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_kernel<T>, dim3(static_cast<unsigned>(units), 1, B),
+                             dim3(pool_threads(p, sizeof(T))), 0, s, p));
   NSA_LAUNCH_OK("pool_rows_kernel");
   return NSA_OK;
 }
@@ -730,7 +707,7 @@ int check_rows16(const char* what, const void* ptr, const int64_t* stride, int e
 int run_score_select(const void* qp, const int64_t* qs, const void* kp, const int64_t* ks, int B,
                      int MG, int H, int D, int64_t NC, int topk, float scale, const Mask& m,
                      int32_t* out_idx, float* out_scores, float* scores, int dtype, cudaStream_t s,
-                     void* seg_ws = nullptr) {
+                     void* seg_ws = nullptr, bool allow_fused = true) {
   ScoreParams sp{static_cast<const char*>(qp), qs[0], qs[1], qs[2], static_cast<const char*>(kp),
                  ks[0], ks[1], ks[2], scores, MG, H, D, NC, scale};
   const size_t smem = (static_cast<size_t>(kScoreCols) * (D + 1) + static_cast<size_t>(kScoreRows) * D) * sizeof(float);
@@ -739,6 +716,15 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
   const bool mma_ok = dtype != NSA_F32 && D % 16 == 0 && D <= 256 && static_cast<int64_t>(H) * B <= 65535 &&
                       aligned16(qp) && aligned16(kp) && (qs[0] * 2) % 16 == 0 && (qs[1] * 2) % 16 == 0 &&
                       (qs[2] * 2) % 16 == 0 && (ks[0] * 2) % 16 == 0 && (ks[1] * 2) % 16 == 0 && (ks[2] * 2) % 16 == 0;
+  // rows short enough to keep their scores in shared memory: scoring and selection in ONE kernel
+  const size_t fused_smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * NC * 4;
+  if (allow_fused && mma_ok && NC <= kFusedNC && fused_smem <= 200 * 1024 && H <= 65535 && B <= 65535) {
+    ScoreSelectParams fp{};
+    fp.sc = sp;
+    fp.sel.NC = NC; fp.sel.MG = MG; fp.sel.H = H; fp.sel.topk = topk; fp.sel.out_idx = out_idx;
+    fp.sel.out_scores = out_scores; fp.sel.mask = m;
+    return dtype == NSA_BF16 ? launch_score_select<__nv_bfloat16>(fp, B, s) : launch_score_select<__half>(fp, B, s);
+  }
   if (mma_ok) {
     const int rc = dtype == NSA_BF16 ? launch_score_mma<__nv_bfloat16>(sp, B, s) : launch_score_mma<__half>(sp, B, s);
     if (rc) return rc;
@@ -780,27 +766,40 @@ int fill_minus_one(int32_t* out_idx, float* out_scores, int64_t n, cudaStream_t 
 
 using namespace nsa;
 
+static int make_pool_params(const char* what, const void* x, const int64_t x_stride[3], void* out,
+                            const int64_t out_stride[3], int32_t B, int64_t N, int32_t H, int32_t D, int32_t size,
+                            int32_t dtype, PoolParams* p, int64_t* NB) {
+  NSA_REQUIRE(B >= 0 && N >= 0 && H >= 0 && D > 0 && size > 0, NSA_ERR_INVALID, "%s: bad size", what);
+  NSA_REQUIRE(dtype >= NSA_BF16 && dtype <= NSA_F32, NSA_ERR_UNSUPPORTED, "%s: unknown dtype %d", what, dtype);
+  const int esz = dtype_size(dtype);
+  NSA_REQUIRE((D * esz) % 16 == 0 && D * esz / 16 <= 128, NSA_ERR_UNSUPPORTED,
+              "%s: head dim %d not supported (row must be a multiple of 16 bytes, <= 2 KiB)", what, D);
+  *NB = cdiv64(N, size);
+  if (B == 0 || N == 0 || H == 0) return NSA_OK;
+  NSA_REQUIRE(B <= 65535 && H <= 65535, NSA_ERR_INVALID, "%s: B and H must be <= 65535", what);
+  int rc;
+  if ((rc = check_rows16(what, x, x_stride, esz))) return rc;
+  NSA_REQUIRE(out != nullptr, NSA_ERR_INVALID, "%s: out is null", what);
+  *p = PoolParams{static_cast<const char*>(x), x_stride[0], x_stride[1], x_stride[2],
+                  static_cast<char*>(out), out_stride[0], out_stride[1], out_stride[2], N, D, size, H, H, 1, 0};
+  p->vec_store = aligned16(out) && (out_stride[0] * esz) % 16 == 0 && (out_stride[1] * esz) % 16 == 0 &&
+                 (out_stride[2] * esz) % 16 == 0;
+  plan_pool(p, *NB, B, esz);
+  return NSA_OK;
+}
+
 extern "C" int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out,
                              const int64_t out_stride[3], int32_t B, int64_t N, int32_t H, int32_t D,
                              int32_t size, int32_t dtype, void* stream) {
-  NSA_REQUIRE(B >= 0 && N >= 0 && H >= 0 && D > 0 && size > 0, NSA_ERR_INVALID, "pool_rows: bad size");
-  NSA_REQUIRE(dtype >= NSA_BF16 && dtype <= NSA_F32, NSA_ERR_UNSUPPORTED, "pool_rows: unknown dtype %d", dtype);
-  const int esz = dtype_size(dtype);
-  NSA_REQUIRE((D * esz) % 16 == 0 && D * esz / 16 <= 128, NSA_ERR_UNSUPPORTED,
-              "pool_rows: head dim %d not supported (row must be a multiple of 16 bytes, <= 2 KiB)", D);
-  if (B == 0 || N == 0 || H == 0) return NSA_OK;
-  NSA_REQUIRE(B <= 65535 && H <= 65535, NSA_ERR_INVALID, "pool_rows: B and H must be <= 65535");
+  PoolParams p{};
+  int64_t NB = 0;
   int rc;
-  if ((rc = check_rows16("pool_rows x", x, x_stride, esz))) return rc;
-  NSA_REQUIRE(out != nullptr, NSA_ERR_INVALID, "pool_rows: out is null");
-  PoolParams p{static_cast<const char*>(x), x_stride[0], x_stride[1], x_stride[2],
-               static_cast<char*>(out), out_stride[0], out_stride[1], out_stride[2], N, D, size, H};
-  const int64_t NB = cdiv64(N, size);
-  NSA_REQUIRE(NB * H <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
+  if ((rc = make_pool_params("pool_rows x", x, x_stride, out, out_stride, B, N, H, D, size, dtype, &p, &NB))) return rc;
+  if (B == 0 || N == 0 || H == 0) return NSA_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == NSA_BF16) return launch_pool<__nv_bfloat16>(p, B, H, NB, s);
-  if (dtype == NSA_F16) return launch_pool<__half>(p, B, H, NB, s);
-  return launch_pool<float>(p, B, H, NB, s);
+  if (dtype == NSA_BF16) return launch_pool<__nv_bfloat16>(p, B, NB, s);
+  if (dtype == NSA_F16) return launch_pool<__half>(p, B, NB, s);
+  return launch_pool<float>(p, B, NB, s);
 }
 
 // scores [B,H,MG,NC] fp32, then (rows longer than 1024 columns) the per-segment candidate lists
@@ -844,14 +843,13 @@ extern "C" int nsa_topk(const void* q_pooled, const int64_t q_stride[3], const v
                           out_idx, out_scores, static_cast<float*>(workspace), dtype, s, seg_ws);
 }
 
-// Pooling of the raw keys + scoring + selection.  Fused (one pass over K, scores written once) when
-// the operands are 16-bit with a head dim the mma tiles cover; otherwise pooling, scoring and
-// selection run as three kernels.  early_k: see pool_score_kernel.
-static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], const void* k,
-                             const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D, int64_t N,
-                             int32_t topk, float scale, const nsa_topk_mask* mask, void* k_pooled_out,
-                             int32_t* out_idx, float* out_scores, void* workspace, size_t workspace_bytes,
-                             int32_t dtype, int early_k, void* stream) {
+// Pooling of the raw keys, then scoring + selection (one kernel when a row's scores fit shared memory).
+extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
+                                   const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H,
+                                   int32_t D, int64_t N, int32_t topk, float scale,
+                                   const nsa_topk_mask* mask, void* k_pooled_out, int32_t* out_idx,
+                                   float* out_scores, void* workspace, size_t workspace_bytes,
+                                   int32_t dtype, void* stream) {
   NSA_REQUIRE(mask != nullptr && mask->block_size > 0, NSA_ERR_INVALID, "pool_score_topk: mask / block_size");
   NSA_REQUIRE(N >= 0, NSA_ERR_INVALID, "pool_score_topk: N < 0");
   const int64_t NC = cdiv64(N, mask->block_size);
@@ -862,46 +860,13 @@ static int pool_score_select(const void* q_pooled, const int64_t q_stride[3], co
   if (rows == 0 && (NC == 0 || !k_pooled_out)) return NSA_OK;
   NSA_REQUIRE(k_pooled_out != nullptr, NSA_ERR_INVALID, "pool_score_topk: k_pooled_out is null");
   const int64_t ps[3] = {NC * H * D, static_cast<int64_t>(H) * D, D};
-  const bool pow2_lanes = D == 16 || D == 32 || D == 64 || D == 128 || D == 256;
-  const bool fused = rows > 0 && NC > 0 && dtype != NSA_F32 && pow2_lanes && NC <= 0x7fffffff && q_pooled && k &&
-                     cdiv64(NC, kFusedCols) * H <= 0x7fffffff && aligned16(q_pooled) && (q_stride[0] * 2) % 16 == 0 && (q_stride[1] * 2) % 16 == 0 &&
-                     (q_stride[2] * 2) % 16 == 0 && aligned16(k) && (k_stride[0] * 2) % 16 == 0 &&
-                     (k_stride[1] * 2) % 16 == 0 && (k_stride[2] * 2) % 16 == 0;
-  if (!fused) {
-    if (NC > 0) {
-      if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
-    }
-    if (rows == 0) return NSA_OK;
-    if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
-    return nsa_topk(q_pooled, q_stride, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx,
-                    out_scores, workspace, workspace_bytes, dtype, stream);
+  if (NC > 0) {
+    if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
   }
-  NSA_REQUIRE(workspace && workspace_bytes >= nsa_topk_workspace_bytes(B, MG, H, NC), NSA_ERR_WORKSPACE,
-              "pool_score_topk: workspace too small");
-  Mask m;
-  if ((rc = fill_mask_checked(mask, MG, NC, &m))) return rc;
-  PoolScoreParams p{};
-  p.pool = PoolParams{static_cast<const char*>(k), k_stride[0], k_stride[1], k_stride[2],
-                      static_cast<char*>(k_pooled_out), ps[0], ps[1], ps[2], N, D, mask->block_size, H};
-  p.q = static_cast<const char*>(q_pooled); p.q_sb = q_stride[0]; p.q_sg = q_stride[1]; p.q_sh = q_stride[2];
-  p.scores = static_cast<float*>(workspace); p.MG = MG; p.H = H; p.NC = NC; p.scale = scale; p.early_k = early_k;
-  rc = dtype == NSA_BF16 ? launch_pool_score<__nv_bfloat16>(p, B, s) : launch_pool_score<__half>(p, B, s);
-  if (rc) return rc;
-  SelectParams sel{};
-  sel.scores = p.scores; sel.cand_ids = nullptr; sel.NC = NC; sel.MG = MG; sel.H = H;
-  sel.seg_len = 0; sel.seg_stride = 0; sel.topk = topk; sel.out_idx = out_idx; sel.out_scores = out_scores;
-  sel.mask = m;
-  return launch_select<false>(sel, rows, s, NC > kSegCols ? static_cast<char*>(workspace) + score_bytes(B, MG, H, NC) : nullptr);
-}
-
-extern "C" int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
-                                   const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H,
-                                   int32_t D, int64_t N, int32_t topk, float scale,
-                                   const nsa_topk_mask* mask, void* k_pooled_out, int32_t* out_idx,
-                                   float* out_scores, void* workspace, size_t workspace_bytes,
-                                   int32_t dtype, void* stream) {
-  return pool_score_select(q_pooled, q_stride, k, k_stride, B, MG, H, D, N, topk, scale, mask, k_pooled_out,
-                           out_idx, out_scores, workspace, workspace_bytes, dtype, 0, stream);
+  if (rows == 0) return NSA_OK;
+  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+  return nsa_topk(q_pooled, q_stride, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx,
+                  out_scores, workspace, workspace_bytes, dtype, stream);
 }
 
 extern "C" int nsa_select_blocks(const void* q, const int64_t q_stride[3], const void* k,
@@ -909,18 +874,44 @@ extern "C" int nsa_select_blocks(const void* q, const int64_t q_stride[3], const
                                  int64_t N, int32_t topk, float scale, const nsa_topk_mask* mask,
                                  void* q_pooled_out, void* k_pooled_out, int32_t* out_idx, float* out_scores,
                                  void* workspace, size_t workspace_bytes, int32_t dtype, void* stream) {
-  NSA_REQUIRE(mask != nullptr && mask->q_group_size > 0, NSA_ERR_INVALID, "select_blocks: mask / q_group_size");
-  NSA_REQUIRE(M >= 0 && cdiv64(M, mask->q_group_size) <= 0x7fffffff, NSA_ERR_INVALID, "select_blocks: bad M");
-  NSA_REQUIRE(q_pooled_out != nullptr || M == 0, NSA_ERR_INVALID, "select_blocks: q_pooled_out is null");
+  NSA_REQUIRE(mask != nullptr && mask->q_group_size > 0 && mask->block_size > 0, NSA_ERR_INVALID,
+              "select_blocks: mask / q_group_size / block_size");
+  NSA_REQUIRE(M >= 0 && N >= 0 && cdiv64(M, mask->q_group_size) <= 0x7fffffff, NSA_ERR_INVALID, "select_blocks: bad M / N");
   const int32_t MG = static_cast<int32_t>(cdiv64(M, mask->q_group_size));
+  const int64_t NC = cdiv64(N, mask->block_size);
   const int64_t qs[3] = {static_cast<int64_t>(MG) * H * D, static_cast<int64_t>(H) * D, D};
+  const int64_t ps[3] = {NC * H * D, static_cast<int64_t>(H) * D, D};
   int rc;
-  if (M > 0 && (rc = nsa_pool_rows(q, q_stride, q_pooled_out, qs, B, M, H, D, mask->q_group_size, dtype, stream))) return rc;
-  // the kernel in front of the fused one is the query pooling just launched, which releases its
-  // dependents only after its own wait: everything older in the stream, K included, is complete by
-  // the time the fused kernel starts, so it may pool K before it waits for the pooled queries
-  return pool_score_select(q_pooled_out, qs, k, k_stride, B, MG, H, D, N, topk, scale, mask, k_pooled_out, out_idx,
-                           out_scores, workspace, workspace_bytes, dtype, M > 0 ? 1 : 0, stream);
+  if ((rc = topk_common_checks(B, MG, H, D, NC, topk, dtype, out_idx))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // both poolings in ONE launch: neither depends on the other
+  PoolParams pq{}, pk{};
+  int64_t nbq = 0, nbk = 0;
+  const bool have_q = B > 0 && M > 0 && H > 0, have_k = B > 0 && N > 0 && H > 0;
+  NSA_REQUIRE(!have_q || q_pooled_out, NSA_ERR_INVALID, "select_blocks: q_pooled_out is null");
+  NSA_REQUIRE(!have_k || k_pooled_out, NSA_ERR_INVALID, "select_blocks: k_pooled_out is null");
+  if (have_q && (rc = make_pool_params("select_blocks q", q, q_stride, q_pooled_out, qs, B, M, H, D, mask->q_group_size, dtype, &pq, &nbq))) return rc;
+  if (have_k && (rc = make_pool_params("select_blocks k", k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, &pk, &nbk))) return rc;
+  if (have_q && have_k) {
+    const int64_t ua = nbq * pq.hsplit, ub = nbk * pk.hsplit;
+    NSA_REQUIRE(ua + ub <= 0x7fffffff, NSA_ERR_INVALID, "select_blocks: too many runs");
+    const int esz = dtype_size(dtype);
+    const int threads = pool_threads(pq, esz) > pool_threads(pk, esz) ? pool_threads(pq, esz) : pool_threads(pk, esz);
+    const dim3 grid(static_cast<unsigned>(ua + ub), 1, B);
+    if (dtype == NSA_BF16) NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_pair_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, pq, pk, ua));
+    else if (dtype == NSA_F16) NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_pair_kernel<__half>, grid, dim3(threads), 0, s, pq, pk, ua));
+    else NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_pair_kernel<float>, grid, dim3(threads), 0, s, pq, pk, ua));
+    NSA_LAUNCH_OK("pool_rows_pair_kernel");
+  } else if (have_q) {
+    if ((rc = nsa_pool_rows(q, q_stride, q_pooled_out, qs, B, M, H, D, mask->q_group_size, dtype, stream))) return rc;
+  } else if (have_k) {
+    if ((rc = nsa_pool_rows(k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, stream))) return rc;
+  }
+  const int64_t rows = static_cast<int64_t>(B) * MG * H;
+  if (rows == 0) return NSA_OK;
+  if (NC == 0) return fill_minus_one(out_idx, out_scores, rows * topk, s);
+  return nsa_topk(q_pooled_out, qs, k_pooled_out, ps, B, MG, H, D, NC, topk, scale, mask, out_idx, out_scores,
+                  workspace, workspace_bytes, dtype, stream);
 }
 
 extern "C" int nsa_merge_candidates(const int32_t* idx, const float* scores, int32_t R, int64_t rows,
@@ -1000,5 +991,5 @@ extern "C" int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_str
   // Every score the selection reads is written by the scoring kernel of the same call, so nothing
   // in the array has to start at zero and whatever an earlier call left behind is never read.
   return run_score_select(q_pooled, q_stride, k_pooled, k_stride, B, MG, H, D, NC, topk, scale, m, out_idx,
-                          out_scores, scratch, dtype, s);
+                          out_scores, scratch, dtype, s, nullptr, /*allow_fused=*/false);
 }
