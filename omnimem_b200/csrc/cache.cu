@@ -357,15 +357,37 @@ __global__ void __launch_bounds__(1024) select_victims_kernel(
 constexpr int kSelectMax = 16384;
 constexpr int kBatch = 8;               // pages a thread examines per batch of loads
 
-__device__ __forceinline__ unsigned long long victim_key(const int32_t* __restrict__ page_owner,
-                                                         const int64_t* __restrict__ page_stamp, int pg,
-                                                         int max_blocks, int protect_from_bid, int64_t epoch) {
-  const int owner = page_owner[pg];
+__device__ __forceinline__ unsigned long long victim_key_of(int owner, int64_t st, int pg, int max_blocks,
+                                                            int protect_from_bid, int64_t epoch) {
   if (owner < 0) return static_cast<unsigned long long>(pg);           // free: before every owned page
   if (owner % max_blocks >= protect_from_bid) return ~0ull;
-  const int64_t st = page_stamp[pg];
   if (st >= epoch) return ~0ull;
   return (static_cast<unsigned long long>(st + 1) << 24) | static_cast<unsigned>(pg);
+}
+
+// Keys of the kBatch pages pg0, pg0 + stride, ...: both arrays are read for every page, without a
+// branch in between, so that the 2 x kBatch loads are in flight together.
+__device__ __forceinline__ void victim_keys(const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp,
+                                            int pg0, int stride, int num_pages, int max_blocks, int protect_from_bid,
+                                            int64_t epoch, unsigned long long* ks);
+
+__device__ __forceinline__ void victim_keys(const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp,
+                                            int pg0, int stride, int num_pages, int max_blocks, int protect_from_bid,
+                                            int64_t epoch, unsigned long long* ks) {
+  int owner[kBatch];
+  int64_t st[kBatch];
+#pragma unroll
+  for (int u = 0; u < kBatch; ++u) {
+    const int pg = pg0 + u * stride;
+    const int pc = pg < num_pages ? pg : 0;
+    owner[u] = page_owner[pc];
+    st[u] = page_stamp[pc];
+  }
+#pragma unroll
+  for (int u = 0; u < kBatch; ++u) {
+    const int pg = pg0 + u * stride;
+    ks[u] = pg < num_pages ? victim_key_of(owner[u], st[u], pg, max_blocks, protect_from_bid, epoch) : ~0ull;
+  }
 }
 
 __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
@@ -389,11 +411,7 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {     // block-uniform trip count
       const int pg0 = base + threadIdx.x;
       unsigned long long ks[kBatch];
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {                    // the batch's loads are independent: in flight together
-        const int pg = pg0 + u * blockDim.x;
-        ks[u] = pg < num_pages ? victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch) : ~0ull;
-      }
+      victim_keys(page_owner, page_stamp, pg0, blockDim.x, num_pages, max_blocks, protect_from_bid, epoch, ks);
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
         // one shared-memory atomic per distinct digit of the warp, not per page: the high bytes of the
@@ -406,17 +424,39 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
       }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int remaining = s_remaining, digit = 255;
-      unsigned int seen = 0u;
-      for (int d = 0; d < 256; ++d) {
-        if (seen + s_hist[d] >= static_cast<unsigned>(remaining)) { digit = d; break; }
-        seen += s_hist[d];
+    if (threadIdx.x < 32) {
+      // the first digit at which the running count reaches what is still wanted: lane l owns bins
+      // 8l .. 8l+7, a warp scan gives the counts in front of each lane
+      const int lane = threadIdx.x;
+      unsigned int bins[8], mine = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { bins[i] = s_hist[8 * lane + i]; mine += bins[i]; }
+      unsigned int incl = mine;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const unsigned int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
       }
-      if (byte == 7) { unsigned int tot = 0u; for (int d = 0; d < 256; ++d) tot += s_hist[d]; s_total = static_cast<int>(tot); }
-      // fewer candidates than asked for: the loop ran off the end (digit 255, every candidate taken)
-      s_remaining = remaining - static_cast<int>(seen);
-      s_prefix = (prefix << 8) | static_cast<unsigned long long>(digit);
+      const unsigned int total_all = __shfl_sync(0xffffffffu, incl, 31);
+      const unsigned int remaining = static_cast<unsigned int>(s_remaining);
+      const unsigned int before = incl - mine;
+      const bool here = before < remaining && incl >= remaining;        // at most one lane
+      const unsigned int who = __ballot_sync(0xffffffffu, here);
+      if (who == 0u) {
+        // fewer candidates than asked for: every candidate is taken (digit 255)
+        if (lane == 0) { s_remaining = static_cast<int>(remaining - total_all); s_prefix = (prefix << 8) | 255ull; }
+      } else if (here) {
+        unsigned int seen = before;
+        int digit = 8 * lane + 7;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (seen + bins[i] >= remaining) { digit = 8 * lane + i; break; }
+          seen += bins[i];
+        }
+        s_remaining = static_cast<int>(remaining - seen);
+        s_prefix = (prefix << 8) | static_cast<unsigned long long>(digit);
+      }
+      if (byte == 7 && lane == 0) s_total = static_cast<int>(total_all);
     }
     __syncthreads();
   }
@@ -431,11 +471,7 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
   for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {
     const int pg0 = base + threadIdx.x;
     unsigned long long ks[kBatch];
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int pg = pg0 + u * blockDim.x;
-      ks[u] = pg < num_pages ? victim_key(page_owner, page_stamp, pg, max_blocks, protect_from_bid, epoch) : ~0ull;
-    }
+    victim_keys(page_owner, page_stamp, pg0, blockDim.x, num_pages, max_blocks, protect_from_bid, epoch, ks);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const bool take_it = ks[u] != ~0ull && ks[u] <= threshold;

@@ -4,10 +4,14 @@
 //   select_kernel      per (b, group, h) row: top-k by (score desc, id asc) over packed
 //                      64-bit keys, -1 padding; also merges per-shard candidate lists
 #include "common.cuh"
+#include "tc_common.cuh"
 
 #include <mutex>
 
 namespace nsa {
+
+int device_status_address(int32_t** out);     // the sticky status word of the tensor-core kernels (sel_fwd_tc.cu)
+
 namespace {
 
 // ---------------------------------------------------------------------------------- pooling
@@ -79,6 +83,111 @@ __global__ void __launch_bounds__(256) pool_rows_kernel(const PoolParams p) {
   chain_release();
   chain_wait();
   pool_rows_body<T>(p, blockIdx.x, blockIdx.z);
+}
+
+// The same pooling for tensors whose rows are contiguous over the heads (x_sh == D, x_sn == H * D):
+// a thread block owns one run of rows for ALL heads and streams it through shared memory with bulk
+// asynchronous copies (cp.async.bulk, kBulkStages stages of up to 24 KiB, whole rows each), so the
+// bytes in flight are set by shared memory - about 96 KiB per thread block, two blocks per SM - not
+// by registers: with 16-byte register loads these kernels had about 85 KiB per SM in flight and
+// stayed near 0.68 of the copy bandwidth.  Thread i owns 16-byte column piece i of the row, adds the
+// rows in ascending order (fp32) and writes its piece of the pooled row.  A wait that gives up
+// (bounded) raises the sticky device status word.
+constexpr int kBulkStages = 4;
+constexpr int kBulkStageBytes = 24 * 1024;
+
+struct BulkPlan { int rows_per_stage; int threads; size_t smem; };
+
+template <typename T>
+__device__ __forceinline__ void pool_rows_bulk_body(const PoolParams& p, int64_t c, int b, int rows_per_stage,
+                                                    uint8_t* stage0, uint64_t* full, volatile int* abort) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int row_bytes = p.H * p.D * static_cast<int>(sizeof(T));
+  const uint32_t stage_bytes = static_cast<uint32_t>(rows_per_stage) * row_bytes;
+  const int64_t n0 = c * p.size;
+  const int n = static_cast<int>(p.N - n0 < p.size ? p.N - n0 : p.size);
+  const int chunks = (n + rows_per_stage - 1) / rows_per_stage;
+  const char* src = p.x + (b * p.x_sb + n0 * p.x_sn) * sizeof(T);
+  auto issue = [&](int i) {                              // thread 0: chunk i into stage i % kBulkStages
+    const int s = i % kBulkStages;
+    const int r0 = i * rows_per_stage;
+    const uint32_t bytes = static_cast<uint32_t>((n - r0 < rows_per_stage ? n - r0 : rows_per_stage)) * row_bytes;
+    tc::mbar_expect_tx(&full[s], bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(stage0 + static_cast<size_t>(s) * stage_bytes)), "l"(src + static_cast<int64_t>(r0) * row_bytes),
+                   "r"(bytes), "r"(smem_u32(&full[s])) : "memory");
+  };
+  if (threadIdx.x == 0)
+    for (int i = 0; i < chunks && i < kBulkStages; ++i) issue(i);
+  const int items = row_bytes / 16;
+  float acc[2][VEC];                                      // up to two column pieces per thread
+#pragma unroll
+  for (int k = 0; k < 2; ++k)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
+  bool ok = true;
+  for (int i = 0; i < chunks; ++i) {
+    const int s = i % kBulkStages;
+    ok = tc::mbar_wait(&full[s], (i / kBulkStages) & 1, abort);
+    if (!ok) break;
+    const int rows = n - i * rows_per_stage < rows_per_stage ? n - i * rows_per_stage : rows_per_stage;
+    const uint8_t* st = stage0 + static_cast<size_t>(s) * stage_bytes;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int item = threadIdx.x + k * blockDim.x;
+      if (item < items) {
+        for (int r = 0; r < rows; ++r) {
+          const uint4 v = *reinterpret_cast<const uint4*>(st + r * row_bytes + item * 16);
+          const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) acc[k][q] += to_f32<T>(e[q]);
+        }
+      }
+    }
+    __syncthreads();                                      // the stage is consumed: refill it
+    if (threadIdx.x == 0 && i + kBulkStages < chunks) issue(i + kBulkStages);
+  }
+  if (!ok) return;
+  const float inv = 1.f / static_cast<float>(n);
+  const int cpr = p.D / VEC;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int item = threadIdx.x + k * blockDim.x;
+    if (item < items) {
+      const int h = item / cpr, col = item % cpr;
+      char* orow = p.out + (b * p.o_sb + c * p.o_sn + h * p.o_sh) * sizeof(T) + col * 16;
+      uint4 o;
+      T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) oe[q] = from_f32<T>(acc[k][q] * inv);
+      if (p.vec_store) {
+        *reinterpret_cast<uint4*>(orow) = o;
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) reinterpret_cast<T*>(orow)[q] = oe[q];
+      }
+    }
+  }
+}
+
+// One or two poolings per launch: thread blocks [0, units_a) serve a (rows_a rows per stage), the rest b.
+template <typename T>
+__global__ void __launch_bounds__(512) pool_rows_bulk_kernel(const PoolParams a, const PoolParams b, int64_t units_a,
+                                                             int rows_a, int rows_b, int32_t* status) {
+  extern __shared__ __align__(128) uint8_t s_bulk[];
+  __shared__ uint64_t full[kBulkStages];
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kBulkStages; ++i) tc::mbar_init(&full[i], 1);
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  chain_release();
+  chain_wait();
+  if (static_cast<int64_t>(blockIdx.x) < units_a) pool_rows_bulk_body<T>(a, blockIdx.x, blockIdx.z, rows_a, s_bulk, full, &s_abort);
+  else pool_rows_bulk_body<T>(b, blockIdx.x - units_a, blockIdx.z, rows_b, s_bulk, full, &s_abort);
+  if (threadIdx.x == 0 && s_abort) atomicExch(status, NSA_ERR_CUDA);
 }
 
 // Two poolings in one launch (the query groups and the key blocks of one selection): thread blocks
@@ -508,13 +617,18 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
 }
 
 // ------------------------------------------------------------------- fused scoring + selection
-// For rows of at most kFusedNC key blocks and 16-bit operands: one thread block per (batch, head,
-// kRowTile pooled query rows) stages the head's pooled keys in shared memory (up to kKeysPerRound
-// per round, one cp.async wave each), scores them with the same m16n8k16 products, in the same
-// order, as score_mma_kernel - the scores carry the same bits - keeps the scores in shared memory,
-// and each warp then selects one row.  No score buffer in global memory, one launch instead of two.
+// For rows of at most kFusedNC key blocks, top-k up to kFusedTopk and 16-bit operands: one thread
+// block per (batch, head, kRowTile pooled query rows) stages the head's pooled keys in shared
+// memory (up to kKeysPerRound per round, one cp.async wave each), scores them with the same
+// m16n8k16 products, in the same order, as score_mma_kernel - the scores carry the same bits - and
+// keeps the scores in shared memory.  The selection of a row is split over kParts warps (a quarter
+// of the columns each: a fourth of the keys to sort per lane), whose lists one warp then merges like
+// per-shard candidate lists; the chain of dependent warp reductions that bounds a one-warp selection
+// shrinks accordingly.  No score buffer in global memory, one launch instead of two.
 constexpr int kRowTile = 8;
+constexpr int kParts = 4;
 constexpr int kFusedNC = 1024;
+constexpr int kFusedTopk = 64;
 constexpr int kKeysPerRound = 512;
 
 struct ScoreSelectParams {
@@ -523,19 +637,22 @@ struct ScoreSelectParams {
 };
 
 template <typename T, int ITEMS>
-__global__ void __launch_bounds__(256) score_select_kernel(const ScoreSelectParams p) {
+__global__ void __launch_bounds__(1024, 1) score_select_kernel(const ScoreSelectParams p) {
   chain_release();
   chain_wait();
   extern __shared__ __align__(16) char s_raw[];
   const int D = p.sc.D, PITCH = D + 8;
-  const int NC = static_cast<int>(p.sc.NC);
+  const int NC = static_cast<int>(p.sc.NC), topk = p.sel.topk;
   T* sQ = reinterpret_cast<T*>(s_raw);                                   // [16][PITCH], rows >= nrow zero
-  T* sK = sQ + 16 * PITCH;                                               // [kKeysPerRound][PITCH]
+  T* sK = sQ + 16 * PITCH;                                               // [kKeysPerRound][PITCH]; later the sort scratch
   float* sS = reinterpret_cast<float*>(sK + kKeysPerRound * PITCH);      // [kRowTile][NC]
+  int32_t* sCi = reinterpret_cast<int32_t*>(sS + kRowTile * NC);         // [kRowTile][kParts][topk] candidate ids
+  float* sCv = reinterpret_cast<float*>(sCi + kRowTile * kParts * topk); //   and their scores
   const int g0 = blockIdx.x * kRowTile;
   const int h = blockIdx.y, b = blockIdx.z;
   const int nrow = min(kRowTile, p.sc.MG - g0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
+  const int nwarp = blockDim.x >> 5;
   const int cpr = D / 8;
   for (int i = threadIdx.x; i < 16 * cpr; i += blockDim.x) {
     const int r = i / cpr, cc = i - r * cpr;
@@ -555,7 +672,7 @@ __global__ void __launch_bounds__(256) score_select_kernel(const ScoreSelectPara
     cp_async_wait<0>();
     __syncthreads();
     const T* qa = sQ + (lane & 15) * PITCH + (lane >> 4) * 8;
-    for (int s8 = warp; s8 < nk8 / 8; s8 += 8) {                         // this warp's 8-key slices
+    for (int s8 = warp; s8 < nk8 / 8; s8 += nwarp) {                     // this warp's 8-key slices
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       const T* kb = sK + (s8 * 8 + gid) * PITCH + t4 * 2;
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -572,13 +689,39 @@ __global__ void __launch_bounds__(256) score_select_kernel(const ScoreSelectPara
     }
   }
   __syncthreads();                                                       // scores complete, key tile dead
-  if (warp < nrow) {
-    const int g = g0 + warp;
+  // ---- stage 1: warp (row, part) takes the top-k of its quarter of the row's columns
+  const int row_l = warp / kParts, part = warp % kParts;
+  unsigned long long (*sorted)[32] = reinterpret_cast<unsigned long long (*)[32]>(sK) + warp * ITEMS;
+  if (warp < kRowTile * kParts && row_l < nrow) {
+    const int g = g0 + row_l;
     const RowMask rm = make_row_mask(p.sel.mask, g);
+    const int c_off = part * ITEMS * 32;
+    const int nc_part = NC - c_off < ITEMS * 32 ? NC - c_off : ITEMS * 32;
+    int32_t* oi = sCi + (row_l * kParts + part) * topk;
+    float* os = sCv + (row_l * kParts + part) * topk;
+    if (nc_part > 0) {
+      warp_select<ITEMS, false>(p.sel, sS + row_l * NC + c_off, rm, nc_part, c_off, 0, oi, os, sorted);
+    } else {
+      for (int i = lane; i < topk; i += 32) { oi[i] = -1; os[i] = -INFINITY; }
+    }
+  }
+  __syncthreads();
+  // ---- stage 2: one warp per row merges the kParts lists (same keys, same order)
+  if (warp < kRowTile * kParts && part == 0 && row_l < nrow) {
+    const int g = g0 + row_l;
     const int64_t row = (static_cast<int64_t>(b) * p.sc.MG + g) * p.sc.H + h;
-    unsigned long long (*sorted)[32] = reinterpret_cast<unsigned long long (*)[32]>(sK) + warp * ITEMS;
-    warp_select<ITEMS, false>(p.sel, sS + warp * NC, rm, NC, 0, row, p.sel.out_idx + row * p.sel.topk,
-                              p.sel.out_scores ? p.sel.out_scores + row * p.sel.topk : nullptr, sorted);
+    SelectParams m = p.sel;
+    m.cand_ids = sCi + row_l * kParts * topk;
+    m.seg_len = topk;
+    m.seg_stride = topk;
+    const float* vals = sCv + row_l * kParts * topk;
+    int32_t* oi = p.sel.out_idx + row * topk;
+    float* os = p.sel.out_scores ? p.sel.out_scores + row * topk : nullptr;
+    const RowMask none{};
+    const int64_t n_cand = static_cast<int64_t>(kParts) * topk;
+    if (topk <= 16) warp_select<2, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
+    else if (topk <= 32) warp_select<4, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
+    else warp_select<8, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
   }
 }
 
@@ -586,14 +729,15 @@ template <typename T>
 int launch_score_select(const ScoreSelectParams& p, int B, cudaStream_t s) {
   const int D = p.sc.D;
   const size_t smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * sizeof(T) +
-                      static_cast<size_t>(kRowTile) * p.sc.NC * sizeof(float);
+                      static_cast<size_t>(kRowTile) * p.sc.NC * sizeof(float) +
+                      static_cast<size_t>(kRowTile) * kParts * p.sel.topk * 8;
   const dim3 grid(cdiv(p.sc.MG, kRowTile), p.sc.H, B);
-  if (p.sc.NC <= 512) {
-    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 16>, grid, dim3(256), smem, s, p));
+  if (p.sc.NC <= kParts * 4 * 32) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 4>, grid, dim3(1024), smem, s, p));
   } else {
-    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 32>, grid, dim3(256), smem, s, p));
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 8>, grid, dim3(1024), smem, s, p));
   }
   NSA_LAUNCH_OK("score_select_kernel");
   return NSA_OK;
@@ -696,6 +840,41 @@ int launch_pool(const PoolParams& p, int B, int64_t NB, cudaStream_t s) {
   return NSA_OK;
 }
 
+// Whether the bulk-copy pooling kernel can serve p (rows contiguous over the heads, at most 16 KiB
+// each, 16-byte aligned), and how it would be launched.
+bool bulk_plan(const PoolParams& p, int B, int esz, BulkPlan* plan) {
+  const int64_t row_bytes = static_cast<int64_t>(p.H) * p.D * esz;
+  if (p.x_sh != p.D || p.x_sn != static_cast<int64_t>(p.H) * p.D) return false;
+  if (row_bytes % 16 != 0 || row_bytes > 16 * 1024 || !aligned16(p.x) || (p.x_sb * esz) % 16 != 0) return false;
+  (void)B;
+  int rows = static_cast<int>(kBulkStageBytes / row_bytes);
+  if (rows < 1) rows = 1;
+  if (rows > p.size) rows = p.size;
+  const int items = static_cast<int>(row_bytes / 16);
+  int threads = (items + 31) / 32 * 32;
+  if (threads > 512) threads = ((items + 1) / 2 + 31) / 32 * 32;
+  plan->rows_per_stage = rows;
+  plan->threads = threads;
+  plan->smem = static_cast<size_t>(kBulkStages) * rows * row_bytes;
+  return true;
+}
+
+template <typename T>
+int launch_pool_bulk(const PoolParams& a, const BulkPlan& pa, int64_t units_a, const PoolParams& b, const BulkPlan& pb,
+                     int64_t units_b, int B, cudaStream_t s) {
+  const size_t smem = pa.smem > pb.smem ? pa.smem : pb.smem;
+  const int threads = pa.threads > pb.threads ? pa.threads : pb.threads;
+  int32_t* status = nullptr;
+  int rc;
+  if ((rc = device_status_address(&status))) return rc;
+  NSA_REQUIRE(units_a + units_b <= 0x7fffffff, NSA_ERR_INVALID, "pool_rows: too many runs");
+  NSA_CUDA_OK(cudaFuncSetAttribute(pool_rows_bulk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  NSA_CUDA_OK(launch_chained(kChainSmall, pool_rows_bulk_kernel<T>, dim3(static_cast<unsigned>(units_a + units_b), 1, B),
+                             dim3(threads), smem, s, a, b, units_a, pa.rows_per_stage, pb.rows_per_stage, status));
+  NSA_LAUNCH_OK("pool_rows_bulk_kernel");
+  return NSA_OK;
+}
+
 int check_rows16(const char* what, const void* ptr, const int64_t* stride, int esz) {
   NSA_REQUIRE(ptr != nullptr, NSA_ERR_INVALID, "%s: null pointer", what);
   NSA_REQUIRE(aligned16(ptr), NSA_ERR_LAYOUT, "%s: base address must be 16-byte aligned", what);
@@ -717,8 +896,9 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
                       aligned16(qp) && aligned16(kp) && (qs[0] * 2) % 16 == 0 && (qs[1] * 2) % 16 == 0 &&
                       (qs[2] * 2) % 16 == 0 && (ks[0] * 2) % 16 == 0 && (ks[1] * 2) % 16 == 0 && (ks[2] * 2) % 16 == 0;
   // rows short enough to keep their scores in shared memory: scoring and selection in ONE kernel
-  const size_t fused_smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * NC * 4;
-  if (allow_fused && mma_ok && NC <= kFusedNC && fused_smem <= 200 * 1024 && H <= 65535 && B <= 65535) {
+  const size_t fused_smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * NC * 4 +
+                            static_cast<size_t>(kRowTile) * kParts * topk * 8;
+  if (allow_fused && mma_ok && NC <= kFusedNC && topk <= kFusedTopk && fused_smem <= 200 * 1024 && H <= 65535 && B <= 65535) {
     ScoreSelectParams fp{};
     fp.sc = sp;
     fp.sel.NC = NC; fp.sel.MG = MG; fp.sel.H = H; fp.sel.topk = topk; fp.sel.out_idx = out_idx;
@@ -797,6 +977,12 @@ extern "C" int nsa_pool_rows(const void* x, const int64_t x_stride[3], void* out
   if ((rc = make_pool_params("pool_rows x", x, x_stride, out, out_stride, B, N, H, D, size, dtype, &p, &NB))) return rc;
   if (B == 0 || N == 0 || H == 0) return NSA_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BulkPlan plan;
+  if (bulk_plan(p, B, dtype_size(dtype), &plan)) {
+    if (dtype == NSA_BF16) return launch_pool_bulk<__nv_bfloat16>(p, plan, NB, p, plan, 0, B, s);
+    if (dtype == NSA_F16) return launch_pool_bulk<__half>(p, plan, NB, p, plan, 0, B, s);
+    return launch_pool_bulk<float>(p, plan, NB, p, plan, 0, B, s);
+  }
   if (dtype == NSA_BF16) return launch_pool<__nv_bfloat16>(p, B, NB, s);
   if (dtype == NSA_F16) return launch_pool<__half>(p, B, NB, s);
   return launch_pool<float>(p, B, NB, s);
@@ -892,7 +1078,14 @@ extern "C" int nsa_select_blocks(const void* q, const int64_t q_stride[3], const
   NSA_REQUIRE(!have_k || k_pooled_out, NSA_ERR_INVALID, "select_blocks: k_pooled_out is null");
   if (have_q && (rc = make_pool_params("select_blocks q", q, q_stride, q_pooled_out, qs, B, M, H, D, mask->q_group_size, dtype, &pq, &nbq))) return rc;
   if (have_k && (rc = make_pool_params("select_blocks k", k, k_stride, k_pooled_out, ps, B, N, H, D, mask->block_size, dtype, &pk, &nbk))) return rc;
-  if (have_q && have_k) {
+  BulkPlan bq, bk;
+  if (have_q && have_k && bulk_plan(pq, B, dtype_size(dtype), &bq) && bulk_plan(pk, B, dtype_size(dtype), &bk)) {
+    // the long tensor first: its thread blocks fill the GPU while the short one's trail behind
+    if (dtype == NSA_BF16) rc = launch_pool_bulk<__nv_bfloat16>(pk, bk, nbk, pq, bq, nbq, B, s);
+    else if (dtype == NSA_F16) rc = launch_pool_bulk<__half>(pk, bk, nbk, pq, bq, nbq, B, s);
+    else rc = launch_pool_bulk<float>(pk, bk, nbk, pq, bq, nbq, B, s);
+    if (rc) return rc;
+  } else if (have_q && have_k) {
     const int64_t ua = nbq * pq.hsplit, ub = nbk * pk.hsplit;
     NSA_REQUIRE(ua + ub <= 0x7fffffff, NSA_ERR_INVALID, "select_blocks: too many runs");
     const int esz = dtype_size(dtype);
