@@ -132,23 +132,24 @@ int nsa_topk_static_scratch(const void* q_pooled, const int64_t q_stride[3], con
                             int64_t NC, int32_t topk, float scale, const nsa_topk_mask* mask,
                             int32_t* out_idx, float* out_scores, int32_t dtype, void* stream);
 
-/* Fused block-compressed key scoring: ONE kernel pools the raw keys k [B,N,H,D] block by block
- * (each key is read exactly once; the pooled keys go to k_pooled_out [B,NC,H,D] contiguous, which
- * must not be NULL) and scores them against q_pooled on the spot; a selection kernel follows as a
- * programmatic dependent.  Same outputs, bit for bit, as nsa_pool_rows + nsa_topk.  16-bit
- * operands with D in {16, 32, 64, 128, 256} and 16-byte aligned rows take the fused kernel; every
- * other call runs pooling, scoring and selection as three kernels.
+/* Block-compressed key scoring from the RAW keys: pools k [B,N,H,D] block by block (each key is
+ * read exactly once, streamed through shared memory with bulk asynchronous copies; the pooled
+ * keys go to k_pooled_out [B,NC,H,D] contiguous, which must not be NULL), then scores and selects
+ * as nsa_topk does: for 16-bit operands, D <= 128, NC <= 1024 and topk <= 64 in ONE kernel that
+ * keeps a row's scores in shared memory (no score buffer in global memory), otherwise as a scoring
+ * and a selection kernel.  Same outputs, bit for bit, as nsa_pool_rows + nsa_topk.
  * Replaces pooling + topk_cuda of the two citations above (the score tile + merge of
- * topk.cu:296-439) in one pass over K. */
+ * topk.cu:296-439). */
 int nsa_pool_score_topk(const void* q_pooled, const int64_t q_stride[3], const void* k,
                         const int64_t k_stride[3], int32_t B, int32_t MG, int32_t H, int32_t D,
                         int64_t N, int32_t topk, float scale, const nsa_topk_mask* mask,
                         void* k_pooled_out, int32_t* out_idx, float* out_scores, void* workspace,
                         size_t workspace_bytes, int32_t dtype, void* stream);
 
-/* The whole block selection from the RAW tensors: pools the queries q [B,M,H,D] in groups of
- * mask->q_group_size (-> q_pooled_out [B,MG,H,D] contiguous, MG = ceil(M / q_group_size)), then
- * runs nsa_pool_score_topk, whose fused kernel pools K while the query pooling is still running.
+/* The whole block selection from the RAW tensors: pools the keys k [B,N,H,D] in blocks of
+ * mask->block_size and the queries q [B,M,H,D] in groups of mask->q_group_size (-> q_pooled_out
+ * [B,MG,H,D] contiguous, MG = ceil(M / q_group_size)) in ONE launch, then scores and selects as
+ * nsa_topk does; the kernels follow one another as programmatic dependents.
  * Workspace: nsa_topk_workspace_bytes(B, MG, H, ceil(N / mask->block_size)).
  * Replaces, in one call, the query-group pooling of nsa/ops/index_topk.py:72-79, the key pooling
  * of models/transformers/causal_wan_nsa_model.py:408-409 and topk_cuda (topk.cu:664-808). */

@@ -49,13 +49,13 @@ __device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, 
 }
 
 // One thread block per (touched block, group of `hc` neighbouring heads).  A thread owns one 16-byte
-// column piece of one head and one quarter of the block's rows, so that the block reads CONTIGUOUS
+// column piece of one head and one eighth of the block's rows, so that the block reads CONTIGUOUS
 // pieces of the [S, H, D] source rows (hc x D elements each) and writes whole page rows; reading one
 // head's 256 bytes out of every source row left the DRAM pages half used.  The pooled key / value of
 // a block written as a whole come from the rows on their way through the registers; a block the call
-// covers only in part is read back from its page.  Sums are fp32: the rows of a quarter in ascending
-// order, then the four quarters in order.
-constexpr int kAppendSlices = 4;
+// covers only in part is read back from its page.  Sums are fp32: the rows of a part in ascending
+// order, then the eight parts in order.
+constexpr int kAppendSlices = 8;
 
 template <typename T, bool ROPE>
 __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p) {
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p)
   if (page >= 0) {
     char* kp = p.k_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
     char* vp = p.v_pool + static_cast<int64_t>(page) * p.page_tokens * row_bytes + col * 16;
-    // ---- copy the rows of this thread's quarter that the call writes
+    // ---- copy the rows of this thread's part that the call writes
     const int c_begin = max(s_begin, row_lo), c_end = min(s_end, row_hi);
     const int64_t src_row = p.s_stride * sizeof(T);
     const char* ksrc = p.k_new + ((blk0 - p.pos0) * p.s_stride + h * p.h_stride) * sizeof(T) + col * 16;
@@ -390,6 +390,11 @@ __device__ __forceinline__ void victim_keys(const int32_t* __restrict__ page_own
   }
 }
 
+// PPT > 0: a thread keeps the keys of its PPT pages (page = i * 1024 + thread) in registers, computed
+// once; PPT == 0: any pool size, keys recomputed from the two arrays in every pass.  With one thread
+// block the kernel is bound by the instructions one SM can issue, and the key (two loads, a modulo)
+// costs five times what a pass does with it.
+template <int PPT>
 __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     const int32_t* __restrict__ page_owner, const int64_t* __restrict__ page_stamp, int num_pages,
     int max_blocks, int protect_from_bid, int64_t epoch, int n_host, const int32_t* __restrict__ n_dev,
@@ -398,20 +403,42 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
   __shared__ unsigned int s_hist[256];
   __shared__ unsigned long long s_prefix;
   __shared__ int s_remaining, s_count, s_total;
+  constexpr int kKeep = PPT > 0 ? PPT : 1;
   int n = n_dev ? *n_dev : n_host;
   if (n > cap) n = cap;
   if (n > kSelectMax) n = kSelectMax;                       // the host sends larger requests to the scan kernel
   if (n <= 0) return;
   if (threadIdx.x == 0) { s_prefix = 0ull; s_remaining = n; s_count = 0; s_total = 0; }
+  unsigned long long keep[kKeep];
+  if (PPT > 0) {
+#pragma unroll
+    for (int b0 = 0; b0 < PPT; b0 += kBatch)
+      victim_keys(page_owner, page_stamp, b0 * 1024 + threadIdx.x, 1024, num_pages, max_blocks, protect_from_bid, epoch,
+                  keep + b0);
+  }
+  const int n_batches = PPT > 0 ? PPT / kBatch : (num_pages + kBatch * 1024 - 1) / (kBatch * 1024);
+  // batch bt of this thread's keys (pages (bt * kBatch + u) * 1024 + thread)
+  auto batch = [&](int bt, unsigned long long* ks) {
+    if (PPT > 0) {
+#pragma unroll
+      for (int b0 = 0; b0 < PPT; b0 += kBatch)
+        if (b0 == bt * kBatch) {
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) ks[u] = keep[b0 + u];
+        }
+    } else {
+      victim_keys(page_owner, page_stamp, bt * kBatch * 1024 + threadIdx.x, 1024, num_pages, max_blocks, protect_from_bid,
+                  epoch, ks);
+    }
+  };
   // ---- the n-th smallest key, one byte at a time from the top
   for (int byte = 7; byte >= 0; --byte) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0u;
     __syncthreads();
     const unsigned long long prefix = s_prefix;
-    for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {     // block-uniform trip count
-      const int pg0 = base + threadIdx.x;
+    for (int bt = 0; bt < n_batches; ++bt) {                // block-uniform trip count
       unsigned long long ks[kBatch];
-      victim_keys(page_owner, page_stamp, pg0, blockDim.x, num_pages, max_blocks, protect_from_bid, epoch, ks);
+      batch(bt, ks);
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
         // one shared-memory atomic per distinct digit of the warp, not per page: the high bytes of the
@@ -468,10 +495,9 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
   while (n_pow2 < take) n_pow2 <<= 1;
   for (int i = threadIdx.x; i < n_pow2; i += blockDim.x) s_list[i] = ~0ull;
   __syncthreads();
-  for (int base = 0; base < num_pages; base += kBatch * blockDim.x) {
-    const int pg0 = base + threadIdx.x;
+  for (int bt = 0; bt < n_batches; ++bt) {
     unsigned long long ks[kBatch];
-    victim_keys(page_owner, page_stamp, pg0, blockDim.x, num_pages, max_blocks, protect_from_bid, epoch, ks);
+    batch(bt, ks);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const bool take_it = ks[u] != ~0ull && ks[u] <= threshold;
@@ -665,7 +691,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
     if (rc) return rc;
   }
   // heads per thread block: whole source rows when the touched blocks alone fill the GPU, else the
-  // heads are split (down to 512-byte pieces); 4 row quarters x hc heads x (D / 8) pieces <= 768 threads
+  // heads are split (down to 512-byte pieces); 8 row parts x hc heads x (D / 8) pieces <= 768 threads
   const int cpr = D * esz / 16;
   int hc = H;
   const int min_hc = (512 + D * esz - 1) / (D * esz);
@@ -677,7 +703,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
   const size_t smem = static_cast<size_t>(kAppendSlices) * hc * 2 * D * sizeof(float);
   const dim3 grid(static_cast<unsigned>(n_touched_blocks), cdiv(H, hc));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (smem > 48 * 1024) {
+  if (smem + 1024 > 48 * 1024) {                  // (static shared memory counts against the 48 KiB default)
     if (rope != nullptr) {
       if (dtype == NSA_BF16) NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       else NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -800,9 +826,20 @@ extern "C" int nsa_cache_select_victims(const int32_t* page_owner, const int64_t
     int n_pow2 = 2;
     while (n_pow2 < n_max) n_pow2 <<= 1;
     const size_t smem = static_cast<size_t>(n_pow2) * sizeof(unsigned long long);
-    NSA_CUDA_OK(cudaFuncSetAttribute(select_victims_radix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectMax * 8));
-    select_victims_radix_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
-        page_owner, page_stamp, num_pages, max_blocks, protect_from_bid, epoch, n, n_dev, cap, victims, status);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (num_pages <= 16 * 1024) {
+      NSA_CUDA_OK(cudaFuncSetAttribute(select_victims_radix_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectMax * 8));
+      select_victims_radix_kernel<16><<<1, 1024, smem, st>>>(page_owner, page_stamp, num_pages, max_blocks, protect_from_bid,
+                                                             epoch, n, n_dev, cap, victims, status);
+    } else if (num_pages <= 32 * 1024) {
+      NSA_CUDA_OK(cudaFuncSetAttribute(select_victims_radix_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectMax * 8));
+      select_victims_radix_kernel<32><<<1, 1024, smem, st>>>(page_owner, page_stamp, num_pages, max_blocks, protect_from_bid,
+                                                             epoch, n, n_dev, cap, victims, status);
+    } else {
+      NSA_CUDA_OK(cudaFuncSetAttribute(select_victims_radix_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelectMax * 8));
+      select_victims_radix_kernel<0><<<1, 1024, smem, st>>>(page_owner, page_stamp, num_pages, max_blocks, protect_from_bid,
+                                                            epoch, n, n_dev, cap, victims, status);
+    }
     NSA_LAUNCH_OK("select_victims_radix_kernel");
     return NSA_OK;
   }

@@ -87,14 +87,15 @@ __global__ void __launch_bounds__(256) pool_rows_kernel(const PoolParams p) {
 
 // The same pooling for tensors whose rows are contiguous over the heads (x_sh == D, x_sn == H * D):
 // a thread block owns one run of rows for ALL heads and streams it through shared memory with bulk
-// asynchronous copies (cp.async.bulk, kBulkStages stages of up to 24 KiB, whole rows each), so the
-// bytes in flight are set by shared memory - about 96 KiB per thread block, two blocks per SM - not
+// asynchronous copies (cp.async.bulk, kBulkStages stages of up to 16 KiB, whole rows each), so the
+// bytes in flight are set by shared memory - about 45 KiB per thread block, four or five blocks per SM,
+// enough blocks resident for a selection's 586 runs to start together - not
 // by registers: with 16-byte register loads these kernels had about 85 KiB per SM in flight and
 // stayed near 0.68 of the copy bandwidth.  Thread i owns 16-byte column piece i of the row, adds the
 // rows in ascending order (fp32) and writes its piece of the pooled row.  A wait that gives up
 // (bounded) raises the sticky device status word.
-constexpr int kBulkStages = 4;
-constexpr int kBulkStageBytes = 24 * 1024;
+constexpr int kBulkStages = 3;
+constexpr int kBulkStageBytes = 16 * 1024;
 
 struct BulkPlan { int rows_per_stage; int threads; size_t smem; };
 
@@ -387,6 +388,34 @@ __device__ __forceinline__ bool visible(const Mask& m, const RowMask& r, int bid
   return valid;
 }
 
+// The same rule without the teacher-forcing layout, as three comparisons per block: for one query
+// row the visible blocks are those with lo <= id < hi that do not lie in [win_lo, win_hi) - the
+// chunk conditions of visible() solved for the block id once per row.
+struct RowBounds { int lo, hi, win_lo, win_hi; };
+
+__device__ __forceinline__ int ceil_div_pos(int64_t a, int64_t b) {            // ceil(a / b) for a >= 0, clamped to int
+  const int64_t q = (a + b - 1) / b;
+  return q > 0x7fffffff ? 0x7fffffff : static_cast<int>(q);
+}
+__device__ __forceinline__ RowBounds make_row_bounds(const Mask& m, const RowMask& r) {
+  RowBounds rb{0, 0x7fffffff, 0, 0};
+  const int64_t ck = m.chunk_size_k, bs = m.block_size;
+  if (m.causal) rb.hi = ceil_div_pos((static_cast<int64_t>(r.q_cid) + 1) * ck, bs);      // k_cid <= q_cid
+  if (r.do_excl) {
+    if (m.ex_sink > 0) rb.lo = ceil_div_pos(static_cast<int64_t>(m.ex_sink) * ck, bs);  // k_cid >= ex_sink
+    if (m.ex_win > 0) {
+      const int64_t first = static_cast<int64_t>(r.q_cid) - m.ex_win + 1;               // k_cid >= first is in the window
+      rb.win_lo = first > 0 ? ceil_div_pos(first * ck, bs) : 0;
+      rb.win_hi = m.causal ? 0x7fffffff : ceil_div_pos((static_cast<int64_t>(r.q_cid) + m.ex_win) * ck, bs);
+      if (rb.win_hi < 0) rb.win_hi = 0;
+    }
+  }
+  return rb;
+}
+__device__ __forceinline__ bool visible_in(const RowBounds& rb, int bid) {
+  return bid >= rb.lo && bid < rb.hi && !(bid >= rb.win_lo && bid < rb.win_hi);
+}
+
 // (score, id) -> 64-bit key; a larger key is a better candidate: higher score first, then the
 // lower id.  0 is reserved for "not a candidate".
 __device__ __forceinline__ unsigned long long pack_key(float s, int id) {
@@ -492,12 +521,78 @@ __global__ void __launch_bounds__(128) select_kernel(const SelectParams p) {
   }
 }
 
+#ifdef NSA_SS_TRACE
+// Debug build only: clock64 stamps of thread 0 of thread block (0,0,0) of the fused kernel.
+__device__ long long g_trace_ss[16];
+#define SS_TRACE(slot) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_trace_ss[slot] = clock64(); } while (0)
+#else
+#define SS_TRACE(slot) do { } while (0)
+#endif
+
 // Rows with at most 32*ITEMS candidates: one warp per row, no block-wide barrier.  Same keys and
-// order as select_kernel.  Every lane sorts its ITEMS keys once; per round the warp's best key is
-// found with two warp reductions (max of the score half, then max of the id half among the lanes
-// that hold it) and the lane that owned it steps to its next key.
-// One warp selects one row (or one 1024-column segment of it): `srow` holds the row's scores (global
-// or shared memory), `sorted` is the warp's [ITEMS][32] scratch in shared memory.
+// order as select_kernel.
+//
+// The selection proper: the warp's candidates as packed keys, ITEMS per lane (0 = no candidate);
+// writes the best `topk` in order and pads with -1 / -inf.  `sorted` is the warp's [ITEMS][32]
+// scratch in shared memory.
+template <int ITEMS>
+__device__ __forceinline__ void warp_take_topk(unsigned long long (&keys)[ITEMS], int topk, int32_t* oi, float* os,
+                                               unsigned long long (*sorted)[32]) {
+  const int lane = threadIdx.x & 31;
+  // Each lane sorts its own keys once, largest first (bitonic network, all indices compile-time
+  // constants, so the keys stay in registers), and parks the list in shared memory; a lane that
+  // owns a round's winner then only steps to its next key.
+#pragma unroll
+  for (int k = 2; k <= ITEMS; k <<= 1)
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1)
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long x = keys[i], y = keys[l];
+          const bool sw = ((i & k) == 0) ? (x < y) : (x > y);
+          keys[i] = sw ? y : x;
+          keys[l] = sw ? x : y;
+        }
+      }
+#pragma unroll
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) sorted[i][lane] = keys[i];      // [rank][lane]: conflict-free for a warp
+  // Per round: the best score half by one warp reduction; the lane that holds it owns the winner.
+  // Only when several lanes hold the same score does a second reduction (over the id half) pick
+  // the lowest id.  The owner writes the winner itself and steps to its next key, which it already
+  // holds in a register; the key after that is fetched off the round's dependency chain.
+  unsigned long long local = keys[0];
+  unsigned long long ahead = ITEMS > 1 ? keys[ITEMS > 1 ? 1 : 0] : 0ull;
+  int next = 2;
+  int r = 0;
+  for (; r < topk; ++r) {
+    const uint32_t lhi = static_cast<uint32_t>(local >> 32), llo = static_cast<uint32_t>(local);
+    const uint32_t bhi = __reduce_max_sync(0xffffffffu, lhi);
+    if (bhi == 0u) break;                                  // the score half of a real key is never 0
+    bool owner = lhi == bhi;
+    const uint32_t holders = __ballot_sync(0xffffffffu, owner);
+    if (holders & (holders - 1u)) {                        // a tie on the score: keys are unique, the id half decides
+      const uint32_t blo = __reduce_max_sync(0xffffffffu, owner ? llo : 0u);
+      owner = owner && llo == blo;
+    }
+    if (owner) {
+      oi[r] = key_id(local);
+      if (os) os[r] = key_score(local);
+      local = ahead;
+      ahead = next < ITEMS ? sorted[next < ITEMS ? next : 0][lane] : 0ull;
+      ++next;
+    }
+  }
+  for (int i = r + lane; i < topk; i += 32) {
+    oi[i] = -1;
+    if (os) os[i] = -INFINITY;
+  }
+}
+
+// One warp selects one row (or one 1024-column segment of it): `srow` holds the row's scores (or the
+// candidates' scores when merging lists), masked and packed into keys here.
 template <int ITEMS, bool MERGE>
 __device__ __forceinline__ void warp_select(const SelectParams& p, const float* srow, const RowMask& rm, int64_t NC,
                                             int64_t c_off, int64_t row, int32_t* oi, float* os,
@@ -536,54 +631,7 @@ __device__ __forceinline__ void warp_select(const SelectParams& p, const float* 
     }
     keys[i] = k;
   }
-  // Each lane sorts its own keys once, largest first (bitonic network, all indices compile-time
-  // constants, so the keys stay in registers), and parks the list in shared memory; a lane that
-  // owns a round's winner then only steps to its next key.
-#pragma unroll
-  for (int k = 2; k <= ITEMS; k <<= 1)
-#pragma unroll
-    for (int j = k >> 1; j > 0; j >>= 1)
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) {
-        const int l = i ^ j;
-        if (l > i) {
-          const unsigned long long x = keys[i], y = keys[l];
-          const bool sw = ((i & k) == 0) ? (x < y) : (x > y);
-          keys[i] = sw ? y : x;
-          keys[l] = sw ? x : y;
-        }
-      }
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) sorted[i][lane] = keys[i];      // [rank][lane]: conflict-free for a warp
-  unsigned long long local = keys[0];
-  int next = 1;
-  // winners are kept one per lane (round r in lane r % 32) and written 32 at a time
-  unsigned long long mine = 0ull;
-  auto flush = [&](int first, int n) {
-    if (lane < n) {
-      oi[first + lane] = key_id(mine);
-      if (os) os[first + lane] = key_score(mine);
-    }
-  };
-  int r = 0;
-  for (; r < p.topk; ++r) {
-    const uint32_t lhi = static_cast<uint32_t>(local >> 32), llo = static_cast<uint32_t>(local);
-    const uint32_t bhi = __reduce_max_sync(0xffffffffu, lhi);
-    if (bhi == 0u) break;                                  // the score half of a real key is never 0
-    const uint32_t blo = __reduce_max_sync(0xffffffffu, lhi == bhi ? llo : 0u);
-    const unsigned long long best = (static_cast<unsigned long long>(bhi) << 32) | blo;
-    if (lane == (r & 31)) mine = best;
-    if ((r & 31) == 31) flush(r - 31, 32);
-    if (local == best) {            // keys are unique: exactly one lane owns the winner
-      local = next < ITEMS ? sorted[next][lane] : 0ull;
-      ++next;
-    }
-  }
-  flush(r & ~31, r & 31);
-  for (int i = r + lane; i < p.topk; i += 32) {
-    oi[i] = -1;
-    if (os) os[i] = -INFINITY;
-  }
+  warp_take_topk<ITEMS>(keys, p.topk, oi, os, sorted);
 }
 
 template <int ITEMS, bool MERGE>
@@ -617,127 +665,191 @@ __global__ void __launch_bounds__(128) select_warp_kernel(const SelectParams p, 
 }
 
 // ------------------------------------------------------------------- fused scoring + selection
-// For rows of at most kFusedNC key blocks, top-k up to kFusedTopk and 16-bit operands: one thread
-// block per (batch, head, kRowTile pooled query rows) stages the head's pooled keys in shared
-// memory (up to kKeysPerRound per round, one cp.async wave each), scores them with the same
-// m16n8k16 products, in the same order, as score_mma_kernel - the scores carry the same bits - and
-// keeps the scores in shared memory.  The selection of a row is split over kParts warps (a quarter
-// of the columns each: a fourth of the keys to sort per lane), whose lists one warp then merges like
-// per-shard candidate lists; the chain of dependent warp reductions that bounds a one-warp selection
-// shrinks accordingly.  No score buffer in global memory, one launch instead of two.
+// For rows of at most kFusedNC key blocks, top-k up to kFusedTopk, 16-bit operands and D <= 128: one
+// thread block per (batch, head, kRowTile pooled query rows).
+//   load    every thread copies its 16-byte column of the head's pooled key rows into padded
+//           shared-memory rows (cp.async, up to kKeysPerRound keys per round); the keys complete on
+//           kKeyGroups barriers so that the products of the first keys run while the rest arrive
+//   score   warp w multiplies key tile w (16 keys) with the query tile: m16n8k16 products with the
+//           keys as the 16-row operand and the kRowTile query rows as the 8-column one, so that no
+//           row of a product is padding; the products and their order over the head dimension are
+//           those of score_mma_kernel - the scores carry the same bits - and each score is masked
+//           and packed into its 64-bit key in shared memory on the spot
+//   select  one warp per row sorts its lane's keys and takes the top-k (warp_take_topk)
+// No score buffer in global memory, one launch instead of two.
 constexpr int kRowTile = 8;
-constexpr int kParts = 4;
 constexpr int kFusedNC = 1024;
 constexpr int kFusedTopk = 64;
+constexpr int kFusedD = 128;
 constexpr int kKeysPerRound = 512;
+constexpr int kKeyGroups = 4;
+constexpr int kGroupKeys = kKeysPerRound / kKeyGroups;
+constexpr int kFusedThreads = 1024;
+
 
 struct ScoreSelectParams {
   ScoreParams sc;          // q, k pooled + strides, MG, H, D, NC, scale (scores pointer unused)
   SelectParams sel;        // topk, out_idx, out_scores, mask (scores pointer unused)
 };
 
+// This thread's cp.async copies so far count as one pending arrival on `bar` (no extra count).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <typename T, int ITEMS>
-__global__ void __launch_bounds__(1024, 1) score_select_kernel(const ScoreSelectParams p) {
-  chain_release();
-  chain_wait();
-  extern __shared__ __align__(16) char s_raw[];
+__global__ void __launch_bounds__(kFusedThreads, 1) score_select_kernel(const ScoreSelectParams p, int32_t* status) {
+  extern __shared__ __align__(128) char s_fused[];
+  __shared__ uint64_t s_bar[kKeyGroups];
+  __shared__ int s_abort;
+  __shared__ RowMask s_rm[kRowTile];
+  __shared__ RowBounds s_rb[kRowTile];
   const int D = p.sc.D, PITCH = D + 8;
-  const int NC = static_cast<int>(p.sc.NC), topk = p.sel.topk;
-  T* sQ = reinterpret_cast<T*>(s_raw);                                   // [16][PITCH], rows >= nrow zero
-  T* sK = sQ + 16 * PITCH;                                               // [kKeysPerRound][PITCH]; later the sort scratch
-  float* sS = reinterpret_cast<float*>(sK + kKeysPerRound * PITCH);      // [kRowTile][NC]
-  int32_t* sCi = reinterpret_cast<int32_t*>(sS + kRowTile * NC);         // [kRowTile][kParts][topk] candidate ids
-  float* sCv = reinterpret_cast<float*>(sCi + kRowTile * kParts * topk); //   and their scores
+  const int NC = static_cast<int>(p.sc.NC), NCP = ((NC + 15) & ~15) + 2, topk = p.sel.topk;
+  T* sQ = reinterpret_cast<T*>(s_fused);                                 // [kRowTile][PITCH], rows >= nrow zero
+  T* sK = sQ + kRowTile * PITCH;                                         // [kKeysPerRound][PITCH]; later the sort scratch
+  unsigned long long* sKey = reinterpret_cast<unsigned long long*>(sK + kKeysPerRound * PITCH);   // [kRowTile][NCP]
   const int g0 = blockIdx.x * kRowTile;
   const int h = blockIdx.y, b = blockIdx.z;
   const int nrow = min(kRowTile, p.sc.MG - g0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t4 = lane & 3;
-  const int nwarp = blockDim.x >> 5;
-  const int cpr = D / 8;
-  for (int i = threadIdx.x; i < 16 * cpr; i += blockDim.x) {
-    const int r = i / cpr, cc = i - r * cpr;
-    const char* src = p.sc.q + (b * p.sc.q_sb + (g0 + r) * p.sc.q_sg + h * p.sc.q_sh) * 2 + cc * 16;
-    cp_async16(sQ + r * PITCH + cc * 8, r < nrow ? src : p.sc.q, r < nrow ? 16 : 0);
+  const int nwarp = kFusedThreads / 32;
+  // ---- set-up that touches no input: barriers and the rows' mask constants
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kKeyGroups; ++i) tc::mbar_init(&s_bar[i], kFusedThreads);
+    tc::fence_barrier_init();
   }
-  for (int k0 = 0; k0 < NC; k0 += kKeysPerRound) {
-    const int nk = min(kKeysPerRound, NC - k0);
-    const int nk8 = (nk + 7) & ~7;                                       // whole n8 slices, the tail zero-filled
-    if (k0 > 0) __syncthreads();                                         // the previous round's keys are consumed
-    for (int i = threadIdx.x; i < nk8 * cpr; i += blockDim.x) {
-      const int r = i / cpr, cc = i - r * cpr;
-      const char* src = p.sc.k + (b * p.sc.k_sb + static_cast<int64_t>(k0 + r) * p.sc.k_sc + h * p.sc.k_sh) * 2 + cc * 16;
-      cp_async16(sK + r * PITCH + cc * 8, r < nk ? src : p.sc.k, r < nk ? 16 : 0);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    const T* qa = sQ + (lane & 15) * PITCH + (lane >> 4) * 8;
-    for (int s8 = warp; s8 < nk8 / 8; s8 += nwarp) {                     // this warp's 8-key slices
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      const T* kb = sK + (s8 * 8 + gid) * PITCH + t4 * 2;
-      for (int kk = 0; kk < D / 16; ++kk) {
-        uint32_t a[4];
-        ldmatrix_x4(a, qa + kk * 16);
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb + kk * 16);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kb + kk * 16 + 8);
-        mma16816<T>(acc, a, b0, b1);
-      }
-      // rows gid (< kRowTile) of the m16 tile are the real ones; rows 8..15 are padding
-      const int c = k0 + s8 * 8 + 2 * t4;
-      if (c < NC) sS[gid * NC + c] = acc[0] * p.sc.scale + 0.f;
-      if (c + 1 < NC) sS[gid * NC + c + 1] = acc[1] * p.sc.scale + 0.f;
-    }
+  if (threadIdx.x < kRowTile) {
+    const RowMask rm = make_row_mask(p.sel.mask, g0 + min(static_cast<int>(threadIdx.x), nrow - 1));
+    s_rm[threadIdx.x] = rm;
+    s_rb[threadIdx.x] = make_row_bounds(p.sel.mask, rm);
   }
-  __syncthreads();                                                       // scores complete, key tile dead
-  // ---- stage 1: warp (row, part) takes the top-k of its quarter of the row's columns
-  const int row_l = warp / kParts, part = warp % kParts;
-  unsigned long long (*sorted)[32] = reinterpret_cast<unsigned long long (*)[32]>(sK) + warp * ITEMS;
-  if (warp < kRowTile * kParts && row_l < nrow) {
-    const int g = g0 + row_l;
-    const RowMask rm = make_row_mask(p.sel.mask, g);
-    const int c_off = part * ITEMS * 32;
-    const int nc_part = NC - c_off < ITEMS * 32 ? NC - c_off : ITEMS * 32;
-    int32_t* oi = sCi + (row_l * kParts + part) * topk;
-    float* os = sCv + (row_l * kParts + part) * topk;
-    if (nc_part > 0) {
-      warp_select<ITEMS, false>(p.sel, sS + row_l * NC + c_off, rm, nc_part, c_off, 0, oi, os, sorted);
-    } else {
-      for (int i = lane; i < topk; i += 32) { oi[i] = -1; os[i] = -INFINITY; }
-    }
-  }
+  const int cpr = D / 8;                                                 // 16-byte chunks per row
+  const int rpp = kFusedThreads / cpr;                                   // rows one pass of the block covers
+  const int r0 = threadIdx.x / cpr, cc = threadIdx.x - r0 * cpr;
   __syncthreads();
-  // ---- stage 2: one warp per row merges the kParts lists (same keys, same order)
-  if (warp < kRowTile * kParts && part == 0 && row_l < nrow) {
-    const int g = g0 + row_l;
-    const int64_t row = (static_cast<int64_t>(b) * p.sc.MG + g) * p.sc.H + h;
-    SelectParams m = p.sel;
-    m.cand_ids = sCi + row_l * kParts * topk;
-    m.seg_len = topk;
-    m.seg_stride = topk;
-    const float* vals = sCv + row_l * kParts * topk;
-    int32_t* oi = p.sel.out_idx + row * topk;
-    float* os = p.sel.out_scores ? p.sel.out_scores + row * topk : nullptr;
-    const RowMask none{};
-    const int64_t n_cand = static_cast<int64_t>(kParts) * topk;
-    if (topk <= 16) warp_select<2, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
-    else if (topk <= 32) warp_select<4, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
-    else warp_select<8, true>(m, vals, none, n_cand, 0, 0, oi, os, sorted);
+  chain_release();
+  chain_wait();
+  SS_TRACE(0);
+  volatile int* abort = &s_abort;
+  uint32_t qf[kFusedD / 16][2];                                          // the query tile's fragments
+  const int nkk = D / 16;
+  bool ok = true;
+  int round = 0;
+  for (int k0 = 0; k0 < NC; k0 += kKeysPerRound, ++round) {
+    const int nk = min(kKeysPerRound, NC - k0);
+    const int nk16 = (nk + 15) & ~15;                                    // whole 16-key tiles, the tail zero-filled
+    if (k0 > 0) __syncthreads();                                         // the previous round's keys are consumed
+    if (k0 == 0 && r0 < kRowTile) {
+      const bool real = r0 < nrow;
+      const char* src = p.sc.q + (b * p.sc.q_sb + (g0 + (real ? r0 : 0)) * p.sc.q_sg + h * p.sc.q_sh) * 2 + cc * 16;
+      cp_async16(sQ + r0 * PITCH + cc * 8, src, real ? 16 : 0);
+    }
+    {
+      const char* kcol = p.sc.k + (b * p.sc.k_sb + static_cast<int64_t>(k0) * p.sc.k_sc + h * p.sc.k_sh) * 2 + cc * 16;
+      const int64_t row_step = p.sc.k_sc * 2;
+      T* dcol = sK + cc * 8;
+#pragma unroll
+      for (int gk = 0; gk < kKeyGroups; ++gk) {
+        const int end = min((gk + 1) * kGroupKeys, nk16);
+        for (int r = gk * kGroupKeys + r0; r < end; r += rpp) {
+          const bool real = r < nk;
+          cp_async16(dcol + r * PITCH, kcol + (real ? r : 0) * row_step, real ? 16 : 0);
+        }
+        cp_async_arrive(&s_bar[gk]);
+      }
+    }
+    SS_TRACE(1 + 4 * round);
+    for (int t = warp; t < nk16 / 16; t += nwarp) {                      // this warp's 16-key tiles
+      ok = __all_sync(0xffffffffu, ok && tc::mbar_wait(&s_bar[(t * 16) / kGroupKeys], round & 1, abort));
+      if (!ok) break;
+      if (k0 == 0 && t == warp) {                                        // (the queries arrive with key group 0)
+        if ((t * 16) / kGroupKeys != 0) ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_bar[0], 0, abort));
+        const T* qb = sQ + gid * PITCH + t4 * 2;
+#pragma unroll
+        for (int kk = 0; kk < kFusedD / 16; ++kk) {
+          if (kk < nkk) {
+            qf[kk][0] = *reinterpret_cast<const uint32_t*>(qb + kk * 16);
+            qf[kk][1] = *reinterpret_cast<const uint32_t*>(qb + kk * 16 + 8);
+          }
+        }
+      }
+      SS_TRACE(2 + 4 * round);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const T* ka = sK + (t * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8;
+#pragma unroll
+      for (int kk = 0; kk < kFusedD / 16; ++kk) {
+        if (kk < nkk) {
+          uint32_t a[4];
+          ldmatrix_x4(a, ka + kk * 16);
+          mma16816<T>(acc, a, qf[kk][0], qf[kk][1]);
+        }
+      }
+      SS_TRACE(3 + 4 * round);
+      // acc[0..1]: key gid of the tile, query rows 2*t4 and 2*t4+1; acc[2..3]: key gid + 8
+      const int c_lo = k0 + t * 16 + gid;
+      const int n0 = 2 * t4;
+      const RowBounds rb0 = s_rb[n0], rb1 = s_rb[n0 + 1];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = c_lo + 8 * half;
+        const int bid = p.sel.mask.id_base + c * p.sel.mask.id_stride;
+        const float s0 = acc[2 * half] * p.sc.scale + 0.f, s1 = acc[2 * half + 1] * p.sc.scale + 0.f;
+        bool v0, v1;
+        if (p.sel.mask.tf) {
+          v0 = visible(p.sel.mask, s_rm[n0], bid);
+          v1 = visible(p.sel.mask, s_rm[n0 + 1], bid);
+        } else {
+          v0 = visible_in(rb0, bid);
+          v1 = visible_in(rb1, bid);
+        }
+        const bool in = c < NC;
+        sKey[n0 * NCP + c] = (in && v0) ? pack_key(s0, bid) : 0ull;
+        sKey[(n0 + 1) * NCP + c] = (in && v1) ? pack_key(s1, bid) : 0ull;
+      }
+      SS_TRACE(4 + 4 * round);
+    }
   }
+  __syncthreads();                                                       // keys complete, key tile dead
+  SS_TRACE(9);
+  // ---- selection: warp r takes row r
+  if (warp < nrow && !s_abort) {
+    unsigned long long (*sorted)[32] = reinterpret_cast<unsigned long long (*)[32]>(sK) + warp * ITEMS;
+    const int64_t row = (static_cast<int64_t>(b) * p.sc.MG + g0 + warp) * p.sc.H + h;
+    const unsigned long long* krow = sKey + warp * NCP;
+    unsigned long long keys[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int c = lane + 32 * i;
+      keys[i] = c < NC ? krow[c] : 0ull;
+    }
+    warp_take_topk<ITEMS>(keys, topk, p.sel.out_idx + row * topk, p.sel.out_scores ? p.sel.out_scores + row * topk : nullptr, sorted);
+  }
+  SS_TRACE(10);
+  if (threadIdx.x == 0 && s_abort) atomicExch(status, NSA_ERR_CUDA);
+}
+
+size_t score_select_smem(int D, int64_t NC) {
+  return static_cast<size_t>(kRowTile + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * (((NC + 15) & ~15) + 2) * 8;
 }
 
 template <typename T>
 int launch_score_select(const ScoreSelectParams& p, int B, cudaStream_t s) {
-  const int D = p.sc.D;
-  const size_t smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * sizeof(T) +
-                      static_cast<size_t>(kRowTile) * p.sc.NC * sizeof(float) +
-                      static_cast<size_t>(kRowTile) * kParts * p.sel.topk * 8;
+  const size_t smem = score_select_smem(p.sc.D, p.sc.NC);
   const dim3 grid(cdiv(p.sc.MG, kRowTile), p.sc.H, B);
-  if (p.sc.NC <= kParts * 4 * 32) {
-    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 4>, grid, dim3(1024), smem, s, p));
-  } else {
+  int32_t* status = nullptr;
+  int rc;
+  if ((rc = device_status_address(&status))) return rc;
+  if (p.sc.NC <= 8 * 32) {
     NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 8>, grid, dim3(1024), smem, s, p));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 8>, grid, dim3(kFusedThreads), smem, s, p, status));
+  } else if (p.sc.NC <= 16 * 32) {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 16>, grid, dim3(kFusedThreads), smem, s, p, status));
+  } else {
+    NSA_CUDA_OK(cudaFuncSetAttribute(score_select_kernel<T, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    NSA_CUDA_OK(launch_chained(kChainSmall, score_select_kernel<T, 32>, grid, dim3(kFusedThreads), smem, s, p, status));
   }
   NSA_LAUNCH_OK("score_select_kernel");
   return NSA_OK;
@@ -896,9 +1008,8 @@ int run_score_select(const void* qp, const int64_t* qs, const void* kp, const in
                       aligned16(qp) && aligned16(kp) && (qs[0] * 2) % 16 == 0 && (qs[1] * 2) % 16 == 0 &&
                       (qs[2] * 2) % 16 == 0 && (ks[0] * 2) % 16 == 0 && (ks[1] * 2) % 16 == 0 && (ks[2] * 2) % 16 == 0;
   // rows short enough to keep their scores in shared memory: scoring and selection in ONE kernel
-  const size_t fused_smem = static_cast<size_t>(16 + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * NC * 4 +
-                            static_cast<size_t>(kRowTile) * kParts * topk * 8;
-  if (allow_fused && mma_ok && NC <= kFusedNC && topk <= kFusedTopk && fused_smem <= 200 * 1024 && H <= 65535 && B <= 65535) {
+  if (allow_fused && mma_ok && D <= kFusedD && NC <= kFusedNC && topk <= kFusedTopk &&
+      score_select_smem(D, NC) <= 220 * 1024 && H <= 65535 && B <= 65535) {
     ScoreSelectParams fp{};
     fp.sc = sp;
     fp.sel.NC = NC; fp.sel.MG = MG; fp.sel.H = H; fp.sel.topk = topk; fp.sel.out_idx = out_idx;
@@ -1158,6 +1269,13 @@ int static_scratch_address(float** out) {
 }
 }  // namespace
 }  // namespace nsa
+
+#ifdef NSA_SS_TRACE
+extern "C" int nsa_debug_trace_ss(long long* out) {
+  NSA_CUDA_OK(cudaMemcpyFromSymbol(out, nsa::g_trace_ss, sizeof(long long) * 16));
+  return NSA_OK;
+}
+#endif
 
 extern "C" size_t nsa_topk_static_scratch_max_scores(void) { return nsa::kStaticScratchFloats; }
 
