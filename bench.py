@@ -305,6 +305,18 @@ def hbm_kernels(ops, dev, d, pk):
     return out
 
 
+def run_hbm_only(args):
+    """Only the isolated HBM / cache kernel timings of `hbm_kernels` (the command the ncu captures of
+    those kernels run): one line with their entries."""
+    from omnimem_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the GPU arm has no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    d = {n: x.to(dev) for n, x in make_inputs(1234, pin=False).items()}
+    emit({"metric": METRIC, "hbm_only": True, "kernels": {"hbm_and_cache": hbm_kernels(ops, dev, d, peaks())}})
+
+
 def run_gpu(args):
     from omnimem_b200 import ops
     rank = int(os.environ.get("RANK", "0"))
@@ -388,9 +400,9 @@ def run_gpu(args):
 
     if args.kernels_only:
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "kernels_only": True, "passes": n_pass, "steps": args.steps,
-                              "ms_per_step": round(ms_total / args.steps, 4),
-                              "value": round(world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, 3)}), flush=True)
+            emit({"metric": METRIC, "kernels_only": True, "passes": n_pass, "steps": args.steps,
+                  "ms_per_step": round(ms_total / args.steps, 4),
+                  "value": round(world * flops_step * args.steps / (ms_total * 1e-3) / 1e12, 3)})
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -533,7 +545,7 @@ def run_gpu(args):
             line["gpu_baseline"] = gpu_baseline(per)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(host, steps=1)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -622,6 +634,19 @@ def run_sharded(args, dist, dev, rank, world):
         return o, l, ids
 
     ms_cached, (out_c, _, idx_c) = timed(cached, steps)
+    # the same two calls replayed as CUDA graphs (collectives included): what the device needs once
+    # the host's launch work is out of the way
+    ms_fly_eager, ms_cached_eager, launch = ms_fly, ms_cached, "eager"
+    if not args.no_graph:
+        try:
+            from omnimem_b200.graph import CapturedStep
+            cap_fly = CapturedStep(lambda: sh.forward(q, k, v, T, bs, G, c["frame"], False))
+            cap_cached = CapturedStep(cached)
+            ms_fly, (out, lse, idx) = timed(cap_fly.replay, steps)
+            ms_cached, (out_c, _, idx_c) = timed(cap_cached.replay, steps)
+            launch = "CUDA graph replay (kernels and collectives of one call captured once)"
+        except Exception as e:                       # capture refused: the eager numbers stand
+            launch = f"eager (graph capture failed: {type(e).__name__})"
     agree = torch.tensor([float(idx.sum().item())], device=dev, dtype=torch.float64)
     lo, hi = agree.clone(), agree.clone()
     if dist is not None:
@@ -660,6 +685,8 @@ def run_sharded(args, dist, dev, rank, world):
         res = {"workload": "config5: selection forward, 4680 queries, 1,048,576-token KV sharded by block (b on rank b mod R), "
                            "top-16 merged after one all-gather, partials by all-to-all of row shares + all-gather of merged rows",
                "ms_per_call": round(ms_fly, 4), "ms_per_call_cached_pooled_keys": round(ms_cached, 4),
+               "launch": launch, "ms_per_call_eager": round(ms_fly_eager, 4),
+               "ms_per_call_cached_pooled_keys_eager": round(ms_cached_eager, 4),
                "single_device_ms_per_call": round(ms_single, 4),
                "strong_scaling_efficiency": round(ms_single / (world * ms_fly), 4),
                "fwd_tflops": round(flops / (ms_fly * 1e-3) / 1e12, 2),
@@ -784,7 +811,7 @@ def run_reference(args):
                          "sample": f"{sample} per step; CPU restatement of the reference's torch path, fp32"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_rollout_only(args):
@@ -808,9 +835,18 @@ def run_rollout_only(args):
                 "unit": "latent frames/s", "n_gpus": world, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "config": {"workload": res["workload"], "model": res["model"]},
                 "rollout": res, "clocks": sampler.stop()}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
+
+
+_LINE_OUT = None
+
+
+def emit(line):
+    out = _LINE_OUT if _LINE_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
@@ -828,11 +864,21 @@ def main():
     ap.add_argument("--rollout-layers", type=int, default=0, help="fewer transformer blocks than 30 (for quick runs)")
     ap.add_argument("--passes", type=int, default=0, help="passes of K steps in the timed region (default: about 2 s worth)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--hbm-only", action="store_true",
+                    help="only the isolated timings of the HBM-bound selection and block-cache kernels (the command their ncu captures run)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident steps only (no end-to-end leg, no CPU baseline): the command profiled by ncu")
     args = ap.parse_args()
+    # stdout carries the JSON line and nothing else: libraries that print there (NCCL's version
+    # banner, torchrun's notes) are sent to stderr, the line goes to the saved descriptor
+    global _LINE_OUT
+    sys.stdout.flush()
+    _LINE_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
+    elif args.hbm_only:
+        run_hbm_only(args)
     elif args.workload != "selection":
         run_rollout_only(args)
     else:
