@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p)
   constexpr int UNROLL = ROPE ? 2 : 4;
   extern __shared__ float s_part[];          // [slices][hc][2][D] partial sums of K and V
   __shared__ int s_page[64];
+  chain_release();
+  chain_wait();
   const int cpr = p.D / VEC;
   const int j = blockIdx.x;
   const int h0 = blockIdx.y * p.hc;
@@ -712,12 +714,13 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
       else NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     }
   }
+  // (a programmatic dependent launch: back-to-back appends overlap one launch's ramp with the tail of the one before)
   if (rope != nullptr) {
-    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, true><<<grid, threads, smem, s>>>(p);
-    else cache_append_kernel<__half, true><<<grid, threads, smem, s>>>(p);
+    if (dtype == NSA_BF16) NSA_CUDA_OK(launch_chained(kChainSmall, cache_append_kernel<__nv_bfloat16, true>, grid, dim3(threads), smem, s, p));
+    else NSA_CUDA_OK(launch_chained(kChainSmall, cache_append_kernel<__half, true>, grid, dim3(threads), smem, s, p));
   } else {
-    if (dtype == NSA_BF16) cache_append_kernel<__nv_bfloat16, false><<<grid, threads, smem, s>>>(p);
-    else cache_append_kernel<__half, false><<<grid, threads, smem, s>>>(p);
+    if (dtype == NSA_BF16) NSA_CUDA_OK(launch_chained(kChainSmall, cache_append_kernel<__nv_bfloat16, false>, grid, dim3(threads), smem, s, p));
+    else NSA_CUDA_OK(launch_chained(kChainSmall, cache_append_kernel<__half, false>, grid, dim3(threads), smem, s, p));
   }
   NSA_LAUNCH_OK("cache_append_kernel");
   return NSA_OK;

@@ -686,6 +686,10 @@ constexpr int kKeyGroups = 4;
 constexpr int kGroupKeys = kKeysPerRound / kKeyGroups;
 constexpr int kFusedThreads = 1024;
 
+// Shared-memory scratch of the selection (one [ITEMS][32] list of 64-bit keys per row); it overlays
+// the key tile, which is dead by then, and sets the size of that region when the tile is smaller.
+constexpr size_t score_select_scratch(int items) { return static_cast<size_t>(kRowTile) * items * 32 * 8; }
+
 
 struct ScoreSelectParams {
   ScoreParams sc;          // q, k pooled + strides, MG, H, D, NC, scale (scores pointer unused)
@@ -708,7 +712,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) score_select_kernel(const Sc
   const int NC = static_cast<int>(p.sc.NC), NCP = ((NC + 15) & ~15) + 2, topk = p.sel.topk;
   T* sQ = reinterpret_cast<T*>(s_fused);                                 // [kRowTile][PITCH], rows >= nrow zero
   T* sK = sQ + kRowTile * PITCH;                                         // [kKeysPerRound][PITCH]; later the sort scratch
-  unsigned long long* sKey = reinterpret_cast<unsigned long long*>(sK + kKeysPerRound * PITCH);   // [kRowTile][NCP]
+  const size_t tile_bytes = static_cast<size_t>(kKeysPerRound) * PITCH * sizeof(T);
+  const size_t region = tile_bytes > score_select_scratch(ITEMS) ? tile_bytes : score_select_scratch(ITEMS);
+  unsigned long long* sKey = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(sK) + region);   // [kRowTile][NCP]
   const int g0 = blockIdx.x * kRowTile;
   const int h = blockIdx.y, b = blockIdx.z;
   const int nrow = min(kRowTile, p.sc.MG - g0);
@@ -831,7 +837,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) score_select_kernel(const Sc
 }
 
 size_t score_select_smem(int D, int64_t NC) {
-  return static_cast<size_t>(kRowTile + kKeysPerRound) * (D + 8) * 2 + static_cast<size_t>(kRowTile) * (((NC + 15) & ~15) + 2) * 8;
+  const int items = NC <= 8 * 32 ? 8 : (NC <= 16 * 32 ? 16 : 32);
+  const size_t tile = static_cast<size_t>(kKeysPerRound) * (D + 8) * 2;
+  const size_t region = tile > score_select_scratch(items) ? tile : score_select_scratch(items);
+  return static_cast<size_t>(kRowTile) * (D + 8) * 2 + region + static_cast<size_t>(kRowTile) * (((NC + 15) & ~15) + 2) * 8;
 }
 
 template <typename T>

@@ -209,6 +209,51 @@ def test_fused_pool_score_select_equals_the_separate_kernels(dev, case):
     assert torch.equal(kp4, kp) and torch.equal(idx, want_i)
 
 
+@pytest.mark.parametrize("case", [
+    # MG, NC, H, D, topk, dtype, mask fields (block, chunk, chunk_k, G, q_off, ex_win, ex_sink, causal, tf, prog, id_base, id_stride)
+    (74, 512, 12, 128, 16, torch.bfloat16, (64, 1560, 1560, 64, 18, 0, 0, 1, 0, 0, 0, 1)),       # the Wan layer shape
+    (20, 1000, 3, 128, 32, torch.bfloat16, (64, 4680, 4680, 64, 9, 2, 1, 0, 0, 1, 0, 1)),        # two key rounds, 32 keys per lane
+    (9, 700, 2, 64, 64, torch.float16, (30, 300, 300, 15, 40, 3, 0, 1, 0, 1, 0, 1)),             # D=64, fp16, top-64
+    (5, 130, 2, 32, 8, torch.bfloat16, (8, 16, 16, 1, 30, 1, 1, 1, 0, 0, 0, 1)),                 # D=32: rows of 4 pieces
+    (17, 257, 1, 16, 4, torch.bfloat16, (4, 8, 8, 2, 60, 0, 2, 0, 0, 1, 0, 1)),                  # D=16, a 1-key last tile
+    (32, 32, 2, 64, 5, torch.bfloat16, (4, 8, 8, 1, 0, 1, 0, 0, 1, 0, 0, 1)),                    # teacher-forcing layout
+    (30, 333, 2, 128, 16, torch.bfloat16, (64, 1560, 1560, 64, 50, 1, 0, 1, 0, 0, 2, 5)),        # shard 2 of 5: global ids
+    (8, 1024, 1, 128, 16, torch.bfloat16, (64, 10 ** 6, 10 ** 6, 64, 0, 0, 0, 0, 0, 0, 0, 1)),   # the longest fused row
+])
+def test_one_kernel_scoring_and_selection_equals_the_two_kernel_path(dev, case):
+    """nsa_topk (scores kept in shared memory, one kernel) against nsa_topk_static_scratch (score
+    buffer + selection kernel) through the C ABI: ids and scores bit for bit, on every mask mode,
+    head dim and tile remainder the one-kernel path serves."""
+    import ctypes as C
+    from omnimem_b200 import _lib
+    MG, NC, H, D, T, dtype, mf = case
+    g = torch.Generator().manual_seed(MG * 1000 + NC)
+    q = torch.randn(1, MG, H, D, generator=g).to(dtype).to(dev)
+    k = torch.randn(1, NC, H, D, generator=g).to(dtype).to(dev)
+    k[:, 3::7] = k[:, 2::7][:, :k[:, 3::7].shape[1]]               # exact score ties between neighbours
+    m = _lib.TopkMask(*mf)
+    code = _lib.NSA_BF16 if dtype == torch.bfloat16 else _lib.NSA_F16
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    lib = _lib.load()
+    ws_bytes = lib.nsa_topk_workspace_bytes(1, MG, H, NC)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    out = []
+    for name in ("nsa_topk", "nsa_topk_static_scratch"):
+        idx = torch.full((1, MG, H, T), -7, dtype=torch.int32, device=dev)
+        sc = torch.full((1, MG, H, T), 7.0, dtype=torch.float32, device=dev)
+        args = [q.data_ptr(), _lib.strides3(q), k.data_ptr(), _lib.strides3(k), 1, MG, H, D, NC, T, D ** -0.5, C.byref(m),
+                idx.data_ptr(), sc.data_ptr()]
+        args += [ws.data_ptr(), ws_bytes] if name == "nsa_topk" else []
+        _lib.call(name, *args, code, stream)
+        out.append((idx, sc))
+    torch.cuda.synchronize()
+    (ia, sa), (ib, sb) = out
+    assert (ia != -7).all() and (ib != -7).all()
+    assert torch.equal(ia, ib), "block ids"
+    assert torch.equal(sa.view(torch.int32), sb.view(torch.int32)), "scores, bit for bit"
+    assert (ia >= 0).any()
+
+
 def test_tf_mask_is_rejected_for_sharded_ids(dev):
     from omnimem_b200 import NSABackendError
     q = torch.randn(1, 8, 2, 64).to(torch.bfloat16).to(dev)
