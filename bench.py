@@ -121,6 +121,9 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------ GPU arm
+RECOMPUTE_BACKWARD = False
+
+
 def gpu_step(ops, d, ev=None, side=None):
     """One pass of the hot path over device tensors; `ev` collects (name, start, stop) events.
     With a `side` stream the inverted index, which depends only on the ids, runs beside the forward."""
@@ -141,20 +144,35 @@ def gpu_step(ops, d, ev=None, side=None):
     idx, qp, kp = timed("score_topk", lambda: ops.select_blocks(d["q"], d["k"], c["topk"], scale, c["block"], c["group"],
                                                                c["frame"], c["frame"], True, q_chunk_offset=c["q_frame0"]))
     kv = ops.DenseKV(d["k"], d["v"])
+    # P and dS are computed once: the dQ kernel stores them (16 KiB per (group, head, slot) pair) and the
+    # dK/dV kernel streams them; --recompute-backward runs the two kernels that each compute S and dP
+    nbytes = 0 if RECOMPUTE_BACKWARD else ops.stored_probabilities_bytes(d["q"], kv, idx, c["block"], c["group"])
+    if nbytes and "pds" not in d:
+        d["pds"] = torch.empty(nbytes, dtype=torch.uint8, device=idx.device)
+    pds = d.get("pds") if nbytes else None
+
+    def index():
+        return ops.inverted_index(idx, -(-c["N"] // c["block"]), c["block"], 1, False, c["group"], with_slots=pds is not None)
+
     if side is not None:
         side.wait_stream(cur)
         with torch.cuda.stream(side):
-            groups, offsets = ops.inverted_index(idx, -(-c["N"] // c["block"]), c["block"], 1, False, c["group"])
+            inv = index()
         out, lse = ops.sel_fwd(d["q"], kv, idx, c["block"], 1, scale, False, c["group"])
         cur.wait_stream(side)
     else:
         out, lse = timed("sel_fwd", lambda: ops.sel_fwd(d["q"], kv, idx, c["block"], 1, scale, False, c["group"]))
-        groups, offsets = timed("inverted_index", lambda: ops.inverted_index(idx, -(-c["N"] // c["block"]), c["block"],
-                                                                             1, False, c["group"]))
-    dq, delta = timed("sel_bwd_dq", lambda: ops.sel_bwd_dq(d["q"], kv, idx, out, lse, d["do"], c["block"], 1, scale,
-                                                           False, c["group"]))
+        inv = timed("inverted_index", index)
+    groups, offsets = inv[0], inv[1]
+    slots = inv[2] if pds is not None else None
+    res = timed("sel_bwd_dq", lambda: ops.sel_bwd_dq(d["q"], kv, idx, out, lse, d["do"], c["block"], 1, scale,
+                                                     False, c["group"], pds=pds))
+    dq, delta = res[0], res[1]
+    if pds is not None and not res[2]:
+        slots = pds = None
     dk, dv = timed("sel_bwd_dkv", lambda: ops.sel_bwd_dkv(d["q"], kv, groups, offsets, lse, delta, d["do"],
-                                                          c["topk"], c["block"], 1, scale, False, c["group"]))
+                                                          c["topk"], c["block"], 1, scale, False, c["group"],
+                                                          slots=slots, pds=pds))
     return idx, out, dq, dk, dv
 
 
@@ -508,7 +526,9 @@ def run_gpu(args):
         roof.pop("ms")
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, copied from the
         # committed ncu summaries of these kernels: a record of that capture, not a measurement of this run
-        ncu_traffic = {"sel_fwd": 193.0e6 + 10.7e6, "sel_bwd_dq": 222.3e6 + 14.4e6, "sel_bwd_dkv": 206.7e6 + 158.0e6}
+        ncu_traffic = {"sel_fwd": 193.0e6 + 10.7e6, "sel_bwd_dq": 257.2e6 + 202.2e6, "sel_bwd_dkv": 262.0e6 + 162.9e6}
+        if RECOMPUTE_BACKWARD:
+            ncu_traffic.update({"sel_bwd_dq": 222.3e6 + 14.4e6, "sel_bwd_dkv": 206.7e6 + 158.0e6})
         roof.update(kernel=dom, traffic=ncu_traffic.get(dom), traffic_unit="bytes per launch",
                     traffic_source="ncu capture of this kernel at this workload (summary under profiles/), not measured by this run",
                     peak_source=pk["source"] + " (burst)",
@@ -863,12 +883,16 @@ def main():
                          "rollout-long: only the rollout of config 3 / config 4, as a line of its own")
     ap.add_argument("--rollout-layers", type=int, default=0, help="fewer transformer blocks than 30 (for quick runs)")
     ap.add_argument("--passes", type=int, default=0, help="passes of K steps in the timed region (default: about 2 s worth)")
+    ap.add_argument("--recompute-backward", action="store_true",
+                    help="dK/dV kernel that recomputes S and dP instead of streaming the P / dS tiles the dQ kernel stored")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--hbm-only", action="store_true",
                     help="only the isolated timings of the HBM-bound selection and block-cache kernels (the command their ncu captures run)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident steps only (no end-to-end leg, no CPU baseline): the command profiled by ncu")
     args = ap.parse_args()
+    global RECOMPUTE_BACKWARD
+    RECOMPUTE_BACKWARD = args.recompute_backward
     # stdout carries the JSON line and nothing else: libraries that print there (NCCL's version
     # banner, torchrun's notes) are sent to stderr, the line goes to the saved descriptor
     global _LINE_OUT

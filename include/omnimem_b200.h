@@ -222,6 +222,43 @@ int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const nsa_kv_sourc
                     float scale, void* workspace, size_t workspace_bytes, int32_t dtype,
                     void* stream);
 
+/* The backward with P and dS computed ONCE.  The reference's backward computes S = Q K^T,
+ * dP = dO V^T and the exponentials in its dQ kernels and again in its dK/dV kernel
+ * (selection_bwd.cu:310-912 and :916-1044); here the dQ call can store P and dS of every (query
+ * group, head, selected slot) pair - bf16, 2 x 8 KiB per pair, nsa_sel_bwd_pds_bytes() in all
+ * (B * MG * H * T * 16 KiB: 233 MB for 74 groups x 12 heads x 16 slots) - and the dK/dV call then
+ * only streams those tiles with the Q / dO rows into its two products.  Sequence:
+ *   nsa_inverted_index_slots  - nsa_inverted_index plus `slots` int32 [B,H,MG*T]: the position of
+ *                               every bucket entry in its group's id list (T <= 256, MG < 2^23);
+ *                               buckets are ordered by (group, slot)
+ *   nsa_sel_bwd_dq_pds        - nsa_sel_bwd_dq; *pds_written (host) = 1 when the tiles were written
+ *                               (bf16, D = 128, 64-token blocks, 16 <= group_size <= 64, T <= 64, H > 1,
+ *                               dense or paged K/V, pds large enough), else 0 and `pds` is untouched
+ *   nsa_sel_bwd_dkv_pds       - nsa_sel_bwd_dkv; with slots and pds non-NULL (only after
+ *                               *pds_written == 1) it takes the tiles, with NULL it recomputes.
+ * dK / dV keep their fixed summation order (ascending group, then slot): bit-reproducible. */
+size_t nsa_sel_bwd_pds_bytes(int32_t B, int64_t M, int32_t H, int32_t T, int32_t group_size);
+int nsa_inverted_index_slots(const int32_t* block_indices, const int64_t idx_stride[4], int32_t B,
+                             int32_t MG, int32_t H, int32_t T, int64_t NS, int32_t block_size,
+                             int32_t chunk_size, int32_t causal, int32_t group_size,
+                             int32_t* groups, int32_t* offsets, int32_t* slots, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int nsa_sel_bwd_dq_pds(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                       const int32_t* block_indices, const int64_t idx_stride[4], const void* out,
+                       const int64_t out_stride[3], const float* lse, const void* d_out,
+                       const int64_t do_stride[3], void* dq, const int64_t dq_stride[3],
+                       float* delta, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
+                       int32_t block_size, int32_t chunk_size, int32_t causal, int32_t group_size,
+                       float scale, void* pds, size_t pds_bytes, int32_t* pds_written,
+                       int32_t dtype, void* stream);
+int nsa_sel_bwd_dkv_pds(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                        const int32_t* groups, const int32_t* offsets, const int32_t* slots,
+                        const void* pds, size_t pds_bytes, const float* lse, const float* delta,
+                        const void* d_out, const int64_t do_stride[3], void* dk, void* dv,
+                        int32_t B, int64_t M, int32_t H, int32_t D, int32_t T, int32_t block_size,
+                        int32_t chunk_size, int32_t causal, int32_t group_size, float scale,
+                        void* workspace, size_t workspace_bytes, int32_t dtype, void* stream);
+
 /* dK/dV of the pointer path (sel_bwd_ptr_cuda, selection_bwd.cu:1409-1527; accessor
  * bwd_common.cuh:64-121).  The K/V block with id `bid` of head h and its fp32 gradient scratch are
  * found through four [H, MAXB] tables of int64 byte addresses (element strides base_stride[0..1]):

@@ -20,7 +20,15 @@ struct IdxParams {
   int B, MG, H, T;
   int64_t NS;
   int block_size, chunk_size, causal, G;
+  int32_t* slots;          // optional second output (same layout as groups): the entry's position in its group's id list
 };
+
+// With a slot output the entries travel as (group << 8 | slot) through scatter and sort (T <= 256,
+// MG < 2^23), so that equal groups stay ordered by slot, and are taken apart at the end.
+constexpr int kSlotBits = 8;
+__device__ __forceinline__ int32_t inv_entry(const IdxParams& p, int g, int t) {
+  return p.slots != nullptr ? ((g << kSlotBits) | t) : g;
+}
 
 __device__ __forceinline__ bool pair_bucket(const IdxParams& p, int b, int g, int h, int t,
                                             int& bucket) {
@@ -46,7 +54,7 @@ __global__ void inv_pass_kernel(const IdxParams p, int32_t* __restrict__ counts,
   if (!pair_bucket(p, b, g, h, t, bucket)) return;
   const int64_t row = static_cast<int64_t>(b) * p.H + h;
   const int pos = atomicAdd(&counts[row * p.NS + bucket], 1);
-  if (SCATTER) groups[row * p.MG * p.T + pos] = g;
+  if (SCATTER) groups[row * p.MG * p.T + pos] = inv_entry(p, g, t);
 }
 
 // One thread block per (b, h) row: exclusive scan of the NS counts -> offsets[NS+1]; the
@@ -95,7 +103,7 @@ __global__ void inv_scan_kernel(int32_t* __restrict__ counts, int32_t* __restric
 // One thread per bucket: insertion sort of its group ids (buckets are short; the scatter pass
 // fills them in arrival order), so every consumer sees ascending groups and sums in a fixed order.
 __global__ void inv_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __restrict__ groups, int64_t NS,
-                                int64_t groups_row, int64_t n_buckets) {
+                                int64_t groups_row, int64_t n_buckets, int32_t* __restrict__ slots) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n_buckets) return;
   const int64_t row = i / NS, s = i % NS;
@@ -107,6 +115,14 @@ __global__ void inv_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __
     int c = a - 1;
     while (c >= 0 && gp[c] > v) { gp[c + 1] = gp[c]; --c; }
     gp[c + 1] = v;
+  }
+  if (slots != nullptr) {
+    int32_t* sp = slots + row * groups_row + o[s];
+    for (int a = 0; a < n; ++a) {
+      const int32_t v = gp[a];
+      gp[a] = v >> kSlotBits;
+      sp[a] = v & ((1 << kSlotBits) - 1);
+    }
   }
 }
 
@@ -168,7 +184,7 @@ __global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int3
   for (int pr = threadIdx.x; pr < pairs; pr += blockDim.x) {
     int bucket;
     const int g = pr / p.T;
-    if (pair_bucket(p, b, g, h, pr % p.T, bucket)) gr[atomicAdd(&s_cnt[bucket], 1)] = g;
+    if (pair_bucket(p, b, g, h, pr % p.T, bucket)) gr[atomicAdd(&s_cnt[bucket], 1)] = inv_entry(p, g, pr % p.T);
   }
   __syncthreads();                                   // scatter (global) visible to the block
   for (int sidx = threadIdx.x; sidx < NS; sidx += blockDim.x) {
@@ -181,10 +197,19 @@ __global__ void __launch_bounds__(1024) inv_fused_kernel(const IdxParams p, int3
       gr[c + 1] = v;
     }
   }
-  if (STAGED) {
+  if (STAGED || p.slots != nullptr) {
     __syncthreads();
     const int total = carry_s;                         // pairs that landed in a bucket
-    for (int i = threadIdx.x; i < total; i += blockDim.x) gr_out[i] = gr[i];
+    int32_t* sl_out = p.slots != nullptr ? p.slots + row * static_cast<int64_t>(pairs) : nullptr;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const int32_t v = gr[i];
+      if (sl_out != nullptr) {
+        gr_out[i] = v >> kSlotBits;
+        sl_out[i] = v & ((1 << kSlotBits) - 1);
+      } else {
+        gr_out[i] = v;
+      }
+    }
   }
 }
 
@@ -740,7 +765,7 @@ int run_inverted_index(const IdxParams& ip, int32_t* groups, int32_t* offsets, i
     NSA_LAUNCH_OK("inv_pass_kernel<scatter>");
     const int64_t n_buckets = rows * ip.NS;
     inv_sort_kernel<<<static_cast<unsigned>(cdiv64(n_buckets, 128)), 128, 0, stream>>>(offsets, groups, ip.NS, pairs,
-                                                                                       n_buckets);
+                                                                                       n_buckets, ip.slots);
     NSA_LAUNCH_OK("inv_sort_kernel");
   }
   return NSA_OK;
@@ -753,7 +778,13 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
                              const int64_t* idx_stride, const void* out, const int64_t* out_stride, const float* lse,
                              const void* d_out, const int64_t* do_stride, void* dq, const int64_t* dq_stride,
                              float* delta, int B, int64_t M, int H, int D, int T, int block_size, int chunk_size,
-                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched);
+                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched,
+                             void* pds);
+int try_launch_sel_bwd_dkv_pds_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* groups,
+                                  const int32_t* slots, const int32_t* offsets, const void* pds, const void* d_out,
+                                  const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
+                                  int block_size, int G, int dtype, int32_t* counter, cudaStream_t stream,
+                                  bool* launched);
 int try_launch_sel_bwd_dkv_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, const int32_t* groups,
                               const int32_t* offsets, const float* lse, const float* delta, const void* d_out,
                               const int64_t* do_stride, void* dk, void* dv, int B, int64_t M, int H, int D, int T,
@@ -768,11 +799,11 @@ extern "C" size_t nsa_inverted_index_workspace_bytes(int32_t B, int32_t H, int64
   return align_up(static_cast<size_t>(B) * H * NS * sizeof(int32_t), 256);
 }
 
-extern "C" int nsa_inverted_index(const int32_t* block_indices, const int64_t idx_stride[4],
-                                  int32_t B, int32_t MG, int32_t H, int32_t T, int64_t NS,
-                                  int32_t block_size, int32_t chunk_size, int32_t causal,
-                                  int32_t group_size, int32_t* groups, int32_t* offsets,
-                                  void* workspace, size_t workspace_bytes, void* stream) {
+extern "C" int nsa_inverted_index_slots(const int32_t* block_indices, const int64_t idx_stride[4],
+                                        int32_t B, int32_t MG, int32_t H, int32_t T, int64_t NS,
+                                        int32_t block_size, int32_t chunk_size, int32_t causal,
+                                        int32_t group_size, int32_t* groups, int32_t* offsets, int32_t* slots,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
   NSA_REQUIRE(B >= 0 && MG >= 0 && H >= 0 && T >= 0 && NS >= 0, NSA_ERR_INVALID, "inverted_index: negative size");
   NSA_REQUIRE(block_size > 0 && chunk_size > 0 && group_size > 0, NSA_ERR_INVALID, "inverted_index: sizes must be > 0");
   NSA_REQUIRE(H <= 65535 && B <= 65535, NSA_ERR_INVALID, "inverted_index: B and H must be <= 65535");
@@ -780,10 +811,21 @@ extern "C" int nsa_inverted_index(const int32_t* block_indices, const int64_t id
               "inverted_index: workspace too small");
   if (B == 0 || H == 0) return NSA_OK;
   NSA_REQUIRE(block_indices && groups && offsets && (workspace || NS == 0), NSA_ERR_INVALID, "inverted_index: null pointer");
+  NSA_REQUIRE(slots == nullptr || (T <= (1 << kSlotBits) && MG < (1 << (31 - kSlotBits))), NSA_ERR_UNSUPPORTED,
+              "inverted_index: the slot output serves T <= %d and fewer than %d query groups", 1 << kSlotBits, 1 << (31 - kSlotBits));
   IdxParams ip{block_indices, idx_stride[0], idx_stride[1], idx_stride[2], idx_stride[3],
-               B, MG, H, T, NS, block_size, chunk_size, causal, group_size};
+               B, MG, H, T, NS, block_size, chunk_size, causal, group_size, slots};
   return run_inverted_index(ip, groups, offsets, static_cast<int32_t*>(workspace),
                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nsa_inverted_index(const int32_t* block_indices, const int64_t idx_stride[4],
+                                  int32_t B, int32_t MG, int32_t H, int32_t T, int64_t NS,
+                                  int32_t block_size, int32_t chunk_size, int32_t causal,
+                                  int32_t group_size, int32_t* groups, int32_t* offsets,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  return nsa_inverted_index_slots(block_indices, idx_stride, B, MG, H, T, NS, block_size, chunk_size, causal, group_size,
+                                  groups, offsets, nullptr, workspace, workspace_bytes, stream);
 }
 
 // workspace layout: delta f32 [B,H,M] | counts i32 [B,H,NS] | offsets i32 [B,H,NS+1] | groups i32 [B,H,MG*T]
@@ -825,6 +867,11 @@ static int bwd_common_checks(const char* op, int32_t B, int64_t M, int32_t H, in
   return NSA_OK;
 }
 
+extern "C" size_t nsa_sel_bwd_pds_bytes(int32_t B, int64_t M, int32_t H, int32_t T, int32_t group_size) {
+  if (group_size <= 0 || B <= 0 || H <= 0 || T <= 0 || M <= 0) return 0;
+  return static_cast<size_t>(B) * cdiv64(M, group_size) * H * T * 16384;
+}
+
 extern "C" int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
                               const int32_t* block_indices, const int64_t idx_stride[4],
                               const void* out, const int64_t out_stride[3], const float* lse,
@@ -833,6 +880,20 @@ extern "C" int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const ns
                               int32_t D, int32_t T, int32_t block_size, int32_t chunk_size,
                               int32_t causal, int32_t group_size, float scale, int32_t dtype,
                               void* stream) {
+  return nsa_sel_bwd_dq_pds(q, q_stride, kv, block_indices, idx_stride, out, out_stride, lse, d_out, do_stride, dq,
+                            dq_stride, delta, B, M, H, D, T, block_size, chunk_size, causal, group_size, scale,
+                            nullptr, 0, nullptr, dtype, stream);
+}
+
+extern "C" int nsa_sel_bwd_dq_pds(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                                  const int32_t* block_indices, const int64_t idx_stride[4],
+                                  const void* out, const int64_t out_stride[3], const float* lse,
+                                  const void* d_out, const int64_t do_stride[3], void* dq,
+                                  const int64_t dq_stride[3], float* delta, int32_t B, int64_t M, int32_t H,
+                                  int32_t D, int32_t T, int32_t block_size, int32_t chunk_size,
+                                  int32_t causal, int32_t group_size, float scale, void* pds, size_t pds_bytes,
+                                  int32_t* pds_written, int32_t dtype, void* stream) {
+  if (pds_written != nullptr) *pds_written = 0;
   int rc;
   if ((rc = bwd_common_checks("sel_bwd_dq", B, M, H, D, T, block_size, chunk_size, group_size, dtype, kv, true))) return rc;
   if (B == 0 || H == 0 || M == 0) return NSA_OK;
@@ -847,11 +908,18 @@ extern "C" int nsa_sel_bwd_dq(const void* q, const int64_t q_stride[3], const ns
   {
     // the page geometry runs on the tcgen05 kernel; every other shape on the general one
     bool launched = false;
+    // the P / dS tiles are written only when the caller wants to know that they were (pds_written),
+    // the buffer holds every (group, head, slot) pair and the lists are short enough for the storing kernel (64 slots)
+    void* tiles = (pds != nullptr && pds_written != nullptr && T <= 64 &&
+                   pds_bytes >= nsa_sel_bwd_pds_bytes(B, M, H, T, group_size) && aligned16(pds)) ? pds : nullptr;
     rc = try_launch_sel_bwd_dq_tc(q, q_stride, kv, block_indices, idx_stride, out, out_stride, lse, d_out, do_stride,
                                   dq, dq_stride, delta, B, M, H, D, T, block_size, chunk_size, causal, group_size,
-                                  scale, dtype, static_cast<cudaStream_t>(stream), &launched);
+                                  scale, dtype, static_cast<cudaStream_t>(stream), &launched, tiles);
     if (rc) return rc;
-    if (launched) return NSA_OK;
+    if (launched) {
+      if (tiles != nullptr) *pds_written = 1;
+      return NSA_OK;
+    }
   }
   p.q = static_cast<const char*>(q); p.q_sb = q_stride[0]; p.q_sm = q_stride[1]; p.q_sh = q_stride[2];
   p.o = static_cast<const char*>(out); p.o_sb = out_stride[0]; p.o_sm = out_stride[1]; p.o_sh = out_stride[2];
@@ -873,6 +941,19 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
                                int32_t block_size, int32_t chunk_size, int32_t causal,
                                int32_t group_size, float scale, void* workspace, size_t workspace_bytes,
                                int32_t dtype, void* stream) {
+  return nsa_sel_bwd_dkv_pds(q, q_stride, kv, groups, offsets, nullptr, nullptr, 0, lse, delta, d_out, do_stride, dk, dv,
+                             B, M, H, D, T, block_size, chunk_size, causal, group_size, scale, workspace,
+                             workspace_bytes, dtype, stream);
+}
+
+extern "C" int nsa_sel_bwd_dkv_pds(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                                   const int32_t* groups, const int32_t* offsets, const int32_t* slots,
+                                   const void* pds, size_t pds_bytes, const float* lse,
+                                   const float* delta, const void* d_out, const int64_t do_stride[3],
+                                   void* dk, void* dv, int32_t B, int64_t M, int32_t H, int32_t D, int32_t T,
+                                   int32_t block_size, int32_t chunk_size, int32_t causal,
+                                   int32_t group_size, float scale, void* workspace, size_t workspace_bytes,
+                                   int32_t dtype, void* stream) {
   int rc;
   if ((rc = bwd_common_checks("sel_bwd_dkv", B, M, H, D, T, block_size, chunk_size, group_size, dtype, kv))) return rc;
   const int64_t N = kv->n_tokens;
@@ -893,6 +974,16 @@ extern "C" int nsa_sel_bwd_dkv(const void* q, const int64_t q_stride[3], const n
   {
     bool launched = false;
     int32_t* counter = (workspace != nullptr && workspace_bytes >= 256) ? static_cast<int32_t*>(workspace) : nullptr;
+    if (pds != nullptr && slots != nullptr) {
+      // P and dS of every pair were stored by the dQ kernel: stream them instead of recomputing S and dP
+      NSA_REQUIRE(pds_bytes >= nsa_sel_bwd_pds_bytes(B, M, H, T, group_size) && aligned16(pds), NSA_ERR_WORKSPACE,
+                  "sel_bwd_dkv: the P/dS buffer is too small or misaligned");
+      rc = try_launch_sel_bwd_dkv_pds_tc(q, q_stride, kv, groups, slots, offsets, pds, d_out, do_stride, dk, dv, B, M, H,
+                                         D, T, block_size, group_size, dtype, counter, s, &launched);
+      if (rc) return rc;
+      if (launched) return NSA_OK;
+      NSA_REQUIRE(false, NSA_ERR_UNSUPPORTED, "sel_bwd_dkv: the stored-probabilities kernel does not serve this call");
+    }
     rc = try_launch_sel_bwd_dkv_tc(q, q_stride, kv, groups, offsets, lse, delta, d_out, do_stride, dk, dv, B, M, H, D,
                                    T, block_size, chunk_size, causal, group_size, scale, dtype, counter, s, &launched);
     if (rc) return rc;
@@ -986,7 +1077,7 @@ extern "C" int nsa_sel_bwd(const void* q, const int64_t q_stride[3], const nsa_k
   if (M > 0) {
     NSA_REQUIRE(block_indices != nullptr, NSA_ERR_INVALID, "sel_bwd: block_indices is null");
     IdxParams ip{block_indices, idx_stride[0], idx_stride[1], idx_stride[2], idx_stride[3],
-                 B, static_cast<int>(MG), H, T, NS, block_size, chunk_size, causal, group_size};
+                 B, static_cast<int>(MG), H, T, NS, block_size, chunk_size, causal, group_size, nullptr};
     if ((rc = run_inverted_index(ip, groups, offsets, counts, static_cast<cudaStream_t>(stream)))) return rc;
     if ((rc = nsa_sel_bwd_dq(q, q_stride, kv, block_indices, idx_stride, out, out_stride, lse, d_out, do_stride,
                              dq, dq_stride, delta, B, M, H, D, T, block_size, chunk_size, causal, group_size,

@@ -20,6 +20,12 @@
 // prologue and stored for the dK/dV kernel.  The epilogue packs the dQ^T fragments to bf16 and
 // stores them transposed (stmatrix.trans) into the first K stage, dead by then, from where TMA
 // tile stores write them.
+//
+// With a P / dS buffer (STORE = true) the row warps also produce P = exp2(S c - LSE log2e) itself, as a
+// second swizzled 8 KiB tile, and the warp that issues dQ^T hands both tiles of the step to a bulk
+// store into the (group, head, slot) pair's place in the buffer: the dK/dV kernel then needs no S, dP
+// or exponential of its own.  The P tile makes it 112 KiB of tiles: two thread blocks still share an
+// SM because the static variables shrink to half a KiB (lists of at most 64 slots).
 #include "sel_common.cuh"
 #include "tc_common.cuh"
 
@@ -45,8 +51,9 @@ using namespace tc;
 constexpr int kThreads = 224;
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTile = 16384;                 // 64 rows x 256 bytes, as two 64-column halves of 8 KiB
-constexpr int kKStages = 3;
-constexpr uint32_t kSmemTiles = kTile + kKStages * kTile + 2 * kTile + 8192;   // dO, K x3, V x2, dS
+constexpr uint32_t kSmemTiles = kTile + 3 * kTile + 2 * kTile + 8192;   // dO, K x3, V x2, dS
+constexpr uint32_t kSmemTilesStore = kSmemTiles + 8192;                 // + P
+constexpr int kMaxSlotsStore = 64;
 
 constexpr uint32_t kColS = 0;      // 64: S (M=64 rows x 64 keys, fp32)
 constexpr uint32_t kColDP = 64;    // 64: dP
@@ -68,31 +75,51 @@ struct TcDqParams {
   int H, T, G, chunk_size, causal;
   float scale, scale_log2;
   int32_t* status;
+  char* pds;            // optional: P and dS of every (group, head, slot) as 2 x 8 KiB swizzled tiles, for the dK/dV kernel
+  int MG;
 };
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+template <bool STORE>
 __global__ void __launch_bounds__(kThreads, 2)
 sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                      const __grid_constant__ CUtensorMap mapDQ, const TcDqParams p) {
+  constexpr int kKStages = 3;
+  constexpr int kSlots = STORE ? kMaxSlotsStore : kMaxSlots;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sDO = tiles;                                 // [2][64][128 B]
   uint8_t* sK = tiles + kTile;                          // kKStages stages; the last one first receives Q (moved to TMEM
                                                         // in the prologue), the first one is the epilogue's dQ staging tile
   uint8_t* sV = tiles + (1 + kKStages) * kTile;         // 2 stages
-  uint8_t* sDS = tiles + (3 + kKStages) * kTile;        // [64 q][128 B] swizzled
+  // dS [64 q][128 B] swizzled; with STORE the P tile (same image) comes first, so that { P, dS } is one 16 KiB piece
+  uint8_t* sP = tiles + (3 + kKStages) * kTile;
+  uint8_t* sDS = STORE ? sP + 8192 : sP;
   uint8_t* sQ = sK + (kKStages - 1) * kTile;            // landing tile of Q
   uint8_t* sOut = sK;                                   // dQ staging tile
 
-  __shared__ uint64_t qdo_full, q_moved, k_full[kKStages], k_empty[kKStages], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full,
-      ds_free, dq_final;
+  __shared__ uint64_t qdo_full, q_moved, k_full[3], k_empty[3], v_full[2], v_empty[2], sdp_full, sdp_free, ds_full,
+      ds_free, dq_final, tile_stored;
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort, s_nb;
-  __shared__ int s_row[kMaxSlots], s_nvis[kMaxSlots];
-  __shared__ float s_part[128];
+  __shared__ int s_row[kSlots];
+  __shared__ uint8_t s_nvis[kSlots];             // visible tokens of a listed block (1..64)
+  __shared__ uint8_t s_slot[kSlots];             // position of a visible block in the group's id list
+  // the partial sums of delta: in a tile nothing has touched yet when they are needed
+  float* s_part = reinterpret_cast<float*>(sDS);
 
+  if (STORE) {
+    // the host sizes the dynamic segment as the tiles plus the padding up to the next 1 KiB boundary
+    // after the static variables; refuse to run if that did not work out
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (tiles + kSmemTilesStore > smem_raw + dyn_bytes) {
+      if (threadIdx.x == 0) atomicExch(p.status, NSA_ERR_CUDA);
+      return;
+    }
+  }
   const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t m0 = static_cast<int64_t>(g) * p.G;
@@ -111,6 +138,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     mbar_init(&sdp_full, 1); mbar_init(&sdp_free, 128);
     mbar_init(&ds_full, 128); mbar_init(&ds_free, 1);
     mbar_init(&dq_final, 1);
+    mbar_init(&tile_stored, 1);
     fence_barrier_init();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
@@ -163,7 +191,8 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (nv > 0) {
         const int pos = base + __popc(live & ((1u << lane) - 1u));
         s_row[pos] = row;
-        s_nvis[pos] = nv;
+        s_nvis[pos] = static_cast<uint8_t>(nv);
+        s_slot[pos] = static_cast<uint8_t>(t);
       }
       base += __popc(live);
     }
@@ -256,16 +285,29 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // K tile [64 keys][128 dims] as two 64-column boxes 8 KiB apart, read with the head dim as M
         const uint64_t dKmn = smem_desc(smem_u32(sK + ks * kTile), 8192, 1024);
         if (el) {
+          if (STORE) {
+            // the step's { P, dS } tiles go to the pair's place in the buffer, one 16 KiB bulk store issued
+            // before the products so that it reads shared memory while they are being issued; the row
+            // warps overwrite the tiles only after the product (ds_free) AND the store (tile_stored) have read them
+            char* dst = p.pds + (((((static_cast<int64_t>(b) * p.MG + g) * p.H + h) * p.T) + s_slot[t]) << 14);
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 16384;" ::"l"(dst), "r"(smem_u32(sP)) : "memory");
+            bulk_commit_group();
+          }
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ss(tm + kColDQ, desc_advance(dKmn, kk * 2048), desc_advance(dDS, kk * 32), idesc, (t > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&k_empty[ks]);
           umma_commit(&ds_free);
           if (t == nb - 1) umma_commit(&dq_final);
+          if (STORE) {
+            bulk_wait_read_all();
+            mbar_arrive(&tile_stored);
+          }
         }
         __syncwarp();
         TRACE(0, 8 + t * 8 + 3);
       }
+      if (STORE && el) bulk_wait_all();
     }
   } else if (warp < 4) {
     // ======================= row arithmetic on accumulator fragments (warps 0-3) =======================
@@ -312,6 +354,9 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const float nl0 = r0 < n_q ? -(p.lse[bhm + r0] * kLog2e - lg) : -INFINITY;
       const float nl1 = r1 < n_q ? -(p.lse[bhm + r1] * kLog2e - lg) : -INFINITY;
       const float sl = p.scale_log2;
+      // exponent offsets of P itself (no scale folded in)
+      const float np0 = r0 < n_q ? -(p.lse[bhm + r0] * kLog2e) : -INFINITY;
+      const float np1 = r1 < n_q ? -(p.lse[bhm + r1] * kLog2e) : -INFINITY;
       // ---- Q from its landing tile into TMEM, in the layout of an M=64 A operand: row r in the lane of
       // accumulator row r, head dims 2c, 2c+1 in column c.  With tcgen05.st.16x128b a thread supplies, per
       // four-column block j, the word (row r0, column 4j + t%4) and the same column of row r1.
@@ -352,7 +397,27 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
         // x[4i], x[4i+1]: row r0, keys 8i+cq, +1;  x[4i+2], x[4i+3]: row r1.  Afterwards x[2i], x[2i+1]
         // hold the packed dS of (r0, r1) for key block i.
-        if (nv == 64) {
+        uint32_t pp[16];                              // STORE: the packed P of (r0, r1) per key block
+        if (STORE) {
+          // P = exp2(S c - LSE log2e) (masked keys: 0) and dS = P (dP - delta) scale from the same exponential
+          const float sc_ = p.scale;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = 8 * i + cq;
+            const float p00 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, np0)) : 0.f;
+            const float p01 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, np0)) : 0.f;
+            const float p10 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, np1)) : 0.f;
+            const float p11 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 3]), sl, np1)) : 0.f;
+            pp[2 * i] = pack2<__nv_bfloat16>(p00, p01);
+            pp[2 * i + 1] = pack2<__nv_bfloat16>(p10, p11);
+            const float d00 = p00 * ((__uint_as_float(y[4 * i]) - delta0) * sc_);
+            const float d01 = p01 * ((__uint_as_float(y[4 * i + 1]) - delta0) * sc_);
+            const float d10 = p10 * ((__uint_as_float(y[4 * i + 2]) - delta1) * sc_);
+            const float d11 = p11 * ((__uint_as_float(y[4 * i + 3]) - delta1) * sc_);
+            x[2 * i] = pack2<__nv_bfloat16>(d00, d01);
+            x[2 * i + 1] = pack2<__nv_bfloat16>(d10, d11);
+          }
+        } else if (nv == 64) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float d00 = fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0)) * (__uint_as_float(y[4 * i]) - delta0);
@@ -379,10 +444,20 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           ok = __all_sync(0xffffffffu, mbar_wait(&ds_free, (t - 1) & 1, abort));
           if (!ok) break;
         }
+        if (STORE && t > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&tile_stored, (t - 1) & 1, abort));
+          if (!ok) break;
+        }
         const uint32_t aDS = smem_u32(sDS) + st_row * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           stmatrix_x4(aDS + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+        if (STORE) {
+          const uint32_t aP = smem_u32(sP) + st_row * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            stmatrix_x4(aP + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), pp[4 * q], pp[4 * q + 1], pp[4 * q + 2], pp[4 * q + 3]);
+        }
         fence_async_smem();                           // make the rows visible to the tensor core's reads
         mbar_arrive(&ds_full);
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 4);
@@ -446,11 +521,13 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
                              const int64_t* idx_stride, const void* out, const int64_t* out_stride, const float* lse,
                              const void* d_out, const int64_t* do_stride, void* dq, const int64_t* dq_stride,
                              float* delta, int B, int64_t M, int H, int D, int T, int block_size, int chunk_size,
-                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched) {
+                             int causal, int G, float scale, int dtype, cudaStream_t stream, bool* launched,
+                             void* pds) {
   *launched = false;
   const char* env = getenv("OMNIMEM_B200_BWD_KERNEL");
   if (env != nullptr && std::string(env) == "general") return NSA_OK;
   if (dtype != NSA_BF16 || D != 128 || block_size != 64 || G > 64 || G < 16 || T > kMaxSlots || H == 1) return NSA_OK;
+  if (pds != nullptr && T > kMaxSlotsStore) pds = nullptr;   // (the caller is told: max_store_slots)
   if (!(scale > 0.f)) return NSA_OK;   // the kernel folds log2(scale) into the exponent
   if (kv->mode != NSA_KV_DENSE && kv->mode != NSA_KV_PAGED) return NSA_OK;
   if (kv->n_tokens <= 0 || M <= 0 || M > 0x7fffffff || kv->n_tokens > 0x7fffffff) return NSA_OK;
@@ -474,12 +551,20 @@ int try_launch_sel_bwd_dq_tc(const void* q, const int64_t* q_stride, const nsa_k
   p.block_table = kv->block_table; p.max_blocks = kv->max_blocks; p.paged = kv->mode == NSA_KV_PAGED;
   p.n_tokens = kv->n_tokens; p.M = M; p.H = H; p.T = T; p.G = G; p.chunk_size = chunk_size; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.pds = static_cast<char*>(pds); p.MG = static_cast<int>(cdiv64(M, G));
   if ((rc = device_status_address(&p.status))) return rc;
-  const size_t smem = kSmemTiles + 1024;
-  NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  NSA_CUDA_OK(cudaFuncSetAttribute(sel_bwd_dq_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+  size_t smem = kSmemTiles + 1024;
+  auto kernel = pds != nullptr ? sel_bwd_dq_tc_kernel<true> : sel_bwd_dq_tc_kernel<false>;
+  if (pds != nullptr) {
+    // 112 KiB of tiles start at the first 1 KiB boundary after the static variables: exactly half an SM
+    cudaFuncAttributes fa;
+    NSA_CUDA_OK(cudaFuncGetAttributes(&fa, kernel));
+    smem = kSmemTilesStore + (1024 - fa.sharedSizeBytes % 1024) % 1024;
+  }
+  NSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  NSA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    static_cast<int>(cudaSharedmemCarveoutMaxShared)));
-  NSA_CUDA_OK(launch_chained(kChainDq, sel_bwd_dq_tc_kernel, dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), dim3(kThreads), smem, stream,
+  NSA_CUDA_OK(launch_chained(kChainDq, kernel, dim3(static_cast<unsigned>(cdiv64(M, G)), H, B), dim3(kThreads), smem, stream,
                              mapQ, mapDO, mapK, mapV, mapDQ, p));
   NSA_LAUNCH_OK("sel_bwd_dq_tc_kernel");
   *launched = true;

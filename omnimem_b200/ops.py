@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -287,6 +288,18 @@ def sel_bwd(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: 
     dq = torch.empty(B, M, H, D, dtype=q.dtype, device=dev)
     dk = torch.empty(B, N, H, D, dtype=q.dtype, device=dev)
     dv = torch.empty(B, N, H, D, dtype=q.dtype, device=dev)
+    nbytes = stored_probabilities_bytes(q, kv, block_indices, block_size, group_size)
+    if nbytes:
+        # P and dS computed once: the dQ kernel stores them, the dK/dV kernel streams them
+        pds = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        NS = -(-N // block_size)
+        groups, offsets, slots = inverted_index(block_indices, NS, block_size, chunk_size, causal, group_size,
+                                                with_slots=True)
+        dq, delta, written = sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size, chunk_size, scale, causal,
+                                        group_size, pds=pds)
+        dk, dv = sel_bwd_dkv(q, kv, groups, offsets, lse, delta, d_out, T, block_size, chunk_size, scale, causal,
+                             group_size, slots=slots if written else None, pds=pds if written else None)
+        return dq, dk, dv
     src = kv.struct()
     with torch.cuda.device(dev):
         wsb = _lib.load().nsa_sel_bwd_workspace_bytes(B, M, H, N, T, block_size, group_size)
@@ -299,23 +312,43 @@ def sel_bwd(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: 
     return dq, dk, dv
 
 
+def stored_probabilities_bytes(q, kv, block_indices, block_size: int, group_size: int) -> int:
+    """Size of the P / dS buffer when the backward of this call can compute them once (dQ kernel
+    stores, dK/dV kernel streams), else 0.  The buffer holds 16 KiB per (query group, head, slot);
+    OMNIMEM_B200_BWD_STORED_MB caps it (default 4096, 0 turns the path off)."""
+    cap_mb = int(os.environ.get("OMNIMEM_B200_BWD_STORED_MB", "4096"))
+    B, M, H, D = q.shape
+    T = block_indices.shape[-1]
+    if (cap_mb <= 0 or q.dtype != torch.bfloat16 or D != 128 or block_size != 64 or not 16 <= group_size <= 64
+            or H == 1 or T > 64 or not isinstance(kv, (DenseKV, PagedKV))):
+        return 0
+    with torch.cuda.device(q.device):
+        n = _lib.load().nsa_sel_bwd_pds_bytes(B, M, H, T, group_size)
+    return n if 0 < n <= cap_mb << 20 else 0
+
+
 def inverted_index(block_indices: torch.Tensor, NS: int, block_size: int, chunk_size: int, causal: bool,
-                   group_size: int):
-    """CSR block -> query groups: (groups int32 [B,H,MG*T], offsets int32 [B,H,NS+1]); bucket
-    order is arrival order (the backward sorts each bucket before using it)."""
+                   group_size: int, with_slots: bool = False):
+    """CSR block -> query groups: (groups int32 [B,H,MG*T], offsets int32 [B,H,NS+1]), every bucket in
+    ascending group order; with_slots adds slots int32 [B,H,MG*T], the position of each entry in its
+    group's id list (buckets then ordered by (group, slot))."""
     _require_cuda(block_indices)
     B, MG, H, T = block_indices.shape
     dev = block_indices.device
     groups = torch.full((B, H, MG * T), -1, dtype=torch.int32, device=dev)
     offsets = torch.zeros(B, H, NS + 1, dtype=torch.int32, device=dev)
+    slots = torch.full((B, H, MG * T), -1, dtype=torch.int32, device=dev) if with_slots else None
     with torch.cuda.device(dev):
         wsb = _lib.load().nsa_inverted_index_workspace_bytes(B, H, NS)
         ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
-        call("nsa_inverted_index", block_indices.data_ptr(), strides4(block_indices), B, MG, H, T, NS,
-             _i32(block_size, "block_size"), _i32(chunk_size, "chunk_size"), int(bool(causal)),
-             _i32(group_size, "group_size"), groups.data_ptr(), offsets.data_ptr(), ws.data_ptr(), wsb,
-             _stream(block_indices))
-    return groups, offsets
+        args = (block_indices.data_ptr(), strides4(block_indices), B, MG, H, T, NS,
+                _i32(block_size, "block_size"), _i32(chunk_size, "chunk_size"), int(bool(causal)),
+                _i32(group_size, "group_size"), groups.data_ptr(), offsets.data_ptr())
+        if with_slots:
+            call("nsa_inverted_index_slots", *args, slots.data_ptr(), ws.data_ptr(), wsb, _stream(block_indices))
+        else:
+            call("nsa_inverted_index", *args, ws.data_ptr(), wsb, _stream(block_indices))
+    return (groups, offsets, slots) if with_slots else (groups, offsets)
 
 
 def merge_partials(outs: torch.Tensor, lses: torch.Tensor):
@@ -416,9 +449,11 @@ def dedup_run(block_indices_flat: torch.Tensor, stamp: torch.Tensor, out: torch.
 
 
 def sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: int, scale: float,
-               causal: bool, group_size: int):
+               causal: bool, group_size: int, pds: Optional[torch.Tensor] = None):
     """First half of the backward: (dq, delta fp32 [B,H,M]).  With a PtrKV source block_indices may
-    be None: the address tables define the slots (the reference's pointer path)."""
+    be None: the address tables define the slots (the reference's pointer path).  With `pds` (a
+    uint8 buffer of stored_probabilities_bytes) the result is (dq, delta, written): written says
+    whether the kernel stored P and dS of every pair there for sel_bwd_dkv."""
     layout = block_indices if block_indices is not None else kv.ptr_k
     _require_cuda(q, layout, out, lse, d_out)
     B, M, H, D = q.shape
@@ -428,17 +463,25 @@ def sel_bwd_dq(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_siz
     delta = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
     src = kv.struct()
     with torch.cuda.device(q.device):
-        call("nsa_sel_bwd_dq", q.data_ptr(), strides3(q), C.byref(src), _ptr(block_indices),
-             strides4(layout), out.data_ptr(), strides3(out), lse.data_ptr(), d_out.data_ptr(),
-             strides3(d_out), dq.data_ptr(), strides3(dq), delta.data_ptr(), B, M, H, D, layout.shape[-1],
-             _i32(block_size, "block_size"), _i32(chunk_size, "chunk_size"), int(bool(causal)),
-             _i32(group_size, "group_size"), float(scale), _dtype(q), _stream(q))
-    return dq, delta
+        args = (q.data_ptr(), strides3(q), C.byref(src), _ptr(block_indices),
+                strides4(layout), out.data_ptr(), strides3(out), lse.data_ptr(), d_out.data_ptr(),
+                strides3(d_out), dq.data_ptr(), strides3(dq), delta.data_ptr(), B, M, H, D, layout.shape[-1],
+                _i32(block_size, "block_size"), _i32(chunk_size, "chunk_size"), int(bool(causal)),
+                _i32(group_size, "group_size"), float(scale))
+        if pds is None:
+            call("nsa_sel_bwd_dq", *args, _dtype(q), _stream(q))
+            return dq, delta
+        written = C.c_int32(0)
+        call("nsa_sel_bwd_dq_pds", *args, pds.data_ptr(), pds.numel() * pds.element_size(), C.byref(written),
+             _dtype(q), _stream(q))
+    return dq, delta, bool(written.value)
 
 
 def sel_bwd_dkv(q, kv, groups, offsets, lse, delta, d_out, T: int, block_size: int, chunk_size: int,
-                scale: float, causal: bool, group_size: int):
-    """Second half of the backward: (dk, dv) [B,N,H,D] from the CSR index and delta."""
+                scale: float, causal: bool, group_size: int, slots: Optional[torch.Tensor] = None,
+                pds: Optional[torch.Tensor] = None):
+    """Second half of the backward: (dk, dv) [B,N,H,D] from the CSR index and delta; with `slots` and
+    `pds` (after a sel_bwd_dq call that reported written) from the stored P / dS tiles."""
     _require_cuda(q, groups, offsets, lse, delta, d_out)
     B, M, H, D = q.shape
     q, d_out = _rows16(q), _rows16(d_out)
@@ -448,7 +491,10 @@ def sel_bwd_dkv(q, kv, groups, offsets, lse, delta, d_out, T: int, block_size: i
     src = kv.struct()
     with torch.cuda.device(q.device):
         ws = torch.empty(256, dtype=torch.uint8, device=q.device)
-        call("nsa_sel_bwd_dkv", q.data_ptr(), strides3(q), C.byref(src), groups.data_ptr(), offsets.data_ptr(),
+        stored = slots is not None and pds is not None
+        call("nsa_sel_bwd_dkv_pds", q.data_ptr(), strides3(q), C.byref(src), groups.data_ptr(), offsets.data_ptr(),
+             slots.data_ptr() if stored else None, pds.data_ptr() if stored else None,
+             pds.numel() * pds.element_size() if stored else 0,
              lse.contiguous().data_ptr(), delta.data_ptr(), d_out.data_ptr(), strides3(d_out), dk.data_ptr(),
              dv.data_ptr(), B, M, H, D, _i32(T, "T"), _i32(block_size, "block_size"),
              _i32(chunk_size, "chunk_size"), int(bool(causal)), _i32(group_size, "group_size"), float(scale),

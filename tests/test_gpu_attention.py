@@ -223,6 +223,77 @@ def test_inverted_index_many_blocks(dev):
     assert torch.equal(groups.cpu()[:, :, :n], g_ref[:, :, :n])
 
 
+def test_inverted_index_slots(dev):
+    """The slot output: entry e of a bucket names (group, slot) with ids[b, group, h, slot] == the
+    bucket's block; groups as without slots, buckets ordered by (group, slot), duplicates kept apart."""
+    g = torch.Generator().manual_seed(27)
+    for NS, T, MG in ((16, 5, 7), (45000, 6, 40)):                     # one-kernel and multi-kernel index
+        ids = torch.randint(-1, NS if NS < 100 else 60, (2, MG, 3, T), generator=g, dtype=torch.int32)
+        ids[0, 1, 0, :2] = 3                                            # a duplicate inside a row
+        plain_g, plain_o = _ops().inverted_index(ids.to(dev), NS, 8, 16, False, 4)
+        groups, offsets, slots = _ops().inverted_index(ids.to(dev), NS, 8, 16, False, 4, with_slots=True)
+        assert torch.equal(offsets, plain_o)
+        n = int(offsets[0, 0, -1])
+        assert torch.equal(groups[:, :, :n], plain_g[:, :, :n])
+        groups, offsets, slots = groups.cpu(), offsets.cpu(), slots.cpu()
+        for b in range(2):
+            for h in range(3):
+                seen = set()
+                for blk in ids[b, :, h].unique().tolist():
+                    if blk < 0:
+                        continue
+                    lo, hi = int(offsets[b, h, blk]), int(offsets[b, h, blk + 1])
+                    pairs = list(zip(groups[b, h, lo:hi].tolist(), slots[b, h, lo:hi].tolist()))
+                    assert pairs == sorted(pairs) and len(set(pairs)) == len(pairs)
+                    for gg, tt in pairs:
+                        assert int(ids[b, gg, h, tt]) == blk
+                    seen.update(pairs)
+                want = {(gg, tt) for gg in range(MG) for tt in range(T) if 0 <= int(ids[b, gg, h, tt]) < NS}
+                assert seen == want
+
+
+@pytest.mark.parametrize("case", [
+    # seed, M, N, H, T, chunk, causal, paged
+    (61, 4680, 6000, 3, 7, 1560, True, False),
+    (62, 200, 1000, 2, 5, 100, True, True),
+    (63, 3072, 384, 2, 4, 3072, False, False),           # 48 query groups per block bucket: long buckets
+    (64, 150, 64 * 40 + 9, 4, 16, 150, False, True),     # ragged last block and group
+])
+def test_backward_from_stored_probabilities(dev, monkeypatch, case):
+    """The backward that computes P and dS once (dQ kernel stores the tiles, dK/dV kernel streams
+    them) against the backward that recomputes them and against the oracle; twice, bit for bit."""
+    seed, M, N, H, T, chunk, causal, paged = case
+    ops = _ops()
+    q, k, v, do, ids = _rand_case(seed, 1, M, N, H, 128, T, 64, 64, chunk, causal)
+    ids[0, 0, 0, T // 2:] = -1
+    ids[0, 1, 1, 1] = ids[0, 1, 1, 0]                                   # a block listed twice in one row
+    scale = 128 ** -0.5
+    qd, kd, vd, dod, idd = (t.to(dev) for t in (q, k, v, do, ids))
+    if paged:
+        from omnimem_b200.cache import BlockKVCache
+        nb = -(-N // 64)
+        cache = BlockKVCache(H, 128, num_pages=H * nb + 3, max_blocks=nb + 2, page_tokens=64, device=dev, host_tier=False)
+        cache.append(kd[0], vd[0])
+        kv = cache.kv_source()
+    else:
+        kv = ops.DenseKV(kd, vd)
+    out, lse = ops.sel_fwd(qd, kv, idd, 64, chunk, scale, causal, 64)
+    assert ops.stored_probabilities_bytes(qd, kv, idd, 64, 64) == (-(-M // 64)) * H * T * 16384
+    got = ops.sel_bwd(qd, kv, idd, out, lse, dod, 64, chunk, scale, causal, 64)
+    again = ops.sel_bwd(qd, kv, idd, out, lse, dod, 64, chunk, scale, causal, 64)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b), "not bit-reproducible"
+    monkeypatch.setenv("OMNIMEM_B200_BWD_STORED_MB", "0")
+    assert ops.stored_probabilities_bytes(qd, kv, idd, 64, 64) == 0
+    ref = ops.sel_bwd(qd, kv, idd, out, lse, dod, 64, chunk, scale, causal, 64)
+    monkeypatch.delenv("OMNIMEM_B200_BWD_STORED_MB")
+    o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), ids, 64, chunk, scale, causal, 64)
+    orc = O.selection_bwd(q.float(), k.float(), v.float(), ids, o_ref, l_ref, do.float(), 64, chunk, scale, causal, 64)
+    for name, a, b, c in zip(("dq", "dk", "dv"), got, ref, orc):
+        assert_close_bf16(a, b, f"stored vs recomputed {name} (seed {seed})")
+        assert_close_bf16(a, c, f"stored {name} vs oracle (seed {seed})")
+
+
 def test_pointer_table_source(dev):
     g = torch.Generator().manual_seed(27)
     B, M, N, H, D, bs, G, T = 1, 128, 512, 2, 128, 64, 64, 3
