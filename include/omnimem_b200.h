@@ -159,6 +159,11 @@ int nsa_select_blocks(const void* q, const int64_t q_stride[3], const void* k,
                       void* k_pooled_out, int32_t* out_idx, float* out_scores, void* workspace,
                       size_t workspace_bytes, int32_t dtype, void* stream);
 
+/* Block-sharded memories (block b on rank b mod R as local block b / R): the ids a rank attends
+ * itself, out[i] = ids[i] / R where ids[i] >= 0 and ids[i] mod R == r, else -1.  No counterpart in
+ * the reference (it has no multi-GPU mode for this path). */
+int nsa_local_block_ids(const int32_t* ids, int64_t n, int32_t R, int32_t r, int32_t* out, void* stream);
+
 /* Merge R candidate lists (idx/scores [R][rows][T], global ids) into the global top-k with
  * the same order rule.  New for block-sharded KV; the order rule is topk.cu:100-102 and the
  * packed-key merge it mirrors is topk.cu:442-471. */

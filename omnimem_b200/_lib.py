@@ -84,6 +84,7 @@ PROTOTYPES = {
                                   C.POINTER(C.c_int32), _i32, _vp]),
     "nsa_sel_bwd_dkv_pds": (_i32, [_vp, _S3, C.POINTER(KVSource), _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _S3, _vp, _vp,
                                    _i32, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _sz, _i32, _vp]),
+    "nsa_local_block_ids": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp]),
     "nsa_merge_partials": (_i32, [_vp, _vp, _i32, _i32, _i64, _i32, _i32, _vp, _vp, _i32, _vp]),
     "nsa_merge_packed_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _i32, _vp]),
     "nsa_sel_bwd_dkv_ptr": (_i32, [_vp, _S3, _vp, _vp, _vp, _vp, _S3, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _i64,

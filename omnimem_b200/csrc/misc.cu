@@ -180,6 +180,28 @@ extern "C" int nsa_merge_packed_rows(const void* parts, int32_t R, int64_t rows,
   return NSA_OK;
 }
 
+namespace nsa {
+namespace {
+__global__ void local_block_ids_kernel(const int32_t* __restrict__ ids, int64_t n, int R, int r, int32_t* __restrict__ out) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int32_t id = ids[i];
+    out[i] = (id >= 0 && id % R == r) ? id / R : -1;
+  }
+}
+}  // namespace
+}  // namespace nsa
+
+extern "C" int nsa_local_block_ids(const int32_t* ids, int64_t n, int32_t R, int32_t r, int32_t* out, void* stream) {
+  NSA_REQUIRE(R >= 1 && r >= 0 && r < R && n >= 0, NSA_ERR_INVALID, "local_block_ids: need 0 <= r < R and n >= 0");
+  if (n == 0) return NSA_OK;
+  NSA_REQUIRE(ids && out, NSA_ERR_INVALID, "local_block_ids: null pointer");
+  const int blocks = static_cast<int>(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
+  nsa::local_block_ids_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, n, R, r, out);
+  NSA_LAUNCH_OK("local_block_ids_kernel");
+  return NSA_OK;
+}
+
 extern "C" int nsa_build_ptr_table(const int32_t* block_indices, const int64_t idx_stride[4],
                                    const int64_t* base_k, const int64_t* base_v,
                                    const int32_t* n_blocks_per_head, int32_t B, int32_t MG, int32_t H,

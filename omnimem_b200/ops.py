@@ -139,7 +139,7 @@ def pool_score_topk(q_pooled: torch.Tensor, k: torch.Tensor, topk: int, scale: f
 def select_blocks(q: torch.Tensor, k: torch.Tensor, topk: int, scale: float, block_size: int, group_size: int,
                   chunk_size: int, chunk_size_k: int, causal: bool, ex_win: int = 0, ex_sink: int = 0,
                   prog_excl: bool = False, tf_mask: bool = False, q_chunk_offset: int = 0,
-                  return_scores: bool = False):
+                  return_scores: bool = False, id_base: int = 0, id_stride: int = 1):
     """Block selection from the raw tensors in one call: q [B,M,H,D] pooled per query group, k
     [B,N,H,D] pooled per key block and scored in the same pass, top-k per (group, head).
     Returns (idx int32 [B,MG,H,topk], q_pooled, k_pooled[, scores])."""
@@ -157,7 +157,7 @@ def select_blocks(q: torch.Tensor, k: torch.Tensor, topk: int, scale: float, blo
     out = torch.empty(B, MG, H, topk, dtype=torch.int32, device=dev)
     scores = torch.empty(B, MG, H, topk, dtype=torch.float32, device=dev) if return_scores else None
     m = _mask(block_size, chunk_size, chunk_size_k, group_size, q_chunk_offset, ex_win, ex_sink,
-              causal, tf_mask, prog_excl)
+              causal, tf_mask, prog_excl, id_base, id_stride)
     with torch.cuda.device(dev):
         wsb = _lib.load().nsa_topk_workspace_bytes(B, MG, H, NC)
         ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
@@ -165,6 +165,20 @@ def select_blocks(q: torch.Tensor, k: torch.Tensor, topk: int, scale: float, blo
              _i32(topk, "topk"), float(scale), C.byref(m), qp.data_ptr(), kp.data_ptr(), out.data_ptr(),
              _ptr(scores), ws.data_ptr(), wsb, _dtype(k), _stream(k))
     return (out, qp, kp, scores) if return_scores else (out, qp, kp)
+
+
+def local_block_ids(idx: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """Ids of a block-sharded memory as rank `rank` of `world` sees them: idx // world where the block
+    is this rank's (idx % world == rank), else -1; int32, same shape."""
+    _require_cuda(idx)
+    if idx.dtype != torch.int32:
+        raise NSABackendError("local_block_ids: ids must be int32")
+    idx = idx.contiguous()
+    out = torch.empty_like(idx)
+    with torch.cuda.device(idx.device):
+        call("nsa_local_block_ids", idx.data_ptr(), idx.numel(), _i32(world, "world"), _i32(rank, "rank"),
+             out.data_ptr(), _stream(idx))
+    return out
 
 
 def merge_candidates(idx: torch.Tensor, scores: torch.Tensor, topk: int):

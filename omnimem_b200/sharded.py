@@ -82,12 +82,19 @@ class ShardedSelection:
         over the local keys."""
         ops = self.ops
         sc = q.shape[-1] ** -0.5 if scale is None else scale
-        qp = ops.pool_rows(q, group_size) if group_size > 1 else q
-        kp = k_pooled_local if k_pooled_local is not None else ops.pool_rows(k_local, block_size)
-        idx, val = ops.topk(qp, kp, topk, sc, block_size, chunk_size, chunk_size, causal,
-                            ex_win=exclude_window_chunks, ex_sink=exclude_sink_chunks, prog_excl=progressive_exclude,
-                            q_chunk_offset=q_chunk_offset, q_group_size=group_size, id_base=self.rank,
-                            id_stride=self.world, return_scores=True)
+        if k_pooled_local is None and group_size > 1 and hasattr(ops, "select_blocks"):
+            # both poolings in one launch, then scoring + selection
+            idx, _, _, val = ops.select_blocks(q, k_local, topk, sc, block_size, group_size, chunk_size, chunk_size, causal,
+                                               ex_win=exclude_window_chunks, ex_sink=exclude_sink_chunks,
+                                               prog_excl=progressive_exclude, q_chunk_offset=q_chunk_offset,
+                                               return_scores=True, id_base=self.rank, id_stride=self.world)
+        else:
+            qp = ops.pool_rows(q, group_size) if group_size > 1 else q
+            kp = k_pooled_local if k_pooled_local is not None else ops.pool_rows(k_local, block_size)
+            idx, val = ops.topk(qp, kp, topk, sc, block_size, chunk_size, chunk_size, causal,
+                                ex_win=exclude_window_chunks, ex_sink=exclude_sink_chunks, prog_excl=progressive_exclude,
+                                q_chunk_offset=q_chunk_offset, q_group_size=group_size, id_base=self.rank,
+                                id_stride=self.world, return_scores=True)
         if self.world == 1:
             return idx, val
         # ids and scores travel as one buffer of 32-bit words
@@ -101,9 +108,12 @@ class ShardedSelection:
         ops = self.ops
         sc = q.shape[-1] ** -0.5 if scale is None else scale
         R, r = self.world, self.rank
-        mine = (idx_global >= 0) & (idx_global % R == r)
-        local_ids = torch.where(mine, torch.div(idx_global, R, rounding_mode="floor"), torch.full_like(idx_global, -1))
-        local_ids = local_ids.to(torch.int32)
+        if hasattr(ops, "local_block_ids"):
+            local_ids = ops.local_block_ids(idx_global, R, r)
+        else:
+            mine = (idx_global >= 0) & (idx_global % R == r)
+            local_ids = torch.where(mine, torch.div(idx_global, R, rounding_mode="floor"), torch.full_like(idx_global, -1))
+            local_ids = local_ids.to(torch.int32)
         kv = ops.DenseKV(k_local, v_local)
         if R == 1:
             return ops.sel_fwd(q, kv, local_ids, block_size, 1, sc, False, group_size)

@@ -117,3 +117,14 @@ def test_nccl_ranks_match_single_device():
         p.join(timeout=300)
         assert p.exitcode == 0
     assert all(ret.get(timeout=10))
+
+
+def test_local_block_ids(dev):
+    """Global ids -> the ids rank r of R attends itself (block b lives on rank b % R as local block b // R)."""
+    from omnimem_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(-1, 500, (2, 9, 3, 16), generator=g, dtype=torch.int32)
+    for R, r in ((1, 0), (2, 1), (5, 3), (8, 0)):
+        got = ops.local_block_ids(ids.to(dev), R, r).cpu()
+        want = torch.where((ids >= 0) & (ids % R == r), ids // R, torch.full_like(ids, -1))
+        assert torch.equal(got, want)
