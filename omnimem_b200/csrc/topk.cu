@@ -529,6 +529,36 @@ __device__ long long g_trace_ss[16];
 #define SS_TRACE(slot) do { } while (0)
 #endif
 
+// Bitonic sort of up to 64 keys held two per lane (element e = i * 32 + lane), largest first; with
+// `both` false the second key of every lane is known to be 0 and only the first 32 are sorted.
+__device__ __forceinline__ void warp_sort64_desc(unsigned long long& k0, unsigned long long& k1, bool both) {
+  const int lane = threadIdx.x & 31;
+  auto exchange = [&](unsigned long long& v, int e, int k, int j) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, j);
+    const bool keep_max = ((e & j) == 0) == ((e & k) == 0);
+    const bool other_larger = other > v;
+    v = (keep_max == other_larger) ? other : v;
+  };
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1)
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      exchange(k0, lane, k, j);
+      if (both) exchange(k1, 32 + lane, k, j);
+    }
+  if (both) {
+    // k = 64: every element sorts downwards; j = 32 pairs the lane's two keys
+    const unsigned long long hi = k0 > k1 ? k0 : k1, lo = k0 > k1 ? k1 : k0;
+    k0 = hi;
+    k1 = lo;
+#pragma unroll
+    for (int j = 16; j > 0; j >>= 1) {
+      exchange(k0, lane, 64, j);
+      exchange(k1, 32 + lane, 64, j);
+    }
+  }
+}
+
 // Rows with at most 32*ITEMS candidates: one warp per row, no block-wide barrier.  Same keys and
 // order as select_kernel.
 //
@@ -539,6 +569,42 @@ template <int ITEMS>
 __device__ __forceinline__ void warp_take_topk(unsigned long long (&keys)[ITEMS], int topk, int32_t* oi, float* os,
                                                unsigned long long (*sorted)[32]) {
   const int lane = threadIdx.x & 31;
+  if (ITEMS >= 2 && topk <= 16) {
+    // Threshold first: the topk-th largest of the 32 lane maxima, tau, has at least topk keys at or
+    // above it, so the row's top-k is among the keys >= tau - a few dozen of the 32 * ITEMS - which
+    // are compacted and sorted across the lanes.  Exact; rows that leave more than 64 such keys (few
+    // candidates spread over fewer than topk lanes) take the general path below.
+    unsigned long long v = keys[0];
+#pragma unroll
+    for (int i = 1; i < ITEMS; ++i) v = keys[i] > v ? keys[i] : v;
+    unsigned long long none = 0ull;
+    warp_sort64_desc(v, none, false);
+    const unsigned long long tau = __shfl_sync(0xffffffffu, v, topk - 1);
+    unsigned long long* cand = &sorted[0][0];
+    int total = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const bool in = keys[i] != 0ull && keys[i] >= tau;
+      const uint32_t m = __ballot_sync(0xffffffffu, in);
+      if (in) {
+        const int pos = total + __popc(m & ((1u << lane) - 1u));
+        if (pos < 64) cand[pos] = keys[i];
+      }
+      total += __popc(m);
+    }
+    __syncwarp();
+    if (total <= 64) {
+      unsigned long long k0 = lane < total ? cand[lane] : 0ull;
+      unsigned long long k1 = lane + 32 < total ? cand[32 + lane] : 0ull;
+      warp_sort64_desc(k0, k1, total > 32);
+      if (lane < topk) {
+        oi[lane] = k0 != 0ull ? key_id(k0) : -1;
+        if (os) os[lane] = k0 != 0ull ? key_score(k0) : -INFINITY;
+      }
+      return;
+    }
+    __syncwarp();                                          // the scratch is reused below
+  }
   // Each lane sorts its own keys once, largest first (bitonic network, all indices compile-time
   // constants, so the keys stay in registers), and parks the list in shared memory; a lane that
   // owns a round's winner then only steps to its next key.
