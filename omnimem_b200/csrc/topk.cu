@@ -683,6 +683,7 @@ __device__ __forceinline__ void warp_select(const SelectParams& p, const float* 
     }
   }
   unsigned long long keys[ITEMS];
+  const RowBounds rb = MERGE ? RowBounds{0, 0, 0, 0} : make_row_bounds(p.mask, rm);   // the row's rules as id intervals
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const int64_t c = lane + 32 * i;
@@ -692,7 +693,8 @@ __device__ __forceinline__ void warp_select(const SelectParams& p, const float* 
         k = cids[i] < 0 ? 0ull : pack_key(vals[i], cids[i]);
       } else {
         const int bid = p.mask.id_base + static_cast<int>(c_off + c) * p.mask.id_stride;
-        k = visible(p.mask, rm, bid) ? pack_key(vals[i], bid) : 0ull;
+        const bool vis = p.mask.tf ? visible(p.mask, rm, bid) : visible_in(rb, bid);
+        k = vis ? pack_key(vals[i], bid) : 0ull;
       }
     }
     keys[i] = k;
