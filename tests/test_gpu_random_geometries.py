@@ -56,8 +56,10 @@ def test_tensor_core_kernels_agree_with_general_kernels_on_random_geometries(dev
         fin = torch.isfinite(lse_g)
         assert torch.equal(torch.isfinite(lse_t), fin), tag + " lse -inf pattern"
         assert torch.allclose(lse_t[fin], lse_g[fin], atol=2e-3, rtol=1e-4), tag + " lse"
-        nsel = max(1.0, MG * T / NS)
-        bound = 4e-2 * max(2.0, nsel ** 0.5 * 2)
-        _close(grad_t[0], grad_g[0], 4e-2, 2e-3, tag + " dq")
-        _close(grad_t[1], grad_g[1], bound, 3e-3 * max(1.0, nsel ** 0.5), tag + " dk")
-        _close(grad_t[2], grad_g[2], bound, 3e-3 * max(1.0, nsel ** 0.5), tag + " dv")
+        # Both kernel families round at the same points (P and dS to bf16, fp32 sums, bf16 results), so
+        # they differ by a rounding flip here and there: measured over the 48 cases max 2.0e-3 (dq),
+        # 1.6e-2 = one bf16 step of a value near 2 (dk), 0 (dv), means below 3e-5.  The bound is the
+        # contract's 2e-2 / 2e-3, or two bf16 steps of the largest value where that is more.
+        for name, a, b in zip(("dq", "dk", "dv"), grad_t, grad_g):
+            step2 = 2.0 ** -7 * float(b.float().abs().max())
+            _close(a, b, max(2e-2, step2), 2e-3, f"{tag} {name}")
