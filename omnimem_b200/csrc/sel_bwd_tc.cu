@@ -5,17 +5,17 @@
 // tiles and 256 TMEM columns each): the block-list / delta prologue and the store epilogue of one
 // block run beside the main loop of the other, and the tensor pipe always has a second queue to
 // draw from.  A step is ONE selected block (64 keys):
-//     S    = Q  K^T         (M=64, N=64, K=128)    Q is the A operand read from TMEM  warp 5 issues
-//     dP   = dO V^T         (M=64, N=64, K=128)                                       warp 5 issues
+//     S    = Q  K^T         (M=64, N=64, K=128)    Q is the A operand read from TMEM  warp 9 issues
+//     dP   = dO V^T         (M=64, N=64, K=128)                                       warp 9 issues
 //     dS   = exp2(S c - LSE + log2 scale) (dP - delta)   on accumulator fragments, stored as bf16
-//            with stmatrix into a swizzled shared tile                                warps 0-3
+//            with stmatrix into a swizzled shared tile                                warps 0-7 (two groups, half the keys each)
 //     dQ^T += K^T dS^T      (M=128 head dims, N=64 rows, K=64 keys; the K tile is read MN-major
-//            in place as A, dS K-major as B)                                          warp 6 issues
+//            in place as A, dS K-major as B)                                          warp 10 issues
 // Accumulating dQ transposed takes 64 TMEM columns instead of 128; the 64 columns saved hold Q,
 // which the row warps move from its landing tile into TMEM in the prologue (tcgen05.st.16x128b),
 // so S reads only K from shared memory and the landing tile becomes a third K stage - a K tile
 // is held from S(t) to dQ(t), two stages left the copy of K(t+2) on the path every other step.
-// Warp 4 builds the list of visible selected blocks and issues every TMA copy (Q and dO once,
+// Warp 8 builds the list of visible selected blocks and issues every TMA copy (Q and dO once,
 // K through a three-stage, V through a two-stage ring).  delta = sum_d(O dO) is reduced in the
 // prologue and stored for the dK/dV kernel.  The epilogue packs the dQ^T fragments to bf16 and
 // stores them transposed (stmatrix.trans) into the first K stage, dead by then, from where TMA
@@ -48,7 +48,8 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads = 224;
+constexpr int kThreads = 352;
+constexpr int kProducerWarp = 8, kScoreWarp = 9, kGradWarp = 10;   // warps 0-7 do the row arithmetic
 constexpr int kMaxSlots = 256;
 constexpr uint32_t kTile = 16384;                 // 64 rows x 256 bytes, as two 64-column halves of 8 KiB
 constexpr uint32_t kSmemTiles = kTile + 3 * kTile + 2 * kTile + 8192;   // dO, K x3, V x2, dS
@@ -132,32 +133,32 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(&qdo_full, 1);
-    mbar_init(&q_moved, 128);
+    mbar_init(&q_moved, 256);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(&sdp_full, 1); mbar_init(&sdp_free, 128);
-    mbar_init(&ds_full, 128); mbar_init(&ds_free, 1);
+    mbar_init(&sdp_full, 1); mbar_init(&sdp_free, 256);
+    mbar_init(&ds_full, 256); mbar_init(&ds_free, 1);
     mbar_init(&dq_final, 1);
     mbar_init(&tile_stored, 1);
     fence_barrier_init();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapDO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
   }
   chain_wait();                                // everything above needs no result of the kernel before this one
-  // ---- row warps start the loads for delta = sum_d O dO right away: thread j takes query row j / 2,
-  // head dims [64 (j & 1), +64)
-  const int drow_q = threadIdx.x >> 1, dhalf = threadIdx.x & 1;
-  uint4 ro_[8], rd_[8];
-  if (warp < 4 && drow_q < n_q) {
-    const uint4* orow = reinterpret_cast<const uint4*>(p.o + (b * p.o_sb + (m0 + drow_q) * p.o_sm + h * p.o_sh) * 2) + dhalf * 8;
-    const uint4* drow = reinterpret_cast<const uint4*>(p.dO + (b * p.do_sb + (m0 + drow_q) * p.do_sm + h * p.do_sh) * 2) + dhalf * 8;
+  // ---- row warps start the loads for delta = sum_d O dO right away: thread j takes query row j / 4,
+  // head dims [32 (j & 3), +32)
+  const int drow_q = threadIdx.x >> 2, dquarter = threadIdx.x & 3;
+  uint4 ro_[4], rd_[4];
+  if (warp < 8 && drow_q < n_q) {
+    const uint4* orow = reinterpret_cast<const uint4*>(p.o + (b * p.o_sb + (m0 + drow_q) * p.o_sm + h * p.o_sh) * 2) + dquarter * 4;
+    const uint4* drow = reinterpret_cast<const uint4*>(p.dO + (b * p.do_sb + (m0 + drow_q) * p.do_sm + h * p.do_sh) * 2) + dquarter * 4;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) { ro_[c] = orow[c]; rd_[c] = drow[c]; }
+    for (int c = 0; c < 4; ++c) { ro_[c] = orow[c]; rd_[c] = drow[c]; }
   }
-  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by warp 4
-  if (warp == 4) {
+  // ---- list of the visible selected blocks (TMA row coordinate, visible tokens), compacted by the producer warp
+  if (warp == kProducerWarp) {
     int base = 0;
     for (int t0 = 0; t0 < p.T; t0 += 32) {
       const int t = t0 + lane;
@@ -206,7 +207,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int nb = s_nb;
   if (threadIdx.x == 0) TRACE(1, 1);
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ======================= TMA producer =======================
     if (lane == 0 && nb > 0) {
       mbar_expect_tx(&qdo_full, 2 * kTile);
@@ -235,7 +236,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_wait(&qdo_full, 0, abort);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kScoreWarp) {
     // ======================= MMA issuer 1: S and dP (whole warp runs the loop, one elected lane issues) =======================
     if (nb > 0) {
       constexpr uint32_t idesc = instr_desc_bf16(64, 64, 0, 0);        // both operands K-major
@@ -270,7 +271,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         TRACE(0, 8 + t * 8 + 1);
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == kGradWarp) {
     // ======================= MMA issuer 2: dQ += dS K =======================
     if (nb > 0) {
       // dQ^T += K^T dS^T: the accumulator is (128 head dims) x (64 rows) and takes 64 TMEM columns instead of 128
@@ -309,23 +310,26 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
       if (STORE && el) bulk_wait_all();
     }
-  } else if (warp < 4) {
-    // ======================= row arithmetic on accumulator fragments (warps 0-3) =======================
-    // Warp w owns query rows 16w .. 16w+15 (TMEM lanes 32w .. 32w+15 of the M=64 accumulators);
-    // thread t holds rows r0 = 16w + t/4 and r1 = r0 + 8, columns 8i + 2(t%4), +1 of every 8-column block i.
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
-    const int cq = (lane & 3) * 2;
+  } else if (warp < 8) {
+    // ======================= row arithmetic on accumulator fragments (warps 0-7) =======================
+    // Two groups of four warps share every step: warps 0-3 take keys 0-31 of the block, warps 4-7 keys
+    // 32-63, which halves the time from S / dP to dS, the link of the chain that bounds a step.  Warps w and
+    // w + 4 own query rows 16(w%4) .. +15 (TMEM lanes 32(w%4) .. +15 of the M=64 accumulators); thread t holds
+    // rows r0 = 16(w%4) + t/4 and r1 = r0 + 8, keys 32 grp + 8i + 2(t%4), +1 of every 8-key block i of its half.
+    const int grp = warp >> 2, wq = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const int r0 = wq * 16 + (lane >> 2), r1 = r0 + 8;
+    const int cq = 32 * grp + (lane & 3) * 2;
     // stmatrix: this thread supplies the address of row (lane%8) of matrix (lane/8); the four matrices of
     // one instruction are (rows +0, block 2q), (rows +8, block 2q), (rows +0, block 2q+1), (rows +8, block 2q+1)
-    const int st_row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-    const int st_chunk = lane >> 4;
-    // delta = sum_d O dO: thread j reduced half a row from the loads issued at the top of the kernel
+    const int st_row = wq * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int st_chunk = 4 * grp + (lane >> 4);
+    // delta = sum_d O dO: thread j reduced a quarter of a row from the loads issued at the top of the kernel
     {
       float part = 0.f;
       if (drow_q < n_q) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           const uint32_t aw[4] = {ro_[c].x, ro_[c].y, ro_[c].z, ro_[c].w}, dw[4] = {rd_[c].x, rd_[c].y, rd_[c].z, rd_[c].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -336,17 +340,19 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
       s_part[threadIdx.x] = part;
     }
-    named_barrier(2, 128);
-    const float delta0 = s_part[2 * r0] + s_part[2 * r0 + 1], delta1 = s_part[2 * r1] + s_part[2 * r1 + 1];
-    if ((lane & 3) == 0) {
+    named_barrier(2, 256);
+    const float delta0 = (s_part[4 * r0] + s_part[4 * r0 + 1]) + (s_part[4 * r0 + 2] + s_part[4 * r0 + 3]);
+    const float delta1 = (s_part[4 * r1] + s_part[4 * r1 + 1]) + (s_part[4 * r1 + 2] + s_part[4 * r1 + 3]);
+    if (grp == 0 && (lane & 3) == 0) {
       if (r0 < n_q) p.delta[bhm + r0] = delta0;
       if (r1 < n_q) p.delta[bhm + r1] = delta1;
     }
+    named_barrier(2, 256);                             // the partial sums are read: their tile may be written
     if (nb == 0) {
       if (drow_q < n_q) {
-        char* drow = p.dq + (b * p.dq_sb + (m0 + drow_q) * p.dq_sm + h * p.dq_sh) * 2 + dhalf * 128;
+        char* drow = p.dq + (b * p.dq_sb + (m0 + drow_q) * p.dq_sm + h * p.dq_sh) * 2 + dquarter * 64;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(drow + c * 16) = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(drow + c * 16) = make_uint4(0, 0, 0, 0);
       }
     } else {
       // exponent offsets: LSE log2e - log2 scale (the scale of dS is folded into the exponent); +inf = no such row
@@ -359,20 +365,18 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const float np1 = r1 < n_q ? -(p.lse[bhm + r1] * kLog2e) : -INFINITY;
       // ---- Q from its landing tile into TMEM, in the layout of an M=64 A operand: row r in the lane of
       // accumulator row r, head dims 2c, 2c+1 in column c.  With tcgen05.st.16x128b a thread supplies, per
-      // four-column block j, the word (row r0, column 4j + t%4) and the same column of row r1.
+      // four-column block j, the word (row r0, column 4j + t%4) and the same column of row r1.  Group g
+      // moves head dims [64 g, +64).
       bool ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full, 0, abort));
       if (ok) {
+        const uint8_t* box = sQ + grp * 8192;
+        uint32_t w[16];
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const uint8_t* box = sQ + hf * 8192;
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            w[2 * j] = *reinterpret_cast<const uint32_t*>(box + r0 * 128 + ((j ^ (r0 & 7)) << 4) + 4 * (lane & 3));
-            w[2 * j + 1] = *reinterpret_cast<const uint32_t*>(box + r1 * 128 + ((j ^ (r1 & 7)) << 4) + 4 * (lane & 3));
-          }
-          tmem_st_16x128b_x8_nowait(tm + lane_base + kColQ + hf * 32, w);
+        for (int j = 0; j < 8; ++j) {
+          w[2 * j] = *reinterpret_cast<const uint32_t*>(box + r0 * 128 + ((j ^ (r0 & 7)) << 4) + 4 * (lane & 3));
+          w[2 * j + 1] = *reinterpret_cast<const uint32_t*>(box + r1 * 128 + ((j ^ (r1 & 7)) << 4) + 4 * (lane & 3));
         }
+        tmem_st_16x128b_x8_nowait(tm + lane_base + kColQ + grp * 32, w);
         tmem_st_wait();
         tc_fence_before();
       }
@@ -384,9 +388,9 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (!ok) break;
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 1);
         tc_fence_after();
-        uint32_t x[32], y[32];
-        tmem_ld_16x256b_x8_nowait(tm + lane_base + kColS, x);
-        tmem_ld_16x256b_x8_nowait(tm + lane_base + kColDP, y);
+        uint32_t x[16], y[16];
+        tmem_ld_16x256b_x4_nowait(tm + lane_base + kColS + 32 * grp, x);
+        tmem_ld_16x256b_x4_nowait(tm + lane_base + kColDP + 32 * grp, y);
         const int nv = s_nvis[t];
         // the dS tile of the previous step must have been consumed: normally long true, so poll once
         // here, where the round trip hides behind the TMEM load
@@ -396,13 +400,13 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_arrive(&sdp_free);
         if (threadIdx.x == 0) TRACE(1, 8 + t * 8 + 2);
         // x[4i], x[4i+1]: row r0, keys 8i+cq, +1;  x[4i+2], x[4i+3]: row r1.  Afterwards x[2i], x[2i+1]
-        // hold the packed dS of (r0, r1) for key block i.
-        uint32_t pp[16];                              // STORE: the packed P of (r0, r1) per key block
+        // hold the packed dS of (r0, r1) for key block i of this group's half.
+        uint32_t pp[8];                               // STORE: the packed P of (r0, r1) per key block
         if (STORE) {
           // P = exp2(S c - LSE log2e) (masked keys: 0) and dS = P (dP - delta) scale from the same exponential
           const float sc_ = p.scale;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const int c = 8 * i + cq;
             const float p00 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, np0)) : 0.f;
             const float p01 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, np0)) : 0.f;
@@ -419,7 +423,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           }
         } else if (nv == 64) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const float d00 = fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0)) * (__uint_as_float(y[4 * i]) - delta0);
             const float d01 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0)) * (__uint_as_float(y[4 * i + 1]) - delta0);
             const float d10 = fast_exp2(fmaf(__uint_as_float(x[4 * i + 2]), sl, nl1)) * (__uint_as_float(y[4 * i + 2]) - delta1);
@@ -429,7 +433,7 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const int c = 8 * i + cq;
             const float d00 = (c < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i]), sl, nl0)) * (__uint_as_float(y[4 * i]) - delta0) : 0.f;
             const float d01 = (c + 1 < nv) ? fast_exp2(fmaf(__uint_as_float(x[4 * i + 1]), sl, nl0)) * (__uint_as_float(y[4 * i + 1]) - delta0) : 0.f;
@@ -450,12 +454,12 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
         const uint32_t aDS = smem_u32(sDS) + st_row * 128;
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
+        for (int q = 0; q < 2; ++q)
           stmatrix_x4(aDS + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
         if (STORE) {
           const uint32_t aP = smem_u32(sP) + st_row * 128;
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+          for (int q = 0; q < 2; ++q)
             stmatrix_x4(aP + static_cast<uint32_t>(((2 * q + st_chunk) ^ (st_row & 7)) << 4), pp[4 * q], pp[4 * q + 1], pp[4 * q + 2], pp[4 * q + 3]);
         }
         fence_async_smem();                           // make the rows visible to the tensor core's reads
@@ -465,35 +469,33 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (threadIdx.x == 0) TRACE(1, 3);
       // ---- epilogue: dQ^T fragments (16 head-dim lanes x 64 rows per load) -> bf16 pairs of adjacent rows,
       // stored TRANSPOSED 8 x 8 at a time into the swizzled [row][head dim] staging tile (the first K stage,
-      // dead once every product has run) -> TMA tile stores
+      // dead once every product has run) -> TMA tile stores.  Group g takes lanes 16 g .. +15 of its quadrant.
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&dq_final, 0, abort));
       if (ok) {
         tc_fence_after();
+        const int lh = grp;
+        uint32_t x[32];
+        tmem_ld_16x256b_x8_nowait(tm + lane_base + (static_cast<uint32_t>(lh * 16) << 16) + kColDQ, x);
+        tmem_ld_wait();
+        // x[4i], x[4i+1]: head dim D0 + lane/4, rows 8i + 2(lane%4), +1;  x[4i+2], x[4i+3]: head dim + 8
+        const int D0 = wq * 32 + lh * 16;
+        const int dsel = D0 + ((lane >> 3) & 1) * 8;     // head dims of the matrix this lane addresses
+        const uint32_t boxa = smem_u32(sOut + (dsel >> 6) * 8192);
+        const uint32_t dchunk = static_cast<uint32_t>((dsel & 63) >> 3);
 #pragma unroll
-        for (int lh = 0; lh < 2; ++lh) {                   // lanes 0-15 and 16-31 of this warp's quadrant
-          uint32_t x[32];
-          tmem_ld_16x256b_x8_nowait(tm + lane_base + (static_cast<uint32_t>(lh * 16) << 16) + kColDQ, x);
-          tmem_ld_wait();
-          // x[4i], x[4i+1]: head dim D0 + lane/4, rows 8i + 2(lane%4), +1;  x[4i+2], x[4i+3]: head dim + 8
-          const int D0 = warp * 32 + lh * 16;
-          const int dsel = D0 + ((lane >> 3) & 1) * 8;     // head dims of the matrix this lane addresses
-          const uint32_t boxa = smem_u32(sOut + (dsel >> 6) * 8192);
-          const uint32_t dchunk = static_cast<uint32_t>((dsel & 63) >> 3);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int i0 = 2 * q, i1 = 2 * q + 1;
-            const uint32_t a0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0]), __uint_as_float(x[4 * i0 + 1]));
-            const uint32_t b0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0 + 2]), __uint_as_float(x[4 * i0 + 3]));
-            const uint32_t a1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1]), __uint_as_float(x[4 * i1 + 1]));
-            const uint32_t b1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1 + 2]), __uint_as_float(x[4 * i1 + 3]));
-            // matrices: (rows 8 i0.., dims D0..), (rows 8 i0.., dims D0+8..), (rows 8 i1.., D0..), (rows 8 i1.., D0+8..)
-            const int qrow = 8 * (2 * q + (lane >> 4)) + (lane & 7);
-            stmatrix_x4_trans(boxa + qrow * 128 + ((dchunk ^ static_cast<uint32_t>(qrow & 7)) << 4), a0, b0, a1, b1);
-          }
+        for (int q = 0; q < 4; ++q) {
+          const int i0 = 2 * q, i1 = 2 * q + 1;
+          const uint32_t a0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0]), __uint_as_float(x[4 * i0 + 1]));
+          const uint32_t b0 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i0 + 2]), __uint_as_float(x[4 * i0 + 3]));
+          const uint32_t a1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1]), __uint_as_float(x[4 * i1 + 1]));
+          const uint32_t b1 = pack2<__nv_bfloat16>(__uint_as_float(x[4 * i1 + 2]), __uint_as_float(x[4 * i1 + 3]));
+          // matrices: (rows 8 i0.., dims D0..), (rows 8 i0.., dims D0+8..), (rows 8 i1.., D0..), (rows 8 i1.., D0+8..)
+          const int qrow = 8 * (2 * q + (lane >> 4)) + (lane & 7);
+          stmatrix_x4_trans(boxa + qrow * 128 + ((dchunk ^ static_cast<uint32_t>(qrow & 7)) << 4), a0, b0, a1, b1);
         }
         fence_async_smem();
       }
-      named_barrier(1, 128);
+      named_barrier(1, 256);
       if (ok && threadIdx.x == 0) {
         for (int dh = 0; dh < 2; ++dh) tma_store_4d(&mapDQ, sOut + dh * 8192, dh * 64, h, static_cast<int>(m0), b);
         bulk_commit_group();
