@@ -82,7 +82,7 @@ class ShardedSelection:
         over the local keys."""
         ops = self.ops
         sc = q.shape[-1] ** -0.5 if scale is None else scale
-        if k_pooled_local is None and group_size > 1 and hasattr(ops, "select_blocks"):
+        if k_pooled_local is None and group_size > 1:
             # both poolings in one launch, then scoring + selection
             idx, _, _, val = ops.select_blocks(q, k_local, topk, sc, block_size, group_size, chunk_size, chunk_size, causal,
                                                ex_win=exclude_window_chunks, ex_sink=exclude_sink_chunks,
@@ -108,12 +108,7 @@ class ShardedSelection:
         ops = self.ops
         sc = q.shape[-1] ** -0.5 if scale is None else scale
         R, r = self.world, self.rank
-        if hasattr(ops, "local_block_ids"):
-            local_ids = ops.local_block_ids(idx_global, R, r)
-        else:
-            mine = (idx_global >= 0) & (idx_global % R == r)
-            local_ids = torch.where(mine, torch.div(idx_global, R, rounding_mode="floor"), torch.full_like(idx_global, -1))
-            local_ids = local_ids.to(torch.int32)
+        local_ids = ops.local_block_ids(idx_global, R, r)
         kv = ops.DenseKV(k_local, v_local)
         if R == 1:
             return ops.sel_fwd(q, kv, local_ids, block_size, 1, sc, False, group_size)

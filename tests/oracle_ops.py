@@ -25,6 +25,20 @@ def topk(q_pooled, k_pooled, topk, scale, block_size, chunk_size, chunk_size_k, 
                          q_group_size=q_group_size, return_scores=return_scores, col_ids=cols)
 
 
+def select_blocks(q, k, topk_, scale, block_size, group_size, chunk_size, chunk_size_k, causal, ex_win=0, ex_sink=0,
+                  prog_excl=False, tf_mask=False, q_chunk_offset=0, return_scores=False, id_base=0, id_stride=1):
+    qp = O.pool_rows(q, group_size) if group_size > 1 else q
+    kp = O.pool_rows(k, block_size)
+    r = topk(qp, kp, topk_, scale, block_size, chunk_size, chunk_size_k, causal, ex_win, ex_sink, prog_excl, tf_mask,
+             q_chunk_offset, group_size, id_base, id_stride, return_scores)
+    return (r[0], qp, kp, r[1]) if return_scores else (r, qp, kp)
+
+
+def local_block_ids(idx, world, rank):
+    mine = (idx >= 0) & (idx % world == rank)
+    return torch.where(mine, torch.div(idx, world, rounding_mode="floor"), torch.full_like(idx, -1)).to(torch.int32)
+
+
 def merge_candidates(idx, scores, topk):
     return O.merge_candidates(list(idx), list(scores), topk)
 
