@@ -425,6 +425,12 @@ int nsa_cache_select_victims(const int32_t* page_owner, const int64_t* page_stam
  *   direction 1 (fetch): slot of keys[1+i] -> pages[i]; then block_table[key] = page,
  *                        owner and stamp set.  keys is a count-first list as written by
  *                        nsa_cache_dedup_touch (out_missing).
+ *   direction 2 (stage): write-behind eviction, first half - pages[i] -> slot i of a STAGING buffer in
+ *                        device memory (passed as host_k / host_v), its owner -> keys[i] (written; -1 =
+ *                        nothing staged); tables updated as by an evict, so the page is free at once;
+ *   direction 3 (drain): second half, meant for a stream of its own - staging slot i (passed as
+ *                        k_pool / v_pool) -> the host slot of keys[i]; a fetch of those keys must be
+ *                        ordered after it (pages and the tables are not used).
  * n = *n_dev when n_dev != NULL (grid sized by cap), else n.  `counters` (device int64 [4], may
  * be NULL): counters[2] += pages evicted, counters[3] += pages fetched (bytes moved = pages x
  * 2 x page_bytes).

@@ -74,9 +74,14 @@ def rope_apply(x: torch.Tensor, rope: RopeSpec) -> torch.Tensor:
 
 
 class BlockKVCache:
+    _drain_streams = {}                       # device index -> the stream the write-behind copies run on
+
     def __init__(self, num_heads: int, head_dim: int, num_pages: int, max_blocks: int,
                  page_tokens: int = 64, dtype: torch.dtype = torch.bfloat16, device="cuda",
-                 host_tier: bool = True, protect_blocks: int = 0):
+                 host_tier: bool = True, protect_blocks: int = 0, write_behind: bool = True):
+        """`write_behind`: the pages an append evicts go to a staging buffer on the device (so they are
+        free at once) and from there to the host tier on a stream of their own, beside the work that
+        follows; which pages are evicted, and when, does not change."""
         dev = torch.device(device)
         if dev.type != "cuda":
             raise NSABackendError("BlockKVCache lives on a CUDA device")
@@ -110,6 +115,9 @@ class BlockKVCache:
         self._evicted_any = False
         self.page_bytes = page_tokens * head_dim * self.k_pool.element_size()
         self._dtype_code = ops._dtype(self.k_pool)
+        self.write_behind = bool(write_behind) and host_tier
+        self._stage_k = self._stage_v = self._stage_keys = None
+        self._drain_event = None                 # recorded behind the last copy from the staging buffer to the host
 
     # ------------------------------------------------------------------------------ helpers
     @property
@@ -165,6 +173,38 @@ class BlockKVCache:
              self.page_owner.data_ptr(), self.page_stamp.data_ptr(), self.epoch, self.counters.data_ptr(),
              self._stream())
 
+    def _wait_drain(self) -> None:
+        """Order the current stream behind the last write-behind copy (before the staging buffer is
+        reused and before anything reads the host tier)."""
+        if self._drain_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._drain_event)
+            self._drain_event = None
+
+    def _evict_write_behind(self, pages: torch.Tensor, n: int) -> None:
+        """Evict `n` listed pages (free ones pass through): to the staging buffer now, to the host
+        tier on the drain stream."""
+        self._wait_drain()
+        if self._stage_keys is None or self._stage_keys.numel() < n:
+            self._stage_k = torch.empty(n, self.page_tokens, self.D, dtype=self.dtype, device=self.device)
+            self._stage_v = torch.empty_like(self._stage_k)
+            self._stage_keys = torch.empty(n, dtype=torch.int32, device=self.device)
+        cur = torch.cuda.current_stream(self.device)
+        call("nsa_cache_move_pages", 2, pages.data_ptr(), self._stage_keys.data_ptr(), n, None, n,
+             self.k_pool.data_ptr(), self.v_pool.data_ptr(), self.page_bytes, self._stage_k.data_ptr(),
+             self._stage_v.data_ptr(), self.block_table.data_ptr(), self.page_owner.data_ptr(),
+             self.page_stamp.data_ptr(), self.epoch, self.counters.data_ptr(), cur.cuda_stream)
+        side = BlockKVCache._drain_streams.get(self.device.index)
+        if side is None:
+            side = BlockKVCache._drain_streams[self.device.index] = torch.cuda.Stream(self.device)
+        staged = torch.cuda.Event()
+        staged.record(cur)
+        side.wait_event(staged)
+        call("nsa_cache_move_pages", 3, None, self._stage_keys.data_ptr(), n, None, n,
+             self._stage_k.data_ptr(), self._stage_v.data_ptr(), self.page_bytes, self.host_k.data_ptr(),
+             self.host_v.data_ptr(), None, None, None, 0, None, side.cuda_stream)
+        self._drain_event = torch.cuda.Event()
+        self._drain_event.record(side)
+
     def _make_resident(self, ids: torch.Tensor, T: int, count: bool, protect_from: Optional[int] = None):
         """Stamp the pages of the listed blocks with the current epoch and bring the ones that have
         no page back from the host tier, evicting (free pages first, then least recently used)
@@ -179,6 +219,7 @@ class BlockKVCache:
              self.epoch, uniq.data_ptr(), miss.data_ptr(), cap, self.counters.data_ptr() if count else None,
              ws.data_ptr(), wsb, self._stream())
         if self._evicted_any and self.host_k is not None:
+            self._wait_drain()                   # a missing block may still be on its way to the host tier
             n_dev = miss[:1]
             victims = self._select_victims(0, n_dev, cap, protect_from)
             self._move(0, victims, None, 0, n_dev, cap)
@@ -226,7 +267,10 @@ class BlockKVCache:
             need = n_new * self.H
             if need:
                 pages = self._select_victims(need, None, need, protect_from)
-                self._move(0, pages, None, need, None, need)          # free pages pass through untouched
+                if self.write_behind:
+                    self._evict_write_behind(pages, need)             # free pages pass through untouched
+                else:
+                    self._move(0, pages, None, need, None, need)
                 new_pages[:, n_exist:] = pages.view(self.H, n_new)
                 if self.n_blocks * self.H + need > self.num_pages:
                     self._evicted_any = True
@@ -260,6 +304,7 @@ class BlockKVCache:
         if self.host_k is None:
             raise NSABackendError("evict_all needs the host tier")
         with torch.cuda.device(self.device):
+            self._wait_drain()
             pages = torch.arange(self.num_pages, dtype=torch.int32, device=self.device)
             self._move(0, pages, None, self.num_pages, None, self.num_pages)
         self._evicted_any = True
@@ -276,6 +321,7 @@ class BlockKVCache:
         return (out, lse) if return_lse else out
 
     def reset(self) -> None:
+        self._wait_drain()
         self.block_table.fill_(-1)
         self.page_owner.fill_(-1)
         self.page_stamp.zero_()

@@ -582,6 +582,41 @@ __global__ void __launch_bounds__(256) move_pages_kernel(const MoveParams p) {
   }
 }
 
+// Write-behind eviction, first half: like an evict, but the page goes to slot i of a staging
+// buffer in device memory (host_k / host_v hold the staging bases here) and its key to stage_keys[i]
+// (-1: nothing staged); tables are updated at once, so the page is free for the caller.
+__global__ void __launch_bounds__(256) stage_pages_kernel(const MoveParams p, int32_t* __restrict__ stage_keys) {
+  const int i = blockIdx.x;
+  const int n = p.n_dev ? *p.n_dev : p.n_host;
+  int key = -1;
+  const int page = i < n ? p.pages[i] : -1;
+  if (page >= 0) key = p.page_owner[page];
+  if (key >= 0) {
+    copy16(p.host_k + static_cast<int64_t>(i) * p.page_bytes, p.k_pool + static_cast<int64_t>(page) * p.page_bytes, p.page_bytes);
+    copy16(p.host_v + static_cast<int64_t>(i) * p.page_bytes, p.v_pool + static_cast<int64_t>(page) * p.page_bytes, p.page_bytes);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    stage_keys[i] = key;
+    if (key >= 0) {
+      p.block_table[key] = -1;
+      p.page_owner[page] = -1;
+      if (p.counters) atomicAdd(p.counters + 2, 1ull);
+    }
+  }
+}
+
+// Second half, on a stream of its own: staging slot i -> the host slot of stage_keys[i].
+// (k_pool / v_pool hold the staging bases here.)
+__global__ void __launch_bounds__(256) drain_pages_kernel(const MoveParams p) {
+  const int i = blockIdx.x;
+  const int key = p.keys[i];
+  if (key < 0) return;
+  copy16(p.host_k + static_cast<int64_t>(key) * p.page_bytes, p.k_pool + static_cast<int64_t>(i) * p.page_bytes, p.page_bytes);
+  copy16(p.host_v + static_cast<int64_t>(key) * p.page_bytes, p.v_pool + static_cast<int64_t>(i) * p.page_bytes, p.page_bytes);
+  __threadfence_system();
+}
+
 // --------------------------------------------- the reference's K1 / K2 contracts, re-expressed
 __global__ void gather_publish_clear_kernel(const int64_t* __restrict__ desc, int64_t n_fetch,
                                             int64_t n_clear, int64_t block_bytes, int wide) {
@@ -857,13 +892,24 @@ extern "C" int nsa_cache_move_pages(int32_t direction, const int32_t* pages, con
                                     void* v_pool, int64_t page_bytes, void* host_k, void* host_v,
                                     int32_t* block_table, int32_t* page_owner, int64_t* page_stamp,
                                     int64_t epoch, int64_t* counters, void* stream) {
-  NSA_REQUIRE(direction == 0 || direction == 1, NSA_ERR_INVALID, "cache_move_pages: direction must be 0 or 1");
+  NSA_REQUIRE(direction >= 0 && direction <= 3, NSA_ERR_INVALID, "cache_move_pages: direction must be 0 .. 3");
   NSA_REQUIRE(n >= 0 && cap >= 0 && page_bytes > 0 && page_bytes % 16 == 0, NSA_ERR_INVALID, "cache_move_pages: bad size");
-  NSA_REQUIRE(pages && k_pool && v_pool && block_table && page_owner && page_stamp, NSA_ERR_INVALID,
+  NSA_REQUIRE(k_pool && v_pool, NSA_ERR_INVALID, "cache_move_pages: null pointer");
+  NSA_REQUIRE(direction == 3 || (pages && block_table && page_owner && page_stamp), NSA_ERR_INVALID,
               "cache_move_pages: null pointer");
-  NSA_REQUIRE(direction == 0 || (keys && host_k && host_v), NSA_ERR_INVALID, "cache_move_pages: fetch needs keys and host slots");
+  NSA_REQUIRE(direction == 0 || (keys && host_k && host_v), NSA_ERR_INVALID,
+              "cache_move_pages: fetch, stage and drain need keys and the second set of slots");
   const int grid = n_dev ? cap : n;
   if (grid == 0) return NSA_OK;
+  if (direction >= 2) {
+    MoveParams sp{pages, keys, n, n_dev, static_cast<char*>(k_pool), static_cast<char*>(v_pool), page_bytes,
+                  static_cast<char*>(host_k), static_cast<char*>(host_v), block_table, page_owner, page_stamp, epoch,
+                  reinterpret_cast<unsigned long long*>(counters)};
+    if (direction == 2) stage_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(sp, const_cast<int32_t*>(keys));
+    else drain_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(sp);
+    NSA_LAUNCH_OK("stage / drain pages kernel");
+    return NSA_OK;
+  }
   MoveParams p{pages, keys, n, n_dev, static_cast<char*>(k_pool), static_cast<char*>(v_pool), page_bytes,
                static_cast<char*>(host_k), static_cast<char*>(host_v), block_table, page_owner, page_stamp, epoch,
                reinterpret_cast<unsigned long long*>(counters)};
