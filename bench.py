@@ -324,6 +324,57 @@ def hbm_kernels(ops, dev, d, pk):
     return out
 
 
+def range_kernels(ops, dev, pk, replays=20):
+    """The range forward (the layer's sliding-window branch) alone, at the rollout's sizes: 4680 queries x
+    12 heads over the pages of 1, 2 and 3 chunks, against the selection forward given the same blocks
+    as a list.  Inputs (29 - 86 MB of K/V) stay in L2; the kernel is bound by the tensor pipe."""
+    M, H, D = 4680, 12, 128
+    scale = D ** -0.5
+    out = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / replays * 1e3
+
+    g = torch.Generator().manual_seed(77)
+    q = torch.randn(1, M, H, D, generator=g).bfloat16().to(dev)
+    for chunks in (1, 2, 3):
+        N = chunks * M
+        nb = -(-N // 64)
+        k = torch.randn(1, N, H, D, generator=g).bfloat16().to(dev)
+        v = torch.randn(1, N, H, D, generator=g).bfloat16().to(dev)
+        kv = ops.DenseKV(k, v)
+        ids = torch.arange(nb, dtype=torch.int32, device=dev).expand(1, -(-M // 64), H, nb)
+        flops = 4.0 * M * N * H * D
+        us_r = timed(lambda: ops.range_fwd(q, kv, 0, nb, 64, scale))
+        us_l = timed(lambda: ops.sel_fwd(q, kv, ids, 64, 1, scale, False, 64))
+        o_r, _ = ops.range_fwd(q, kv, 0, nb, 64, scale)
+        o_l, _ = ops.sel_fwd(q, kv, ids, 64, 1, scale, False, 64)
+        out[f"{chunks}_chunks"] = {
+            "blocks": nb, "us": round(us_r, 1), "tflops": round(flops / us_r / 1e6, 1),
+            "frac": round(flops / us_r / 1e6 / pk["tensor"], 3), "peak": pk["tensor"], "bound": "tensor",
+            "us_listed_on_sel_fwd": round(us_l, 1), "max_abs_vs_listed": float((o_r.float() - o_l.float()).abs().max())}
+    return out
+
+
+def run_range_only(args):
+    """Only `range_kernels` (the command the ncu capture of the range forward runs)."""
+    from omnimem_b200 import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the GPU arm has no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    emit({"metric": "range_fwd_tflops", "range_only": True, "kernels": {"range_fwd": range_kernels(ops, dev, peaks())}})
+
+
 def run_hbm_only(args):
     """Only the isolated HBM / cache kernel timings of `hbm_kernels` (the command the ncu captures of
     those kernels run): one line with their entries."""
@@ -755,12 +806,14 @@ def run_rollout(args, dist, dev, rank, world, long_video=False):
                         "a fresh conditioning tensor every 40 frames" if long_video else
                         "config3: 21 latent frames (480x832, 81 frames) in 3-frame chunks, 4 denoising steps + 1 cache-write forward per chunk"),
            "model": f"Wan2.1-T2V-1.3B shape, {shape.num_layers} blocks, dim {shape.dim}, {shape.num_heads} heads, ffn {shape.ffn_dim}, random bf16 weights",
-           "attention": "cmp + swa + selection (top-16 of 64-token blocks per 64-query group), all three on the selection forward kernel",
+           "attention": "cmp + swa on the range forward (128-row tiles), selection (top-16 of 64-token blocks per 64-query group) on the selection forward",
            "latent_frames_per_second": round(world * plan.latent_frames / secs, 3), "seconds": round(secs, 3),
            "forwards": res.forwards, "ms_per_forward": round(secs * 1e3 / res.forwards, 2),
            "rollouts": world, "cache": res.cache, "gpu_mem_gib": round(mem, 1), "device_status_clean": True}
     if breakdown is not None:
         out["ms_per_forward_by_section_bracketed"] = breakdown
+        from omnimem_b200 import ops
+        out["window_attention_kernel"] = range_kernels(ops, dev, peaks())
     del model, caches
     torch.cuda.empty_cache()
     return out
@@ -889,6 +942,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     ap.add_argument("--hbm-only", action="store_true",
                     help="only the isolated timings of the HBM-bound selection and block-cache kernels (the command their ncu captures run)")
+    ap.add_argument("--range-only", action="store_true",
+                    help="only the isolated timings of the range forward at the rollout's window sizes (the command its ncu capture runs)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident steps only (no end-to-end leg, no CPU baseline): the command profiled by ncu")
     args = ap.parse_args()
@@ -904,6 +959,8 @@ def main():
         run_reference(args)
     elif args.hbm_only:
         run_hbm_only(args)
+    elif args.range_only:
+        run_range_only(args)
     elif args.workload != "selection":
         run_rollout_only(args)
     else:

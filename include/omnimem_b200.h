@@ -181,6 +181,24 @@ int nsa_sel_fwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* k
                 int32_t D, int32_t T, int32_t block_size, int32_t chunk_size, int32_t causal,
                 int32_t group_size, float scale, int32_t dtype, void* stream);
 
+/* Attention of every query over ONE contiguous range of KV blocks, [first_block, first_block +
+ * n_blocks) clipped to kv->n_tokens, not causal: out [B,M,H,D] and lse float [B,H,M], the same
+ * results as nsa_sel_fwd with every query group listing exactly those blocks (blocks without a
+ * page are skipped; an empty range gives out = 0, lse = -inf).  Because the list is shared, the
+ * kernel works on 128 query rows per thread block instead of one group.  Built for bf16, D = 128,
+ * block_size = 64, H > 1, dense or paged K/V, n_blocks <= 1024: NSA_ERR_UNSUPPORTED otherwise
+ * (list the blocks and call nsa_sel_fwd).
+ * A long range over few query tiles is cut into spans that run on thread blocks of their own and
+ * are joined by nsa_merge_partials, when `workspace` (nsa_range_fwd_workspace_bytes, 0 when no cut
+ * pays) is given and `out` is contiguous; without it the call runs uncut.
+ * Serves the layer's compressed and sliding-window branches, which the reference runs through
+ * its dense attention() (models/transformers/causal_wan_nsa_model.py:506-508). */
+size_t nsa_range_fwd_workspace_bytes(int32_t B, int64_t M, int32_t H, int32_t D, int32_t n_blocks);
+int nsa_range_fwd(const void* q, const int64_t q_stride[3], const nsa_kv_source* kv,
+                  int32_t first_block, int32_t n_blocks, void* out, const int64_t out_stride[3],
+                  float* lse, int32_t B, int64_t M, int32_t H, int32_t D, int32_t block_size,
+                  float scale, void* workspace, size_t workspace_bytes, int32_t dtype, void* stream);
+
 /* Inverted (block -> query groups) CSR index: groups int32 [B,H,MG*T], offsets int32
  * [B,H,NS+1]; pairs that are negative, out of range or causally invisible are dropped.
  * Replaces build_inverted_index_impl (inverted_index.cu:106-178). */

@@ -207,6 +207,12 @@ int try_launch_sel_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_s
                           int64_t M, int H, int D, int T, int block_size, int chunk_size, int causal, int G,
                           float scale, int dtype, int32_t* status, cudaStream_t stream, bool* launched);
 
+int try_launch_sel_range_fwd_tc(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int first_block,
+                                int n_blocks, void* out, const int64_t* out_stride, float* lse, int B, int64_t M,
+                                int H, int D, int block_size, float scale, int dtype, int splits,
+                                cudaStream_t stream, bool* launched);
+int range_fwd_splits(int B, int64_t M, int H, int n_blocks);
+
 int check_strides16(const char* what, const void* ptr, const int64_t* stride, int n, int esz) {
   NSA_REQUIRE(ptr != nullptr, NSA_ERR_INVALID, "%s: null pointer", what);
   NSA_REQUIRE(aligned16(ptr), NSA_ERR_LAYOUT, "%s: base address must be 16-byte aligned", what);
@@ -312,4 +318,56 @@ extern "C" int nsa_sel_fwd(const void* q, const int64_t q_stride[3], const nsa_k
   }
   return D == 128 ? launch<__half, 128>(p, static_cast<int>(MG), s)
                   : launch<__half, 64>(p, static_cast<int>(MG), s);
+}
+
+extern "C" size_t nsa_range_fwd_workspace_bytes(int32_t B, int64_t M, int32_t H, int32_t D, int32_t n_blocks) {
+  if (B <= 0 || M <= 0 || H <= 0 || D <= 0 || n_blocks <= 0) return 0;
+  const int splits = nsa::range_fwd_splits(B, M, H, n_blocks);
+  if (splits == 1) return 0;
+  const size_t outs = static_cast<size_t>(splits) * B * M * H * D * 2;
+  return ((outs + 255) & ~static_cast<size_t>(255)) + static_cast<size_t>(splits) * B * H * M * 4;
+}
+
+extern "C" int nsa_range_fwd(const void* q, const int64_t* q_stride, const nsa_kv_source* kv, int32_t first_block,
+                             int32_t n_blocks, void* out, const int64_t* out_stride, float* lse, int32_t B,
+                             int64_t M, int32_t H, int32_t D, int32_t block_size, float scale, void* workspace,
+                             size_t workspace_bytes, int32_t dtype, void* stream) {
+  using namespace nsa;
+  NSA_REQUIRE(q && kv && out && lse && q_stride && out_stride, NSA_ERR_INVALID, "range_fwd: null pointer");
+  NSA_REQUIRE(first_block >= 0 && n_blocks >= 0, NSA_ERR_INVALID, "range_fwd: first_block %d, n_blocks %d",
+              first_block, n_blocks);
+  if (B == 0 || M == 0 || H == 0) return NSA_OK;
+  NSA_REQUIRE(static_cast<int64_t>(B) <= 65535 && H <= 65535, NSA_ERR_INVALID, "range_fwd: B and H must be <= 65535");
+  NSA_REQUIRE(kv->mode == NSA_KV_DENSE || B == 1, NSA_ERR_INVALID, "range_fwd: paged K/V needs B == 1");
+  int rc = check_strides16("q", q, q_stride, 3, 2);
+  if (rc) return rc;
+  rc = check_strides16("out", out, out_stride, 3, 2);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // spans of the range on thread blocks of their own, when that fills the machine better and the
+  // caller gave the room for their partial results (the merged output is written contiguous)
+  int splits = n_blocks > 0 ? range_fwd_splits(B, M, H, n_blocks) : 1;
+  const size_t outs_bytes = (static_cast<size_t>(splits) * B * M * H * D * 2 + 255) & ~static_cast<size_t>(255);
+  const bool contiguous = out_stride[2] == D && out_stride[1] == static_cast<int64_t>(H) * D &&
+                          (B == 1 || out_stride[0] == M * H * D);
+  if (splits > 1 && (workspace == nullptr || !aligned16(workspace) || !contiguous || B * splits > 65535 ||
+                     workspace_bytes < outs_bytes + static_cast<size_t>(splits) * B * H * M * 4))
+    splits = 1;
+  bool launched = false;
+  if (splits > 1) {
+    char* part_out = static_cast<char*>(workspace);
+    float* part_lse = reinterpret_cast<float*>(part_out + outs_bytes);
+    const int64_t part_stride[3] = {M * H * D, static_cast<int64_t>(H) * D, D};
+    rc = try_launch_sel_range_fwd_tc(q, q_stride, kv, first_block, n_blocks, part_out, part_stride, part_lse, B, M, H,
+                                     D, block_size, scale, dtype, splits, s, &launched);
+    if (rc) return rc;
+    if (launched) return nsa_merge_partials(part_out, part_lse, splits, B, M, H, D, out, lse, dtype, stream);
+  }
+  rc = try_launch_sel_range_fwd_tc(q, q_stride, kv, first_block, n_blocks, out, out_stride, lse, B, M, H, D,
+                                   block_size, scale, dtype, 1, s, &launched);
+  if (rc) return rc;
+  NSA_REQUIRE(launched, NSA_ERR_UNSUPPORTED,
+              "range_fwd: built for bf16, D = 128, 64-token blocks, H > 1, dense or paged K/V, at most 1024 blocks; "
+              "list the blocks and call nsa_sel_fwd for anything else");
+  return NSA_OK;
 }

@@ -287,6 +287,43 @@ def sel_fwd(q: torch.Tensor, kv, block_indices: Optional[torch.Tensor], block_si
     return out, lse
 
 
+def range_fwd(q: torch.Tensor, kv, first_block: int, n_blocks: int, block_size: int, scale: float,
+              out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Attention of every query over the blocks [first_block, first_block + n_blocks) of `kv`, not
+    causal: (out [B,M,H,D], lse fp32 [B,H,M]), what sel_fwd returns when every query group lists
+    exactly those blocks.  Shapes the range kernel is not built for (anything but bf16, D = 128,
+    64-token blocks, H > 1, dense or paged K/V, <= 1024 blocks) go to sel_fwd with the list spelt out."""
+    _require_cuda(q)
+    B, M, H, D = q.shape
+    first_block, n_blocks = _i32(first_block, "first_block"), _i32(n_blocks, "n_blocks")
+    if first_block < 0 or n_blocks < 0:
+        raise NSABackendError(f"range_fwd: first_block {first_block}, n_blocks {n_blocks}")
+    covered = (q.dtype == torch.bfloat16 and D == 128 and block_size == 64 and H > 1 and scale > 0
+               and isinstance(kv, (DenseKV, PagedKV)) and n_blocks <= 1024 and kv.n_tokens > 0
+               and os.environ.get("OMNIMEM_B200_RANGE_KERNEL", "") != "listed")   # test hook: always list the blocks
+    if not covered:
+        G = 64
+        ids = torch.arange(first_block, first_block + max(n_blocks, 1), dtype=torch.int32, device=q.device)
+        if n_blocks == 0:
+            ids = torch.full_like(ids, -1)
+        ids = ids.expand(B, -(-M // G), H, ids.numel())
+        return sel_fwd(q, kv, ids, block_size, 1, scale, False, G, out=out)
+    q = _rows16(q)
+    if out is None:
+        out = torch.empty(B, M, H, D, dtype=q.dtype, device=q.device)
+    elif out.shape != q.shape or out.dtype != q.dtype or _rows16(out) is not out:
+        raise NSABackendError("range_fwd: `out` must have q's shape and dtype, unit innermost stride and 16-byte aligned rows")
+    lse = torch.empty(B, H, M, dtype=torch.float32, device=q.device)
+    src = kv.struct()
+    with torch.cuda.device(q.device):
+        nbytes = _lib.load().nsa_range_fwd_workspace_bytes(B, M, H, D, n_blocks) if out.is_contiguous() else 0
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+        call("nsa_range_fwd", q.data_ptr(), strides3(q), C.byref(src), first_block, n_blocks, out.data_ptr(),
+             strides3(out), lse.data_ptr(), B, M, H, D, _i32(block_size, "block_size"), float(scale), _ptr(ws), nbytes,
+             _dtype(q), _stream(q))
+    return out, lse
+
+
 def sel_bwd(q, kv, block_indices, out, lse, d_out, block_size: int, chunk_size: int, scale: float,
             causal: bool, group_size: int):
     """(dq [B,M,H,D] q.dtype, dk, dv [B,N,H,D] k dtype, contiguous)."""

@@ -170,21 +170,16 @@ class NSASelfAttention(nn.Module):
         with timer("cache_append"):
             cache.append(k, v, pos0=start_token, rope=rope)
         nb = cache.n_blocks
-        MG = -(-S // p.group)
-        dev = x.device
-        # compressed branch: attention over the pooled history, run by the selection forward over a
-        # dense [1, nb, H, D] view of the pooled keys / values with every block listed
+        # compressed branch: attention over the pooled history, a dense [1, nb, H, D] view of the pooled
+        # keys / values taken as one range of blocks
         with timer("cmp"):
-            t_cmp = -(-nb // p.block)
-            ids_cmp = torch.arange(t_cmp, dtype=torch.int32, device=dev).expand(1, MG, H, t_cmp)
-            o_cmp, _ = ops.sel_fwd(qr, ops.DenseKV(cache.pooled_keys(), cache.pooled_values()), ids_cmp, p.block, 1,
-                                   scale, False, p.group)
+            o_cmp, _ = ops.range_fwd(qr, ops.DenseKV(cache.pooled_keys(), cache.pooled_values()), 0,
+                                     -(-nb // p.block), p.block, scale)
         # sliding-window branch: the pages of the last window_chunks chunks through the block table
         with timer("swa"):
             first_tok = max(0, start_token - (p.window_chunks - 1) * S)
             first_blk = first_tok // p.block
-            ids_swa = torch.arange(first_blk, nb, dtype=torch.int32, device=dev).expand(1, MG, H, nb - first_blk)
-            o_swa, _ = ops.sel_fwd(qr, cache.kv_source(), ids_swa, p.block, 1, scale, False, p.group)
+            o_swa, _ = ops.range_fwd(qr, cache.kv_source(), first_blk, nb - first_blk, p.block, scale)
         # selection branch
         q_chunk = start_token // S
         if p.progressive_exclude or should_use_selection_attention(nb * p.block, S, p.exclude_window_chunks, 0, causal=False):
