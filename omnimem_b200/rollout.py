@@ -16,8 +16,8 @@ What runs where:
   * linear layers, norms, cross-attention (SDPA), feed-forward: torch;
   * key rotary embedding + pooling + page append (one kernel), query rotary embedding, query-group
     pooling, scoring + top-k, LRU touch / evict / fetch, all THREE attention branches (the selection
-    forward kernel over: the selected pages, the window's pages, the pooled history as a dense
-    tensor), and the gated sum: this library.
+    forward kernel over the selected pages; the range forward kernel over the window's pages and
+    over the pooled history as a dense tensor), and the gated sum: this library.
 Tokens stay in (frame, row, column) order and a block is 64 consecutive tokens (the reference pools
 spatial tiles of 15 x 2 tokens; 64-token blocks cut across rows and chunk boundaries, which the block
 cache is built for).  The window starts at the block that holds its first token.
