@@ -321,6 +321,27 @@ def hbm_kernels(ops, dev, d, pk):
     out["cache_evict_fetch"] = {"us_evict_plus_fetch": round(us, 1), "bytes_each_way": int(mv_bytes), "bound": "pcie",
                                 "achieved": round(2 * mv_bytes / (us * 1e-6) / 1e9, 1), "peak": 2 * pcie, "unit": "GB/s (both directions summed)",
                                 "note": f"{n_vict} pages to the pinned host tier and back (kernel copies through unified addressing)"}
+    del cache
+    # ---- delivery rooflines of the streaming dK/dV kernel: its copy shape (one block per SM, four stages of
+    # three 16 KiB bulk copies) with nothing computed, over an L2-resident and an HBM-resident buffer
+    for name, mb in (("bulk_stream_l2_resident", 96), ("bulk_stream_hbm_resident", 1536)):
+        buf = torch.empty(mb << 20, dtype=torch.uint8, device=dev)
+        buf.view(torch.int32).random_()
+        passes = max(1, 3072 // mb)
+        run = lambda: _lib.call("nsa_probe_bulk_stream", buf.data_ptr(), buf.numel(), passes, stream().cuda_stream)
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        moved = (buf.numel() // 49152) * 49152 * passes
+        out[name] = {"buffer_mb": mb, "passes": passes, "us": round(e0.elapsed_time(e1) * 1e3, 1),
+                     "achieved": round(moved / (e0.elapsed_time(e1) * 1e-3) / 1e9, 1), "unit": "GB/s",
+                     "note": "copies only; the rate operands can reach shared memory at in that kernel's shape"}
+        del buf
     return out
 
 

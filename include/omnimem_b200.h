@@ -472,6 +472,13 @@ int nsa_block_range(int64_t* table, int32_t* n_valid, int32_t H, int64_t MB, int
                     int64_t block_bytes, int64_t n_valid_value, int32_t write_k, int32_t write_v,
                     int32_t clear, void* stream);
 
+/* Measurement aid (no counterpart in the reference): one thread block per SM pulls the whole buffer
+ * `passes` times into shared memory with 16 KiB bulk copies, three per stage, four stages - the
+ * streaming dK/dV kernel's copy shape with nothing computed.  The caller times the launch; bytes
+ * moved = floor(bytes / 49152) * 49152 * passes.  bench.py quotes the rate over an L2-resident and
+ * over an HBM-resident buffer as that kernel's delivery rooflines. */
+int nsa_probe_bulk_stream(const void* buf, size_t bytes, int32_t passes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

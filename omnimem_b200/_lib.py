@@ -65,6 +65,7 @@ PROTOTYPES = {
     "nsa_merge_candidates": (_i32, [_vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),
     "nsa_sel_fwd": (_i32, [_vp, _S3, C.POINTER(KVSource), _vp, _S3, _vp, _S3, _vp, _i32, _i64, _i32,
                            _i32, _i32, _i32, _i32, _i32, _i32, _f32, _i32, _vp]),
+    "nsa_probe_bulk_stream": (_i32, [_vp, _sz, _i32, _vp]),
     "nsa_range_fwd_workspace_bytes": (_sz, [_i32, _i64, _i32, _i32, _i32]),
     "nsa_range_fwd": (_i32, [_vp, _S3, C.POINTER(KVSource), _i32, _i32, _vp, _S3, _vp, _i32, _i64, _i32, _i32,
                              _i32, _f32, _vp, _sz, _i32, _vp]),
