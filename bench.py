@@ -591,6 +591,14 @@ def run_gpu(args):
                 ach = amount / (ms * 1e-3) / 1e12
                 entry.update(bound=bound, achieved=round(ach, 2), peak=pk["tensor"], frac=round(ach / pk["tensor"], 4),
                              unit="TFLOP/s")
+            if n == "sel_bwd_dkv" and not RECOMPUTE_BACKWARD:
+                # the streaming kernel computes nothing twice; what it must move through HBM once: Q and dO rows,
+                # the stored P / dS tiles (16 KiB per pair), dK and dV of every token
+                cc = CFG
+                nbytes = (2 * cc["M"] + 2 * cc["N"]) * cc["H"] * cc["D"] * 2 + (-(-cc["M"] // cc["group"])) * cc["H"] * cc["topk"] * 16384
+                entry["hbm"] = {"bytes": nbytes, "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "peak": pk["hbm"], "unit": "GB/s",
+                                "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm"], 4),
+                                "note": "the bound that is nearer for this kernel: algorithmic bytes over the measured copy rate"}
             kernels[n] = entry
         if extra is not None:
             kernels["hbm_and_cache"] = extra
