@@ -140,3 +140,31 @@ def test_range_cut_into_spans_and_merged(dev, monkeypatch, splits):
         o_ref, l_ref = O.selection_fwd(q.float(), k.float(), v.float(), ids, 64, 1, scale, False, 64)
         _compare(os_, ls_, o_ref, l_ref, f"{splits} spans vs oracle (case {seed})")
         assert_close_bf16(os_, o1, f"{splits} spans vs uncut (case {seed})", max_abs=1.6e-2, mean_abs=1e-3)
+
+
+def test_c_entry_refuses_what_it_is_not_built_for(dev):
+    """The C entry itself (no Python fallback in front of it): fp16 and 32-token blocks are refused with
+    NSA_ERR_UNSUPPORTED and a message, a negative range with NSA_ERR_INVALID; nothing is launched."""
+    import ctypes as C
+    from omnimem_b200 import _lib
+    ops = _ops()
+    q = torch.randn(1, 128, 2, 128, device=dev).half()
+    k = torch.randn(1, 256, 2, 128, device=dev).half()
+    kv = ops.DenseKV(k, k.clone())
+    out = torch.empty_like(q)
+    lse = torch.empty(1, 2, 128, dtype=torch.float32, device=dev)
+    src = kv.struct()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(qt, first, n, bs, dtype):
+        return _lib.call("nsa_range_fwd", qt.data_ptr(), _lib.strides3(qt), C.byref(src), first, n, out.data_ptr(),
+                         _lib.strides3(out), lse.data_ptr(), 1, 128, 2, 128, bs, 128 ** -0.5, None, 0, dtype, stream)
+
+    with pytest.raises(_lib.NSABackendError, match="range_fwd: built for bf16"):
+        call(q, 0, 4, 64, _lib.NSA_F16)
+    with pytest.raises(_lib.NSABackendError, match="range_fwd: built for bf16"):
+        call(q, 0, 4, 32, _lib.NSA_BF16)
+    with pytest.raises(_lib.NSABackendError, match="first_block"):
+        call(q, -1, 4, 64, _lib.NSA_BF16)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
