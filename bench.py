@@ -434,6 +434,8 @@ def run_gpu(args):
         idx, out, dq, dk, dv = gpu_step(ops, d)
     torch.cuda.synchronize()
     flops_fwd = executed_flops_fwd(idx)
+    # selected (head, block) pairs counted once: ids [1, MG, H, T] -> per head the distinct block ids
+    uniq_pairs = sum(int(torch.unique(idx[0, :, h][idx[0, :, h] >= 0]).numel()) for h in range(idx.shape[2]))
     flops_step = int(flops_fwd * 3.5)
 
     # ---- per-kernel times: eager launches, one pair of events around each.  A spin kernel goes first
@@ -591,6 +593,17 @@ def run_gpu(args):
                 ach = amount / (ms * 1e-3) / 1e12
                 entry.update(bound=bound, achieved=round(ach, 2), peak=pk["tensor"], frac=round(ach / pk["tensor"], 4),
                              unit="TFLOP/s")
+            if n in ("sel_fwd", "sel_bwd_dq"):
+                # the other bound of the two tensor-core kernels: what each must move through HBM once.  K / V rows
+                # of the selected (head, block) pairs, counted once each; Q, out / dQ rows; for dQ also dO, out
+                # (the delta prologue) and, when it stores them, the P / dS tiles
+                cc = CFG
+                row = cc["H"] * cc["D"] * 2
+                nbytes = 2 * uniq_pairs * cc["block"] * cc["D"] * 2 + (2 if n == "sel_fwd" else 4) * cc["M"] * row
+                if n == "sel_bwd_dq" and not RECOMPUTE_BACKWARD:
+                    nbytes += (-(-cc["M"] // cc["group"])) * cc["H"] * cc["topk"] * 16384
+                entry["hbm"] = {"bytes": nbytes, "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "peak": pk["hbm"], "unit": "GB/s",
+                                "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm"], 4)}
             if n == "sel_bwd_dkv" and not RECOMPUTE_BACKWARD:
                 # the streaming kernel computes nothing twice; what it must move through HBM once: Q and dO rows,
                 # the stored P / dS tiles (16 KiB per pair), dK and dV of every token
@@ -605,6 +618,19 @@ def run_gpu(args):
         dom = max((n for n in per if n in work), key=lambda n: per[n])
         roof = dict(kernels[dom])
         roof.pop("ms")
+        # which roof binds: the one whose minimum time for this launch is the longer (tensor work at the measured
+        # cuBLAS rate against algorithmic bytes at the measured copy rate); the other one is kept beside it
+        hbm_view = roof.pop("hbm", None)
+        if hbm_view is not None:
+            t_tensor = work[dom][1] / (pk["tensor"] * 1e12)
+            t_hbm = hbm_view["bytes"] / (pk["hbm"] * 1e9)
+            tensor_view = {k: roof[k] for k in ("achieved", "peak", "frac", "unit")}
+            if t_hbm > t_tensor:
+                roof.update(bound="hbm", achieved=hbm_view["achieved"], peak=hbm_view["peak"], frac=hbm_view["frac"], unit="GB/s",
+                            algorithmic_bytes=hbm_view["bytes"], tensor=tensor_view)
+            else:
+                roof.update(hbm=hbm_view)
+            roof["min_time_us"] = {"tensor": round(t_tensor * 1e6, 1), "hbm": round(t_hbm * 1e6, 1)}
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, copied from the
         # committed ncu summaries of these kernels: a record of that capture, not a measurement of this run
         ncu_traffic = {"sel_fwd": 193.0e6 + 10.7e6, "sel_bwd_dq": 257.2e6 + 202.2e6, "sel_bwd_dkv": 262.0e6 + 162.9e6}
@@ -613,7 +639,7 @@ def run_gpu(args):
         roof.update(kernel=dom, traffic=ncu_traffic.get(dom), traffic_unit="bytes per launch",
                     traffic_source="ncu capture of this kernel at this workload (summary under profiles/), not measured by this run",
                     peak_source=pk["source"] + " (burst)",
-                    note="achieved = algorithmic work of the kernel / mean CUDA-event time of its launches "
+                    note="achieved = algorithmic work (bytes for an HBM bound, flops for a tensor bound) of the kernel / mean CUDA-event time of its launches "
                          "(eager pass, launches queued behind a spin kernel so the brackets exclude host latency)")
         value = world * flops_step * args.steps / (ms_total * 1e-3) / 1e12
         e2e_val = world * flops_step * args.steps / (ms_e2e * 1e-3) / 1e12
