@@ -36,16 +36,24 @@ struct AppendParams {
 };
 
 // frame / row / column of token t of a chunk stored in (f h w fs hs ws) order
-__device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, int& fr, int& hr, int& wr) {
-  const int ws = static_cast<int>(t % p.pool_w); t /= p.pool_w;
-  const int hs = static_cast<int>(t % p.pool_h); t /= p.pool_h;
-  const int fs = static_cast<int>(t % p.pool_f); t /= p.pool_f;
-  const int wq = p.grid_w / p.pool_w, hq = p.grid_h / p.pool_h;
+template <typename I>
+__device__ __forceinline__ void rope_position_t(const AppendParams& p, I t, int& fr, int& hr, int& wr) {
+  const I pw = static_cast<I>(p.pool_w), ph = static_cast<I>(p.pool_h), pf = static_cast<I>(p.pool_f);
+  const int ws = static_cast<int>(t % pw); t /= pw;
+  const int hs = static_cast<int>(t % ph); t /= ph;
+  const int fs = static_cast<int>(t % pf); t /= pf;
+  const I wq = static_cast<I>(p.grid_w / p.pool_w), hq = static_cast<I>(p.grid_h / p.pool_h);
   const int wo = static_cast<int>(t % wq); t /= wq;
   const int ho = static_cast<int>(t % hq); t /= hq;
   fr = static_cast<int>(t) * p.pool_f + fs;
   hr = ho * p.pool_h + hs;
   wr = wo * p.pool_w + ws;
+}
+// (five divisions per call: in 32 bits whenever the token index allows, a 64-bit division costs
+// several times as many instructions and this runs once per row and thread)
+__device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, int& fr, int& hr, int& wr) {
+  if (static_cast<uint64_t>(t) <= 0xffffffffull) rope_position_t<uint32_t>(p, static_cast<uint32_t>(t), fr, hr, wr);
+  else rope_position_t<int64_t>(p, t, fr, hr, wr);
 }
 
 // One thread block per (touched block, group of `hc` neighbouring heads).  A thread owns one 16-byte
@@ -56,6 +64,7 @@ __device__ __forceinline__ void rope_position(const AppendParams& p, int64_t t, 
 // covers only in part is read back from its page.  Sums are fp32: the rows of a part in ascending
 // order, then the eight parts in order.
 constexpr int kAppendSlices = 8;
+constexpr int kRopeRows = 128;              // page sizes up to this keep their rows' positions in shared memory
 
 template <typename T, bool ROPE>
 __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p) {
@@ -63,6 +72,7 @@ __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p)
   constexpr int UNROLL = ROPE ? 2 : 4;
   extern __shared__ float s_part[];          // [slices][hc][2][D] partial sums of K and V
   __shared__ int s_page[64];
+  __shared__ int s_pos[ROPE ? 3 * kRopeRows : 1];   // ROPE: frame / row / column of each row of the block
   chain_release();
   chain_wait();
   const int cpr = p.D / VEC;
@@ -90,6 +100,29 @@ __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p)
     }
     if (page >= 0) p.page_stamp[page] = p.epoch;
     s_page[hl] = page;
+  }
+  // ROPE: what a pair of a thread's piece is multiplied with depends on the row's position and on the
+  // pair's index alone, so the table, its row length and the coordinate that indexes it are chosen once
+  // per thread (a warp's threads sit in different tables: choosing inside the row loop diverged), and
+  // the positions of the block's rows are worked out once per thread block
+  const double2* tb[VEC / 2];
+  int tb_len[VEC / 2], tb_sel[VEC / 2];
+  if (ROPE) {
+#pragma unroll
+    for (int i = 0; i < VEC / 2; ++i) {
+      const int jj = col * (VEC / 2) + i;                  // complex pair of the head
+      if (jj < p.c_f) { tb[i] = p.rope_f + static_cast<int64_t>(p.start_frame) * p.c_f + jj; tb_len[i] = p.c_f; tb_sel[i] = 0; }
+      else if (jj < p.c_f + p.c_h) { tb[i] = p.rope_h + (jj - p.c_f); tb_len[i] = p.c_h; tb_sel[i] = 1; }
+      else { tb[i] = p.rope_w + (jj - p.c_f - p.c_h); tb_len[i] = p.c_w; tb_sel[i] = 2; }
+    }
+    if (p.page_tokens <= kRopeRows) {
+      const int64_t t0 = bid * p.page_tokens - p.pos0;     // chunk-local index of the block's first row (may be < 0)
+      for (int r = threadIdx.x; r < p.page_tokens; r += blockDim.x) {
+        int fr = 0, hr = 0, wr = 0;
+        if (t0 + r >= 0 && t0 + r < p.S) rope_position(p, t0 + r, fr, hr, wr);
+        s_pos[r] = fr; s_pos[kRopeRows + r] = hr; s_pos[2 * kRopeRows + r] = wr;
+      }
+    }
   }
   __syncthreads();
   const int page = live ? s_page[hl] : -1;
@@ -127,16 +160,14 @@ __global__ void __launch_bounds__(768) cache_append_kernel(const AppendParams p)
         const int r = rb + u;
         if (r >= c_end) continue;
         if (ROPE) {
-          int fr, hr, wr;
-          rope_position(p, blk0 - p.pos0 + r, fr, hr, wr);
+          int pos[3];
+          if (p.page_tokens <= kRopeRows) { pos[0] = s_pos[r]; pos[1] = s_pos[kRopeRows + r]; pos[2] = s_pos[2 * kRopeRows + r]; }
+          else rope_position(p, blk0 - p.pos0 + r, pos[0], pos[1], pos[2]);
           T* e = reinterpret_cast<T*>(&kq[u]);
 #pragma unroll
           for (int i = 0; i < VEC / 2; ++i) {
-            const int jj = col * (VEC / 2) + i;                  // complex pair of the head
-            double2 w;
-            if (jj < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + jj];
-            else if (jj < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (jj - p.c_f)];
-            else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (jj - p.c_f - p.c_h)];
+            const int at = tb_sel[i] == 0 ? pos[0] : tb_sel[i] == 1 ? pos[1] : pos[2];
+            const double2 w = tb[i][static_cast<int64_t>(at) * tb_len[i]];
             const double xr = static_cast<double>(to_f32<T>(e[2 * i])), xi = static_cast<double>(to_f32<T>(e[2 * i + 1]));
             // float64 product, then float64 -> float32 -> T, as view_as_real(...).type_as(x) does
             e[2 * i] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
@@ -208,10 +239,20 @@ __global__ void __launch_bounds__(256) rope_apply_kernel(const AppendParams p, c
   const int64_t total = p.S * p.H * cpr;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int cc = static_cast<int>(i % cpr);
-    const int64_t sh = i / cpr;
-    const int h = static_cast<int>(sh % p.H);
-    const int64_t t = sh / p.H;
+    int cc, h;
+    int64_t t;
+    if (total <= 0xffffffffll) {
+      const uint32_t i32 = static_cast<uint32_t>(i), sh = i32 / static_cast<uint32_t>(cpr);
+      cc = static_cast<int>(i32 - sh * static_cast<uint32_t>(cpr));
+      const uint32_t t32 = sh / static_cast<uint32_t>(p.H);
+      h = static_cast<int>(sh - t32 * static_cast<uint32_t>(p.H));
+      t = t32;
+    } else {
+      cc = static_cast<int>(i % cpr);
+      const int64_t sh = i / cpr;
+      h = static_cast<int>(sh % p.H);
+      t = sh / p.H;
+    }
     uint4 q = *reinterpret_cast<const uint4*>(p.k_new + (t * p.s_stride + h * p.h_stride) * sizeof(T) + cc * 16);
     int fr, hr, wr;
     rope_position(p, t, fr, hr, wr);
@@ -219,10 +260,12 @@ __global__ void __launch_bounds__(256) rope_apply_kernel(const AppendParams p, c
 #pragma unroll
     for (int k = 0; k < VEC / 2; ++k) {
       const int j = cc * (VEC / 2) + k;
-      double2 w;
-      if (j < p.c_f) w = p.rope_f[static_cast<int64_t>(p.start_frame + fr) * p.c_f + j];
-      else if (j < p.c_f + p.c_h) w = p.rope_h[static_cast<int64_t>(hr) * p.c_h + (j - p.c_f)];
-      else w = p.rope_w[static_cast<int64_t>(wr) * p.c_w + (j - p.c_f - p.c_h)];
+      // one load through a selected table instead of three branches: a warp's threads sit in different tables
+      const bool in_f = j < p.c_f, in_h = j < p.c_f + p.c_h;
+      const double2* tbp = in_f ? p.rope_f + j : in_h ? p.rope_h + (j - p.c_f) : p.rope_w + (j - p.c_f - p.c_h);
+      const int len = in_f ? p.c_f : in_h ? p.c_h : p.c_w;
+      const int at = in_f ? p.start_frame + fr : in_h ? hr : wr;
+      const double2 w = tbp[static_cast<int64_t>(at) * len];
       const double xr = static_cast<double>(to_f32<T>(e[2 * k])), xi = static_cast<double>(to_f32<T>(e[2 * k + 1]));
       e[2 * k] = from_f32<T>(static_cast<float>(xr * w.x - xi * w.y));
       e[2 * k + 1] = from_f32<T>(static_cast<float>(xr * w.y + xi * w.x));
@@ -740,7 +783,7 @@ static int cache_append_impl(const void* k_new, const void* v_new, const int64_t
   const size_t smem = static_cast<size_t>(kAppendSlices) * hc * 2 * D * sizeof(float);
   const dim3 grid(static_cast<unsigned>(n_touched_blocks), cdiv(H, hc));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (smem + 1024 > 48 * 1024) {                  // (static shared memory counts against the 48 KiB default)
+  if (smem + 4096 > 48 * 1024) {                  // (static shared memory counts against the 48 KiB default)
     if (rope != nullptr) {
       if (dtype == NSA_BF16) NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       else NSA_CUDA_OK(cudaFuncSetAttribute(cache_append_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
