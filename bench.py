@@ -270,7 +270,17 @@ def hbm_kernels(ops, dev, d, pk):
     specs = [RopeSpec(freqs, (30, 52), 3 * i, (1, 1, 1)).struct(dev, D) for i in range(n_chunks)]
     us = graph_time_us([(lambda i=i: raw_append(i, specs[i])) for i in range(n_chunks)])
     out["cache_append_rope"] = entry(us, app_bytes, pk["hbm"], note="the same with the rotary embedding applied on the way in (float64 products)")
-    del cache, chunks
+    # query rotary embedding of one chunk (14.4 MB in, 14.4 MB out), eight chunks in rotation
+    q_out = torch.empty(S, H, D, device=dev, dtype=torch.bfloat16)
+
+    def rope_q(i):
+        x = chunks[i][0]
+        _lib.call("nsa_rope_apply", x.data_ptr(), (C.c_int64 * 3)(x.stride(0), x.stride(1), 0), S, H, D, q_out.data_ptr(),
+                  _lib.NSA_BF16, C.byref(specs[i]), stream(dev).cuda_stream)
+
+    us = graph_time_us([(lambda i=i: rope_q(i)) for i in range(n_chunks)])
+    out["rope_apply"] = entry(us, 2 * S * H * D * 2, pk["hbm"], note="query rotary embedding of a 4680-token chunk (float64 products)")
+    del cache, chunks, q_out
 
     # ---- LRU machinery at the 48-frame cap: 1170 blocks x 12 heads = 14040 pages, a selection of 888 x 16 ids
     MB = 1170

@@ -412,3 +412,22 @@ def test_append_with_rotary_embedding_matches_rope_then_append(dev, pool):
     fused.check_status()
     with pytest.raises(Exception):
         fused.append(k[:50].to(dev), v[:50].to(dev), rope=RopeSpec(freqs, (h, w), start, pool))   # not whole frames
+
+
+@pytest.mark.parametrize("case", [(90, 5, 64, (5, 6), (1, 1, 1)),      # S not a multiple of the kernel's token group, D = 64
+                                  (96, 3, 128, (4, 6), (2, 2, 2)),     # pooled-window token order
+                                  (30, 130, 64, (5, 6), (1, 1, 1))],   # more row pieces than a thread block holds
+                         ids=["ragged_d64", "pooled_order", "wide"])
+def test_query_rotary_embedding_shapes(dev, case):
+    """rope_apply bit for bit against the oracle's restatement of the reference function, from a strided view."""
+    from omnimem_b200.cache import RopeSpec, rope_apply
+    S, H, D, (gh, gw), pool = case
+    freqs = torch.cat([O.rope_params(1024, D - 4 * (D // 6)), O.rope_params(1024, 2 * (D // 6)),
+                       O.rope_params(1024, 2 * (D // 6))], dim=1)
+    g = torch.Generator().manual_seed(S + H)
+    wide = torch.randn(S, H, 2 * D, generator=g).to(torch.bfloat16)
+    x = wide[:, :, D:]                                                  # row stride 2 D, 16-byte aligned
+    f = S // (gh * gw)
+    ref = O.reorder_rope_apply(x.contiguous(), (f, gh, gw), freqs, 7, pool)
+    got = rope_apply(wide.to(dev)[:, :, D:], RopeSpec(freqs, (gh, gw), 7, pool))
+    assert torch.equal(got.cpu(), ref)
