@@ -446,14 +446,15 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
     int cap, int32_t* __restrict__ victims, int32_t* status) {
   extern __shared__ unsigned long long s_list[];            // the selected keys, padded to a power of two
   __shared__ unsigned int s_hist[256];
-  __shared__ unsigned long long s_prefix;
+  __shared__ unsigned long long s_prefix, s_or, s_and;
   __shared__ int s_remaining, s_count, s_total;
   constexpr int kKeep = PPT > 0 ? PPT : 1;
   int n = n_dev ? *n_dev : n_host;
   if (n > cap) n = cap;
   if (n > kSelectMax) n = kSelectMax;                       // the host sends larger requests to the scan kernel
   if (n <= 0) return;
-  if (threadIdx.x == 0) { s_prefix = 0ull; s_remaining = n; s_count = 0; s_total = 0; }
+  if (threadIdx.x == 0) { s_prefix = 0ull; s_remaining = n; s_count = 0; s_total = 0; s_or = 0ull; s_and = ~0ull; }
+  __syncthreads();
   unsigned long long keep[kKeep];
   if (PPT > 0) {
 #pragma unroll
@@ -476,8 +477,37 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
                   epoch, ks);
     }
   };
+  // ---- bytes on which every candidate key agrees need no pass (the free flag and the high bytes of
+  // stamp and page id are alike for all of them: five or six of the eight): OR and AND of the keys
+  {
+    unsigned long long o = 0ull, a = ~0ull;
+    int cnt = 0;
+    for (int bt = 0; bt < n_batches; ++bt) {
+      unsigned long long ks[kBatch];
+      batch(bt, ks);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (ks[u] != ~0ull) { o |= ks[u]; a &= ks[u]; ++cnt; }
+    }
+    const unsigned lo_o = __reduce_or_sync(0xffffffffu, static_cast<unsigned>(o)), hi_o = __reduce_or_sync(0xffffffffu, static_cast<unsigned>(o >> 32));
+    const unsigned lo_a = __reduce_and_sync(0xffffffffu, static_cast<unsigned>(a)), hi_a = __reduce_and_sync(0xffffffffu, static_cast<unsigned>(a >> 32));
+    cnt = __reduce_add_sync(0xffffffffu, cnt);
+    if ((threadIdx.x & 31) == 0) {
+      atomicOr(&s_or, (static_cast<unsigned long long>(hi_o) << 32) | lo_o);
+      atomicAnd(&s_and, (static_cast<unsigned long long>(hi_a) << 32) | lo_a);
+      atomicAdd(&s_total, cnt);
+    }
+    __syncthreads();
+  }
+  const unsigned long long all_or = s_or, differs = s_or ^ s_and;
+  const bool enough = s_total >= n;                         // else every candidate is taken and no digit matters
   // ---- the n-th smallest key, one byte at a time from the top
-  for (int byte = 7; byte >= 0; --byte) {
+  for (int byte = 7; byte >= 0 && enough; --byte) {
+    if (((differs >> (8 * byte)) & 255ull) == 0ull) {       // block-uniform
+      if (threadIdx.x == 0) s_prefix = (s_prefix << 8) | ((all_or >> (8 * byte)) & 255ull);
+      __syncthreads();
+      continue;
+    }
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0u;
     __syncthreads();
     const unsigned long long prefix = s_prefix;
@@ -528,7 +558,6 @@ __global__ void __launch_bounds__(1024) select_victims_radix_kernel(
         s_remaining = static_cast<int>(remaining - seen);
         s_prefix = (prefix << 8) | static_cast<unsigned long long>(digit);
       }
-      if (byte == 7 && lane == 0) s_total = static_cast<int>(total_all);
     }
     __syncthreads();
   }
