@@ -431,3 +431,36 @@ def test_query_rotary_embedding_shapes(dev, case):
     ref = O.reorder_rope_apply(x.contiguous(), (f, gh, gw), freqs, 7, pool)
     got = rope_apply(wide.to(dev)[:, :, D:], RopeSpec(freqs, (gh, gw), 7, pool))
     assert torch.equal(got.cpu(), ref)
+
+
+def test_rotary_embedding_is_bit_exact_on_a_full_chunk(dev):
+    """The rotary embedding must round exactly as the reference's float64 product does: a full chunk of
+    random rows (7.2 M elements, a few hundred of which land next to a bf16 rounding boundary, where
+    float32 arithmetic would round the other way), rows built to cancel (xr = xi against angles near 45
+    degrees, xr = -xi), zeros of both signs, tiny and huge magnitudes, through both kernels."""
+    from omnimem_b200.cache import RopeSpec, rope_apply
+    H, D, gh, gw, f = 12, 128, 30, 52, 3
+    S = f * gh * gw
+    freqs = torch.cat([O.rope_params(1024, D - 4 * (D // 6)), O.rope_params(1024, 2 * (D // 6)),
+                       O.rope_params(1024, 2 * (D // 6))], dim=1)
+    g = torch.Generator().manual_seed(2024)
+    x = torch.randn(S, H, D, generator=g)
+    # every eighth row: equal / opposite real and imaginary parts, so that real or imaginary results cancel
+    x[::8, :, 1::2] = x[::8, :, 0::2]
+    x[4::8, :, 1::2] = -x[4::8, :, 0::2]
+    x[1::64] *= 2.0 ** -60
+    x[2::64] *= 2.0 ** 60
+    x[3::64] = 0.0
+    x[5::64, :, ::2] = -0.0
+    x = x.to(torch.bfloat16)
+    for start in (0, 9, 333):
+        ref = O.reorder_rope_apply(x, (f, gh, gw), freqs, start, (1, 1, 1))
+        got = rope_apply(x.to(dev), RopeSpec(freqs, (gh, gw), start, (1, 1, 1))).cpu()
+        same = got.view(torch.int16) == ref.view(torch.int16)
+        assert bool(same.all()), f"start {start}: {int((~same).sum())} of {same.numel()} elements differ"
+    # the append kernel's copy of the rotation
+    cache = _mk(dev, H=H, D=D, pages=H * 80, max_blocks=80, host_tier=False)
+    cache.append(x.to(dev), x.to(dev), rope=RopeSpec(freqs, (gh, gw), 9, (1, 1, 1)))
+    K, _ = _dense_from_cache(cache)
+    ref = O.reorder_rope_apply(x, (f, gh, gw), freqs, 9, (1, 1, 1))
+    assert torch.equal(K[:S].view(torch.int16), ref.view(torch.int16))
