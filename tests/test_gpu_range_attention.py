@@ -168,3 +168,40 @@ def test_c_entry_refuses_what_it_is_not_built_for(dev):
         call(q, -1, 4, 64, _lib.NSA_BF16)
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
+
+
+def test_full_size_window_properties(dev):
+    """The rollout's window at full size (4680 queries x 12 heads over three chunks of pages): the range
+    taken whole equals its two halves merged by their log-sum-exps; V -> 2 V doubles the output and leaves
+    the log-sum-exp alone; a sample of rows against the oracle."""
+    ops = _ops()
+    M, H, D = 4680, 12, 128
+    N = 3 * M
+    nb = -(-N // 64)
+    g = torch.Generator(device=dev).manual_seed(31)
+    q = torch.randn(1, M, H, D, generator=g, device=dev).bfloat16()
+    k = torch.randn(1, N, H, D, generator=g, device=dev).bfloat16()
+    v = torch.randn(1, N, H, D, generator=g, device=dev).bfloat16()
+    scale = D ** -0.5
+    kv = ops.DenseKV(k, v)
+    out, lse = ops.range_fwd(q, kv, 0, nb, 64, scale)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    # halves merged
+    cut = 97
+    o1, l1 = ops.range_fwd(q, kv, 0, cut, 64, scale)
+    o2, l2 = ops.range_fwd(q, kv, cut, nb - cut, 64, scale)
+    om, lm = ops.merge_partials(torch.stack([o1, o2]), torch.stack([l1, l2]))
+    assert_close_bf16(om, out, "halves merged vs whole", max_abs=4e-3, mean_abs=3e-4)
+    assert torch.allclose(lm, lse, atol=1e-4, rtol=1e-5)
+    # linear in V
+    o_2v, l_2v = ops.range_fwd(q, ops.DenseKV(k, (v.float() * 2).bfloat16()), 0, nb, 64, scale)
+    assert torch.equal(l_2v, lse)
+    assert torch.equal(o_2v, (out.float() * 2).bfloat16())
+    # a sample of rows (first tile, a middle one, the ragged last one) of three heads against the oracle
+    rows = torch.cat([torch.arange(0, 64), torch.arange(2304, 2368), torch.arange(M - 72, M)])
+    heads = [0, 5, 11]
+    qs = q[:, rows][:, :, heads].cpu()
+    ks, vs = k[:, :, heads].cpu(), v[:, :, heads].cpu()
+    ids = _listed(0, nb, 1, rows.numel(), len(heads))
+    o_ref, l_ref = O.selection_fwd(qs.float(), ks.float(), vs.float(), ids, 64, 1, scale, False, 64)
+    _compare(out[:, rows][:, :, heads], lse[:, heads][:, :, rows], o_ref, l_ref, "full-size sample vs oracle")
