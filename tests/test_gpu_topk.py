@@ -293,7 +293,8 @@ def test_head_group_pooling_before_selection(dev):
     assert torch.equal(same, parallel_nsa_topk(q.to(dev), k.to(dev), T, 64, None, 128, True, group_size=G))
 
 
-@pytest.mark.parametrize("topk,NC,causal", [(32, 9000, False), (100, 9000, False), (16, 16384, True), (16, 1025, True)])
+@pytest.mark.parametrize("topk,NC,causal", [(32, 9000, False), (100, 9000, False), (16, 16384, True), (16, 1025, True),
+                                            (160, 3000, False), (200, 700, False), (129, 1500, True)])   # top-k beyond 128
 def test_topk_long_rows(dev, topk, NC, causal):
     """Rows of more than 1024 key blocks: per-segment lists merged in a second stage (top-k up to 64)
     or the block-wide kernel (larger top-k); 9000 keys do not fit the shared-memory key cache."""
