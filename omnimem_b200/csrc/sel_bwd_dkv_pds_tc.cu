@@ -251,9 +251,9 @@ sel_bwd_dkv_pds_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid
         const uint32_t r = iu / ns;
         blk = static_cast<int>(iu - r * ns);
         ib = static_cast<int>(r / static_cast<uint32_t>(p.H));
-        // heads in descending order: the dQ kernel wrote the tiles of the last heads last, they are the
-        // ones still in L2
-        ih = p.H - 1 - static_cast<int>(r - static_cast<uint32_t>(ib) * static_cast<uint32_t>(p.H));
+        // heads in ascending order: the dQ kernel takes the heads from the last to the first, so the tiles
+        // of the first heads were written last and are the ones still in L2
+        ih = static_cast<int>(r - static_cast<uint32_t>(ib) * static_cast<uint32_t>(p.H));
         const int32_t* offs = p.offsets + (static_cast<int64_t>(ib) * p.H + ih) * (p.NS + 1);
         beg = offs[blk];
         n_ent = offs[blk + 1] - beg;

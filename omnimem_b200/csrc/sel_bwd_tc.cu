@@ -121,7 +121,9 @@ sel_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       return;
     }
   }
-  const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // heads in descending order: the forward, which ran just before in a training step, read the K / V of
+  // the last heads last, so they are the ones still in L2
+  const int g = blockIdx.x, h = p.H - 1 - static_cast<int>(blockIdx.y), b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t m0 = static_cast<int64_t>(g) * p.G;
   const int n_q = static_cast<int>(p.M - m0 < p.G ? p.M - m0 : p.G);
